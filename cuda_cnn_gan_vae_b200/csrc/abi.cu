@@ -1,0 +1,272 @@
+// Library state (error text, precision mode, scratch arena) and the C-ABI entry points of the
+// convolution trio and the dense products: argument validation in the manner of the reference
+// (which throws a C string where this returns B200_E_SHAPE) and dispatch between the tcgen05
+// implicit-GEMM kernels and the general CUDA-core kernels.
+#include "common.cuh"
+#include "kernels.h"
+#include <cstring>
+#include <mutex>
+
+namespace b200 {
+
+static thread_local char g_error[512] = "";
+static thread_local int g_path = B200_PATH_NONE;
+static int g_precision = B200_TF32X3;
+
+void set_error(const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+int fail(int code, const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+void set_path(int p) { g_path = p; }
+int precision() { return g_precision; }
+
+static const int kMaxDevices = 64;
+static Arena g_arena[kMaxDevices];
+static int g_sm_count[kMaxDevices];
+static std::mutex g_mutex;
+
+static int current_device()
+{
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= kMaxDevices) return 0;
+    return d;
+}
+
+int sm_count()
+{
+    int d = current_device();
+    if (!g_sm_count[d]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, d) != cudaSuccess || n <= 0) n = 148;
+        g_sm_count[d] = n;
+    }
+    return g_sm_count[d];
+}
+
+int arena_reserve(size_t bytes, cudaStream_t stream)
+{
+    std::lock_guard<std::mutex> lock(g_mutex);
+    Arena &a = g_arena[current_device()];
+    if (a.cap >= bytes) return B200_OK;
+    // grow: wait for every kernel that may still read the old block, then replace it
+    B200_CUDA(cudaStreamSynchronize(stream));
+    if (a.base) B200_CUDA(cudaFree(a.base));
+    a.base = nullptr;
+    a.cap = 0;
+    size_t want = align_up(bytes + bytes / 8, (size_t)1 << 21);
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, want);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(B200_E_NOMEM, "scratch arena: cudaMalloc(%zu) failed: %s", want, cudaGetErrorString(e));
+    }
+    a.base = (char *)p;
+    a.cap = want;
+    a.used = 0;
+    return B200_OK;
+}
+
+void *arena_take(size_t bytes)
+{
+    Arena &a = g_arena[current_device()];
+    size_t off = align_up(a.used, 1024);
+    if (off + bytes > a.cap) return nullptr;
+    a.used = off + bytes;
+    return a.base + off;
+}
+
+void arena_reset() { g_arena[current_device()].used = 0; }
+
+static int check_geom(const b200_conv_geom *g)
+{
+    if (!g) return fail(B200_E_ARG, "null geometry");
+    if (g->kernel_amount <= 0) return fail(B200_E_SHAPE, "convolution needs at least one kernel");
+    if (g->in_z <= 0 || g->in_y <= 0 || g->in_x <= 0 || g->kernel_x <= 0 || g->kernel_y <= 0 || g->stride_x <= 0 ||
+        g->stride_y <= 0 || g->padding_x < 0 || g->padding_y < 0)
+        return fail(B200_E_SHAPE, "non-positive convolution geometry");
+    return B200_OK;
+}
+
+static int check_forward_dims(const b200_conv_geom *g)
+{
+    int ox = (g->in_x - g->kernel_x + 2 * g->padding_x) / g->stride_x + 1;
+    int oy = (g->in_y - g->kernel_y + 2 * g->padding_y) / g->stride_y + 1;
+    if (ox != g->out_x || oy != g->out_y || ox <= 0 || oy <= 0)
+        return fail(B200_E_SHAPE, "wrong output size for convolution: expected %dx%d, got %dx%d", oy, ox, g->out_y, g->out_x);
+    return B200_OK;
+}
+
+}  // namespace b200
+
+using namespace b200;
+#define ST(s) ((cudaStream_t)(s))
+
+extern "C" {
+
+const char *b200_last_error(void) { return g_error; }
+int b200_last_path(void) { return g_path; }
+int b200_get_precision(void) { return g_precision; }
+
+int b200_set_precision(int mode)
+{
+    if (mode != B200_TF32X3 && mode != B200_TF32 && mode != B200_FP32) return fail(B200_E_ARG, "unknown precision mode %d", mode);
+    g_precision = mode;
+    return B200_OK;
+}
+
+size_t b200_scratch_bytes(void) { return g_arena[current_device()].cap; }
+
+int b200_stream_status(void *stream)
+{
+    cudaError_t e = cudaStreamSynchronize(ST(stream));
+    if (e != cudaSuccess) return fail(B200_E_CUDA, "stream failed: %s", cudaGetErrorString(e));
+    unsigned code = tc_read_status(1);
+    if (code) return fail(B200_E_TIMEOUT, "a device-side wait gave up (code 0x%x); results of the last calls are invalid", code);
+    return B200_OK;
+}
+
+int b200_shutdown(void)
+{
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int keep = 0;
+    cudaGetDevice(&keep);
+    for (int d = 0; d < kMaxDevices; d++) {
+        if (!g_arena[d].base) continue;
+        if (cudaSetDevice(d) == cudaSuccess) {
+            cudaDeviceSynchronize();
+            cudaFree(g_arena[d].base);
+        }
+        g_arena[d] = Arena();
+    }
+    cudaSetDevice(keep);
+    return B200_OK;
+}
+
+int b200_conv_forward(const b200_conv_geom *g, float *out, int out_w, const float *image, int image_w,
+                      const float *kernel, int kernel_w, const float *bias, int bias_w, void *stream)
+{
+    int r = check_geom(g);
+    if (r) return r;
+    if ((r = check_forward_dims(g))) return r;
+    if (!out || !image || !kernel) return fail(B200_E_ARG, "null tensor pointer");
+    if (out_w <= 0 || image_w <= 0 || kernel_w <= 0 || (bias && bias_w <= 0)) return fail(B200_E_SHAPE, "non-positive W count");
+    if (g_precision != B200_FP32 && kernel_w == 1 && (!bias || bias_w == 1) && image_w == out_w) {
+        r = tc_conv_forward(*g, out, image, kernel, bias, out_w, g_precision, ST(stream));
+        if (r == B200_OK) { set_path(B200_PATH_TCGEN05); return r; }
+        if (r != TC_UNSUPPORTED) return r;
+    }
+    set_path(B200_PATH_SIMT);
+    return simt_conv_forward(*g, out, out_w, image, image_w, kernel, kernel_w, bias, bias_w, ST(stream));
+}
+
+int b200_conv_backward(const b200_conv_geom *g, float *out_delta, int out_w, const float *delta, int delta_w,
+                       const float *kernel, int kernel_w, const float *bias, int bias_w, void *stream)
+{
+    int r = check_geom(g);
+    if (r) return r;
+    if (!out_delta || !delta || !kernel) return fail(B200_E_ARG, "null tensor pointer");
+    if (out_w <= 0 || delta_w <= 0 || kernel_w <= 0 || (bias && bias_w <= 0)) return fail(B200_E_SHAPE, "non-positive W count");
+    if (g->out_y <= 0 || g->out_x <= 0) return fail(B200_E_SHAPE, "non-positive delta size");
+    if (g_precision != B200_FP32 && kernel_w == 1 && !bias && delta_w == out_w) {
+        r = tc_conv_backward(*g, out_delta, delta, kernel, out_w, g_precision, ST(stream));
+        if (r == B200_OK) { set_path(B200_PATH_TCGEN05); return r; }
+        if (r != TC_UNSUPPORTED) return r;
+    }
+    set_path(B200_PATH_SIMT);
+    return simt_conv_backward(*g, out_delta, out_w, delta, delta_w, kernel, kernel_w, bias, bias_w, ST(stream));
+}
+
+int b200_conv_wgrad(const b200_conv_geom *g, float *dkernel, int dkernel_w, float *dbias, int dbias_w,
+                    const float *image, int image_w, const float *delta, int delta_w, void *stream)
+{
+    int r = check_geom(g);
+    if (r) return r;
+    if (!dkernel || !dbias || !image || !delta) return fail(B200_E_ARG, "null tensor pointer");
+    if (dkernel_w <= 0 || dbias_w <= 0 || image_w <= 0 || delta_w <= 0) return fail(B200_E_SHAPE, "non-positive W count");
+    // per-sample contract of the reference: one weight gradient per w.  The tensor-core kernel
+    // serves the batch-summed entry point; a per-sample result is inherently one skinny product
+    // per sample and runs on the CUDA cores in the reference's summation order.
+    set_path(B200_PATH_SIMT);
+    return simt_conv_wgrad(*g, dkernel, dkernel_w, dbias, dbias_w, image, image_w, delta, delta_w, ST(stream));
+}
+
+int b200_conv_back_wgrad(const b200_conv_geom *g, float *dkernel, int dkernel_w, float *dbias, int dbias_w,
+                         const float *image, int image_w, const float *delta, int delta_w, void *stream)
+{
+    int r = b200_conv_wgrad(g, dkernel, dkernel_w, dbias, dbias_w, delta, delta_w, image, image_w, stream);
+    if (r) return r;
+    return b200_fill(dbias, (size_t)dbias_w * g->kernel_amount, 0.f, stream);
+}
+
+int b200_conv_wgrad_batch(const b200_conv_geom *g, float *dkernel, float *dbias, int accumulate,
+                          const float *image, const float *delta, int batch, void *stream)
+{
+    int r = check_geom(g);
+    if (r) return r;
+    if (!dkernel || !image || !delta) return fail(B200_E_ARG, "null tensor pointer");
+    if (batch <= 0) return fail(B200_E_SHAPE, "non-positive batch");
+    if (g_precision != B200_FP32) {
+        r = tc_conv_wgrad_batch(*g, dkernel, dbias, accumulate, image, delta, batch, g_precision, ST(stream));
+        if (r == B200_OK) { set_path(B200_PATH_TCGEN05); return r; }
+        if (r != TC_UNSUPPORTED) return r;
+    }
+    // general path: per-sample gradients into scratch, then the W reduction (the reference sequence)
+    set_path(B200_PATH_SIMT);
+    const size_t klen = (size_t)g->in_z * g->kernel_y * g->kernel_x * g->kernel_amount;
+    const size_t bytes = sizeof(float) * ((size_t)batch * klen + (size_t)batch * g->kernel_amount) + 4096;
+    if ((r = arena_reserve(bytes, ST(stream)))) return r;
+    arena_reset();
+    float *dk = (float *)arena_take(sizeof(float) * batch * klen);
+    float *db = (float *)arena_take(sizeof(float) * batch * g->kernel_amount);
+    B200_CUDA(cudaMemsetAsync(dk, 0, sizeof(float) * batch * klen, ST(stream)));
+    B200_CUDA(cudaMemsetAsync(db, 0, sizeof(float) * batch * g->kernel_amount, ST(stream)));
+    if ((r = simt_conv_wgrad(*g, dk, batch, db, batch, image, batch, delta, batch, ST(stream)))) return r;
+    if (!accumulate) {
+        B200_CUDA(cudaMemsetAsync(dkernel, 0, sizeof(float) * klen, ST(stream)));
+        if (dbias) B200_CUDA(cudaMemsetAsync(dbias, 0, sizeof(float) * g->kernel_amount, ST(stream)));
+    }
+    if ((r = b200_add_sum_w(dkernel, 1, dkernel, 1, dk, batch, klen, 1.f, 1.f, stream))) return r;
+    if (dbias && (r = b200_add_sum_w(dbias, 1, dbias, 1, db, batch, g->kernel_amount, 1.f, 1.f, stream))) return r;
+    return B200_OK;
+}
+
+int b200_mul(float *out, int out_w, const float *left, int left_w, const float *right, int right_w,
+             int z, int ly, int lx, int rx, int transpose_left, void *stream)
+{
+    if (!out || !left || !right) return fail(B200_E_ARG, "null tensor pointer");
+    if (out_w <= 0 || left_w <= 0 || right_w <= 0 || z <= 0 || ly <= 0 || lx <= 0 || rx <= 0)
+        return fail(B200_E_SHAPE, "non-positive matrix size");
+    if (g_precision != B200_FP32 && z == 1) {
+        int r = TC_UNSUPPORTED;
+        const int m = transpose_left ? lx : ly, kd = transpose_left ? ly : lx;
+        if (left_w == 1 && right_w == 1 && out_w == 1) {
+            // one plain product: A = left (row-major m x kd, or stored kd x m when transposed), B = right stored kd x rx
+            r = tc_gemm(out, left, right, m, rx, kd, transpose_left, 1, g_precision, ST(stream));
+        } else if (rx == 1 && left_w == 1 && right_w == out_w) {
+            // the Linear layer: one weight matrix applied to a batch of column vectors.  All samples
+            // form one product out[B x m] = X[B x kd] * W^T: A = right (row-major B x kd), B operand = left.
+            //   transpose_left = 0: left is m x kd  => B is stored N x K (K-major)
+            //   transpose_left = 1: left is kd x m  => B is stored K x N (N-major)
+            r = tc_gemm(out, right, left, out_w, m, kd, 0, transpose_left, g_precision, ST(stream));
+        }
+        if (r == B200_OK) { set_path(B200_PATH_TCGEN05); return r; }
+        if (r != TC_UNSUPPORTED) return r;
+    }
+    set_path(B200_PATH_SIMT);
+    return simt_mul(out, out_w, left, left_w, right, right_w, z, ly, lx, rx, transpose_left, ST(stream));
+}
+
+}  // extern "C"

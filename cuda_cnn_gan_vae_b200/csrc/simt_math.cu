@@ -1,0 +1,718 @@
+// Memory-bound kernels of the hot path and their C-ABI entry points: element-wise arithmetic with
+// W-broadcast, reductions over W and over the Y,X plane, activations, pooling, resampling, fused
+// batch-norm, the VAE reparameterisation and Adam.  All of them stream through HBM once with
+// 128-bit accesses where the alignment allows; grids are sized in multiples of the SM count.
+#include "common.cuh"
+#include "kernels.h"
+#include <cmath>
+
+namespace b200 {
+
+static inline int stream_grid(size_t work_items, int block)
+{
+    size_t blocks = (work_items + block - 1) / block;
+    size_t cap = (size_t)sm_count() * 16;
+    if (blocks < 1) blocks = 1;
+    return (int)(blocks < cap ? blocks : cap);
+}
+
+static inline bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
+
+// ---------------------------------------------------------------------------------------------
+// element-wise with W-broadcast: out[w][i] = F(left[w%Lw][i], right[w%Rw][i])
+// ---------------------------------------------------------------------------------------------
+struct OpAdd { float ls, rs; __device__ float operator()(float l, float r) const { return __fadd_rn(__fmul_rn(ls, l), __fmul_rn(rs, r)); } };
+struct OpSub { float ls, rs; __device__ float operator()(float l, float r) const { return __fsub_rn(__fmul_rn(ls, l), __fmul_rn(rs, r)); } };
+struct OpMul { __device__ float operator()(float l, float r) const { return __fmul_rn(l, r); } };
+
+template <class F, bool VEC>
+__global__ void binary_kernel(float *__restrict__ out, int out_w, const float *left, int left_w,
+                              const float *right, int right_w, size_t n, F f)
+{
+    const size_t per_w = VEC ? n / 4 : n;
+    const size_t total = per_w * out_w;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        size_t w = idx / per_w, i = idx - w * per_w;
+        if (VEC) {
+            float4 l = reinterpret_cast<const float4 *>(left + (w % left_w) * n)[i];
+            float4 r = reinterpret_cast<const float4 *>(right + (w % right_w) * n)[i];
+            float4 o = make_float4(f(l.x, r.x), f(l.y, r.y), f(l.z, r.z), f(l.w, r.w));
+            reinterpret_cast<float4 *>(out + w * n)[i] = o;
+        } else {
+            out[w * n + i] = f(left[(w % left_w) * n + i], right[(w % right_w) * n + i]);
+        }
+    }
+}
+
+template <class F>
+static int launch_binary(float *out, int out_w, const float *left, int left_w, const float *right, int right_w,
+                         size_t n, F f, cudaStream_t s)
+{
+    if (!out || !left || !right) return fail(B200_E_ARG, "null tensor pointer");
+    if (out_w <= 0 || left_w <= 0 || right_w <= 0) return fail(B200_E_SHAPE, "non-positive W count");
+    if (!n) return B200_OK;
+    bool vec = (n % 4 == 0) && aligned16(out) && aligned16(left) && aligned16(right);
+    size_t total = (vec ? n / 4 : n) * out_w;
+    if (vec) binary_kernel<F, true><<<stream_grid(total, 256), 256, 0, s>>>(out, out_w, left, left_w, right, right_w, n, f);
+    else binary_kernel<F, false><<<stream_grid(total, 256), 256, 0, s>>>(out, out_w, left, left_w, right, right_w, n, f);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// unary with W-broadcast of the input
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float unary_apply(float v, int op, float a, float b)
+{
+    switch (op) {
+    case 0: return __fmul_rn(__fmul_rn(v, v), a);
+    case 1: return __fmul_rn(__fsqrt_rn(__fadd_rn(v, b)), a);
+    case 2: return __fdiv_rn(1.0f, v);
+    default: return __fmul_rn(v, a);
+    }
+}
+
+__global__ void unary_kernel(float *__restrict__ out, int out_w, const float *in, int in_w, size_t n, int op, float a, float b)
+{
+    const size_t total = n * out_w;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        size_t w = idx / n, i = idx - w * n;
+        out[idx] = unary_apply(in[(w % in_w) * n + i], op, a, b);
+    }
+}
+
+__global__ void fill_kernel(float *__restrict__ out, size_t n, float v)
+{
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) out[i] = v;
+}
+
+// ---------------------------------------------------------------------------------------------
+// AddSumW: out[0][i] = ls*sum_w left[w][i] + rs*sum_w right[w][i]; out[w>0][i] = 0.  One thread per
+// element walks W sequentially (the reference order); neighbouring threads read neighbouring
+// addresses, so every pass over a w-slice is fully coalesced.
+// ---------------------------------------------------------------------------------------------
+__global__ void add_sum_w_kernel(float *out, int out_w, const float *left, int left_w, const float *right, int right_w,
+                                 size_t n, float ls, float rs)
+{
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float sl = 0.f, sr = 0.f;
+        for (int w = 0; w < left_w; w++) sl = __fadd_rn(sl, left[(size_t)w * n + i]);
+        sl = __fmul_rn(sl, ls);
+        for (int w = 0; w < right_w; w++) sr = __fadd_rn(sr, right[(size_t)w * n + i]);
+        sr = __fmul_rn(sr, rs);
+        out[i] = __fadd_rn(sl, sr);
+        for (int w = 1; w < out_w; w++) out[(size_t)w * n + i] = 0.f;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// AddBias (+ optional activation): t[w,z,:,:] = f(t + bias[w%Bw,z])
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float act_sigmoid(float v)
+{
+    if (v > 30.f) v = 29.99999f;
+    if (v < -30.f) v = -29.99999f;
+    return 1.0f / (1.0f + expf(-v));
+}
+__device__ __forceinline__ float act_tanh(float v)
+{
+    if (v > 30.f) v = 29.99999f;
+    if (v < -30.f) v = -29.99999f;
+    return tanhf(v);
+}
+__device__ __forceinline__ float act_apply(float v, int func, float slope)
+{
+    switch (func) {
+    case B200_ACT_SIGMOID: return act_sigmoid(v);
+    case B200_ACT_RELU: return v > 0.f ? v : 0.f;
+    case B200_ACT_LEAKY_RELU: return v > 0.f ? v : slope * v;
+    case B200_ACT_LINEAR: return v;
+    case B200_ACT_TANH: return act_tanh(v);
+    default: {
+        const float c = 0.7978845608f;  // sqrt(2/pi)
+        float ft = tanhf(c * (v + 0.044715f * v * v * v));
+        return 0.5f * v * (1.f + ft);
+    }
+    }
+}
+__device__ __forceinline__ float act_derivative(float v, int func, float slope)
+{
+    switch (func) {
+    case B200_ACT_SIGMOID: { float s = act_sigmoid(v); return (1.0f - s) * s; }
+    case B200_ACT_RELU: return v >= 0.f ? 1.f : 0.f;
+    case B200_ACT_LEAKY_RELU: return v >= 0.f ? 1.f : slope;
+    case B200_ACT_LINEAR: return 1.f;
+    case B200_ACT_TANH: { float t = act_tanh(v); return 1.f - t * t; }
+    default: {
+        const float c = 0.7978845608f;
+        float ft = c * (v + 0.044715f * v * v * v);
+        float fa = c * (1.f + 3.f * 0.044715f * v * v);
+        float sech = 1.f / coshf(ft);
+        return 0.5f * ((1.f + tanhf(ft)) + 0.5f * v * sech * sech) * fa;
+    }
+    }
+}
+
+template <bool VEC>
+__global__ void bias_act_kernel(float *t, float *pre, int t_w, int z, size_t yx, const float *__restrict__ bias, int bias_w,
+                                int func, float slope)
+{
+    const size_t per_plane = VEC ? yx / 4 : yx;
+    const size_t total = per_plane * z * t_w;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        size_t plane = idx / per_plane;
+        int zz = plane % z;
+        size_t w = plane / z;
+        float b = bias[(w % bias_w) * z + zz];
+        if (VEC) {
+            float4 v = reinterpret_cast<float4 *>(t)[idx];
+            v.x = __fadd_rn(v.x, b); v.y = __fadd_rn(v.y, b); v.z = __fadd_rn(v.z, b); v.w = __fadd_rn(v.w, b);
+            if (pre) reinterpret_cast<float4 *>(pre)[idx] = v;
+            if (func != B200_ACT_LINEAR) {
+                v.x = act_apply(v.x, func, slope); v.y = act_apply(v.y, func, slope);
+                v.z = act_apply(v.z, func, slope); v.w = act_apply(v.w, func, slope);
+            }
+            reinterpret_cast<float4 *>(t)[idx] = v;
+        } else {
+            float v = __fadd_rn(t[idx], b);
+            if (pre) pre[idx] = v;
+            t[idx] = func != B200_ACT_LINEAR ? act_apply(v, func, slope) : v;
+        }
+    }
+}
+
+__global__ void activation_kernel(float *__restrict__ out, const float *__restrict__ in, const float *__restrict__ err,
+                                  size_t n, int func, int derivative, float slope)
+{
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float v = in[i];
+        float r = derivative ? act_derivative(v, func, slope) : act_apply(v, func, slope);
+        out[i] = err ? r * err[i] : r;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// SummXY: out[w,z] = sum of one Y,X plane.  One warp (small planes) or one block (large planes)
+// per plane; float4 loads, warp-shuffle tree, fixed order => reproducible run to run.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__global__ void summ_xy_kernel(float *__restrict__ out, int out_w, const float *__restrict__ in, int in_w, int z, size_t yx)
+{
+    __shared__ float part[32];
+    const int planes = out_w * z;
+    for (int p = blockIdx.x; p < planes; p += gridDim.x) {
+        int w = p / z, zz = p % z;
+        const float *src = in + ((size_t)(w % in_w) * z + zz) * yx;
+        float s = 0.f;
+        if ((yx % 4 == 0) && (((uintptr_t)src & 15) == 0)) {
+            const float4 *s4 = reinterpret_cast<const float4 *>(src);
+            for (size_t i = threadIdx.x; i < yx / 4; i += blockDim.x) { float4 v = s4[i]; s += (v.x + v.y) + (v.z + v.w); }
+        } else {
+            for (size_t i = threadIdx.x; i < yx; i += blockDim.x) s += src[i];
+        }
+        s = warp_sum(s);
+        if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            float v = threadIdx.x < (blockDim.x >> 5) ? part[threadIdx.x] : 0.f;
+            v = warp_sum(v);
+            if (threadIdx.x == 0) out[p] = v;
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// pooling / resampling
+// ---------------------------------------------------------------------------------------------
+__global__ void maxpool_kernel(float *__restrict__ out, uint2 *__restrict__ pos, const float *__restrict__ in,
+                               size_t planes, int in_y, int in_x, int pool_x, int pool_y)
+{
+    const int oy = in_y / pool_y, ox = in_x / pool_x;
+    const size_t total = planes * oy * ox;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        int x = idx % ox;
+        size_t t = idx / ox;
+        int y = t % oy;
+        size_t pl = t / oy;
+        const float *p = in + pl * in_y * in_x;
+        int ix = x * pool_x, iy = y * pool_y;
+        float m = p[(size_t)iy * in_x + ix];
+        uint32_t mx = ix, my = iy;
+        if (pool_x == 2 && pool_y == 2 && (in_x % 2 == 0)) {
+            float2 r0 = *reinterpret_cast<const float2 *>(p + (size_t)iy * in_x + ix);
+            float2 r1 = *reinterpret_cast<const float2 *>(p + (size_t)(iy + 1) * in_x + ix);
+            if (r0.y > m) { m = r0.y; mx = ix + 1; my = iy; }
+            if (r1.x > m) { m = r1.x; mx = ix; my = iy + 1; }
+            if (r1.y > m) { m = r1.y; mx = ix + 1; my = iy + 1; }
+        } else {
+            for (int py = 0; py < pool_y; py++)
+                for (int px = 0; px < pool_x; px++) {
+                    float e = p[(size_t)(iy + py) * in_x + ix + px];
+                    if (e > m) { m = e; mx = ix + px; my = iy + py; }
+                }
+        }
+        out[idx] = m;
+        pos[idx] = make_uint2(mx, my);
+    }
+}
+
+// Backward of max-pooling as a gather over the OUTPUT (race-free, writes every element once):
+// out[y,x] = delta of the window that owns (y,x) if that window's argmax is (x,y), else 0.
+__global__ void maxpool_backward_kernel(float *__restrict__ out, const uint2 *__restrict__ pos, const float *__restrict__ delta,
+                                        size_t planes, int out_y, int out_x, int pool_x, int pool_y)
+{
+    const int dy = out_y / pool_y, dx = out_x / pool_x;
+    const size_t total = planes * out_y * out_x;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        int x = idx % out_x;
+        size_t t = idx / out_x;
+        int y = t % out_y;
+        size_t pl = t / out_y;
+        int wy = y / pool_y, wx = x / pool_x;
+        float v = 0.f;
+        if (wy < dy && wx < dx) {
+            size_t i = (pl * dy + wy) * dx + wx;
+            uint2 ps = pos[i];
+            if (ps.x == (uint32_t)x && ps.y == (uint32_t)y) v = delta[i];
+        }
+        out[idx] = v;
+    }
+}
+
+__global__ void upsample_kernel(float *__restrict__ out, const float *__restrict__ in, size_t planes, int in_y, int in_x,
+                                int out_y, int out_x, int ux, int uy)
+{
+    const size_t total = planes * out_y * out_x;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        int x = idx % out_x;
+        size_t t = idx / out_x;
+        int y = t % out_y;
+        size_t pl = t / out_y;
+        int iy = y / uy, ix = x / ux;
+        out[idx] = (ix < in_x && iy < in_y) ? in[(pl * in_y + iy) * in_x + ix] : 0.f;
+    }
+}
+
+__global__ void downsample_kernel(float *__restrict__ out, const float *__restrict__ in, size_t planes, int in_y, int in_x,
+                                  int out_y, int out_x, int dsx, int dsy)
+{
+    const size_t total = planes * out_y * out_x;
+    const float div = (float)(dsx * dsy);
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        int x = idx % out_x;
+        size_t t = idx / out_x;
+        int y = t % out_y;
+        size_t pl = t / out_y;
+        float s = 0.f;
+        for (int dx = 0; dx < dsx; dx++) {
+            int xp = x * dsx + dx;
+            if (xp >= in_x) continue;
+            for (int dy = 0; dy < dsy; dy++) {
+                int yp = y * dsy + dy;
+                if (yp >= in_y) continue;
+                s = __fadd_rn(s, in[(pl * in_y + yp) * in_x + xp]);
+            }
+        }
+        out[idx] = __fdiv_rn(s, div);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// fused batch-norm (statistics per element over W).  One thread per (z,y,x) element; the W column is
+// walked three times (mean, variance, normalise) and stays in L1/L2 between the passes, so HBM sees
+// one read of x and one write each of y and xhat.  Arithmetic follows the reference sequence.
+// ---------------------------------------------------------------------------------------------
+__global__ void bn_forward_kernel(float *__restrict__ y, float *__restrict__ xhat, float *__restrict__ ivar,
+                                  float *__restrict__ mean, float *__restrict__ var, float *new_mean, float *new_var,
+                                  const float *__restrict__ x, const float *__restrict__ gamma, const float *__restrict__ beta,
+                                  int W, size_t n, float momentum, float eps)
+{
+    const float invN = (float)(1.0 / (double)(float)W);
+    const float om = (float)(1.0 - (double)momentum);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float s = 0.f;
+        for (int w = 0; w < W; w++) s = __fadd_rn(s, x[(size_t)w * n + i]);
+        float mu = __fadd_rn(0.f, __fmul_rn(s, invN));
+        float q = 0.f;
+        for (int w = 0; w < W; w++) {
+            float d = __fsub_rn(x[(size_t)w * n + i], mu);
+            q = __fadd_rn(q, __fmul_rn(__fmul_rn(d, d), 1.0f));
+        }
+        float vr = __fadd_rn(0.f, __fmul_rn(q, invN));
+        float iv = __fdiv_rn(1.0f, __fmul_rn(__fsqrt_rn(__fadd_rn(vr, eps)), 1.0f));
+        mean[i] = mu; var[i] = vr; ivar[i] = iv;
+        if (new_mean) new_mean[i] = __fadd_rn(__fmul_rn(momentum, new_mean[i]), __fmul_rn(om, mu));
+        if (new_var) new_var[i] = __fadd_rn(__fmul_rn(momentum, new_var[i]), __fmul_rn(om, vr));
+        float g = gamma[i], b = beta[i];
+        for (int w = 0; w < W; w++) {
+            float h = __fmul_rn(__fsub_rn(x[(size_t)w * n + i], mu), iv);
+            xhat[(size_t)w * n + i] = h;
+            y[(size_t)w * n + i] = __fadd_rn(__fmul_rn(g, h), b);
+        }
+    }
+}
+
+__global__ void bn_backward_kernel(float *__restrict__ dx, float *dgamma, float *dbeta, const float *__restrict__ dy,
+                                   const float *__restrict__ xhat, const float *__restrict__ ivar, const float *__restrict__ gamma,
+                                   int W, size_t n, int create_delta_weight)
+{
+    const float N = (float)W;
+    const float invN = (float)(1.0 / (double)N);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float g = gamma[i], iv = ivar[i];
+        float sb = 0.f, sc = 0.f, sg = 0.f, sbeta = 0.f;
+        for (int w = 0; w < W; w++) {
+            float d = dy[(size_t)w * n + i], h = xhat[(size_t)w * n + i];
+            float dh = __fmul_rn(d, g);
+            sb = __fadd_rn(sb, dh);
+            sc = __fadd_rn(sc, __fmul_rn(dh, h));
+            sg = __fadd_rn(sg, __fmul_rn(d, h));
+            sbeta = __fadd_rn(sbeta, d);
+        }
+        if (create_delta_weight) {
+            dgamma[i] = __fadd_rn(dgamma[i], sg);
+            dbeta[i] = __fadd_rn(dbeta[i], sbeta);
+        }
+        for (int w = 0; w < W; w++) {
+            float d = dy[(size_t)w * n + i], h = xhat[(size_t)w * n + i];
+            float v = __fmul_rn(__fmul_rn(d, g), N);
+            v = __fsub_rn(v, __fmul_rn(h, sc));
+            v = __fsub_rn(v, sb);
+            v = __fmul_rn(v, iv);
+            dx[(size_t)w * n + i] = __fmul_rn(v, invN);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// VAE output layer
+// ---------------------------------------------------------------------------------------------
+__global__ void vae_forward_kernel(float *__restrict__ z, const float *__restrict__ mu, const float *__restrict__ logvar,
+                                   const float *__restrict__ eps, size_t total, float *kl_partial)
+{
+    __shared__ float part[32];
+    float kl = 0.f;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float lv = logvar[i], m = mu[i];
+        lv = fminf(fmaxf(lv, -10.f), 10.f);
+        z[i] = m + expf(lv * 0.5f) * eps[i];
+        kl += 1.f + lv - m * m - expf(lv);
+    }
+    kl = warp_sum(kl);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = kl;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < (blockDim.x >> 5) ? part[threadIdx.x] : 0.f;
+        v = warp_sum(v);
+        if (threadIdx.x == 0 && kl_partial) kl_partial[blockIdx.x] = v;
+    }
+}
+
+__global__ void vae_backward_kernel(float *__restrict__ d_mu, float *__restrict__ d_logvar, const float *__restrict__ delta,
+                                    const float *__restrict__ mu, const float *__restrict__ logvar, const float *__restrict__ eps,
+                                    size_t total, float k)
+{
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float lv = logvar[i], d = delta[i];
+        d_logvar[i] = d * (0.5f * eps[i] * expf(lv * 0.5f)) - 0.5f * (1.f - expf(lv)) * k;
+        d_mu[i] = d + mu[i] * k;
+    }
+}
+
+__global__ void adam_kernel(float *__restrict__ weight, const float *__restrict__ dweight, float *__restrict__ m, float *__restrict__ v,
+                            size_t n, float batch, double speed, double beta1, double beta2, double epsilon, double c1, double c2)
+{
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float dw = __fdiv_rn(dweight[i], batch);
+        float mm = (float)(beta1 * m[i] + (1.0 - beta1) * dw);
+        float vv = (float)(beta2 * v[i] + (1.0 - beta2) * dw * dw);
+        float mc = (float)(mm / c1);
+        float vc = (float)(vv / c2);
+        float step = (float)(speed * mc / (sqrt((double)vc) + epsilon));
+        m[i] = mm; v[i] = vv;
+        weight[i] = __fsub_rn(weight[i], step);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// CUDA-core GEMM with W-broadcast (general shapes; k summed in increasing order like the CPU backend)
+// ---------------------------------------------------------------------------------------------
+__global__ void simt_mul_kernel(float *__restrict__ out, int out_w, const float *__restrict__ left, int left_w,
+                                const float *__restrict__ right, int right_w, int Z, int LY, int LX, int RX, int tl)
+{
+    // tl == 0: out (LY x RX) = left (LY x LX) * right (LX x RX)
+    // tl == 1: out (LX x RX) = left^T, left is (LY x LX), right (LY x RX)
+    const int OR = tl ? LX : LY, KD = tl ? LY : LX;
+    const size_t total = (size_t)out_w * Z * OR * RX;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        int x = idx % RX;
+        size_t t = idx / RX;
+        int y = t % OR; t /= OR;
+        int z = t % Z;
+        int w = t / Z;
+        const float *lb = left + ((size_t)(w % left_w) * Z + z) * LY * LX;
+        const float *rb = right + ((size_t)(w % right_w) * Z + z) * (size_t)KD * RX;
+        float acc = 0.f;
+        if (!tl) for (int k = 0; k < KD; k++) acc = __fadd_rn(acc, __fmul_rn(lb[(size_t)y * LX + k], rb[(size_t)k * RX + x]));
+        else     for (int k = 0; k < KD; k++) acc = __fadd_rn(acc, __fmul_rn(lb[(size_t)k * LX + y], rb[(size_t)k * RX + x]));
+        out[idx] = acc;
+    }
+}
+
+int simt_mul(float *out, int out_w, const float *left, int left_w, const float *right, int right_w,
+             int z, int ly, int lx, int rx, int transpose_left, cudaStream_t s)
+{
+    size_t total = (size_t)out_w * z * (transpose_left ? lx : ly) * rx;
+    if (!total) return B200_OK;
+    simt_mul_kernel<<<stream_grid(total, 256), 256, 0, s>>>(out, out_w, left, left_w, right, right_w, z, ly, lx, rx, transpose_left);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+#define ST(s) ((cudaStream_t)(s))
+
+extern "C" {
+
+int b200_add(float *out, int out_w, const float *left, int left_w, const float *right, int right_w,
+             size_t n, float ls, float rs, int subtract, void *stream)
+{
+    if (subtract) return launch_binary(out, out_w, left, left_w, right, right_w, n, OpSub{ls, rs}, ST(stream));
+    return launch_binary(out, out_w, left, left_w, right, right_w, n, OpAdd{ls, rs}, ST(stream));
+}
+
+int b200_item_product(float *out, int out_w, const float *left, int left_w, const float *right, int right_w,
+                      size_t n, void *stream)
+{
+    return launch_binary(out, out_w, left, left_w, right, right_w, n, OpMul{}, ST(stream));
+}
+
+int b200_add_sum_w(float *out, int out_w, const float *left, int left_w, const float *right, int right_w,
+                   size_t n, float ls, float rs, void *stream)
+{
+    if (!out || !left || !right) return fail(B200_E_ARG, "null tensor pointer");
+    if (out_w <= 0 || left_w <= 0 || right_w <= 0) return fail(B200_E_SHAPE, "non-positive W count");
+    if (!n) return B200_OK;
+    add_sum_w_kernel<<<stream_grid(n, 128), 128, 0, ST(stream)>>>(out, out_w, left, left_w, right, right_w, n, ls, rs);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+static int bias_act_launch(float *t, float *pre, int t_w, int z, size_t yx, const float *bias, int bias_w, int func,
+                           float leaky_slope, cudaStream_t s)
+{
+    if (!t || !bias) return fail(B200_E_ARG, "null tensor pointer");
+    if (t_w <= 0 || z <= 0 || bias_w <= 0) return fail(B200_E_SHAPE, "non-positive size");
+    if (func < 0 || func > 5) return fail(B200_E_ARG, "unknown activation %d", func);
+    if (!yx) return B200_OK;
+    bool vec = (yx % 4 == 0) && aligned16(t) && (!pre || aligned16(pre));
+    size_t total = (vec ? yx / 4 : yx) * z * t_w;
+    if (vec) bias_act_kernel<true><<<stream_grid(total, 256), 256, 0, s>>>(t, pre, t_w, z, yx, bias, bias_w, func, leaky_slope);
+    else bias_act_kernel<false><<<stream_grid(total, 256), 256, 0, s>>>(t, pre, t_w, z, yx, bias, bias_w, func, leaky_slope);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+int b200_add_bias(float *t, int t_w, int z, size_t yx, const float *bias, int bias_w, void *stream)
+{
+    return bias_act_launch(t, nullptr, t_w, z, yx, bias, bias_w, B200_ACT_LINEAR, 0.f, ST(stream));
+}
+
+int b200_bias_activation(float *t, float *pre, int t_w, int z, size_t yx, const float *bias, int func,
+                         float leaky_slope, void *stream)
+{
+    return bias_act_launch(t, pre, t_w, z, yx, bias, 1, func, leaky_slope, ST(stream));
+}
+
+int b200_summ_xy(float *out, int out_w, const float *in, int in_w, int z, size_t yx, void *stream)
+{
+    if (!out || !in) return fail(B200_E_ARG, "null tensor pointer");
+    if (out_w <= 0 || in_w <= 0 || z <= 0) return fail(B200_E_SHAPE, "non-positive size");
+    int planes = out_w * z;
+    int block = yx >= 4096 ? 256 : (yx >= 512 ? 128 : 32);
+    int grid = planes < sm_count() * 16 ? planes : sm_count() * 16;
+    summ_xy_kernel<<<grid, block, 0, ST(stream)>>>(out, out_w, in, in_w, z, yx);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+int b200_unary(float *out, int out_w, const float *in, int in_w, size_t n, int op, float a, float b, void *stream)
+{
+    if (!out || !in) return fail(B200_E_ARG, "null tensor pointer");
+    if (out_w <= 0 || in_w <= 0 || op < 0 || op > 3) return fail(B200_E_ARG, "bad unary arguments");
+    if (!n) return B200_OK;
+    unary_kernel<<<stream_grid(n * out_w, 256), 256, 0, ST(stream)>>>(out, out_w, in, in_w, n, op, a, b);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+int b200_fill(float *out, size_t n, float value, void *stream)
+{
+    if (!out) return fail(B200_E_ARG, "null tensor pointer");
+    if (!n) return B200_OK;
+    fill_kernel<<<stream_grid(n, 256), 256, 0, ST(stream)>>>(out, n, value);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+int b200_activation(float *out, const float *in, size_t n, int func, int derivative, float leaky_slope, void *stream)
+{
+    if (!out || !in) return fail(B200_E_ARG, "null tensor pointer");
+    if (func < 0 || func > 5) return fail(B200_E_ARG, "unknown activation %d", func);
+    if (!n) return B200_OK;
+    activation_kernel<<<stream_grid(n, 256), 256, 0, ST(stream)>>>(out, in, nullptr, n, func, derivative, leaky_slope);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+int b200_activation_backward(float *out, const float *z, const float *error, size_t n, int func, float leaky_slope,
+                             void *stream)
+{
+    if (!out || !z || !error) return fail(B200_E_ARG, "null tensor pointer");
+    if (func < 0 || func > 5) return fail(B200_E_ARG, "unknown activation %d", func);
+    if (!n) return B200_OK;
+    activation_kernel<<<stream_grid(n, 256), 256, 0, ST(stream)>>>(out, z, error, n, func, 1, leaky_slope);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+int b200_maxpool(float *out, uint32_t *pos, const float *in, int w, int z, int in_y, int in_x, int pool_x, int pool_y,
+                 void *stream)
+{
+    if (!out || !pos || !in) return fail(B200_E_ARG, "null tensor pointer");
+    if (pool_x <= 0 || pool_y <= 0 || in_y < pool_y || in_x < pool_x) return fail(B200_E_SHAPE, "bad pooling geometry");
+    size_t planes = (size_t)w * z;
+    size_t total = planes * (in_y / pool_y) * (in_x / pool_x);
+    if (!total) return B200_OK;
+    maxpool_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(out, reinterpret_cast<uint2 *>(pos), in, planes, in_y, in_x, pool_x, pool_y);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+int b200_maxpool_backward(float *out, const uint32_t *pos, const float *delta, int w, int z, int out_y, int out_x,
+                          int pool_x, int pool_y, void *stream)
+{
+    if (!out || !pos || !delta) return fail(B200_E_ARG, "null tensor pointer");
+    if (pool_x <= 0 || pool_y <= 0) return fail(B200_E_SHAPE, "bad pooling geometry");
+    size_t planes = (size_t)w * z;
+    size_t total = planes * out_y * out_x;
+    if (!total) return B200_OK;
+    maxpool_backward_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(out, reinterpret_cast<const uint2 *>(pos), delta, planes,
+                                                                           out_y, out_x, pool_x, pool_y);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+int b200_upsample(float *out, const float *in, int w, int z, int in_y, int in_x, int ux, int uy, void *stream)
+{
+    if (!out || !in) return fail(B200_E_ARG, "null tensor pointer");
+    if (ux <= 0 || uy <= 0) return fail(B200_E_SHAPE, "bad upsampling factor");
+    size_t planes = (size_t)w * z;
+    size_t total = planes * in_y * uy * in_x * ux;
+    if (!total) return B200_OK;
+    upsample_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(out, in, planes, in_y, in_x, in_y * uy, in_x * ux, ux, uy);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+int b200_downsample(float *out, const float *in, int w, int z, int in_y, int in_x, int dx, int dy, void *stream)
+{
+    if (!out || !in) return fail(B200_E_ARG, "null tensor pointer");
+    if (dx <= 0 || dy <= 0) return fail(B200_E_SHAPE, "bad downsampling factor");
+    size_t planes = (size_t)w * z;
+    size_t total = planes * (in_y / dy) * (in_x / dx);
+    if (!total) return B200_OK;
+    downsample_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(out, in, planes, in_y, in_x, in_y / dy, in_x / dx, dx, dy);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+int b200_bn_forward(float *y, float *xhat, float *ivar, float *mean, float *var, float *new_mean, float *new_var,
+                    const float *x, const float *gamma, const float *beta, int w, size_t n, float momentum, float eps,
+                    void *stream)
+{
+    if (!y || !xhat || !ivar || !mean || !var || !x || !gamma || !beta) return fail(B200_E_ARG, "null tensor pointer");
+    if (w <= 0) return fail(B200_E_SHAPE, "non-positive batch");
+    if (!n) return B200_OK;
+    bn_forward_kernel<<<stream_grid(n, 128), 128, 0, ST(stream)>>>(y, xhat, ivar, mean, var, new_mean, new_var, x, gamma, beta,
+                                                                  w, n, momentum, eps);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+int b200_bn_backward(float *dx, float *dgamma, float *dbeta, const float *dy, const float *xhat, const float *ivar,
+                     const float *gamma, int w, size_t n, int create_delta_weight, void *stream)
+{
+    if (!dx || !dy || !xhat || !ivar || !gamma) return fail(B200_E_ARG, "null tensor pointer");
+    if (create_delta_weight && (!dgamma || !dbeta)) return fail(B200_E_ARG, "null gradient pointer");
+    if (w <= 0) return fail(B200_E_SHAPE, "non-positive batch");
+    if (!n) return B200_OK;
+    bn_backward_kernel<<<stream_grid(n, 128), 128, 0, ST(stream)>>>(dx, dgamma, dbeta, dy, xhat, ivar, gamma, w, n, create_delta_weight);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+int b200_vae_forward(float *z, const float *mu, const float *logvar, const float *eps, int batch, size_t n,
+                     float *kl_host, void *stream)
+{
+    if (!z || !mu || !logvar || !eps) return fail(B200_E_ARG, "null tensor pointer");
+    if (batch <= 0) return fail(B200_E_SHAPE, "non-positive batch");
+    size_t total = (size_t)batch * n;
+    if (!total) return B200_OK;
+    int grid = stream_grid(total, 256);
+    float *partial = nullptr;
+    if (kl_host) {
+        int r = arena_reserve(sizeof(float) * grid, ST(stream));
+        if (r) return r;
+        arena_reset();
+        partial = (float *)arena_take(sizeof(float) * grid);
+    }
+    vae_forward_kernel<<<grid, 256, 0, ST(stream)>>>(z, mu, logvar, eps, total, partial);
+    B200_LAUNCH_CHECK();
+    if (kl_host) {
+        float *h = (float *)malloc(sizeof(float) * grid);
+        if (!h) return fail(B200_E_NOMEM, "host allocation failed");
+        cudaError_t e = cudaMemcpyAsync(h, partial, sizeof(float) * grid, cudaMemcpyDeviceToHost, ST(stream));
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ST(stream));
+        if (e != cudaSuccess) { free(h); return fail(B200_E_CUDA, "kl readback failed: %s", cudaGetErrorString(e)); }
+        double kl = 0;
+        for (int i = 0; i < grid; i++) kl += h[i];
+        free(h);
+        *kl_host = (float)(-0.5 * kl / batch);
+    }
+    return B200_OK;
+}
+
+int b200_vae_backward(float *d_mu, float *d_logvar, const float *delta, const float *mu, const float *logvar,
+                      const float *eps, size_t total, float kl_speed, void *stream)
+{
+    if (!d_mu || !d_logvar || !delta || !mu || !logvar || !eps) return fail(B200_E_ARG, "null tensor pointer");
+    if (!total) return B200_OK;
+    vae_backward_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(d_mu, d_logvar, delta, mu, logvar, eps, total, kl_speed);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+int b200_adam(float *weight, const float *dweight, float *m, float *v, size_t n, uint32_t batch_size, double speed,
+              double beta1, double beta2, double epsilon, double iteration, void *stream)
+{
+    if (!weight || !dweight || !m || !v) return fail(B200_E_ARG, "null tensor pointer");
+    if (!batch_size) return fail(B200_E_ARG, "batch_size must be positive");
+    if (!n) return B200_OK;
+    double c1 = 1.0 - pow(beta1, iteration), c2 = 1.0 - pow(beta2, iteration);
+    adam_kernel<<<stream_grid(n, 256), 256, 0, ST(stream)>>>(weight, dweight, m, v, n, (float)batch_size, speed, beta1, beta2, epsilon, c1, c2);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,847 @@
+// tcgen05 implicit-GEMM kernels for sm_100a: forward convolution, backward-data convolution
+// (= transposed convolution), batch-summed weight gradient and the dense GEMM of the Linear layer.
+//
+// One warp-specialised persistent kernel serves all four problems.  Per CTA (one per SM):
+//   warp 0      TMA producer: streams 128 x 32 (A) and BN x 32 (B) TF32 tiles into a ring of
+//               shared-memory stages with cp.async.bulk.tensor (128-byte swizzle); zero fill of
+//               out-of-range coordinates implements the convolution padding and every ragged edge;
+//   warp 1      MMA issuer: one thread issues tcgen05.mma kind::tf32 (M=128, N=BN, K=8), four per
+//               stage (twelve in 3xTF32 mode), accumulating in tensor memory; two accumulator
+//               stages let the epilogue of tile i overlap the main loop of tile i+1;
+//   warps 2-5   epilogue: tcgen05.ld of the accumulator (lane = output row), bias, coalesced stores.
+// The problems differ only in how a (tile, step) pair maps to TMA coordinates and in the epilogue:
+//   CONV   rows = 128 output pixels (a BI x BH x BW box of the NHWC activation pack), columns =
+//          filters, K = (tap, 32-channel chunk).  Strided convolutions read a phase-split pack (one
+//          sub-image per (y mod s, x mod s)), strided backward convolutions run one stride-1
+//          problem per output phase, so no structural zero is ever multiplied.
+//   WGRAD  rows = filters, columns = input channels, K = output pixels (batch folded into K), both
+//          operands MN-major straight from the NHWC packs; split-K partial sums go to scratch and a
+//          second kernel reduces them in a fixed order (run-to-run reproducible).
+//   GEMM   plain C = A*B with either operand K-major or MN-major.
+// Every mbarrier wait is bounded: after ~1 s of polling the kernel records a status code in
+// host-visible memory, tells the other warps to stop and returns normally.
+#include "common.cuh"
+#include "kernels.h"
+#include "tc_ptx.cuh"
+#include <cstring>
+
+namespace b200 {
+
+enum { MODE_CONV = 0, MODE_WGRAD = 1, MODE_GEMM = 2 };
+
+constexpr int kThreads = 192;
+constexpr int kABytes = 128 * 128;        // 128 rows x 32 tf32
+constexpr int kMaxTaps = 64;
+constexpr int kMaxPhases = 16;
+constexpr long long kWaitCycles = 2000000000LL;
+
+struct TapEntry { int8_t dy, dx; uint8_t in_phase, wtap; };
+
+struct PhaseInfo {
+    int tile_begin;            // first M-tile of this output phase
+    int tiles_x, tiles_y, tiles_i;
+    int ext_y, ext_x;          // output extent of the phase (rows / columns it owns)
+    int off_y, off_x;          // position of the phase inside the full output
+    int tap_begin, tap_count;
+};
+
+struct TcParams {
+    int stages, BN, acc_stride, tmem_cols;
+    int a_boxes, b_boxes;
+    uint32_t a_box_bytes, b_box_bytes, b_bytes, stage_bytes;
+    uint32_t a_lbo, a_sbo, a_kadv, a_layout, b_lbo, b_sbo, b_kadv, b_layout, idesc;
+    int num_tiles;
+    unsigned *status;
+    // CONV
+    int n_tiles_n, c_chunks, phases, BW, BH, BI, n_img, k_out, OH, OW, out_stride_y, out_stride_x;
+    PhaseInfo phase[kMaxPhases];
+    TapEntry taps[kMaxTaps];
+    float *out;
+    const float *bias;
+    // WGRAD
+    int ft_n, ct_n, taps_n, splits, chunks_x, chunks_y, chunks_i, k_rows, c_cols;
+    long long chunks_total;
+    float *partial;
+    // GEMM
+    int M, N, K, ldc, a_mn, b_mn;
+};
+
+struct TileCtx {
+    int nsteps;
+    int nt;                    // CONV/GEMM: n tile
+    int ph, tx, ty, ig;        // CONV
+    int ft, tap, ct, split;    // WGRAD
+    long long chunk_begin;     // WGRAD
+    int mt;                    // GEMM
+};
+
+template <int MODE>
+__device__ __forceinline__ TileCtx decode_tile(const TcParams &p, int tile)
+{
+    TileCtx c;
+    if (MODE == MODE_CONV) {
+        c.nt = tile % p.n_tiles_n;
+        int mt = tile / p.n_tiles_n;
+        int ph = 0;
+        while (ph + 1 < p.phases && mt >= p.phase[ph + 1].tile_begin) ph++;
+        const PhaseInfo &pi = p.phase[ph];
+        int local = mt - pi.tile_begin;
+        c.ph = ph;
+        c.tx = local % pi.tiles_x;
+        c.ty = (local / pi.tiles_x) % pi.tiles_y;
+        c.ig = local / (pi.tiles_x * pi.tiles_y);
+        c.nsteps = pi.tap_count * p.c_chunks;
+    } else if (MODE == MODE_WGRAD) {
+        c.split = tile % p.splits;
+        int rest = tile / p.splits;
+        c.ct = rest % p.ct_n; rest /= p.ct_n;
+        c.tap = rest % p.taps_n;
+        c.ft = rest / p.taps_n;
+        long long b = p.chunks_total * c.split / p.splits;
+        long long e = p.chunks_total * (c.split + 1) / p.splits;
+        c.chunk_begin = b;
+        c.nsteps = (int)(e - b);
+    } else {
+        c.nt = tile % p.n_tiles_n;
+        c.mt = tile / p.n_tiles_n;
+        c.nsteps = (p.K + 31) / 32;
+    }
+    return c;
+}
+
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned *status, unsigned code)
+{
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 128; i++)
+            if (ptx::mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitCycles) {
+            *abort_flag = 1;
+            atomicExch(status, code);
+            __threadfence_system();
+            return false;
+        }
+    }
+}
+
+template <int MODE, bool X3>
+__global__ void __launch_bounds__(kThreads, 1)
+tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ CUtensorMap mapA_lo,
+          const __grid_constant__ CUtensorMap mapB_hi, const __grid_constant__ CUtensorMap mapB_lo,
+          const __grid_constant__ TcParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)p.stages * p.stage_bytes);
+    // barrier layout: full[stages], empty[stages], tfull[2], tempty[2]
+    const uint32_t bar_base = ptx::smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (p.stages + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * p.stages + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * p.stages + 2 + a); };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * p.stages + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; s++) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; a++) { ptx::mbar_init(tfull_bar(a), 1); ptx::mbar_init(tempty_bar(a), 4); }
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::prefetch_tensormap(&mapA_hi);
+        ptx::prefetch_tensormap(&mapB_hi);
+        if (X3) { ptx::prefetch_tensormap(&mapA_lo); ptx::prefetch_tensormap(&mapB_lo); }
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), (uint32_t)p.tmem_cols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const uint32_t a_bytes = kABytes;
+    const uint32_t off_a_lo = a_bytes;
+    const uint32_t off_b_hi = X3 ? 2 * a_bytes : a_bytes;
+    const uint32_t off_b_lo = off_b_hi + p.b_bytes;
+    const uint32_t stage_tx = (a_bytes + p.b_bytes) * (X3 ? 2u : 1u);
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+                const TileCtx c = decode_tile<MODE>(p, tile);
+                for (int step = 0; step < c.nsteps; step++) {
+                    if (!wait_bar(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 0x100u + B200_E_TIMEOUT)) { ok = false; break; }
+                    const uint32_t fb = full_bar(stage);
+                    ptx::mbar_arrive_expect_tx(fb, stage_tx);
+                    const uint32_t sbase = ptx::smem_u32(smem + (size_t)stage * p.stage_bytes);
+                    int a0, a1, a2, a3, a4, b0, b1, b2, b3, b4;
+                    int a_step0 = 0, b_step0 = 0;   // which coordinate advances per box (always coordinate 0)
+                    if (MODE == MODE_CONV) {
+                        const PhaseInfo &pi = p.phase[c.ph];
+                        const int ti = step / p.c_chunks, cc = step - ti * p.c_chunks;
+                        const TapEntry t = p.taps[pi.tap_begin + ti];
+                        a0 = cc * 32; a1 = c.tx * p.BW + t.dx; a2 = c.ty * p.BH + t.dy; a3 = c.ig * p.BI; a4 = t.in_phase;
+                        b0 = cc * 32; b1 = t.wtap; b2 = c.nt * p.BN; b3 = 0; b4 = 0;
+                    } else if (MODE == MODE_WGRAD) {
+                        const long long q = c.chunk_begin + step;
+                        const int cx = (int)(q % p.chunks_x);
+                        const long long r = q / p.chunks_x;
+                        const int cy = (int)(r % p.chunks_y);
+                        const int ci = (int)(r / p.chunks_y);
+                        const TapEntry t = p.taps[c.tap];
+                        a0 = c.ft * 128; a1 = cx * p.BW; a2 = cy * p.BH; a3 = ci * p.BI; a4 = 0;
+                        b0 = c.ct * p.BN; b1 = cx * p.BW + t.dx; b2 = cy * p.BH + t.dy; b3 = ci * p.BI; b4 = t.in_phase;
+                        a_step0 = 32; b_step0 = 32;
+                    } else {
+                        const int k0 = step * 32;
+                        if (p.a_mn) { a0 = c.mt * 128; a1 = k0; a_step0 = 32; } else { a0 = k0; a1 = c.mt * 128; }
+                        if (p.b_mn) { b0 = c.nt * p.BN; b1 = k0; b_step0 = 32; } else { b0 = k0; b1 = c.nt * p.BN; }
+                        a2 = a3 = a4 = b2 = b3 = b4 = 0;
+                    }
+                    for (int j = 0; j < p.a_boxes; j++) {
+                        ptx::tma_load_5d(sbase + j * p.a_box_bytes, &mapA_hi, fb, a0 + j * a_step0, a1, a2, a3, a4);
+                        if (X3) ptx::tma_load_5d(sbase + off_a_lo + j * p.a_box_bytes, &mapA_lo, fb, a0 + j * a_step0, a1, a2, a3, a4);
+                    }
+                    for (int j = 0; j < p.b_boxes; j++) {
+                        ptx::tma_load_5d(sbase + off_b_hi + j * p.b_box_bytes, &mapB_hi, fb, b0 + j * b_step0, b1, b2, b3, b4);
+                        if (X3) ptx::tma_load_5d(sbase + off_b_lo + j * p.b_box_bytes, &mapB_lo, fb, b0 + j * b_step0, b1, b2, b3, b4);
+                    }
+                    if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int tile_iter = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, tile_iter++) {
+                const TileCtx c = decode_tile<MODE>(p, tile);
+                const int acc = tile_iter & 1;
+                const uint32_t acc_phase = (uint32_t)(tile_iter >> 1) & 1u;
+                if (!wait_bar(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 0x200u + B200_E_TIMEOUT)) break;
+                ptx::tc_fence_after();
+                const uint32_t d = tmem_base + (uint32_t)(acc * p.acc_stride);
+                for (int step = 0; step < c.nsteps; step++) {
+                    if (!wait_bar(full_bar(stage), phase, abort_flag, p.status, 0x300u + B200_E_TIMEOUT)) { ok = false; break; }
+                    ptx::tc_fence_after();
+                    const uint32_t sbase = ptx::smem_u32(smem + (size_t)stage * p.stage_bytes);
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const uint64_t a_hi = ptx::smem_desc(sbase + k * p.a_kadv, p.a_lbo, p.a_sbo, p.a_layout);
+                        const uint64_t b_hi = ptx::smem_desc(sbase + off_b_hi + k * p.b_kadv, p.b_lbo, p.b_sbo, p.b_layout);
+                        const uint32_t first = (step > 0 || k > 0) ? 1u : 0u;
+                        if (X3) {
+                            const uint64_t a_lo = ptx::smem_desc(sbase + off_a_lo + k * p.a_kadv, p.a_lbo, p.a_sbo, p.a_layout);
+                            const uint64_t b_lo = ptx::smem_desc(sbase + off_b_lo + k * p.b_kadv, p.b_lbo, p.b_sbo, p.b_layout);
+                            ptx::mma_tf32(d, a_lo, b_hi, p.idesc, first);   // small terms first
+                            ptx::mma_tf32(d, a_hi, b_lo, p.idesc, 1u);
+                            ptx::mma_tf32(d, a_hi, b_hi, p.idesc, 1u);
+                        } else {
+                            ptx::mma_tf32(d, a_hi, b_hi, p.idesc, first);
+                        }
+                    }
+                    ptx::mma_commit(empty_bar(stage));
+                    if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) ptx::mma_commit(tfull_bar(acc));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        int tile_iter = 0;
+        for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, tile_iter++) {
+            const TileCtx c = decode_tile<MODE>(p, tile);
+            const int acc = tile_iter & 1;
+            const uint32_t acc_phase = (uint32_t)(tile_iter >> 1) & 1u;
+            bool ok = wait_bar(tfull_bar(acc), acc_phase, abort_flag, p.status, 0x400u + B200_E_TIMEOUT);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * p.acc_stride);
+            float v[16];
+            if (MODE == MODE_CONV) {
+                const PhaseInfo &pi = p.phase[c.ph];
+                const int bx = row % p.BW, by = (row / p.BW) % p.BH, bi = row / (p.BW * p.BH);
+                const int n = c.ig * p.BI + bi, yy = c.ty * p.BH + by, xx = c.tx * p.BW + bx;
+                const bool valid = n < p.n_img && yy < pi.ext_y && xx < pi.ext_x;
+                const size_t plane = (size_t)p.OH * p.OW;
+                float *dst = p.out + (size_t)n * p.k_out * plane + (size_t)(yy * p.out_stride_y + pi.off_y) * p.OW +
+                             (xx * p.out_stride_x + pi.off_x);
+                for (int c0 = 0; c0 < p.BN; c0 += 16) {
+                    ptx::tmem_ld16(taddr + c0, v);
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const int k = c.nt * p.BN + c0 + j;
+                        if (valid && k < p.k_out) dst[(size_t)k * plane] = p.bias ? __fadd_rn(v[j], p.bias[k]) : v[j];
+                    }
+                }
+            } else if (MODE == MODE_WGRAD) {
+                const int f = c.ft * 128 + row;
+                float *dst = p.partial + (((size_t)c.split * p.taps_n + c.tap) * p.c_cols) * p.k_rows + f;
+                for (int c0 = 0; c0 < p.BN; c0 += 16) {
+                    ptx::tmem_ld16(taddr + c0, v);
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const int ch = c.ct * p.BN + c0 + j;
+                        if (f < p.k_rows && ch < p.c_cols) dst[(size_t)ch * p.k_rows] = v[j];
+                    }
+                }
+            } else {
+                const int m = c.mt * 128 + row;
+                float *dst = p.out + (size_t)m * p.ldc + c.nt * p.BN;
+                for (int c0 = 0; c0 < p.BN; c0 += 16) {
+                    ptx::tmem_ld16(taddr + c0, v);
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const int n = c.nt * p.BN + c0 + j;
+                        if (m < p.M && n < p.N) dst[c0 + j] = v[j];
+                    }
+                }
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+        }
+    }
+
+    if (*abort_flag) {   // give TMA copies still in flight time to land before the CTA's shared memory is released
+        const long long t0 = clock64();
+        while (clock64() - t0 < 200000) __nanosleep(200);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// operand packing (memory-bound pre-passes)
+// ---------------------------------------------------------------------------------------------------
+
+// NCHW fp32 -> phase-split NHWC, TF32-rounded high part and (optionally) TF32-rounded remainder:
+//   dst[ph][n][h/sy][w/sx][c],  ph = (h % sy) * sx + (w % sx),  channel pitch Cp (multiple of 4).
+__global__ void pack_act_kernel(const float *__restrict__ src, float *__restrict__ hi, float *__restrict__ lo,
+                                int N, int C, int H, int W, int Cp, int sy, int sx, int Hs, int Ws)
+{
+    __shared__ float tile[32][33];
+    const int n = blockIdx.z, h = blockIdx.y, w0 = blockIdx.x * 32;
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    const bool row_ok = h < H;
+    const int hq = h / sy, hr = h % sy;
+    for (int c0 = 0; c0 < Cp; c0 += 32) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            int c = c0 + ty + 8 * i, w = w0 + tx;
+            tile[ty + 8 * i][tx] = (row_ok && c < C && w < W) ? src[(((size_t)n * C + c) * H + h) * W + w] : 0.f;
+        }
+        __syncthreads();
+        const int c = c0 + tx;
+        if (c < Cp) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                int wl = ty + 8 * i, w = w0 + wl;
+                if (w < Ws * sx) {
+                    int ph = hr * sx + (w % sx);
+                    size_t o = ((((size_t)ph * N + n) * Hs + hq) * Ws + (w / sx)) * Cp + c;
+                    float v = tile[tx][wl];
+                    float vh = ptx::to_tf32(v);
+                    hi[o] = vh;
+                    if (lo) lo[o] = ptx::to_tf32(v - vh);
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// Weights [K][C][taps] -> rows x taps x inner (pitch ip):
+//   forward  (rot = 0): dst[k][tap][c] = W[k][c][tap]
+//   backward (rot = 1): dst[c][tap][k] = W[k][c][taps-1-tap]   (kernel rotated by 180 degrees)
+__global__ void pack_weight_kernel(const float *__restrict__ src, float *__restrict__ hi, float *__restrict__ lo,
+                                   int K, int C, int taps, int ip, int rot)
+{
+    const int rows = rot ? C : K, inner = rot ? K : C;
+    const size_t total = (size_t)rows * taps * ip;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        int i = idx % ip;
+        size_t t = idx / ip;
+        int tap = t % taps;
+        int r = t / taps;
+        float v = 0.f;
+        if (i < inner) v = rot ? src[((size_t)i * C + r) * taps + (taps - 1 - tap)] : src[((size_t)r * C + i) * taps + tap];
+        float vh = ptx::to_tf32(v);
+        hi[idx] = vh;
+        if (lo) lo[idx] = ptx::to_tf32(v - vh);
+    }
+}
+
+__global__ void split_tf32_kernel(const float *__restrict__ src, float *__restrict__ hi, float *__restrict__ lo, size_t n)
+{
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float v = src[i];
+        float vh = ptx::to_tf32(v);
+        hi[i] = vh;
+        if (lo) lo[i] = ptx::to_tf32(v - vh);
+    }
+}
+
+// dkernel[f][c*taps + tap] (+)= sum over splits (in increasing order) of partial[split][tap][c][f]
+__global__ void wgrad_reduce_kernel(float *__restrict__ dkernel, const float *__restrict__ partial, int splits, int taps,
+                                    int C, int K, int accumulate)
+{
+    const size_t total = (size_t)K * C * taps;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        // idx enumerates (tap, c, f) with f fastest so that the reads are coalesced
+        int f = idx % K;
+        size_t t = idx / K;
+        int c = t % C;
+        int tap = t / C;
+        float s = 0.f;
+        for (int sp = 0; sp < splits; sp++) s += partial[(((size_t)sp * taps + tap) * C + c) * K + f];
+        size_t o = ((size_t)f * C + c) * taps + tap;
+        dkernel[o] = accumulate ? dkernel[o] + s : s;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// 5-D fp32 tensor map with 128-byte swizzle (32-byte atoms when the operand is MN-major); dims[0] is the contiguous dimension, pitch[i] is the
+// stride of dimension i+1 in ELEMENTS.  Unused trailing dimensions have size 1.
+static int make_map(CUtensorMap *m, const float *base, const long long dims[5], const long long pitch[4], const int box[5],
+                    bool mn_major = false)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(B200_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t gd[5], gs[4];
+    cuuint32_t bx[5], es[5];
+    for (int i = 0; i < 5; i++) { gd[i] = (cuuint64_t)dims[i]; bx[i] = (cuuint32_t)box[i]; es[i] = 1; }
+    for (int i = 0; i < 4; i++) gs[i] = (cuuint64_t)pitch[i] * sizeof(float);
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float *>(base), gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(B200_E_CUDA, "cuTensorMapEncodeTiled failed (%d) dims %lld %lld %lld %lld %lld box %d %d %d %d %d", (int)r,
+                    dims[0], dims[1], dims[2], dims[3], dims[4], box[0], box[1], box[2], box[3], box[4]);
+    return B200_OK;
+}
+
+static int pow2_ceil(int v) { int p = 1; while (p < v) p <<= 1; return p; }
+static int floor_div(int a, int b) { int q = a / b; if ((a % b != 0) && ((a < 0) != (b < 0))) q--; return q; }
+static int pos_mod(int a, int b) { int r = a % b; return r < 0 ? r + b : r; }
+
+// Host-visible status word of the current device (pinned, mapped): device-side waits that give up
+// write a code here; the library reads it without synchronising.
+static unsigned *g_status_host[64];
+static unsigned *g_status_dev[64];
+
+static int status_word(unsigned **dev)
+{
+    int d = 0;
+    cudaGetDevice(&d);
+    if (d < 0 || d >= 64) d = 0;
+    if (!g_status_host[d]) {
+        void *h = nullptr, *dp = nullptr;
+        B200_CUDA(cudaHostAlloc(&h, sizeof(unsigned), cudaHostAllocMapped));
+        *(unsigned *)h = 0;
+        B200_CUDA(cudaHostGetDevicePointer(&dp, h, 0));
+        g_status_host[d] = (unsigned *)h;
+        g_status_dev[d] = (unsigned *)dp;
+    }
+    *dev = g_status_dev[d];
+    return B200_OK;
+}
+
+unsigned tc_read_status(int clear)
+{
+    int d = 0;
+    cudaGetDevice(&d);
+    if (d < 0 || d >= 64 || !g_status_host[d]) return 0;
+    unsigned v = *(volatile unsigned *)g_status_host[d];
+    if (clear) *(volatile unsigned *)g_status_host[d] = 0;
+    return v;
+}
+
+static size_t g_smem_optin = 0;
+
+template <int MODE>
+static int launch_tc(const CUtensorMap maps[4], TcParams &p, bool x3, cudaStream_t s)
+{
+    if (!g_smem_optin) {
+        int d = 0, v = 0;
+        cudaGetDevice(&d);
+        B200_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, d));
+        g_smem_optin = (size_t)v;
+    }
+    p.b_bytes = (uint32_t)p.b_boxes * p.b_box_bytes;
+    p.stage_bytes = (uint32_t)((kABytes + p.b_bytes) * (x3 ? 2 : 1));
+    const size_t fixed = 1024 /*alignment slack*/ + 256 /*barriers*/;
+    int stages = (int)((g_smem_optin - fixed) / p.stage_bytes);
+    if (stages > 8) stages = 8;
+    if (stages < 2) return TC_UNSUPPORTED;
+    p.stages = stages;
+    int cols = 2 * p.acc_stride;
+    if (cols < 32) cols = 32;
+    p.tmem_cols = cols;
+    int r = status_word(&p.status);
+    if (r) return r;
+    const size_t smem = (size_t)stages * p.stage_bytes + fixed;
+    int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+    if (grid < 1) return B200_OK;
+    if (x3) {
+        B200_CUDA(cudaFuncSetAttribute(tc_kernel<MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        tc_kernel<MODE, true><<<grid, kThreads, smem, s>>>(maps[0], maps[1], maps[2], maps[3], p);
+    } else {
+        B200_CUDA(cudaFuncSetAttribute(tc_kernel<MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        tc_kernel<MODE, false><<<grid, kThreads, smem, s>>>(maps[0], maps[0], maps[2], maps[2], p);
+    }
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+static void set_kmajor(TcParams &p, bool a_side, int rows)
+{
+    if (a_side) { p.a_boxes = 1; p.a_box_bytes = kABytes; p.a_lbo = 16; p.a_sbo = 1024; p.a_kadv = 32; p.a_layout = 2; }
+    else { p.b_boxes = 1; p.b_box_bytes = (uint32_t)rows * 128; p.b_lbo = 16; p.b_sbo = 1024; p.b_kadv = 32; p.b_layout = 2; }
+}
+static void set_mnmajor(TcParams &p, bool a_side, int extent)
+{
+    // MN-major 32-bit operands: 32 elements (128 B) contiguous along M/N per k-row, rows 128 B apart,
+    // swizzled in 32-byte atoms over groups of 4 rows (SBO = 512 B between groups); one TMA box is
+    // 32 k-rows x 32 elements = 4 KB, boxes follow each other along M/N (LBO); one MMA eats 8 rows.
+    if (a_side) { p.a_boxes = 4; p.a_box_bytes = 4096; p.a_lbo = 4096; p.a_sbo = 512; p.a_kadv = 1024; p.a_layout = 1; }
+    else { p.b_boxes = extent / 32; p.b_box_bytes = 4096; p.b_lbo = 4096; p.b_sbo = 512; p.b_kadv = 1024; p.b_layout = 1; }
+}
+
+static int pack_act(const float *src, float *hi, float *lo, int N, int C, int H, int W, int Cp, int sy, int sx, int Hs, int Ws,
+                    cudaStream_t s)
+{
+    dim3 grid(ceil_div(Ws * sx, 32), Hs * sy, N), block(32, 8);
+    if (grid.y > 65535 || grid.z > 65535) return TC_UNSUPPORTED;
+    pack_act_kernel<<<grid, block, 0, s>>>(src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+static int pack_weight(const float *src, float *hi, float *lo, int K, int C, int taps, int ip, int rot, cudaStream_t s)
+{
+    size_t total = (size_t)(rot ? C : K) * taps * ip;
+    int grid = (int)((total + 255) / 256);
+    if (grid > sm_count() * 16) grid = sm_count() * 16;
+    pack_weight_kernel<<<grid, 256, 0, s>>>(src, hi, lo, K, C, taps, ip, rot);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+static bool geom_supported(const b200_conv_geom &g)
+{
+    if (g.kernel_x * g.kernel_y > kMaxTaps) return false;
+    if (g.stride_x * g.stride_y > kMaxPhases) return false;
+    if (g.kernel_x > 100 || g.kernel_y > 100 || g.padding_x > 100 || g.padding_y > 100) return false;   // tap offsets are int8
+    return true;
+}
+
+// M-tile shape: 128 output positions as a BI x BH x BW box over (image, row, column).
+static void tile_shape(int ext_y, int ext_x, int target, int *BW, int *BH, int *BI)
+{
+    *BW = pow2_ceil(ext_x) < target ? pow2_ceil(ext_x) : target;
+    int rest = target / *BW;
+    *BH = pow2_ceil(ext_y) < rest ? pow2_ceil(ext_y) : rest;
+    *BI = rest / *BH;
+}
+
+// Shared body of the forward convolution and of one backward-data convolution: `act` is the tensor
+// that is gathered (channels act_c, size act_y x act_x, phase-split by (sy, sx) when the gather is
+// strided), `out` the tensor produced (k_out channels, OH x OW), written at (yy*osy + ry, xx*osx + rx).
+static int run_conv(bool backward, const b200_conv_geom &g, float *out, const float *act, const float *kernel, const float *bias,
+                    int batch, int precision, cudaStream_t s)
+{
+    if (!geom_supported(g)) return TC_UNSUPPORTED;
+    const bool x3 = precision == B200_TF32X3;
+    const int taps = g.kernel_x * g.kernel_y;
+    const int act_c = backward ? g.kernel_amount : g.in_z;
+    const int act_y = backward ? g.out_y : g.in_y, act_x = backward ? g.out_x : g.in_x;
+    const int k_out = backward ? g.in_z : g.kernel_amount;
+    const int OH = backward ? g.in_y : g.out_y, OW = backward ? g.in_x : g.out_x;
+    const int sy = backward ? 1 : g.stride_y, sx = backward ? 1 : g.stride_x;        // phase split of the gathered tensor
+    const int osy = backward ? g.stride_y : 1, osx = backward ? g.stride_x : 1;      // output phases
+    const int Cp = (int)align_up(act_c, 4);
+    const int Hs = ceil_div(act_y, sy), Ws = ceil_div(act_x, sx);
+    const size_t act_elems = (size_t)sy * sx * batch * Hs * Ws * Cp;
+    const size_t w_elems = (size_t)k_out * taps * Cp;
+    const size_t bytes = sizeof(float) * (act_elems + w_elems) * (x3 ? 2 : 1) + 8192;
+    int r = arena_reserve(bytes, s);
+    if (r) return r;
+    arena_reset();
+    float *a_hi = (float *)arena_take(sizeof(float) * act_elems);
+    float *a_lo = x3 ? (float *)arena_take(sizeof(float) * act_elems) : nullptr;
+    float *w_hi = (float *)arena_take(sizeof(float) * w_elems);
+    float *w_lo = x3 ? (float *)arena_take(sizeof(float) * w_elems) : nullptr;
+    if (!a_hi || !w_hi || (x3 && (!a_lo || !w_lo))) return fail(B200_E_NOMEM, "scratch arena exhausted");
+    if ((r = pack_act(act, a_hi, a_lo, batch, act_c, act_y, act_x, Cp, sy, sx, Hs, Ws, s))) return r;
+    if ((r = pack_weight(kernel, w_hi, w_lo, g.kernel_amount, g.in_z, taps, Cp, backward ? 1 : 0, s))) return r;
+
+    TcParams p;
+    memset(&p, 0, sizeof(p));
+    p.BN = (int)align_up(k_out < 256 ? k_out : 256, 16);
+    p.acc_stride = pow2_ceil(p.BN);
+    set_kmajor(p, true, 128);
+    set_kmajor(p, false, p.BN);
+    p.idesc = make_idesc_tf32(p.BN, 0, 0);
+    p.n_tiles_n = ceil_div(k_out, p.BN);
+    p.c_chunks = ceil_div(act_c, 32);
+    p.n_img = batch; p.k_out = k_out; p.OH = OH; p.OW = OW; p.out_stride_y = osy; p.out_stride_x = osx;
+    p.out = out; p.bias = bias;
+
+    // output phases and their tap lists
+    const int pad_y = backward ? g.kernel_y - 1 - g.padding_y : g.padding_y;
+    const int pad_x = backward ? g.kernel_x - 1 - g.padding_x : g.padding_x;
+    const int ext_y0 = ceil_div(OH, osy), ext_x0 = ceil_div(OW, osx);
+    tile_shape(ext_y0, ext_x0, 128, &p.BW, &p.BH, &p.BI);
+    int ntaps = 0, mtiles = 0, nph = 0;
+    bool any_empty = false;
+    for (int ry = 0; ry < osy; ry++)
+        for (int rx = 0; rx < osx; rx++) {
+            PhaseInfo pi;
+            pi.off_y = ry; pi.off_x = rx;
+            pi.ext_y = (OH - ry + osy - 1) / osy; pi.ext_x = (OW - rx + osx - 1) / osx;
+            pi.tap_begin = ntaps; pi.tap_count = 0;
+            if (pi.ext_y <= 0 || pi.ext_x <= 0) continue;
+            for (int ky = 0; ky < g.kernel_y; ky++)
+                for (int kx = 0; kx < g.kernel_x; kx++) {
+                    TapEntry t;
+                    if (!backward) {
+                        // input row = sy*oy + ky - pad = sy*(oy + dy) + phase
+                        t.dy = (int8_t)floor_div(ky - pad_y, sy); t.dx = (int8_t)floor_div(kx - pad_x, sx);
+                        t.in_phase = (uint8_t)(pos_mod(ky - pad_y, sy) * sx + pos_mod(kx - pad_x, sx));
+                    } else {
+                        // delta row = (osy*yy + ry + ky - pad) / osy, only taps where the division is exact
+                        int ny = ry + ky - pad_y, nx = rx + kx - pad_x;
+                        if (pos_mod(ny, osy) != 0 || pos_mod(nx, osx) != 0) continue;
+                        t.dy = (int8_t)floor_div(ny, osy); t.dx = (int8_t)floor_div(nx, osx);
+                        t.in_phase = 0;
+                    }
+                    t.wtap = (uint8_t)(ky * g.kernel_x + kx);
+                    p.taps[ntaps++] = t;
+                    pi.tap_count++;
+                }
+            if (pi.tap_count == 0) { any_empty = true; ntaps = pi.tap_begin; continue; }
+            pi.tiles_x = ceil_div(pi.ext_x, p.BW); pi.tiles_y = ceil_div(pi.ext_y, p.BH); pi.tiles_i = ceil_div(batch, p.BI);
+            pi.tile_begin = mtiles;
+            mtiles += pi.tiles_x * pi.tiles_y * pi.tiles_i;
+            p.phase[nph++] = pi;
+        }
+    if (any_empty) B200_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * (size_t)batch * k_out * OH * OW, s));
+    if (nph == 0) return B200_OK;
+    p.phases = nph;
+    p.num_tiles = mtiles * p.n_tiles_n;
+
+    CUtensorMap maps[4];
+    {
+        const long long dims[5] = {act_c, Ws, Hs, batch, (long long)sy * sx};
+        const long long pitch[4] = {Cp, (long long)Ws * Cp, (long long)Hs * Ws * Cp, (long long)batch * Hs * Ws * Cp};
+        const int box[5] = {32, p.BW, p.BH, p.BI, 1};
+        if ((r = make_map(&maps[0], a_hi, dims, pitch, box))) return r;
+        if (x3 && (r = make_map(&maps[1], a_lo, dims, pitch, box))) return r;
+    }
+    {
+        const long long dims[5] = {act_c, taps, k_out, 1, 1};
+        const long long pitch[4] = {Cp, (long long)taps * Cp, (long long)k_out * taps * Cp, (long long)k_out * taps * Cp};
+        const int box[5] = {32, 1, p.BN, 1, 1};
+        if ((r = make_map(&maps[2], w_hi, dims, pitch, box))) return r;
+        if (x3 && (r = make_map(&maps[3], w_lo, dims, pitch, box))) return r;
+    }
+    return launch_tc<MODE_CONV>(maps, p, x3, s);
+}
+
+int tc_conv_forward(const b200_conv_geom &g, float *out, const float *image, const float *kernel, const float *bias,
+                    int batch, int precision, cudaStream_t s)
+{
+    return run_conv(false, g, out, image, kernel, bias, batch, precision, s);
+}
+
+int tc_conv_backward(const b200_conv_geom &g, float *out_delta, const float *delta, const float *kernel, int batch,
+                     int precision, cudaStream_t s)
+{
+    return run_conv(true, g, out_delta, delta, kernel, nullptr, batch, precision, s);
+}
+
+int tc_conv_wgrad_batch(const b200_conv_geom &g, float *dkernel, float *dbias, int accumulate, const float *image,
+                        const float *delta, int batch, int precision, cudaStream_t s)
+{
+    if (!geom_supported(g)) return TC_UNSUPPORTED;
+    const bool x3 = precision == B200_TF32X3;
+    const int taps = g.kernel_x * g.kernel_y;
+    const int C = g.in_z, K = g.kernel_amount;
+    const int sy = g.stride_y, sx = g.stride_x;
+    const int Cp = (int)align_up(C, 4), Kp = (int)align_up(K, 4);
+    const int Hs = ceil_div(g.in_y, sy), Ws = ceil_div(g.in_x, sx);
+    const size_t x_elems = (size_t)sy * sx * batch * Hs * Ws * Cp;
+    const size_t d_elems = (size_t)batch * g.out_y * g.out_x * Kp;
+
+    TcParams p;
+    memset(&p, 0, sizeof(p));
+    p.BN = (int)align_up(C < 256 ? C : 256, 32);
+    p.acc_stride = pow2_ceil(p.BN);
+    set_mnmajor(p, true, 128);
+    set_mnmajor(p, false, p.BN);
+    p.idesc = make_idesc_tf32(p.BN, 1, 1);
+    p.ft_n = ceil_div(K, 128); p.ct_n = ceil_div(C, p.BN); p.taps_n = taps;
+    p.k_rows = K; p.c_cols = C;
+    tile_shape(g.out_y, g.out_x, 32, &p.BW, &p.BH, &p.BI);
+    p.chunks_x = ceil_div(g.out_x, p.BW); p.chunks_y = ceil_div(g.out_y, p.BH); p.chunks_i = ceil_div(batch, p.BI);
+    p.chunks_total = (long long)p.chunks_x * p.chunks_y * p.chunks_i;
+    const int base = p.ft_n * p.ct_n * taps;
+    long long splits = sm_count() / base;
+    if (splits < 1) splits = 1;
+    if (splits > p.chunks_total) splits = p.chunks_total;
+    if (splits > 64) splits = 64;
+    p.splits = (int)splits;
+    p.num_tiles = base * p.splits;
+    for (int ky = 0; ky < g.kernel_y; ky++)
+        for (int kx = 0; kx < g.kernel_x; kx++) {
+            TapEntry t;
+            t.dy = (int8_t)floor_div(ky - g.padding_y, sy); t.dx = (int8_t)floor_div(kx - g.padding_x, sx);
+            t.in_phase = (uint8_t)(pos_mod(ky - g.padding_y, sy) * sx + pos_mod(kx - g.padding_x, sx));
+            t.wtap = (uint8_t)(ky * g.kernel_x + kx);
+            p.taps[ky * g.kernel_x + kx] = t;
+        }
+
+    const size_t part_elems = (size_t)p.splits * taps * C * K;
+    const size_t db_elems = dbias ? (size_t)batch * K : 0;
+    const size_t bytes = sizeof(float) * ((x_elems + d_elems) * (x3 ? 2 : 1) + part_elems + db_elems) + 16384;
+    int r = arena_reserve(bytes, s);
+    if (r) return r;
+    arena_reset();
+    float *x_hi = (float *)arena_take(sizeof(float) * x_elems);
+    float *x_lo = x3 ? (float *)arena_take(sizeof(float) * x_elems) : nullptr;
+    float *d_hi = (float *)arena_take(sizeof(float) * d_elems);
+    float *d_lo = x3 ? (float *)arena_take(sizeof(float) * d_elems) : nullptr;
+    p.partial = (float *)arena_take(sizeof(float) * part_elems);
+    float *db_tmp = dbias ? (float *)arena_take(sizeof(float) * db_elems) : nullptr;
+    if (!x_hi || !d_hi || !p.partial || (x3 && (!x_lo || !d_lo)) || (dbias && !db_tmp)) return fail(B200_E_NOMEM, "scratch arena exhausted");
+    if ((r = pack_act(image, x_hi, x_lo, batch, C, g.in_y, g.in_x, Cp, sy, sx, Hs, Ws, s))) return r;
+    if ((r = pack_act(delta, d_hi, d_lo, batch, K, g.out_y, g.out_x, Kp, 1, 1, g.out_y, g.out_x, s))) return r;
+
+    CUtensorMap maps[4];
+    {
+        const long long dims[5] = {K, g.out_x, g.out_y, batch, 1};
+        const long long pitch[4] = {Kp, (long long)g.out_x * Kp, (long long)g.out_y * g.out_x * Kp, (long long)batch * g.out_y * g.out_x * Kp};
+        const int box[5] = {32, p.BW, p.BH, p.BI, 1};
+        if ((r = make_map(&maps[0], d_hi, dims, pitch, box, true))) return r;
+        if (x3 && (r = make_map(&maps[1], d_lo, dims, pitch, box, true))) return r;
+    }
+    {
+        const long long dims[5] = {C, Ws, Hs, batch, (long long)sy * sx};
+        const long long pitch[4] = {Cp, (long long)Ws * Cp, (long long)Hs * Ws * Cp, (long long)batch * Hs * Ws * Cp};
+        const int box[5] = {32, p.BW, p.BH, p.BI, 1};
+        if ((r = make_map(&maps[2], x_hi, dims, pitch, box, true))) return r;
+        if (x3 && (r = make_map(&maps[3], x_lo, dims, pitch, box, true))) return r;
+    }
+    if ((r = launch_tc<MODE_WGRAD>(maps, p, x3, s))) return r;
+    {
+        size_t total = (size_t)K * C * taps;
+        int grid = (int)((total + 255) / 256);
+        if (grid > sm_count() * 16) grid = sm_count() * 16;
+        wgrad_reduce_kernel<<<grid, 256, 0, s>>>(dkernel, p.partial, p.splits, taps, C, K, accumulate);
+        B200_LAUNCH_CHECK();
+    }
+    if (dbias) {
+        // bias gradient: plane sums of delta per (sample, filter), then the reduction over the batch
+        if ((r = b200_summ_xy(db_tmp, batch, delta, batch, K, (size_t)g.out_y * g.out_x, s))) return r;
+        if (!accumulate) B200_CUDA(cudaMemsetAsync(dbias, 0, sizeof(float) * K, s));
+        if ((r = b200_add_sum_w(dbias, 1, dbias, 1, db_tmp, batch, K, 1.f, 1.f, s))) return r;
+    }
+    return B200_OK;
+}
+
+int tc_gemm(float *out, const float *a, const float *b, int m, int n, int k, int a_mn_major, int b_mn_major,
+            int precision, cudaStream_t s)
+{
+    // TMA needs 16-byte aligned bases and row pitches
+    const int a_pitch = a_mn_major ? m : k, b_pitch = b_mn_major ? n : k;
+    if ((a_pitch % 4) || (b_pitch % 4)) return TC_UNSUPPORTED;
+    if ((size_t)m * n < 4096 || k < 8) return TC_UNSUPPORTED;      // too small to be worth a tensor-core launch
+    const bool x3 = precision == B200_TF32X3;
+    const size_t a_elems = (size_t)m * k, b_elems = (size_t)n * k;
+    const size_t bytes = sizeof(float) * (a_elems + b_elems) * (x3 ? 2 : 1) + 8192;
+    int r = arena_reserve(bytes, s);
+    if (r) return r;
+    arena_reset();
+    float *a_hi = (float *)arena_take(sizeof(float) * a_elems);
+    float *a_lo = x3 ? (float *)arena_take(sizeof(float) * a_elems) : nullptr;
+    float *b_hi = (float *)arena_take(sizeof(float) * b_elems);
+    float *b_lo = x3 ? (float *)arena_take(sizeof(float) * b_elems) : nullptr;
+    if (!a_hi || !b_hi || (x3 && (!a_lo || !b_lo))) return fail(B200_E_NOMEM, "scratch arena exhausted");
+    int grid = sm_count() * 8;
+    split_tf32_kernel<<<grid, 256, 0, s>>>(a, a_hi, a_lo, a_elems);
+    B200_LAUNCH_CHECK();
+    split_tf32_kernel<<<grid, 256, 0, s>>>(b, b_hi, b_lo, b_elems);
+    B200_LAUNCH_CHECK();
+
+    TcParams p;
+    memset(&p, 0, sizeof(p));
+    p.BN = (int)align_up(n < 256 ? n : 256, b_mn_major ? 32 : 16);
+    p.acc_stride = pow2_ceil(p.BN);
+    if (a_mn_major) set_mnmajor(p, true, 128); else set_kmajor(p, true, 128);
+    if (b_mn_major) set_mnmajor(p, false, p.BN); else set_kmajor(p, false, p.BN);
+    p.idesc = make_idesc_tf32(p.BN, a_mn_major, b_mn_major);
+    p.M = m; p.N = n; p.K = k; p.ldc = n; p.a_mn = a_mn_major; p.b_mn = b_mn_major;
+    p.n_tiles_n = ceil_div(n, p.BN);
+    p.num_tiles = ceil_div(m, 128) * p.n_tiles_n;
+    p.out = out;
+
+    CUtensorMap maps[4];
+    {
+        const long long d0 = a_mn_major ? m : k, d1 = a_mn_major ? k : m;
+        const long long dims[5] = {d0, d1, 1, 1, 1};
+        const long long pitch[4] = {d0, d0 * d1, d0 * d1, d0 * d1};
+        const int box[5] = {32, a_mn_major ? 32 : 128, 1, 1, 1};
+        if ((r = make_map(&maps[0], a_hi, dims, pitch, box, a_mn_major != 0))) return r;
+        if (x3 && (r = make_map(&maps[1], a_lo, dims, pitch, box, a_mn_major != 0))) return r;
+    }
+    {
+        const long long d0 = b_mn_major ? n : k, d1 = b_mn_major ? k : n;
+        const long long dims[5] = {d0, d1, 1, 1, 1};
+        const long long pitch[4] = {d0, d0 * d1, d0 * d1, d0 * d1};
+        const int box[5] = {32, b_mn_major ? 32 : p.BN, 1, 1, 1};
+        if ((r = make_map(&maps[2], b_hi, dims, pitch, box, b_mn_major != 0))) return r;
+        if (x3 && (r = make_map(&maps[3], b_lo, dims, pitch, box, b_mn_major != 0))) return r;
+    }
+    return launch_tc<MODE_GEMM>(maps, p, x3, s);
+}
+
+}  // namespace b200

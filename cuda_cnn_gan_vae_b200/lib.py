@@ -1,0 +1,69 @@
+"""ctypes binding of libb200conv.so: one Python callable per symbol of include/b200conv.h."""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libb200conv.so")
+
+
+class ConvGeom(C.Structure):
+    """struct b200_conv_geom."""
+    _fields_ = [(n, C.c_int) for n in ("in_z", "in_y", "in_x", "kernel_amount", "kernel_y", "kernel_x", "stride_y",
+                                       "stride_x", "padding_y", "padding_x", "out_y", "out_x")]
+
+
+_fp, _vp, _i, _sz, _f, _d = C.c_void_p, C.c_void_p, C.c_int, C.c_size_t, C.c_float, C.c_double
+_G = C.POINTER(ConvGeom)
+
+# name -> (restype, argtypes); must list every function declared in include/b200conv.h
+SIGNATURES = {
+    "b200_last_error": (C.c_char_p, []),
+    "b200_last_path": (_i, []),
+    "b200_set_precision": (_i, [_i]),
+    "b200_get_precision": (_i, []),
+    "b200_shutdown": (_i, []),
+    "b200_scratch_bytes": (_sz, []),
+    "b200_stream_status": (_i, [_vp]),
+    "b200_conv_forward": (_i, [_G, _fp, _i, _fp, _i, _fp, _i, _fp, _i, _vp]),
+    "b200_conv_backward": (_i, [_G, _fp, _i, _fp, _i, _fp, _i, _fp, _i, _vp]),
+    "b200_conv_wgrad": (_i, [_G, _fp, _i, _fp, _i, _fp, _i, _fp, _i, _vp]),
+    "b200_conv_back_wgrad": (_i, [_G, _fp, _i, _fp, _i, _fp, _i, _fp, _i, _vp]),
+    "b200_conv_wgrad_batch": (_i, [_G, _fp, _fp, _i, _fp, _fp, _i, _vp]),
+    "b200_mul": (_i, [_fp, _i, _fp, _i, _fp, _i, _i, _i, _i, _i, _i, _vp]),
+    "b200_add": (_i, [_fp, _i, _fp, _i, _fp, _i, _sz, _f, _f, _i, _vp]),
+    "b200_add_sum_w": (_i, [_fp, _i, _fp, _i, _fp, _i, _sz, _f, _f, _vp]),
+    "b200_add_bias": (_i, [_fp, _i, _i, _sz, _fp, _i, _vp]),
+    "b200_summ_xy": (_i, [_fp, _i, _fp, _i, _i, _sz, _vp]),
+    "b200_unary": (_i, [_fp, _i, _fp, _i, _sz, _i, _f, _f, _vp]),
+    "b200_item_product": (_i, [_fp, _i, _fp, _i, _fp, _i, _sz, _vp]),
+    "b200_fill": (_i, [_fp, _sz, _f, _vp]),
+    "b200_activation": (_i, [_fp, _fp, _sz, _i, _i, _f, _vp]),
+    "b200_activation_backward": (_i, [_fp, _fp, _fp, _sz, _i, _f, _vp]),
+    "b200_bias_activation": (_i, [_fp, _fp, _i, _i, _sz, _fp, _i, _f, _vp]),
+    "b200_maxpool": (_i, [_fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _vp]),
+    "b200_maxpool_backward": (_i, [_fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _vp]),
+    "b200_upsample": (_i, [_fp, _fp, _i, _i, _i, _i, _i, _i, _vp]),
+    "b200_downsample": (_i, [_fp, _fp, _i, _i, _i, _i, _i, _i, _vp]),
+    "b200_bn_forward": (_i, [_fp] * 10 + [_i, _sz, _f, _f, _vp]),
+    "b200_bn_backward": (_i, [_fp] * 7 + [_i, _sz, _i, _vp]),
+    "b200_vae_forward": (_i, [_fp, _fp, _fp, _fp, _i, _sz, C.POINTER(C.c_float), _vp]),
+    "b200_vae_backward": (_i, [_fp] * 6 + [_sz, _f, _vp]),
+    "b200_adam": (_i, [_fp, _fp, _fp, _fp, _sz, C.c_uint32, _d, _d, _d, _d, _d, _vp]),
+}
+
+_lib = None
+
+
+def load():
+    """Loads the C-ABI library.  Raises if it has not been built: there is no fallback path."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: run `python -m cuda_cnn_gan_vae_b200.build` (nvcc, sm_100a)")
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib

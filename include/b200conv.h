@@ -1,0 +1,208 @@
+/*
+ * b200conv.h -- C ABI of the B200 (sm_100a) convolution hot-path library (libb200conv.so).
+ *
+ * Drop-in boundary for the tensor-math layer of da-nie/CUDA-CNN-GAN-VAE: every entry point below
+ * replaces one static method of the reference's CTensorConv / CTensorMath / CTensorApplyFunc
+ * classes (the reference file:line is cited on each).  The reference has no C ABI of its own; its
+ * header-only templates call CUDA kernels directly, so the binding a maintainer adds is a thin
+ * header whose static methods forward to these functions (shipped in host/ of this package).
+ *
+ * Conventions
+ *  - All tensors are dense fp32 in the reference layout W,Z,Y,X (W = batch, Z = channels), i.e.
+ *    NCHW; every pointer is a DEVICE pointer unless a name ends in _host.  Position tensors of
+ *    max-pooling are pairs {uint32 X, uint32 Y} (the reference's SPos).
+ *  - Every operand carries its own W count and is indexed with (w % count): the reference's
+ *    W-broadcast rule (cpu/ctensorconv.h:113-116).
+ *  - Convolution weights are [Wk][K][C*kh*kw], a filter row ordered c*kh*kw + ky*kw + kx
+ *    (cpu/ctensorconv.h:138); bias is [Wb][K].
+ *  - `stream` is a cudaStream_t passed as void*.  Calls are asynchronous on that stream; they
+ *    never exit the process and never throw.  Return value 0 = success, otherwise a B200_E_* code;
+ *    b200_last_error() gives the text of the last failure on the calling thread.
+ *  - Scratch memory (packed operands, split-K partial sums) comes from a per-device arena that the
+ *    library grows with cudaMalloc on demand and releases in b200_shutdown().
+ */
+#ifndef B200CONV_H
+#define B200CONV_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    B200_OK = 0,
+    B200_E_SHAPE = 1,      /* inconsistent sizes (the reference throws a C string here)            */
+    B200_E_ARG = 2,        /* null pointer / unsupported value                                      */
+    B200_E_CUDA = 3,       /* a CUDA runtime or driver call failed                                  */
+    B200_E_TIMEOUT = 4,    /* a bounded device-side wait gave up; the context stays usable          */
+    B200_E_NOMEM = 5,      /* a fixed-size scratch area is too small for this call                  */
+    B200_E_NCCL = 6
+};
+
+/* Arithmetic of the tensor-core contractions.  B200_TF32X3 (default) splits every operand into a
+ * TF32 high and low part and issues three MMAs per product (error ~2^-21, meets 1e-4 against the
+ * fp32 CPU backend); B200_TF32 issues one (error ~2^-11, 2e-3); B200_FP32 forces the CUDA-core
+ * fp32 kernels for every shape. */
+enum { B200_TF32X3 = 0, B200_TF32 = 1, B200_FP32 = 2 };
+
+/* Which implementation the last convolution / GEMM call on this thread used. */
+enum { B200_PATH_NONE = 0, B200_PATH_SIMT = 1, B200_PATH_TCGEN05 = 2 };
+
+/* Geometry of one convolution layer, named as in the reference signatures
+ * (cuda/ctensorconv.cu.h:63-66).  out_y/out_x are the spatial size of the forward output
+ * ((in - kernel + 2*padding)/stride + 1); for the backward pass in_y/in_x is the size of the
+ * tensor being produced. */
+typedef struct b200_conv_geom {
+    int in_z, in_y, in_x;          /* image channels, height, width                               */
+    int kernel_amount;             /* number of filters K                                          */
+    int kernel_y, kernel_x;
+    int stride_y, stride_x;
+    int padding_y, padding_x;
+    int out_y, out_x;
+} b200_conv_geom;
+
+/* Activation codes (netlayer/neuron.cu.h NEURON_FUNCTION_*; scalar definitions
+ * cpu/ctensorapplyfunc.h:128-257).  LEAKY_RELU uses the slope given to the call (the reference
+ * constant is 0.1). */
+enum { B200_ACT_SIGMOID = 0, B200_ACT_RELU = 1, B200_ACT_LEAKY_RELU = 2, B200_ACT_LINEAR = 3,
+       B200_ACT_TANH = 4, B200_ACT_GELU = 5 };
+
+/* ---- library control ------------------------------------------------------------------------ */
+const char *b200_last_error(void);
+int b200_last_path(void);
+int b200_set_precision(int mode);
+int b200_get_precision(void);
+/* Frees the scratch arena of every device.  Safe to call more than once. */
+int b200_shutdown(void);
+/* Bytes currently held by the scratch arena of the current device. */
+size_t b200_scratch_bytes(void);
+/* Waits for `stream` and reports what the kernels recorded: B200_OK, B200_E_CUDA if the stream
+ * failed, B200_E_TIMEOUT if a bounded device-side wait (mbarrier) gave up.  The reference's
+ * counterpart is the cudaDeviceSynchronize + HANDLE_ERROR pair after every launch
+ * (cuda/ctensormath.cu.h:1980-1981, cuda/handle_error.cu.h:7-18), minus the exit(). */
+int b200_stream_status(void *stream);
+
+/* ---- convolution trio ------------------------------------------------------------------------ */
+
+/* CTensorConv::ForwardConvolution (cuda/ctensorconv.cu.h:276-315, cpu/ctensorconv.h:84-148):
+ * out[w,k,oy,ox] = bias[w%Wb,k] + sum_{ky,kx,c} kernel[w%Wk,k,c,ky,kx] * image[w%Wi,c,s*oy+ky-p,s*ox+kx-p]. */
+int b200_conv_forward(const b200_conv_geom *g, float *out, int out_w,
+                      const float *image, int image_w, const float *kernel, int kernel_w,
+                      const float *bias, int bias_w, void *stream);
+
+/* CTensorConv::BackwardConvolution (cuda/ctensorconv.cu.h:683-725, cpu/ctensorconv.h:196-266):
+ * out_delta[w,c,y,x] = sum_{ky,kx,f} kernel[f,c,kh-1-ky,kw-1-kx] * delta[w,f,(y+ky-p')/s,(x+kx-p')/s]
+ * over taps where the division is exact and in range, p' = k-1-p.  Also the forward pass of the
+ * transposed-convolution layer.  `bias` may be NULL; if given it is added once per contributing tap
+ * and filter, which is what the reference CPU backend does (every reference caller passes zeros). */
+int b200_conv_backward(const b200_conv_geom *g, float *out_delta, int out_w,
+                       const float *delta, int delta_w, const float *kernel, int kernel_w,
+                       const float *bias, int bias_w, void *stream);
+
+/* CTensorConv::CreateDeltaWeightAndBias (cuda/ctensorconv.cu.h:1168-1211, cpu/ctensorconv.h:319-386):
+ * for every w < dkernel_w:  dkernel[w] += wgrad(image[w%Wi], delta[w%Wd]),  dbias[w%Wb] += sum delta.
+ * Accumulates into the existing contents. */
+int b200_conv_wgrad(const b200_conv_geom *g, float *dkernel, int dkernel_w, float *dbias, int dbias_w,
+                    const float *image, int image_w, const float *delta, int delta_w, void *stream);
+
+/* CTensorConv::CreateBackDeltaWeightAndBias (cuda/ctensorconv.cu.h:1218-1222): the same with image
+ * and delta exchanged (`image` = layer input with kernel_amount channels of size out_y x out_x,
+ * `delta` = error of the layer output with in_z channels of size in_y x in_x); dbias is zeroed. */
+int b200_conv_back_wgrad(const b200_conv_geom *g, float *dkernel, int dkernel_w, float *dbias, int dbias_w,
+                         const float *image, int image_w, const float *delta, int delta_w, void *stream);
+
+/* Batch-summed weight gradient used by the layers: what CNetLayerConvolution::TrainingBackward
+ * obtains from CreateDeltaWeightAndBias into a per-sample tensor followed by two AddSumW passes
+ * (netlayer/cnetlayerconvolution.cu.h:501-508), without materialising the per-sample tensor:
+ *   dkernel[K][C*kh*kw] (+)= sum_w wgrad(image[w], delta[w]),  dbias[K] (+)= sum_w sum_yx delta[w].
+ * accumulate = 0 overwrites, 1 adds to the existing contents.  dbias may be NULL. */
+int b200_conv_wgrad_batch(const b200_conv_geom *g, float *dkernel, float *dbias, int accumulate,
+                          const float *image, const float *delta, int batch, void *stream);
+
+/* ---- dense products -------------------------------------------------------------------------- */
+
+/* CTensorMath::Mul (cuda/ctensormath.cu.h:2237, cpu/ctensormath.h:531-595) when transpose_left = 0:
+ *   out[w,z] (LY x RX) = left[w%Lw,z] (LY x LX) * right[w%Rw,z] (LX x RX);
+ * CTensorMath::TransponseMul (:2249, cpu :643-712) when transpose_left = 1:
+ *   out[w,z] (LX x RX) = left[w%Lw,z]^T (left is LY x LX) * right[w%Rw,z] (LY x RX). */
+int b200_mul(float *out, int out_w, const float *left, int left_w, const float *right, int right_w,
+             int z, int ly, int lx, int rx, int transpose_left, void *stream);
+
+/* ---- element-wise, reductions ---------------------------------------------------------------- */
+
+/* CTensorMath::Add / Sub (cuda/ctensormath.cu.h:837,1021; cpu :235,314): out[w] = ls*left[w%Lw] +/- rs*right[w%Rw];
+ * n = Z*Y*X elements per w. */
+int b200_add(float *out, int out_w, const float *left, int left_w, const float *right, int right_w,
+             size_t n, float ls, float rs, int subtract, void *stream);
+/* CTensorMath::AddSumW (cuda :914, cpu :273): out[0] = ls*sum_w left + rs*sum_w right, out[w>0] = 0.
+ * out may alias left or right. */
+int b200_add_sum_w(float *out, int out_w, const float *left, int left_w, const float *right, int right_w,
+                   size_t n, float ls, float rs, void *stream);
+/* CTensorMath::AddBias (cuda :1328, cpu :352): t[w,z,:,:] += bias[w%Bw,z]. */
+int b200_add_bias(float *t, int t_w, int z, size_t yx, const float *bias, int bias_w, void *stream);
+/* CTensorMath::SummXY (cuda :1396, cpu :455): out[w,z] = sum_{y,x} in[w%Iw,z,:,:]. */
+int b200_summ_xy(float *out, int out_w, const float *in, int in_w, int z, size_t yx, void *stream);
+/* CTensorMath::Pow2 (op 0: i*i*a), SQRT (op 1: sqrt(i+b)*a), Inv (op 2: 1/i), Mul by scalar (op 3: i*a)
+ * (cuda :1196,1262,702,2291; cpu :387,421,163,721), input W-broadcast. */
+int b200_unary(float *out, int out_w, const float *in, int in_w, size_t n, int op, float a, float b, void *stream);
+/* CTensorMath::TensorItemProduction (cuda :2425, cpu :822). */
+int b200_item_product(float *out, int out_w, const float *left, int left_w, const float *right, int right_w,
+                      size_t n, void *stream);
+/* CTensorMath::Fill (cuda :637, cpu :154). */
+int b200_fill(float *out, size_t n, float value, void *stream);
+
+/* CTensorApplyFunc::Apply* / ApplyDifferential* (cuda/ctensorapplyfunc.cu.h:325-866): out = f(in) or f'(in). */
+int b200_activation(float *out, const float *in, size_t n, int func, int derivative, float leaky_slope, void *stream);
+/* CNetLayerFunction::SetOutputError (netlayer/cnetlayerfunction.cu.h:347-358) fused: out = f'(z) * error. */
+int b200_activation_backward(float *out, const float *z, const float *error, size_t n, int func, float leaky_slope,
+                             void *stream);
+/* AddBias followed by an activation in one pass: t[w,z,:,:] = f(t + bias[z]) (cuda/ctensormath.cu.h:1328 +
+ * ctensorapplyfunc.cu.h Apply*).  pre may be NULL; if given it receives t + bias (the value the
+ * activation layer keeps for its derivative). */
+int b200_bias_activation(float *t, float *pre, int t_w, int z, size_t yx, const float *bias, int func,
+                         float leaky_slope, void *stream);
+
+/* ---- pooling / resampling -------------------------------------------------------------------- */
+
+/* CTensorMath::MaxPooling (cuda :2693, cpu :955-1013): window max and absolute argmax {X,Y}; ties keep the
+ * first element of the row-major scan. */
+int b200_maxpool(float *out, uint32_t *pos, const float *in, int w, int z, int in_y, int in_x, int pool_x, int pool_y,
+                 void *stream);
+/* CTensorMath::MaxPoolingBackward (cuda :2767, cpu :1019-1055): out zeroed, out[argmax] = delta. */
+int b200_maxpool_backward(float *out, const uint32_t *pos, const float *delta, int w, int z, int out_y, int out_x,
+                          int pool_x, int pool_y, void *stream);
+/* CTensorMath::UpSampling (cuda :2518, cpu :868) and DownSampling (cuda :2600, cpu :908; mean, used as the
+ * backward of UpSampling). */
+int b200_upsample(float *out, const float *in, int w, int z, int in_y, int in_x, int ux, int uy, void *stream);
+int b200_downsample(float *out, const float *in, int w, int z, int in_y, int in_x, int dx, int dy, void *stream);
+
+/* ---- fused layer kernels --------------------------------------------------------------------- */
+
+/* CNetLayerBatchNormalization::Forward, training mode (netlayer/cnetlayerbatchnormalization.cu.h:301-379):
+ * statistics per (z,y,x) element over the batch W; n = Z*Y*X.  Writes y, xhat (W*n each), ivar, mean,
+ * var (n each); if new_mean/new_var are non-NULL they are updated as m*old + (1-m)*batch statistic. */
+int b200_bn_forward(float *y, float *xhat, float *ivar, float *mean, float *var, float *new_mean, float *new_var,
+                    const float *x, const float *gamma, const float *beta, int w, size_t n, float momentum, float eps,
+                    void *stream);
+/* CNetLayerBatchNormalization::TrainingBackward (:578-604): dx, and dgamma += sum_w dy*xhat,
+ * dbeta += sum_w dy when create_delta_weight != 0. */
+int b200_bn_backward(float *dx, float *dgamma, float *dbeta, const float *dy, const float *xhat, const float *ivar,
+                     const float *gamma, int w, size_t n, int create_delta_weight, void *stream);
+/* CNetLayerVAECoderOutput::Forward (netlayer/cnetlayervaecoderoutput.cu.h:251-280) with the noise eps
+ * supplied by the caller: z = mu + exp(clamp(logvar,-10,10)/2)*eps; *kl_host (host pointer, may be NULL;
+ * the call synchronises the stream if given) receives -0.5/batch * sum(1+lv-mu^2-exp(lv)). */
+int b200_vae_forward(float *z, const float *mu, const float *logvar, const float *eps, int batch, size_t n,
+                     float *kl_host, void *stream);
+/* CNetLayerVAECoderOutput::SetOutputError (:424-455). */
+int b200_vae_backward(float *d_mu, float *d_logvar, const float *delta, const float *mu, const float *logvar,
+                      const float *eps, size_t total, float kl_speed, void *stream);
+/* CTensorMath::Adam (cuda :2978-3022, cpu :1119-1165).  iteration is used as given (the CPU backend's rule). */
+int b200_adam(float *weight, const float *dweight, float *m, float *v, size_t n, uint32_t batch_size, double speed,
+              double beta1, double beta2, double epsilon, double iteration, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200CONV_H */

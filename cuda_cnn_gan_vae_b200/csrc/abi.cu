@@ -30,6 +30,8 @@ int fail(int code, const char *fmt, ...)
     return code;
 }
 
+static unsigned long long g_launches = 0;
+void count_launch() { g_launches++; }
 void set_path(int p) { g_path = p; }
 int precision() { return g_precision; }
 
@@ -128,6 +130,16 @@ int b200_set_precision(int mode)
 }
 
 size_t b200_scratch_bytes(void) { return g_arena[current_device()].cap; }
+
+unsigned long long b200_launch_count(void) { return g_launches; }
+
+int b200_profile_tensor_core(int enable)
+{
+    tc_profile_enable(enable);
+    return B200_OK;
+}
+
+int b200_profile_read(double *total_ms, int *launches) { return tc_profile_read(total_ms, launches); }
 
 int b200_stream_status(void *stream)
 {

@@ -22,7 +22,13 @@ int precision();
                                 __FILE__, __LINE__);                                                 \
     } while (0)
 
-#define B200_LAUNCH_CHECK() B200_CUDA(cudaGetLastError())
+// Every kernel launch of the library goes through this check, which also counts it.
+void count_launch();
+#define B200_LAUNCH_CHECK()          \
+    do {                             \
+        ::b200::count_launch();      \
+        B200_CUDA(cudaGetLastError()); \
+    } while (0)
 
 // Scratch arena: one growing cudaMalloc block per device, carved by bump allocation for the
 // duration of one library call.  The stream order of the call protects reuse between calls on the

@@ -33,4 +33,7 @@ int tc_gemm(float *out, const float *a, const float *b, int m, int n, int k, int
 // Status word written by device-side waits that gave up (0 = none); clear != 0 resets it.
 unsigned tc_read_status(int clear);
 
+void tc_profile_enable(int on);
+int tc_profile_read(double *total_ms, int *launches);
+
 }  // namespace b200

@@ -120,12 +120,12 @@ __device__ __forceinline__ float act_tanh(float v)
     if (v < -30.f) v = -29.99999f;
     return tanhf(v);
 }
-__device__ __forceinline__ float act_apply(float v, int func, float slope)
+__device__ __forceinline__ float act_apply(float v, int func, double slope)
 {
     switch (func) {
     case B200_ACT_SIGMOID: return act_sigmoid(v);
     case B200_ACT_RELU: return v > 0.f ? v : 0.f;
-    case B200_ACT_LEAKY_RELU: return v > 0.f ? v : slope * v;
+    case B200_ACT_LEAKY_RELU: return v > 0.f ? v : (float)(slope * (double)v);   // the reference multiplies in double
     case B200_ACT_LINEAR: return v;
     case B200_ACT_TANH: return act_tanh(v);
     default: {
@@ -135,12 +135,12 @@ __device__ __forceinline__ float act_apply(float v, int func, float slope)
     }
     }
 }
-__device__ __forceinline__ float act_derivative(float v, int func, float slope)
+__device__ __forceinline__ float act_derivative(float v, int func, double slope)
 {
     switch (func) {
     case B200_ACT_SIGMOID: { float s = act_sigmoid(v); return (1.0f - s) * s; }
     case B200_ACT_RELU: return v >= 0.f ? 1.f : 0.f;
-    case B200_ACT_LEAKY_RELU: return v >= 0.f ? 1.f : slope;
+    case B200_ACT_LEAKY_RELU: return v >= 0.f ? 1.f : (float)slope;
     case B200_ACT_LINEAR: return 1.f;
     case B200_ACT_TANH: { float t = act_tanh(v); return 1.f - t * t; }
     default: {
@@ -155,7 +155,7 @@ __device__ __forceinline__ float act_derivative(float v, int func, float slope)
 
 template <bool VEC>
 __global__ void bias_act_kernel(float *t, float *pre, int t_w, int z, size_t yx, const float *__restrict__ bias, int bias_w,
-                                int func, float slope)
+                                int func, double slope)
 {
     const size_t per_plane = VEC ? yx / 4 : yx;
     const size_t total = per_plane * z * t_w;
@@ -182,7 +182,7 @@ __global__ void bias_act_kernel(float *t, float *pre, int t_w, int z, size_t yx,
 }
 
 __global__ void activation_kernel(float *__restrict__ out, const float *__restrict__ in, const float *__restrict__ err,
-                                  size_t n, int func, int derivative, float slope)
+                                  size_t n, int func, int derivative, double slope)
 {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         float v = in[i];
@@ -509,7 +509,7 @@ int b200_add_sum_w(float *out, int out_w, const float *left, int left_w, const f
 }
 
 static int bias_act_launch(float *t, float *pre, int t_w, int z, size_t yx, const float *bias, int bias_w, int func,
-                           float leaky_slope, cudaStream_t s)
+                           double leaky_slope, cudaStream_t s)
 {
     if (!t || !bias) return fail(B200_E_ARG, "null tensor pointer");
     if (t_w <= 0 || z <= 0 || bias_w <= 0) return fail(B200_E_SHAPE, "non-positive size");
@@ -525,11 +525,11 @@ static int bias_act_launch(float *t, float *pre, int t_w, int z, size_t yx, cons
 
 int b200_add_bias(float *t, int t_w, int z, size_t yx, const float *bias, int bias_w, void *stream)
 {
-    return bias_act_launch(t, nullptr, t_w, z, yx, bias, bias_w, B200_ACT_LINEAR, 0.f, ST(stream));
+    return bias_act_launch(t, nullptr, t_w, z, yx, bias, bias_w, B200_ACT_LINEAR, 0.0, ST(stream));
 }
 
 int b200_bias_activation(float *t, float *pre, int t_w, int z, size_t yx, const float *bias, int func,
-                         float leaky_slope, void *stream)
+                         double leaky_slope, void *stream)
 {
     return bias_act_launch(t, pre, t_w, z, yx, bias, 1, func, leaky_slope, ST(stream));
 }
@@ -565,7 +565,7 @@ int b200_fill(float *out, size_t n, float value, void *stream)
     return B200_OK;
 }
 
-int b200_activation(float *out, const float *in, size_t n, int func, int derivative, float leaky_slope, void *stream)
+int b200_activation(float *out, const float *in, size_t n, int func, int derivative, double leaky_slope, void *stream)
 {
     if (!out || !in) return fail(B200_E_ARG, "null tensor pointer");
     if (func < 0 || func > 5) return fail(B200_E_ARG, "unknown activation %d", func);
@@ -575,7 +575,7 @@ int b200_activation(float *out, const float *in, size_t n, int func, int derivat
     return B200_OK;
 }
 
-int b200_activation_backward(float *out, const float *z, const float *error, size_t n, int func, float leaky_slope,
+int b200_activation_backward(float *out, const float *z, const float *error, size_t n, int func, double leaky_slope,
                              void *stream)
 {
     if (!out || !z || !error) return fail(B200_E_ARG, "null tensor pointer");

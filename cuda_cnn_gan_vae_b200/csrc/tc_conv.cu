@@ -24,6 +24,7 @@
 #include "kernels.h"
 #include "tc_ptx.cuh"
 #include <cstring>
+#include <vector>
 
 namespace b200 {
 
@@ -371,6 +372,43 @@ __global__ void pack_act_kernel(const float *__restrict__ src, float *__restrict
     }
 }
 
+// Same re-layout with 128-bit accesses: a block moves 32 pixels x 32 channels per iteration, one
+// float4 load (4 pixels of one channel) and one float4 store per plane (4 channels of one pixel) per
+// thread.  Needs W % 4 == 0 and a 16-byte aligned source.
+__global__ void __launch_bounds__(256)
+pack_act_vec_kernel(const float *__restrict__ src, float *__restrict__ hi, float *__restrict__ lo,
+                    int N, int C, int H, int W, int Cp, int sy, int sx, int Hs, int Ws)
+{
+    __shared__ float tile[32][33];
+    const int n = blockIdx.z, h = blockIdx.y, w0 = blockIdx.x * 32;
+    const int tid = threadIdx.x;
+    const int lc = tid >> 3, lq = tid & 7;          // load role: channel lc of the chunk, pixel quad lq
+    const int sp = tid >> 3, sq = tid & 7;          // store role: pixel sp of the tile, channel quad sq
+    const bool row_ok = h < H;
+    const int hq = h / sy, hr = h % sy;
+    const int wl = w0 + 4 * lq;
+    const int ws = w0 + sp;
+    const int ph = hr * sx + (ws % sx);
+    const size_t obase = ((((size_t)ph * N + n) * Hs + hq) * Ws + (ws / sx)) * Cp;
+    for (int c0 = 0; c0 < Cp; c0 += 32) {
+        const int c = c0 + lc;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row_ok && c < C && wl < W) v = *reinterpret_cast<const float4 *>(src + (((size_t)n * C + c) * H + h) * W + wl);
+        tile[lc][4 * lq + 0] = v.x; tile[lc][4 * lq + 1] = v.y; tile[lc][4 * lq + 2] = v.z; tile[lc][4 * lq + 3] = v.w;
+        __syncthreads();
+        const int cq = c0 + 4 * sq;
+        if (ws < Ws * sx && cq < Cp) {
+            float4 a = make_float4(tile[4 * sq + 0][sp], tile[4 * sq + 1][sp], tile[4 * sq + 2][sp], tile[4 * sq + 3][sp]);
+            float4 b = make_float4(ptx::to_tf32(a.x), ptx::to_tf32(a.y), ptx::to_tf32(a.z), ptx::to_tf32(a.w));
+            *reinterpret_cast<float4 *>(hi + obase + cq) = b;
+            if (lo)
+                *reinterpret_cast<float4 *>(lo + obase + cq) =
+                    make_float4(ptx::to_tf32(a.x - b.x), ptx::to_tf32(a.y - b.y), ptx::to_tf32(a.z - b.z), ptx::to_tf32(a.w - b.w));
+        }
+        __syncthreads();
+    }
+}
+
 // Weights [K][C][taps] -> rows x taps x inner (pitch ip):
 //   forward  (rot = 0): dst[k][tap][c] = W[k][c][tap]
 //   backward (rot = 1): dst[c][tap][k] = W[k][c][taps-1-tap]   (kernel rotated by 180 degrees)
@@ -497,6 +535,45 @@ unsigned tc_read_status(int clear)
 
 static size_t g_smem_optin = 0;
 
+// Optional timing of the tensor-core kernel alone: a pair of events around every launch, read back
+// by tc_profile_read().  Used by the benchmark to put a live duration under the roofline figure.
+struct EventPair { cudaEvent_t a, b; };
+static bool g_profile = false;
+static std::vector<EventPair> g_pending, g_pool;
+
+void tc_profile_enable(int on) { g_profile = on != 0; }
+
+int tc_profile_read(double *total_ms, int *launches)
+{
+    double ms = 0;
+    int n = 0;
+    for (EventPair &e : g_pending) {
+        float t = 0.f;
+        B200_CUDA(cudaEventSynchronize(e.b));
+        B200_CUDA(cudaEventElapsedTime(&t, e.a, e.b));
+        ms += t;
+        n++;
+        g_pool.push_back(e);
+    }
+    g_pending.clear();
+    if (total_ms) *total_ms = ms;
+    if (launches) *launches = n;
+    return B200_OK;
+}
+
+static int profile_begin(EventPair *e, cudaStream_t s)
+{
+    if (g_pool.empty()) {
+        B200_CUDA(cudaEventCreate(&e->a));
+        B200_CUDA(cudaEventCreate(&e->b));
+    } else {
+        *e = g_pool.back();
+        g_pool.pop_back();
+    }
+    B200_CUDA(cudaEventRecord(e->a, s));
+    return B200_OK;
+}
+
 template <int MODE>
 static int launch_tc(const CUtensorMap maps[4], TcParams &p, bool x3, cudaStream_t s)
 {
@@ -521,6 +598,8 @@ static int launch_tc(const CUtensorMap maps[4], TcParams &p, bool x3, cudaStream
     const size_t smem = (size_t)stages * p.stage_bytes + fixed;
     int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
     if (grid < 1) return B200_OK;
+    EventPair ev;
+    if (g_profile && (r = profile_begin(&ev, s))) return r;
     if (x3) {
         B200_CUDA(cudaFuncSetAttribute(tc_kernel<MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         tc_kernel<MODE, true><<<grid, kThreads, smem, s>>>(maps[0], maps[1], maps[2], maps[3], p);
@@ -529,6 +608,10 @@ static int launch_tc(const CUtensorMap maps[4], TcParams &p, bool x3, cudaStream
         tc_kernel<MODE, false><<<grid, kThreads, smem, s>>>(maps[0], maps[0], maps[2], maps[2], p);
     }
     B200_LAUNCH_CHECK();
+    if (g_profile) {
+        B200_CUDA(cudaEventRecord(ev.b, s));
+        g_pending.push_back(ev);
+    }
     return B200_OK;
 }
 
@@ -551,7 +634,10 @@ static int pack_act(const float *src, float *hi, float *lo, int N, int C, int H,
 {
     dim3 grid(ceil_div(Ws * sx, 32), Hs * sy, N), block(32, 8);
     if (grid.y > 65535 || grid.z > 65535) return TC_UNSUPPORTED;
-    pack_act_kernel<<<grid, block, 0, s>>>(src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws);
+    if (W % 4 == 0 && ((uintptr_t)src & 15) == 0)
+        pack_act_vec_kernel<<<grid, 256, 0, s>>>(src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws);
+    else
+        pack_act_kernel<<<grid, block, 0, s>>>(src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }

@@ -24,6 +24,9 @@ SIGNATURES = {
     "b200_shutdown": (_i, []),
     "b200_scratch_bytes": (_sz, []),
     "b200_stream_status": (_i, [_vp]),
+    "b200_launch_count": (C.c_ulonglong, []),
+    "b200_profile_tensor_core": (_i, [_i]),
+    "b200_profile_read": (_i, [C.POINTER(C.c_double), C.POINTER(C.c_int)]),
     "b200_conv_forward": (_i, [_G, _fp, _i, _fp, _i, _fp, _i, _fp, _i, _vp]),
     "b200_conv_backward": (_i, [_G, _fp, _i, _fp, _i, _fp, _i, _fp, _i, _vp]),
     "b200_conv_wgrad": (_i, [_G, _fp, _i, _fp, _i, _fp, _i, _fp, _i, _vp]),
@@ -37,9 +40,9 @@ SIGNATURES = {
     "b200_unary": (_i, [_fp, _i, _fp, _i, _sz, _i, _f, _f, _vp]),
     "b200_item_product": (_i, [_fp, _i, _fp, _i, _fp, _i, _sz, _vp]),
     "b200_fill": (_i, [_fp, _sz, _f, _vp]),
-    "b200_activation": (_i, [_fp, _fp, _sz, _i, _i, _f, _vp]),
-    "b200_activation_backward": (_i, [_fp, _fp, _fp, _sz, _i, _f, _vp]),
-    "b200_bias_activation": (_i, [_fp, _fp, _i, _i, _sz, _fp, _i, _f, _vp]),
+    "b200_activation": (_i, [_fp, _fp, _sz, _i, _i, _d, _vp]),
+    "b200_activation_backward": (_i, [_fp, _fp, _fp, _sz, _i, _d, _vp]),
+    "b200_bias_activation": (_i, [_fp, _fp, _i, _i, _sz, _fp, _i, _d, _vp]),
     "b200_maxpool": (_i, [_fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _vp]),
     "b200_maxpool_backward": (_i, [_fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _vp]),
     "b200_upsample": (_i, [_fp, _fp, _i, _i, _i, _i, _i, _i, _vp]),

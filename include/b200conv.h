@@ -64,8 +64,8 @@ typedef struct b200_conv_geom {
 } b200_conv_geom;
 
 /* Activation codes (netlayer/neuron.cu.h NEURON_FUNCTION_*; scalar definitions
- * cpu/ctensorapplyfunc.h:128-257).  LEAKY_RELU uses the slope given to the call (the reference
- * constant is 0.1). */
+ * cpu/ctensorapplyfunc.h:128-257).  LEAKY_RELU uses the slope given to the call, a double multiplied
+ * in double precision as the reference does with its constant 0.1. */
 enum { B200_ACT_SIGMOID = 0, B200_ACT_RELU = 1, B200_ACT_LEAKY_RELU = 2, B200_ACT_LINEAR = 3,
        B200_ACT_TANH = 4, B200_ACT_GELU = 5 };
 
@@ -83,6 +83,14 @@ size_t b200_scratch_bytes(void);
  * counterpart is the cudaDeviceSynchronize + HANDLE_ERROR pair after every launch
  * (cuda/ctensormath.cu.h:1980-1981, cuda/handle_error.cu.h:7-18), minus the exit(). */
 int b200_stream_status(void *stream);
+
+/* Number of kernels this library has launched in this process (all devices, all threads). */
+unsigned long long b200_launch_count(void);
+/* Measurement aid with no reference counterpart: when enabled, every launch of the tcgen05 kernel
+ * is bracketed by a pair of CUDA events on its stream; b200_profile_read() waits for the recorded
+ * launches and returns their summed duration in milliseconds and their number, then forgets them. */
+int b200_profile_tensor_core(int enable);
+int b200_profile_read(double *total_ms, int *launches);
 
 /* ---- convolution trio ------------------------------------------------------------------------ */
 
@@ -154,15 +162,15 @@ int b200_item_product(float *out, int out_w, const float *left, int left_w, cons
 int b200_fill(float *out, size_t n, float value, void *stream);
 
 /* CTensorApplyFunc::Apply* / ApplyDifferential* (cuda/ctensorapplyfunc.cu.h:325-866): out = f(in) or f'(in). */
-int b200_activation(float *out, const float *in, size_t n, int func, int derivative, float leaky_slope, void *stream);
+int b200_activation(float *out, const float *in, size_t n, int func, int derivative, double leaky_slope, void *stream);
 /* CNetLayerFunction::SetOutputError (netlayer/cnetlayerfunction.cu.h:347-358) fused: out = f'(z) * error. */
-int b200_activation_backward(float *out, const float *z, const float *error, size_t n, int func, float leaky_slope,
+int b200_activation_backward(float *out, const float *z, const float *error, size_t n, int func, double leaky_slope,
                              void *stream);
 /* AddBias followed by an activation in one pass: t[w,z,:,:] = f(t + bias[z]) (cuda/ctensormath.cu.h:1328 +
  * ctensorapplyfunc.cu.h Apply*).  pre may be NULL; if given it receives t + bias (the value the
  * activation layer keeps for its derivative). */
 int b200_bias_activation(float *t, float *pre, int t_w, int z, size_t yx, const float *bias, int func,
-                         float leaky_slope, void *stream);
+                         double leaky_slope, void *stream);
 
 /* ---- pooling / resampling -------------------------------------------------------------------- */
 

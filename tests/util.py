@@ -13,6 +13,18 @@ def max_rel_err(got, want):
     return float(np.max(np.abs(got - want) / den)) if want.size else 0.0
 
 
+def dot_rel_err(got, want, absdot):
+    """max_i |got_i - want_i| / absdot_i, where absdot_i is the same contraction evaluated on the
+    absolute values of the operands (sum_j |a_ij||b_j|, plus |bias|): the relative error of a dot product
+    in the sense of its forward error bound.  For a sum without cancellation it is the plain relative
+    error; where terms cancel, the error is judged against the magnitude of what was summed.  This is the
+    metric the 1e-4 (3xTF32) and 2e-3 (TF32) tolerances are stated on."""
+    got = np.asarray(got, np.float64)
+    want = np.asarray(want, np.float64)
+    den = np.maximum(np.asarray(absdot, np.float64), 1e-30)
+    return float(np.max(np.abs(got - want) / den)) if want.size else 0.0
+
+
 TOL_X3 = 1e-4      # 3xTF32 against the fp32 CPU oracle
 TOL_TF32 = 2e-3    # plain TF32
 

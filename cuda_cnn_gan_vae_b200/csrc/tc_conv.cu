@@ -174,51 +174,61 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
-                const TileCtx c = decode_tile<MODE>(p, tile);
-                for (int step = 0; step < c.nsteps; step++) {
-                    if (!wait_bar(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 0x100u + B200_E_TIMEOUT)) { ok = false; break; }
-                    const uint32_t fb = full_bar(stage);
-                    ptx::mbar_arrive_expect_tx(fb, stage_tx);
-                    const uint32_t sbase = ptx::smem_u32(smem + (size_t)stage * p.stage_bytes);
-                    int a0, a1, a2, a3, a4, b0, b1, b2, b3, b4;
-                    int a_step0 = 0, b_step0 = 0;   // which coordinate advances per box (always coordinate 0)
-                    if (MODE == MODE_CONV) {
-                        const PhaseInfo &pi = p.phase[c.ph];
-                        const int ti = step / p.c_chunks, cc = step - ti * p.c_chunks;
-                        const TapEntry t = p.taps[pi.tap_begin + ti];
-                        a0 = cc * 32; a1 = c.tx * p.BW + t.dx; a2 = c.ty * p.BH + t.dy; a3 = c.ig * p.BI; a4 = t.in_phase;
-                        b0 = cc * 32; b1 = t.wtap; b2 = c.nt * p.BN; b3 = 0; b4 = 0;
-                    } else if (MODE == MODE_WGRAD) {
-                        const long long q = c.chunk_begin + step;
-                        const int cx = (int)(q % p.chunks_x);
-                        const long long r = q / p.chunks_x;
-                        const int cy = (int)(r % p.chunks_y);
-                        const int ci = (int)(r / p.chunks_y);
-                        const TapEntry t = p.taps[c.tap];
-                        a0 = c.ft * 128; a1 = cx * p.BW; a2 = cy * p.BH; a3 = ci * p.BI; a4 = 0;
-                        b0 = c.ct * p.BN; b1 = cx * p.BW + t.dx; b2 = cy * p.BH + t.dy; b3 = ci * p.BI; b4 = t.in_phase;
-                        a_step0 = 32; b_step0 = 32;
-                    } else {
-                        const int k0 = step * 32;
-                        if (p.a_mn) { a0 = c.mt * 128; a1 = k0; a_step0 = 32; } else { a0 = k0; a1 = c.mt * 128; }
-                        if (p.b_mn) { b0 = c.nt * p.BN; b1 = k0; b_step0 = 32; } else { b0 = k0; b1 = c.nt * p.BN; }
-                        a2 = a3 = a4 = b2 = b3 = b4 = 0;
-                    }
-                    for (int j = 0; j < p.a_boxes; j++) {
-                        ptx::tma_load_5d(sbase + j * p.a_box_bytes, &mapA_hi, fb, a0 + j * a_step0, a1, a2, a3, a4);
-                        if (X3) ptx::tma_load_5d(sbase + off_a_lo + j * p.a_box_bytes, &mapA_lo, fb, a0 + j * a_step0, a1, a2, a3, a4);
-                    }
-                    for (int j = 0; j < p.b_boxes; j++) {
-                        ptx::tma_load_5d(sbase + off_b_hi + j * p.b_box_bytes, &mapB_hi, fb, b0 + j * b_step0, b1, b2, b3, b4);
-                        if (X3) ptx::tma_load_5d(sbase + off_b_lo + j * p.b_box_bytes, &mapB_lo, fb, b0 + j * b_step0, b1, b2, b3, b4);
-                    }
-                    if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        // The whole warp walks the tile/step sequence; lane 0 owns the barrier handshake and each box
+        // of a stage is issued by its own lane, so a stage of many small boxes (MN-major operands,
+        // 3xTF32 planes) costs one issue slot instead of one per box.
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        const int planes = X3 ? 2 : 1;
+        const int n_a = p.a_boxes * planes, n_boxes = (p.a_boxes + p.b_boxes) * planes;
+        for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+            const TileCtx c = decode_tile<MODE>(p, tile);
+            for (int step = 0; step < c.nsteps; step++) {
+                if (lane == 0) ok = wait_bar(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 0x100u + B200_E_TIMEOUT);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                const uint32_t fb = full_bar(stage);
+                if (lane == 0) ptx::mbar_arrive_expect_tx(fb, stage_tx);
+                __syncwarp();
+                const uint32_t sbase = ptx::smem_u32(smem + (size_t)stage * p.stage_bytes);
+                int a0, a1, a2, a3, a4, b0, b1, b2, b3, b4;
+                int a_step0 = 0, b_step0 = 0;   // advance of coordinate 0 from one box of an operand to the next
+                if (MODE == MODE_CONV) {
+                    const PhaseInfo &pi = p.phase[c.ph];
+                    const int ti = step / p.c_chunks, cc = step - ti * p.c_chunks;
+                    const TapEntry t = p.taps[pi.tap_begin + ti];
+                    a0 = cc * 32; a1 = c.tx * p.BW + t.dx; a2 = c.ty * p.BH + t.dy; a3 = c.ig * p.BI; a4 = t.in_phase;
+                    b0 = cc * 32; b1 = t.wtap; b2 = c.nt * p.BN; b3 = 0; b4 = 0;
+                } else if (MODE == MODE_WGRAD) {
+                    const long long q = c.chunk_begin + step;
+                    const int cx = (int)(q % p.chunks_x);
+                    const long long r = q / p.chunks_x;
+                    const int cy = (int)(r % p.chunks_y);
+                    const int ci = (int)(r / p.chunks_y);
+                    const TapEntry t = p.taps[c.tap];
+                    // coordinate 4 walks the 32-channel blocks, so one box brings all blocks of the operand
+                    a0 = 0; a1 = cx * p.BW; a2 = cy * p.BH; a3 = ci * p.BI; a4 = c.ft * 4;
+                    b0 = 0; b1 = cx * p.BW + t.dx; b2 = cy * p.BH + t.dy; b3 = t.in_phase * p.n_img + ci * p.BI; b4 = c.ct * (p.BN / 32);
+                } else {
+                    const int k0 = step * 32;
+                    a2 = a3 = a4 = b2 = b3 = b4 = 0;
+                    if (p.a_mn) { a0 = 0; a1 = k0; a4 = c.mt * 4; } else { a0 = k0; a1 = c.mt * 128; }
+                    if (p.b_mn) { b0 = 0; b1 = k0; b4 = c.nt * (p.BN / 32); } else { b0 = k0; b1 = c.nt * p.BN; }
                 }
+                for (int box = lane; box < n_boxes; box += 32) {
+                    if (box < n_a) {
+                        const int j = box / planes, lo = box - j * planes;
+                        ptx::tma_load_5d(sbase + (lo ? off_a_lo : 0u) + j * p.a_box_bytes, lo ? &mapA_lo : &mapA_hi, fb,
+                                         a0 + j * a_step0, a1, a2, a3, a4);
+                    } else {
+                        const int bb = box - n_a;
+                        const int j = bb / planes, lo = bb - j * planes;
+                        ptx::tma_load_5d(sbase + (lo ? off_b_lo : off_b_hi) + j * p.b_box_bytes, lo ? &mapB_lo : &mapB_hi, fb,
+                                         b0 + j * b_step0, b1, b2, b3, b4);
+                    }
+                }
+                if (++stage == p.stages) { stage = 0; phase ^= 1u; }
             }
         }
     } else if (warp == 1) {
@@ -497,6 +507,20 @@ static int make_map(CUtensorMap *m, const float *base, const long long dims[5], 
     return B200_OK;
 }
 
+// Tensor map of an MN-major operand stored as [rows...][E] (E contiguous elements per row, pitch
+// `pitch0`): dimension 0 is a 32-element block of E, dimension 4 the block index (stride 128 bytes), so
+// a box {32, b1, b2, b3, nblocks} lands in shared memory as nblocks consecutive [rows][32] blocks.  The
+// last block may reach past E (into the next row, by at most 31 elements past the end of the buffer,
+// which the caller pads): those elements only ever meet zero-filled or masked partners.
+static int make_blocked_map(CUtensorMap *m, const float *base, long long E, const long long dims123[3], const long long pitch[3],
+                            const int box123[3], int nblocks_box)
+{
+    const long long dims[5] = {32, dims123[0], dims123[1], dims123[2], (E + 31) / 32};
+    const long long pit[4] = {pitch[0], pitch[1], pitch[2], 32};
+    const int box[5] = {32, box123[0], box123[1], box123[2], nblocks_box};
+    return make_map(m, base, dims, pit, box, true);
+}
+
 static int pow2_ceil(int v) { int p = 1; while (p < v) p <<= 1; return p; }
 static int floor_div(int a, int b) { int q = a / b; if ((a % b != 0) && ((a < 0) != (b < 0))) q--; return q; }
 static int pos_mod(int a, int b) { int r = a % b; return r < 0 ? r + b : r; }
@@ -623,10 +647,12 @@ static void set_kmajor(TcParams &p, bool a_side, int rows)
 static void set_mnmajor(TcParams &p, bool a_side, int extent)
 {
     // MN-major 32-bit operands: 32 elements (128 B) contiguous along M/N per k-row, rows 128 B apart,
-    // swizzled in 32-byte atoms over groups of 4 rows (SBO = 512 B between groups); one TMA box is
-    // 32 k-rows x 32 elements = 4 KB, boxes follow each other along M/N (LBO); one MMA eats 8 rows.
-    if (a_side) { p.a_boxes = 4; p.a_box_bytes = 4096; p.a_lbo = 4096; p.a_sbo = 512; p.a_kadv = 1024; p.a_layout = 1; }
-    else { p.b_boxes = extent / 32; p.b_box_bytes = 4096; p.b_lbo = 4096; p.b_sbo = 512; p.b_kadv = 1024; p.b_layout = 1; }
+    // swizzled in 32-byte atoms over groups of 4 rows (SBO = 512 B between groups); a block of
+    // 32 k-rows x 32 elements is 4 KB, blocks follow each other along M/N (LBO); one MMA eats 8 rows.
+    // All 32-element blocks of an operand arrive in ONE box: the tensor map carries the block index
+    // as an extra dimension with a 128-byte stride (see make_blocked_map), the box is 32 x 32 x blocks.
+    if (a_side) { p.a_boxes = 1; p.a_box_bytes = 4 * 4096; p.a_lbo = 4096; p.a_sbo = 512; p.a_kadv = 1024; p.a_layout = 1; }
+    else { p.b_boxes = 1; p.b_box_bytes = (uint32_t)(extent / 32) * 4096; p.b_lbo = 4096; p.b_sbo = 512; p.b_kadv = 1024; p.b_layout = 1; }
 }
 
 static int pack_act(const float *src, float *hi, float *lo, int N, int C, int H, int W, int Cp, int sy, int sx, int Hs, int Ws,
@@ -806,7 +832,7 @@ int tc_conv_wgrad_batch(const b200_conv_geom &g, float *dkernel, float *dbias, i
     set_mnmajor(p, false, p.BN);
     p.idesc = make_idesc_tf32(p.BN, 1, 1);
     p.ft_n = ceil_div(K, 128); p.ct_n = ceil_div(C, p.BN); p.taps_n = taps;
-    p.k_rows = K; p.c_cols = C;
+    p.k_rows = K; p.c_cols = C; p.n_img = batch;
     tile_shape(g.out_y, g.out_x, 32, &p.BW, &p.BH, &p.BI);
     p.chunks_x = ceil_div(g.out_x, p.BW); p.chunks_y = ceil_div(g.out_y, p.BH); p.chunks_i = ceil_div(batch, p.BI);
     p.chunks_total = (long long)p.chunks_x * p.chunks_y * p.chunks_i;
@@ -828,14 +854,14 @@ int tc_conv_wgrad_batch(const b200_conv_geom &g, float *dkernel, float *dbias, i
 
     const size_t part_elems = (size_t)p.splits * taps * C * K;
     const size_t db_elems = dbias ? (size_t)batch * K : 0;
-    const size_t bytes = sizeof(float) * ((x_elems + d_elems) * (x3 ? 2 : 1) + part_elems + db_elems) + 16384;
+    const size_t bytes = sizeof(float) * ((x_elems + d_elems) * (x3 ? 2 : 1) + part_elems + db_elems) + 32768;
     int r = arena_reserve(bytes, s);
     if (r) return r;
     arena_reset();
-    float *x_hi = (float *)arena_take(sizeof(float) * x_elems);
-    float *x_lo = x3 ? (float *)arena_take(sizeof(float) * x_elems) : nullptr;
-    float *d_hi = (float *)arena_take(sizeof(float) * d_elems);
-    float *d_lo = x3 ? (float *)arena_take(sizeof(float) * d_elems) : nullptr;
+    float *x_hi = (float *)arena_take(sizeof(float) * x_elems + 256);      // +256: see make_blocked_map
+    float *x_lo = x3 ? (float *)arena_take(sizeof(float) * x_elems + 256) : nullptr;
+    float *d_hi = (float *)arena_take(sizeof(float) * d_elems + 256);
+    float *d_lo = x3 ? (float *)arena_take(sizeof(float) * d_elems + 256) : nullptr;
     p.partial = (float *)arena_take(sizeof(float) * part_elems);
     float *db_tmp = dbias ? (float *)arena_take(sizeof(float) * db_elems) : nullptr;
     if (!x_hi || !d_hi || !p.partial || (x3 && (!x_lo || !d_lo)) || (dbias && !db_tmp)) return fail(B200_E_NOMEM, "scratch arena exhausted");
@@ -844,18 +870,19 @@ int tc_conv_wgrad_batch(const b200_conv_geom &g, float *dkernel, float *dbias, i
 
     CUtensorMap maps[4];
     {
-        const long long dims[5] = {K, g.out_x, g.out_y, batch, 1};
-        const long long pitch[4] = {Kp, (long long)g.out_x * Kp, (long long)g.out_y * g.out_x * Kp, (long long)batch * g.out_y * g.out_x * Kp};
-        const int box[5] = {32, p.BW, p.BH, p.BI, 1};
-        if ((r = make_map(&maps[0], d_hi, dims, pitch, box, true))) return r;
-        if (x3 && (r = make_map(&maps[1], d_lo, dims, pitch, box, true))) return r;
+        const long long dims[3] = {g.out_x, g.out_y, batch};
+        const long long pitch[3] = {Kp, (long long)g.out_x * Kp, (long long)g.out_y * g.out_x * Kp};
+        const int box[3] = {p.BW, p.BH, p.BI};
+        if ((r = make_blocked_map(&maps[0], d_hi, K, dims, pitch, box, 4))) return r;
+        if (x3 && (r = make_blocked_map(&maps[1], d_lo, K, dims, pitch, box, 4))) return r;
     }
     {
-        const long long dims[5] = {C, Ws, Hs, batch, (long long)sy * sx};
-        const long long pitch[4] = {Cp, (long long)Ws * Cp, (long long)Hs * Ws * Cp, (long long)batch * Hs * Ws * Cp};
-        const int box[5] = {32, p.BW, p.BH, p.BI, 1};
-        if ((r = make_map(&maps[2], x_hi, dims, pitch, box, true))) return r;
-        if (x3 && (r = make_map(&maps[3], x_lo, dims, pitch, box, true))) return r;
+        // phase and image index share one dimension ([phase][n] is contiguous in the pack)
+        const long long dims[3] = {Ws, Hs, (long long)batch * sy * sx};
+        const long long pitch[3] = {Cp, (long long)Ws * Cp, (long long)Hs * Ws * Cp};
+        const int box[3] = {p.BW, p.BH, p.BI};
+        if ((r = make_blocked_map(&maps[2], x_hi, C, dims, pitch, box, p.BN / 32))) return r;
+        if (x3 && (r = make_blocked_map(&maps[3], x_lo, C, dims, pitch, box, p.BN / 32))) return r;
     }
     if ((r = launch_tc<MODE_WGRAD>(maps, p, x3, s))) return r;
     {
@@ -883,14 +910,14 @@ int tc_gemm(float *out, const float *a, const float *b, int m, int n, int k, int
     if ((size_t)m * n < 4096 || k < 8) return TC_UNSUPPORTED;      // too small to be worth a tensor-core launch
     const bool x3 = precision == B200_TF32X3;
     const size_t a_elems = (size_t)m * k, b_elems = (size_t)n * k;
-    const size_t bytes = sizeof(float) * (a_elems + b_elems) * (x3 ? 2 : 1) + 8192;
+    const size_t bytes = sizeof(float) * (a_elems + b_elems) * (x3 ? 2 : 1) + 16384;
     int r = arena_reserve(bytes, s);
     if (r) return r;
     arena_reset();
-    float *a_hi = (float *)arena_take(sizeof(float) * a_elems);
-    float *a_lo = x3 ? (float *)arena_take(sizeof(float) * a_elems) : nullptr;
-    float *b_hi = (float *)arena_take(sizeof(float) * b_elems);
-    float *b_lo = x3 ? (float *)arena_take(sizeof(float) * b_elems) : nullptr;
+    float *a_hi = (float *)arena_take(sizeof(float) * a_elems + 256);      // +256: see make_blocked_map
+    float *a_lo = x3 ? (float *)arena_take(sizeof(float) * a_elems + 256) : nullptr;
+    float *b_hi = (float *)arena_take(sizeof(float) * b_elems + 256);
+    float *b_lo = x3 ? (float *)arena_take(sizeof(float) * b_elems + 256) : nullptr;
     if (!a_hi || !b_hi || (x3 && (!a_lo || !b_lo))) return fail(B200_E_NOMEM, "scratch arena exhausted");
     int grid = sm_count() * 8;
     split_tf32_kernel<<<grid, 256, 0, s>>>(a, a_hi, a_lo, a_elems);
@@ -911,21 +938,24 @@ int tc_gemm(float *out, const float *a, const float *b, int m, int n, int k, int
     p.out = out;
 
     CUtensorMap maps[4];
-    {
-        const long long d0 = a_mn_major ? m : k, d1 = a_mn_major ? k : m;
-        const long long dims[5] = {d0, d1, 1, 1, 1};
-        const long long pitch[4] = {d0, d0 * d1, d0 * d1, d0 * d1};
-        const int box[5] = {32, a_mn_major ? 32 : 128, 1, 1, 1};
-        if ((r = make_map(&maps[0], a_hi, dims, pitch, box, a_mn_major != 0))) return r;
-        if (x3 && (r = make_map(&maps[1], a_lo, dims, pitch, box, a_mn_major != 0))) return r;
-    }
-    {
-        const long long d0 = b_mn_major ? n : k, d1 = b_mn_major ? k : n;
-        const long long dims[5] = {d0, d1, 1, 1, 1};
-        const long long pitch[4] = {d0, d0 * d1, d0 * d1, d0 * d1};
-        const int box[5] = {32, b_mn_major ? 32 : p.BN, 1, 1, 1};
-        if ((r = make_map(&maps[2], b_hi, dims, pitch, box, b_mn_major != 0))) return r;
-        if (x3 && (r = make_map(&maps[3], b_lo, dims, pitch, box, b_mn_major != 0))) return r;
+    for (int side = 0; side < 2; side++) {
+        const bool mn = side == 0 ? a_mn_major != 0 : b_mn_major != 0;
+        const long long ext = side == 0 ? m : n;                 // M or N extent of this operand
+        float *hi = side == 0 ? a_hi : b_hi, *lo = side == 0 ? a_lo : b_lo;
+        const int rows_box = side == 0 ? 128 : p.BN;
+        if (mn) {   // stored [k][ext]
+            const long long dims[3] = {k, 1, 1};
+            const long long pitch[3] = {ext, ext * k, ext * k};
+            const int box[3] = {32, 1, 1};
+            if ((r = make_blocked_map(&maps[2 * side], hi, ext, dims, pitch, box, rows_box / 32))) return r;
+            if (x3 && (r = make_blocked_map(&maps[2 * side + 1], lo, ext, dims, pitch, box, rows_box / 32))) return r;
+        } else {    // stored [ext][k]
+            const long long dims[5] = {k, ext, 1, 1, 1};
+            const long long pitch[4] = {k, (long long)k * ext, (long long)k * ext, (long long)k * ext};
+            const int box[5] = {32, rows_box, 1, 1, 1};
+            if ((r = make_map(&maps[2 * side], hi, dims, pitch, box))) return r;
+            if (x3 && (r = make_map(&maps[2 * side + 1], lo, dims, pitch, box))) return r;
+        }
     }
     return launch_tc<MODE_GEMM>(maps, p, x3, s);
 }

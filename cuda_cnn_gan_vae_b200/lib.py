@@ -32,6 +32,8 @@ SIGNATURES = {
     "b200_conv_wgrad": (_i, [_G, _fp, _i, _fp, _i, _fp, _i, _fp, _i, _vp]),
     "b200_conv_back_wgrad": (_i, [_G, _fp, _i, _fp, _i, _fp, _i, _fp, _i, _vp]),
     "b200_conv_wgrad_batch": (_i, [_G, _fp, _fp, _i, _fp, _fp, _i, _vp]),
+    "b200_conv_wgrad_batch_static": (_i, [_G, _fp, _fp, _i, _fp, _fp, _i, _vp]),
+    "b200_static_scratch_bytes": (_sz, []),
     "b200_mul": (_i, [_fp, _i, _fp, _i, _fp, _i, _i, _i, _i, _i, _i, _vp]),
     "b200_add": (_i, [_fp, _i, _fp, _i, _fp, _i, _sz, _f, _f, _i, _vp]),
     "b200_add_sum_w": (_i, [_fp, _i, _fp, _i, _fp, _i, _sz, _f, _f, _vp]),

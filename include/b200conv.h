@@ -129,6 +129,23 @@ int b200_conv_back_wgrad(const b200_conv_geom *g, float *dkernel, int dkernel_w,
 int b200_conv_wgrad_batch(const b200_conv_geom *g, float *dkernel, float *dbias, int accumulate,
                           const float *image, const float *delta, int batch, void *stream);
 
+/* Allocation-free form of b200_conv_wgrad_batch (no counterpart in the reference, which allocates
+ * its per-sample gradient tensors up front in the layer objects).  For callers that must not allocate
+ * device memory where they call the library: hosts that hand out all device memory from their own pool
+ * at start-up, loops that cannot take the device-wide stall of cudaMalloc/cudaFree, and program phases
+ * in which the CUDA runtime refuses allocations.  Same arguments and result as b200_conv_wgrad_batch
+ * (fp32 CUDA-core arithmetic in the reference summation order, whatever the precision mode), but the
+ * per-sample scratch lives in a fixed 16 MiB array inside the library image (b200_static_scratch_bytes(),
+ * held by every GPU that loads the library until the process exits): batch * (K*C*kh*kw + K) floats must
+ * fit, otherwise the call returns B200_E_NOMEM and does nothing.  It calls no cudaMalloc / cudaFree.
+ * The first call on each device looks up the array's device address; make that first call outside any
+ * stream capture, with the device current.  All calls on a device share the array, which keeps the last
+ * call's contents (this call clears what it needs first): two calls whose kernels overlap on the GPU
+ * (different streams, no ordering between them) race on it. */
+int b200_conv_wgrad_batch_static(const b200_conv_geom *g, float *dkernel, float *dbias, int accumulate,
+                                 const float *image, const float *delta, int batch, void *stream);
+size_t b200_static_scratch_bytes(void);
+
 /* ---- dense products -------------------------------------------------------------------------- */
 
 /* CTensorMath::Mul (cuda/ctensormath.cu.h:2237, cpu/ctensormath.h:531-595) when transpose_left = 0:

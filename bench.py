@@ -4,8 +4,8 @@
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--batch B] [--skip-cpu]
 
 Workload: the data-parallel convolution sweep -- batch 1024 of 256x32x32 N(0,1) images, 256 filters
-3x3, stride 1, padding 1, He-normal weights, N(0,1) upstream delta; one step = ForwardConvolution +
-BackwardConvolution + batch-summed CreateDeltaWeightAndBias over the whole batch (and, for N > 1, the
+3x3, stride 1, padding 1, He-normal weights, N(0,1) upstream delta; one step = the convolution layer's Forward (ForwardConvolution) and
+TrainingBackward (BackwardConvolution + batch-summed CreateDeltaWeightAndBias) over the whole batch (and, for N > 1, the
 NCCL all-reduce of the dW/dB arena).  The batch is split over the N ranks (strong scaling).
 Metric: algorithmic convolution TFLOP/s, 3 passes x 2*N*K*C*kh*kw*OH*OW flops per step; the extra MMAs
 of the 3xTF32 mode and packing passes are not counted as work.
@@ -225,10 +225,13 @@ def main():
     db = arena[K * Cc * k * k:].view(1, K, 1, 1)
     step_flops = flops_per_sample(c) * c["batch"]
 
+    layer = ops.ConvLayer(Cc, H, W, K, k, k, 1, 1, 1, 1, B)
+
     def step():
-        ops.CTensorConv.ForwardConvolution(y, x, wt, k, k, Cc, K, bias, 1, 1, 1, 1)
-        ops.CTensorConv.BackwardConvolution(dx, delta, wt, k, k, Cc, K, None, 1, 1, 1, 1)
-        ops.CTensorConv.CreateDeltaWeightAndBiasBatch(dk, k, k, Cc, K, db, x, delta, 1, 1, 1, 1, accumulate=False)
+        # the layer's Forward and TrainingBackward (netlayer/cnetlayerconvolution.cu.h:310,484): forward
+        # convolution, then backward-data and the batch-summed weight/bias gradient written into the arena
+        layer.forward(y, x, wt, bias)
+        layer.backward(dx, dk, db, delta, x, wt, accumulate=False)
         if world > 1:
             dist.all_reduce(arena)
 

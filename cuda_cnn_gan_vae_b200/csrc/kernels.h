@@ -30,6 +30,27 @@ int tc_conv_wgrad_batch(const b200_conv_geom &g, float *dkernel, float *dbias, i
 int tc_gemm(float *out, const float *a, const float *b, int m, int n, int k, int a_mn_major, int b_mn_major,
             int precision, cudaStream_t s);
 
+// Packed operands of the tensor-core kernels (tc_conv.cu): a phase-split NHWC copy of an activation
+// tensor, TF32-rounded high part `hi` and (3xTF32 only) remainder `lo`.  Buffers hold elems() floats
+// plus kPackPad bytes (the blocked tensor maps of MN-major operands may read that far past the end).
+struct ActPack {
+    float *hi = nullptr, *lo = nullptr;
+    int n = 0, c = 0, h = 0, w = 0;          // the source tensor
+    int cp = 0, sy = 1, sx = 1, hs = 0, ws = 0;
+    size_t elems() const { return (size_t)sy * sx * n * hs * ws * cp; }
+};
+constexpr size_t kPackPad = 256;
+ActPack act_pack_shape(int n, int c, int h, int w, int sy, int sx);
+int act_pack_fill(const ActPack &pk, const float *src, cudaStream_t s);
+size_t weight_pack_elems(const b200_conv_geom &g, bool backward);
+int weight_pack_fill(const b200_conv_geom &g, bool backward, const float *kernel, float *hi, float *lo, cudaStream_t s);
+int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack &act, const float *w_hi, const float *w_lo,
+              const float *bias, bool x3, cudaStream_t s);
+size_t wgrad_partial_elems(const b200_conv_geom &g, int batch);
+int wgrad_gemm(const b200_conv_geom &g, float *dkernel, int accumulate, const ActPack &x, const ActPack &d, float *partial,
+               bool x3, cudaStream_t s);
+int dbias_batch(float *dbias, int accumulate, const float *delta, int batch, int K, size_t plane, float *db_tmp, cudaStream_t s);
+
 // Status word written by device-side waits that gave up (0 = none); clear != 0 resets it.
 unsigned tc_read_status(int clear);
 

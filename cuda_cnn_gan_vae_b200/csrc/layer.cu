@@ -1,0 +1,204 @@
+// Layer-level entry points: the pair Forward / TrainingBackward of the reference's convolution
+// layer (netlayer/cnetlayerconvolution.cu.h:310-318, 484-515) and of its transposed-convolution
+// layer (netlayer/cnetlayerbackconvolution.cu.h:303-313, 475-497) as two calls on a small context
+// object.  What the context adds over the stateless tensor-math entry points is operand reuse: the
+// packed copy of the layer input made for the forward pass also feeds the weight gradient, and the
+// packed output error is made once for both the input error and the weight gradient.
+#include "common.cuh"
+#include "kernels.h"
+#include <cstring>
+#include <new>
+
+struct b200_conv_layer {
+    b200_conv_geom g;
+    int batch;
+    int transposed;
+    int device;
+    enum { IN_HI, IN_LO, ER_HI, ER_LO, W_HI, W_LO, PARTIAL, DB_TMP, NBUF };
+    float *buf[NBUF];
+    size_t cap[NBUF];            // bytes
+    int in_valid;                // the kept input pack matches the last forward call
+    int in_precision;
+};
+
+namespace b200 {
+
+static int ensure(b200_conv_layer *l, int which, size_t bytes, cudaStream_t s)
+{
+    if (l->cap[which] >= bytes) return B200_OK;
+    if (l->buf[which]) {
+        B200_CUDA(cudaStreamSynchronize(s));
+        B200_CUDA(cudaFree(l->buf[which]));
+        l->buf[which] = nullptr;
+        l->cap[which] = 0;
+    }
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(B200_E_NOMEM, "conv layer: cudaMalloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
+    }
+    l->buf[which] = (float *)p;
+    l->cap[which] = bytes;
+    return B200_OK;
+}
+
+// Shapes of the two packs of a layer.  "in" is what the layer's forward pass gathers, "er" what its
+// backward pass gathers.
+static ActPack in_shape(const b200_conv_layer *l)
+{
+    const b200_conv_geom &g = l->g;
+    return l->transposed ? act_pack_shape(l->batch, g.kernel_amount, g.out_y, g.out_x, 1, 1)
+                         : act_pack_shape(l->batch, g.in_z, g.in_y, g.in_x, g.stride_y, g.stride_x);
+}
+static ActPack er_shape(const b200_conv_layer *l)
+{
+    const b200_conv_geom &g = l->g;
+    return l->transposed ? act_pack_shape(l->batch, g.in_z, g.in_y, g.in_x, g.stride_y, g.stride_x)
+                         : act_pack_shape(l->batch, g.kernel_amount, g.out_y, g.out_x, 1, 1);
+}
+
+static int pack_into(b200_conv_layer *l, int hi_slot, ActPack &pk, const float *src, bool x3, cudaStream_t s)
+{
+    int r;
+    const size_t bytes = sizeof(float) * pk.elems() + kPackPad;
+    if ((r = ensure(l, hi_slot, bytes, s))) return r;
+    if (x3 && (r = ensure(l, hi_slot + 1, bytes, s))) return r;
+    pk.hi = l->buf[hi_slot];
+    pk.lo = x3 ? l->buf[hi_slot + 1] : nullptr;
+    return act_pack_fill(pk, src, s);
+}
+
+static int pack_weights(b200_conv_layer *l, bool backward, const float *kernel, bool x3, cudaStream_t s)
+{
+    int r;
+    const size_t bytes = sizeof(float) * weight_pack_elems(l->g, backward);
+    if ((r = ensure(l, b200_conv_layer::W_HI, bytes, s))) return r;
+    if (x3 && (r = ensure(l, b200_conv_layer::W_LO, bytes, s))) return r;
+    return weight_pack_fill(l->g, backward, kernel, l->buf[b200_conv_layer::W_HI], x3 ? l->buf[b200_conv_layer::W_LO] : nullptr, s);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_conv_layer_create(b200_conv_layer **layer, const b200_conv_geom *g, int batch, int transposed)
+{
+    if (!layer || !g) return fail(B200_E_ARG, "null argument");
+    if (batch <= 0 || g->kernel_amount <= 0 || g->in_z <= 0 || g->in_y <= 0 || g->in_x <= 0 || g->kernel_x <= 0 ||
+        g->kernel_y <= 0 || g->stride_x <= 0 || g->stride_y <= 0 || g->padding_x < 0 || g->padding_y < 0)
+        return fail(B200_E_SHAPE, "non-positive convolution geometry");
+    const int ox = (g->in_x - g->kernel_x + 2 * g->padding_x) / g->stride_x + 1;
+    const int oy = (g->in_y - g->kernel_y + 2 * g->padding_y) / g->stride_y + 1;
+    if (ox != g->out_x || oy != g->out_y || ox <= 0 || oy <= 0)
+        return fail(B200_E_SHAPE, "wrong output size for convolution: expected %dx%d, got %dx%d", oy, ox, g->out_y, g->out_x);
+    b200_conv_layer *l = new (std::nothrow) b200_conv_layer;
+    if (!l) return fail(B200_E_NOMEM, "host allocation failed");
+    memset(l, 0, sizeof(*l));
+    l->g = *g;
+    l->batch = batch;
+    l->transposed = transposed != 0;
+    cudaGetDevice(&l->device);
+    *layer = l;
+    return B200_OK;
+}
+
+int b200_conv_layer_destroy(b200_conv_layer *l)
+{
+    if (!l) return B200_OK;
+    for (int i = 0; i < b200_conv_layer::NBUF; i++)
+        if (l->buf[i]) cudaFree(l->buf[i]);
+    delete l;
+    return B200_OK;
+}
+
+int b200_conv_layer_forward(b200_conv_layer *l, float *out, const float *input, const float *kernel, const float *bias, void *stream)
+{
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!l || !out || !input || !kernel) return fail(B200_E_ARG, "null argument");
+    const int prec = precision();
+    l->in_valid = 0;
+    int r = TC_UNSUPPORTED;
+    if (prec != B200_FP32) {
+        const bool x3 = prec == B200_TF32X3;
+        ActPack in = in_shape(l);
+        if ((r = pack_into(l, b200_conv_layer::IN_HI, in, input, x3, s)) == B200_OK &&
+            (r = pack_weights(l, l->transposed, kernel, x3, s)) == B200_OK)
+            r = conv_gemm(l->transposed, l->g, out, in, l->buf[b200_conv_layer::W_HI], l->buf[b200_conv_layer::W_LO],
+                          l->transposed ? nullptr : bias, x3, s);
+        if (r == B200_OK) {
+            l->in_valid = 1;
+            l->in_precision = prec;
+            set_path(B200_PATH_TCGEN05);
+            return r;
+        }
+        if (r != TC_UNSUPPORTED) return r;
+    }
+    // general path: the stateless tensor-math entry points
+    if (!l->transposed) return b200_conv_forward(&l->g, out, l->batch, input, l->batch, kernel, 1, bias, 1, stream);
+    return b200_conv_backward(&l->g, out, l->batch, input, l->batch, kernel, 1, nullptr, 0, stream);
+}
+
+int b200_conv_layer_backward(b200_conv_layer *l, float *input_delta, float *dkernel, float *dbias, int accumulate,
+                             const float *output_delta, const float *input, const float *kernel, void *stream)
+{
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!l || !output_delta || !input || !kernel) return fail(B200_E_ARG, "null argument");
+    if (!input_delta && !dkernel) return B200_OK;
+    const b200_conv_geom &g = l->g;
+    const int prec = precision();
+    int r = TC_UNSUPPORTED;
+    if (prec != B200_FP32) {
+        const bool x3 = prec == B200_TF32X3;
+        ActPack in = in_shape(l), er = er_shape(l);
+        r = pack_into(l, b200_conv_layer::ER_HI, er, output_delta, x3, s);
+        if (r == B200_OK && input_delta) {
+            // error of the layer input: BackwardConvolution for a convolution layer, ForwardConvolution
+            // (zero bias) for a transposed-convolution layer
+            if ((r = pack_weights(l, !l->transposed, kernel, x3, s)) == B200_OK)
+                r = conv_gemm(!l->transposed, g, input_delta, er, l->buf[b200_conv_layer::W_HI], l->buf[b200_conv_layer::W_LO], nullptr, x3, s);
+        }
+        if (r == B200_OK && dkernel) {
+            if (l->in_valid && l->in_precision == prec) {
+                in.hi = l->buf[b200_conv_layer::IN_HI];
+                in.lo = x3 ? l->buf[b200_conv_layer::IN_LO] : nullptr;
+            } else {
+                r = pack_into(l, b200_conv_layer::IN_HI, in, input, x3, s);      // forward was not run in this mode
+            }
+            if (r == B200_OK) r = ensure(l, b200_conv_layer::PARTIAL, sizeof(float) * wgrad_partial_elems(g, l->batch), s);
+            // image role / delta role of the weight gradient: (input, error) for a convolution layer,
+            // (error, input) for a transposed-convolution layer
+            if (r == B200_OK)
+                r = l->transposed ? wgrad_gemm(g, dkernel, accumulate, er, in, l->buf[b200_conv_layer::PARTIAL], x3, s)
+                                  : wgrad_gemm(g, dkernel, accumulate, in, er, l->buf[b200_conv_layer::PARTIAL], x3, s);
+            if (r == B200_OK && dbias) {
+                if (l->transposed) {
+                    // the reference clears the bias gradient of this layer (cuda/ctensorconv.cu.h:1221)
+                    if (!accumulate) B200_CUDA(cudaMemsetAsync(dbias, 0, sizeof(float) * g.kernel_amount, s));
+                } else if ((r = ensure(l, b200_conv_layer::DB_TMP, sizeof(float) * (size_t)l->batch * g.kernel_amount, s)) == B200_OK) {
+                    r = dbias_batch(dbias, accumulate, output_delta, l->batch, g.kernel_amount, (size_t)g.out_y * g.out_x,
+                                    l->buf[b200_conv_layer::DB_TMP], s);
+                }
+            }
+        }
+        if (r == B200_OK) { set_path(B200_PATH_TCGEN05); return r; }
+        if (r != TC_UNSUPPORTED) return r;
+    }
+    // general path
+    if (input_delta) {
+        r = l->transposed ? b200_conv_forward(&g, input_delta, l->batch, output_delta, l->batch, kernel, 1, nullptr, 0, stream)
+                          : b200_conv_backward(&g, input_delta, l->batch, output_delta, l->batch, kernel, 1, nullptr, 0, stream);
+        if (r) return r;
+    }
+    if (dkernel) {
+        r = l->transposed ? b200_conv_wgrad_batch(&g, dkernel, nullptr, accumulate, output_delta, input, l->batch, stream)
+                          : b200_conv_wgrad_batch(&g, dkernel, dbias, accumulate, input, output_delta, l->batch, stream);
+        if (r) return r;
+        if (l->transposed && dbias && !accumulate) B200_CUDA(cudaMemsetAsync(dbias, 0, sizeof(float) * g.kernel_amount, s));
+    }
+    return B200_OK;
+}
+
+}  // extern "C"

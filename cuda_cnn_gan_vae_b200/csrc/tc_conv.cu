@@ -695,36 +695,54 @@ static void tile_shape(int ext_y, int ext_x, int target, int *BW, int *BH, int *
     *BI = rest / *BH;
 }
 
-// Shared body of the forward convolution and of one backward-data convolution: `act` is the tensor
-// that is gathered (channels act_c, size act_y x act_x, phase-split by (sy, sx) when the gather is
-// strided), `out` the tensor produced (k_out channels, OH x OW), written at (yy*osy + ry, xx*osx + rx).
-static int run_conv(bool backward, const b200_conv_geom &g, float *out, const float *act, const float *kernel, const float *bias,
-                    int batch, int precision, cudaStream_t s)
+// ---------------------------------------------------------------------------------------------------
+// packed operands
+// ---------------------------------------------------------------------------------------------------
+
+// Shape of the phase-split NHWC pack of an n x c x h x w tensor gathered with stride (sy, sx).
+ActPack act_pack_shape(int n, int c, int h, int w, int sy, int sx)
+{
+    ActPack pk;
+    pk.n = n; pk.c = c; pk.h = h; pk.w = w; pk.sy = sy; pk.sx = sx;
+    pk.cp = (int)align_up(c, 4);
+    pk.hs = ceil_div(h, sy); pk.ws = ceil_div(w, sx);
+    return pk;
+}
+
+int act_pack_fill(const ActPack &pk, const float *src, cudaStream_t s)
+{
+    return pack_act(src, pk.hi, pk.lo, pk.n, pk.c, pk.h, pk.w, pk.cp, pk.sy, pk.sx, pk.hs, pk.ws, s);
+}
+
+size_t weight_pack_elems(const b200_conv_geom &g, bool backward)
+{
+    const int taps = g.kernel_x * g.kernel_y;
+    return backward ? (size_t)g.in_z * taps * align_up(g.kernel_amount, 4) : (size_t)g.kernel_amount * taps * align_up(g.in_z, 4);
+}
+
+int weight_pack_fill(const b200_conv_geom &g, bool backward, const float *kernel, float *hi, float *lo, cudaStream_t s)
+{
+    const int taps = g.kernel_x * g.kernel_y;
+    const int ip = (int)align_up(backward ? g.kernel_amount : g.in_z, 4);
+    return pack_weight(kernel, hi, lo, g.kernel_amount, g.in_z, taps, ip, backward ? 1 : 0, s);
+}
+
+// Forward convolution, or one backward-data convolution, on packed operands: `act` is the packed
+// tensor that is gathered (image, split by the stride, for the forward pass; delta, unsplit, for the
+// backward pass), w_hi/w_lo the matching weight pack, `out` the NCHW tensor produced.
+int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack &act, const float *w_hi, const float *w_lo,
+              const float *bias, bool x3, cudaStream_t s)
 {
     if (!geom_supported(g)) return TC_UNSUPPORTED;
-    const bool x3 = precision == B200_TF32X3;
+    const int batch = act.n;
     const int taps = g.kernel_x * g.kernel_y;
-    const int act_c = backward ? g.kernel_amount : g.in_z;
-    const int act_y = backward ? g.out_y : g.in_y, act_x = backward ? g.out_x : g.in_x;
+    const int act_c = act.c;
     const int k_out = backward ? g.in_z : g.kernel_amount;
     const int OH = backward ? g.in_y : g.out_y, OW = backward ? g.in_x : g.out_x;
-    const int sy = backward ? 1 : g.stride_y, sx = backward ? 1 : g.stride_x;        // phase split of the gathered tensor
+    const int sy = act.sy, sx = act.sx;                                               // phase split of the gathered tensor
     const int osy = backward ? g.stride_y : 1, osx = backward ? g.stride_x : 1;      // output phases
-    const int Cp = (int)align_up(act_c, 4);
-    const int Hs = ceil_div(act_y, sy), Ws = ceil_div(act_x, sx);
-    const size_t act_elems = (size_t)sy * sx * batch * Hs * Ws * Cp;
-    const size_t w_elems = (size_t)k_out * taps * Cp;
-    const size_t bytes = sizeof(float) * (act_elems + w_elems) * (x3 ? 2 : 1) + 8192;
-    int r = arena_reserve(bytes, s);
-    if (r) return r;
-    arena_reset();
-    float *a_hi = (float *)arena_take(sizeof(float) * act_elems);
-    float *a_lo = x3 ? (float *)arena_take(sizeof(float) * act_elems) : nullptr;
-    float *w_hi = (float *)arena_take(sizeof(float) * w_elems);
-    float *w_lo = x3 ? (float *)arena_take(sizeof(float) * w_elems) : nullptr;
-    if (!a_hi || !w_hi || (x3 && (!a_lo || !w_lo))) return fail(B200_E_NOMEM, "scratch arena exhausted");
-    if ((r = pack_act(act, a_hi, a_lo, batch, act_c, act_y, act_x, Cp, sy, sx, Hs, Ws, s))) return r;
-    if ((r = pack_weight(kernel, w_hi, w_lo, g.kernel_amount, g.in_z, taps, Cp, backward ? 1 : 0, s))) return r;
+    const int Cp = act.cp, Hs = act.hs, Ws = act.ws;
+    int r;
 
     TcParams p;
     memset(&p, 0, sizeof(p));
@@ -786,8 +804,8 @@ static int run_conv(bool backward, const b200_conv_geom &g, float *out, const fl
         const long long dims[5] = {act_c, Ws, Hs, batch, (long long)sy * sx};
         const long long pitch[4] = {Cp, (long long)Ws * Cp, (long long)Hs * Ws * Cp, (long long)batch * Hs * Ws * Cp};
         const int box[5] = {32, p.BW, p.BH, p.BI, 1};
-        if ((r = make_map(&maps[0], a_hi, dims, pitch, box))) return r;
-        if (x3 && (r = make_map(&maps[1], a_lo, dims, pitch, box))) return r;
+        if ((r = make_map(&maps[0], act.hi, dims, pitch, box))) return r;
+        if (x3 && (r = make_map(&maps[1], act.lo, dims, pitch, box))) return r;
     }
     {
         const long long dims[5] = {act_c, taps, k_out, 1, 1};
@@ -797,6 +815,28 @@ static int run_conv(bool backward, const b200_conv_geom &g, float *out, const fl
         if (x3 && (r = make_map(&maps[3], w_lo, dims, pitch, box))) return r;
     }
     return launch_tc<MODE_CONV>(maps, p, x3, s);
+}
+
+static int run_conv(bool backward, const b200_conv_geom &g, float *out, const float *act, const float *kernel, const float *bias,
+                    int batch, int precision, cudaStream_t s)
+{
+    if (!geom_supported(g)) return TC_UNSUPPORTED;
+    const bool x3 = precision == B200_TF32X3;
+    ActPack pk = backward ? act_pack_shape(batch, g.kernel_amount, g.out_y, g.out_x, 1, 1)
+                          : act_pack_shape(batch, g.in_z, g.in_y, g.in_x, g.stride_y, g.stride_x);
+    const size_t w_elems = weight_pack_elems(g, backward);
+    const size_t bytes = (sizeof(float) * (pk.elems() + w_elems) + kPackPad) * (x3 ? 2 : 1) + 8192;
+    int r = arena_reserve(bytes, s);
+    if (r) return r;
+    arena_reset();
+    pk.hi = (float *)arena_take(sizeof(float) * pk.elems() + kPackPad);
+    pk.lo = x3 ? (float *)arena_take(sizeof(float) * pk.elems() + kPackPad) : nullptr;
+    float *w_hi = (float *)arena_take(sizeof(float) * w_elems);
+    float *w_lo = x3 ? (float *)arena_take(sizeof(float) * w_elems) : nullptr;
+    if (!pk.hi || !w_hi || (x3 && (!pk.lo || !w_lo))) return fail(B200_E_NOMEM, "scratch arena exhausted");
+    if ((r = act_pack_fill(pk, act, s))) return r;
+    if ((r = weight_pack_fill(g, backward, kernel, w_hi, w_lo, s))) return r;
+    return conv_gemm(backward, g, out, pk, w_hi, w_lo, bias, x3, s);
 }
 
 int tc_conv_forward(const b200_conv_geom &g, float *out, const float *image, const float *kernel, const float *bias,
@@ -811,18 +851,37 @@ int tc_conv_backward(const b200_conv_geom &g, float *out_delta, const float *del
     return run_conv(true, g, out_delta, delta, kernel, nullptr, batch, precision, s);
 }
 
-int tc_conv_wgrad_batch(const b200_conv_geom &g, float *dkernel, float *dbias, int accumulate, const float *image,
-                        const float *delta, int batch, int precision, cudaStream_t s)
+// Split-K plan of the weight gradient: number of CTAs along the pixel dimension.
+static int wgrad_splits(const b200_conv_geom &g, int batch)
+{
+    int BW, BH, BI;
+    tile_shape(g.out_y, g.out_x, 32, &BW, &BH, &BI);
+    const long long chunks = (long long)ceil_div(g.out_x, BW) * ceil_div(g.out_y, BH) * ceil_div(batch, BI);
+    const int BN = (int)align_up(g.in_z < 256 ? g.in_z : 256, 32);
+    const int base = ceil_div(g.kernel_amount, 128) * ceil_div(g.in_z, BN) * g.kernel_x * g.kernel_y;
+    long long splits = sm_count() / base;
+    if (splits < 1) splits = 1;
+    if (splits > chunks) splits = chunks;
+    if (splits > 64) splits = 64;
+    return (int)splits;
+}
+
+size_t wgrad_partial_elems(const b200_conv_geom &g, int batch)
+{
+    return (size_t)wgrad_splits(g, batch) * g.kernel_x * g.kernel_y * g.in_z * g.kernel_amount;
+}
+
+// Batch-summed weight gradient on packed operands: x = image pack (split by the stride), d = delta
+// pack (unsplit); `partial` holds wgrad_partial_elems() floats.
+int wgrad_gemm(const b200_conv_geom &g, float *dkernel, int accumulate, const ActPack &x, const ActPack &d, float *partial,
+               bool x3, cudaStream_t s)
 {
     if (!geom_supported(g)) return TC_UNSUPPORTED;
-    const bool x3 = precision == B200_TF32X3;
+    const int batch = x.n;
     const int taps = g.kernel_x * g.kernel_y;
     const int C = g.in_z, K = g.kernel_amount;
     const int sy = g.stride_y, sx = g.stride_x;
-    const int Cp = (int)align_up(C, 4), Kp = (int)align_up(K, 4);
-    const int Hs = ceil_div(g.in_y, sy), Ws = ceil_div(g.in_x, sx);
-    const size_t x_elems = (size_t)sy * sx * batch * Hs * Ws * Cp;
-    const size_t d_elems = (size_t)batch * g.out_y * g.out_x * Kp;
+    int r;
 
     TcParams p;
     memset(&p, 0, sizeof(p));
@@ -836,13 +895,9 @@ int tc_conv_wgrad_batch(const b200_conv_geom &g, float *dkernel, float *dbias, i
     tile_shape(g.out_y, g.out_x, 32, &p.BW, &p.BH, &p.BI);
     p.chunks_x = ceil_div(g.out_x, p.BW); p.chunks_y = ceil_div(g.out_y, p.BH); p.chunks_i = ceil_div(batch, p.BI);
     p.chunks_total = (long long)p.chunks_x * p.chunks_y * p.chunks_i;
-    const int base = p.ft_n * p.ct_n * taps;
-    long long splits = sm_count() / base;
-    if (splits < 1) splits = 1;
-    if (splits > p.chunks_total) splits = p.chunks_total;
-    if (splits > 64) splits = 64;
-    p.splits = (int)splits;
-    p.num_tiles = base * p.splits;
+    p.splits = wgrad_splits(g, batch);
+    p.num_tiles = p.ft_n * p.ct_n * taps * p.splits;
+    p.partial = partial;
     for (int ky = 0; ky < g.kernel_y; ky++)
         for (int kx = 0; kx < g.kernel_x; kx++) {
             TapEntry t;
@@ -852,52 +907,65 @@ int tc_conv_wgrad_batch(const b200_conv_geom &g, float *dkernel, float *dbias, i
             p.taps[ky * g.kernel_x + kx] = t;
         }
 
-    const size_t part_elems = (size_t)p.splits * taps * C * K;
-    const size_t db_elems = dbias ? (size_t)batch * K : 0;
-    const size_t bytes = sizeof(float) * ((x_elems + d_elems) * (x3 ? 2 : 1) + part_elems + db_elems) + 32768;
-    int r = arena_reserve(bytes, s);
-    if (r) return r;
-    arena_reset();
-    float *x_hi = (float *)arena_take(sizeof(float) * x_elems + 256);      // +256: see make_blocked_map
-    float *x_lo = x3 ? (float *)arena_take(sizeof(float) * x_elems + 256) : nullptr;
-    float *d_hi = (float *)arena_take(sizeof(float) * d_elems + 256);
-    float *d_lo = x3 ? (float *)arena_take(sizeof(float) * d_elems + 256) : nullptr;
-    p.partial = (float *)arena_take(sizeof(float) * part_elems);
-    float *db_tmp = dbias ? (float *)arena_take(sizeof(float) * db_elems) : nullptr;
-    if (!x_hi || !d_hi || !p.partial || (x3 && (!x_lo || !d_lo)) || (dbias && !db_tmp)) return fail(B200_E_NOMEM, "scratch arena exhausted");
-    if ((r = pack_act(image, x_hi, x_lo, batch, C, g.in_y, g.in_x, Cp, sy, sx, Hs, Ws, s))) return r;
-    if ((r = pack_act(delta, d_hi, d_lo, batch, K, g.out_y, g.out_x, Kp, 1, 1, g.out_y, g.out_x, s))) return r;
-
     CUtensorMap maps[4];
     {
         const long long dims[3] = {g.out_x, g.out_y, batch};
-        const long long pitch[3] = {Kp, (long long)g.out_x * Kp, (long long)g.out_y * g.out_x * Kp};
+        const long long pitch[3] = {d.cp, (long long)g.out_x * d.cp, (long long)g.out_y * g.out_x * d.cp};
         const int box[3] = {p.BW, p.BH, p.BI};
-        if ((r = make_blocked_map(&maps[0], d_hi, K, dims, pitch, box, 4))) return r;
-        if (x3 && (r = make_blocked_map(&maps[1], d_lo, K, dims, pitch, box, 4))) return r;
+        if ((r = make_blocked_map(&maps[0], d.hi, K, dims, pitch, box, 4))) return r;
+        if (x3 && (r = make_blocked_map(&maps[1], d.lo, K, dims, pitch, box, 4))) return r;
     }
     {
         // phase and image index share one dimension ([phase][n] is contiguous in the pack)
-        const long long dims[3] = {Ws, Hs, (long long)batch * sy * sx};
-        const long long pitch[3] = {Cp, (long long)Ws * Cp, (long long)Hs * Ws * Cp};
+        const long long dims[3] = {x.ws, x.hs, (long long)batch * sy * sx};
+        const long long pitch[3] = {x.cp, (long long)x.ws * x.cp, (long long)x.hs * x.ws * x.cp};
         const int box[3] = {p.BW, p.BH, p.BI};
-        if ((r = make_blocked_map(&maps[2], x_hi, C, dims, pitch, box, p.BN / 32))) return r;
-        if (x3 && (r = make_blocked_map(&maps[3], x_lo, C, dims, pitch, box, p.BN / 32))) return r;
+        if ((r = make_blocked_map(&maps[2], x.hi, C, dims, pitch, box, p.BN / 32))) return r;
+        if (x3 && (r = make_blocked_map(&maps[3], x.lo, C, dims, pitch, box, p.BN / 32))) return r;
     }
     if ((r = launch_tc<MODE_WGRAD>(maps, p, x3, s))) return r;
-    {
-        size_t total = (size_t)K * C * taps;
-        int grid = (int)((total + 255) / 256);
-        if (grid > sm_count() * 16) grid = sm_count() * 16;
-        wgrad_reduce_kernel<<<grid, 256, 0, s>>>(dkernel, p.partial, p.splits, taps, C, K, accumulate);
-        B200_LAUNCH_CHECK();
-    }
-    if (dbias) {
-        // bias gradient: plane sums of delta per (sample, filter), then the reduction over the batch
-        if ((r = b200_summ_xy(db_tmp, batch, delta, batch, K, (size_t)g.out_y * g.out_x, s))) return r;
-        if (!accumulate) B200_CUDA(cudaMemsetAsync(dbias, 0, sizeof(float) * K, s));
-        if ((r = b200_add_sum_w(dbias, 1, dbias, 1, db_tmp, batch, K, 1.f, 1.f, s))) return r;
-    }
+    size_t total = (size_t)K * C * taps;
+    int grid = (int)((total + 255) / 256);
+    if (grid > sm_count() * 16) grid = sm_count() * 16;
+    wgrad_reduce_kernel<<<grid, 256, 0, s>>>(dkernel, p.partial, p.splits, taps, C, K, accumulate);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+// Bias gradient: plane sums of delta per (sample, filter), then the reduction over the batch.
+// db_tmp holds batch * K floats.
+int dbias_batch(float *dbias, int accumulate, const float *delta, int batch, int K, size_t plane, float *db_tmp, cudaStream_t s)
+{
+    int r;
+    if ((r = b200_summ_xy(db_tmp, batch, delta, batch, K, plane, s))) return r;
+    if (!accumulate) B200_CUDA(cudaMemsetAsync(dbias, 0, sizeof(float) * K, s));
+    return b200_add_sum_w(dbias, 1, dbias, 1, db_tmp, batch, (size_t)K, 1.f, 1.f, s);
+}
+
+int tc_conv_wgrad_batch(const b200_conv_geom &g, float *dkernel, float *dbias, int accumulate, const float *image,
+                        const float *delta, int batch, int precision, cudaStream_t s)
+{
+    if (!geom_supported(g)) return TC_UNSUPPORTED;
+    const bool x3 = precision == B200_TF32X3;
+    ActPack x = act_pack_shape(batch, g.in_z, g.in_y, g.in_x, g.stride_y, g.stride_x);
+    ActPack d = act_pack_shape(batch, g.kernel_amount, g.out_y, g.out_x, 1, 1);
+    const size_t part_elems = wgrad_partial_elems(g, batch);
+    const size_t db_elems = dbias ? (size_t)batch * g.kernel_amount : 0;
+    const size_t bytes = (sizeof(float) * (x.elems() + d.elems()) + 2 * kPackPad) * (x3 ? 2 : 1) + sizeof(float) * (part_elems + db_elems) + 32768;
+    int r = arena_reserve(bytes, s);
+    if (r) return r;
+    arena_reset();
+    x.hi = (float *)arena_take(sizeof(float) * x.elems() + kPackPad);
+    x.lo = x3 ? (float *)arena_take(sizeof(float) * x.elems() + kPackPad) : nullptr;
+    d.hi = (float *)arena_take(sizeof(float) * d.elems() + kPackPad);
+    d.lo = x3 ? (float *)arena_take(sizeof(float) * d.elems() + kPackPad) : nullptr;
+    float *partial = (float *)arena_take(sizeof(float) * part_elems);
+    float *db_tmp = dbias ? (float *)arena_take(sizeof(float) * db_elems) : nullptr;
+    if (!x.hi || !d.hi || !partial || (x3 && (!x.lo || !d.lo)) || (dbias && !db_tmp)) return fail(B200_E_NOMEM, "scratch arena exhausted");
+    if ((r = act_pack_fill(x, image, s))) return r;
+    if ((r = act_pack_fill(d, delta, s))) return r;
+    if ((r = wgrad_gemm(g, dkernel, accumulate, x, d, partial, x3, s))) return r;
+    if (dbias) return dbias_batch(dbias, accumulate, delta, batch, g.kernel_amount, (size_t)g.out_y * g.out_x, db_tmp, s);
     return B200_OK;
 }
 

@@ -32,6 +32,10 @@ SIGNATURES = {
     "b200_conv_wgrad": (_i, [_G, _fp, _i, _fp, _i, _fp, _i, _fp, _i, _vp]),
     "b200_conv_back_wgrad": (_i, [_G, _fp, _i, _fp, _i, _fp, _i, _fp, _i, _vp]),
     "b200_conv_wgrad_batch": (_i, [_G, _fp, _fp, _i, _fp, _fp, _i, _vp]),
+    "b200_conv_layer_create": (_i, [C.POINTER(C.c_void_p), _G, _i, _i]),
+    "b200_conv_layer_destroy": (_i, [_vp]),
+    "b200_conv_layer_forward": (_i, [_vp, _fp, _fp, _fp, _fp, _vp]),
+    "b200_conv_layer_backward": (_i, [_vp, _fp, _fp, _fp, _i, _fp, _fp, _fp, _vp]),
     "b200_conv_wgrad_batch_static": (_i, [_G, _fp, _fp, _i, _fp, _fp, _i, _vp]),
     "b200_static_scratch_bytes": (_sz, []),
     "b200_mul": (_i, [_fp, _i, _fp, _i, _fp, _i, _i, _i, _i, _i, _i, _vp]),

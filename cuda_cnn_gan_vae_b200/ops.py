@@ -351,3 +351,39 @@ def vae_backward(delta, mu, logvar, eps, kl_speed):
     _check(load().b200_vae_backward(_ptr(dmu), _ptr(dlv), _ptr(delta), _ptr(mu), _ptr(logvar), _ptr(eps), mu.numel(),
                                     kl_speed, _stream()))
     return dmu, dlv
+
+
+class ConvLayer:
+    """Forward / TrainingBackward of the reference's convolution layer (netlayer/cnetlayerconvolution.cu.h:310,484)
+    or, with transposed=True, of its transposed-convolution layer (netlayer/cnetlayerbackconvolution.cu.h:303,475).
+    The library context keeps the packed layer input between the two calls."""
+
+    def __init__(self, in_z, in_y, in_x, kernel_amount, kernel_x, kernel_y, stride_x, stride_y, padding_x, padding_y, batch,
+                 transposed=False):
+        self.g = geom(in_z, in_y, in_x, kernel_amount, kernel_x, kernel_y, stride_x, stride_y, padding_x, padding_y)
+        self.batch, self.transposed = batch, transposed
+        self._h = C.c_void_p()
+        _check(load().b200_conv_layer_create(C.byref(self._h), C.byref(self.g), batch, int(transposed)))
+
+    def forward(self, output, inp, kernel, bias=None):
+        _t(output), _t(inp), _t(kernel)
+        _check(load().b200_conv_layer_forward(self._h, _ptr(output), _ptr(inp), _ptr(kernel),
+                                              _ptr(bias) if bias is not None else None, _stream()))
+
+    def backward(self, input_delta, dkernel, dbias, output_delta, inp, kernel, accumulate=True):
+        _t(output_delta), _t(inp), _t(kernel)
+        _check(load().b200_conv_layer_backward(self._h, _ptr(input_delta) if input_delta is not None else None,
+                                               _ptr(dkernel) if dkernel is not None else None,
+                                               _ptr(dbias) if dbias is not None else None, int(accumulate),
+                                               _ptr(output_delta), _ptr(inp), _ptr(kernel), _stream()))
+
+    def close(self):
+        if self._h:
+            load().b200_conv_layer_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -129,6 +129,31 @@ int b200_conv_back_wgrad(const b200_conv_geom *g, float *dkernel, int dkernel_w,
 int b200_conv_wgrad_batch(const b200_conv_geom *g, float *dkernel, float *dbias, int accumulate,
                           const float *image, const float *delta, int batch, void *stream);
 
+/* ---- layer-level calls ------------------------------------------------------------------------- */
+
+/* The Forward / TrainingBackward pair of the reference's convolution layer
+ * (netlayer/cnetlayerconvolution.cu.h:310-318 and 484-515) and, with transposed != 0, of its
+ * transposed-convolution layer (netlayer/cnetlayerbackconvolution.cu.h:303-313 and 475-497), on a
+ * context object that owns the packed operands: the packed layer input made by the forward call is
+ * reused by the weight gradient, and the packed output error is shared by the input-error and the
+ * weight-gradient kernels.  `g` always describes the underlying convolution; for a transposed layer the
+ * layer input has kernel_amount channels of out_y x out_x and the layer output in_z channels of
+ * in_y x in_x.  One context serves one layer and one stream at a time; create/destroy allocate and free
+ * device memory (buffers grow on first use). */
+typedef struct b200_conv_layer b200_conv_layer;
+int b200_conv_layer_create(b200_conv_layer **layer, const b200_conv_geom *g, int batch, int transposed);
+int b200_conv_layer_destroy(b200_conv_layer *layer);
+/* out = conv(input) + bias (convolution layer) or the transposed convolution of input (transposed layer;
+ * its bias is ignored, as in the reference's CUDA backend). */
+int b200_conv_layer_forward(b200_conv_layer *layer, float *out, const float *input, const float *kernel, const float *bias,
+                            void *stream);
+/* input_delta (may be NULL) = error of the layer input; dkernel / dbias (may be NULL) (+)= batch-summed
+ * gradients (dbias of a transposed layer is cleared, as the reference does).  `input` must hold what the
+ * forward call saw: it is only read when the kept pack cannot be used (no forward call yet, precision
+ * mode changed, or the CUDA-core path). */
+int b200_conv_layer_backward(b200_conv_layer *layer, float *input_delta, float *dkernel, float *dbias, int accumulate,
+                             const float *output_delta, const float *input, const float *kernel, void *stream);
+
 /* Allocation-free form of b200_conv_wgrad_batch (no counterpart in the reference, which allocates
  * its per-sample gradient tensors up front in the layer objects).  For callers that must not allocate
  * device memory where they call the library: hosts that hand out all device memory from their own pool

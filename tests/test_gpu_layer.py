@@ -1,0 +1,101 @@
+"""The layer-level calls (Forward / TrainingBackward of the convolution and transposed-convolution layers)
+against the CPU oracle's sequence of tensor routines, through the C-ABI."""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from tests.util import TOL_TF32, TOL_X3, conv_inputs, dot_rel_err  # noqa: E402
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from cuda_cnn_gan_vae_b200 import ops as o
+    yield o
+    o.set_precision(o.TF32X3)
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+CASES = [(4, 64, 16, 16, 96, 3, 1, 1), (4, 3, 64, 64, 64, 4, 2, 1), (3, 40, 12, 12, 24, 3, 1, 1), (6, 128, 8, 8, 256, 4, 2, 1)]
+
+
+@pytest.mark.parametrize("case", CASES)
+@pytest.mark.parametrize("mode", ["x3", "tf32", "fp32"])
+def test_convolution_layer(ops, port, case, mode):
+    """cnetlayerconvolution.cu.h: Forward = ForwardConvolution; TrainingBackward = BackwardConvolution with a zero
+    bias + per-sample CreateDeltaWeightAndBias + AddSumW into dKernel/dBias (accumulating)."""
+    B, C, H, W, K, k, s, p = case
+    ops.set_precision({"x3": ops.TF32X3, "tf32": ops.TF32, "fp32": ops.FP32}[mode])
+    tol = {"x3": TOL_X3, "tf32": TOL_TF32, "fp32": 1e-5}[mode]
+    x, wt, b, d = conv_inputs(sum(case) + 1, B, C, H, W, K, k, s, p)
+    layer = ops.ConvLayer(C, H, W, K, k, k, s, s, p, p, B)
+    X, WT, BI, D = dev(x), dev(wt), dev(b), dev(d)
+    base_k = np.random.default_rng(1).normal(0, 1, (1, 1, K, C * k * k)).astype(np.float32)
+    base_b = np.random.default_rng(2).normal(0, 1, (1, K, 1, 1)).astype(np.float32)
+    zb = np.zeros((1, K), np.float32)
+    ax, aw, ab, ad = np.abs(x), np.abs(wt), np.abs(b), np.abs(d)
+    for rep in range(2):                       # twice: the context is reused step after step
+        y = torch.full(d.shape, float("nan"), device="cuda")
+        layer.forward(y, X, WT, BI)
+        if mode != "fp32":
+            assert ops.last_path() == ops.PATH_TCGEN05
+        dx = torch.full(x.shape, float("nan"), device="cuda")
+        dk, db = dev(base_k), dev(base_b)
+        layer.backward(dx, dk, db, D, X, WT, accumulate=True)
+        ops.stream_status()
+        assert dot_rel_err(y.cpu().numpy(), port.conv_forward(x, wt[0], b.reshape(1, K), k, k, s, s, p, p),
+                           port.conv_forward(ax, aw[0], ab.reshape(1, K), k, k, s, s, p, p)) <= tol
+        assert dot_rel_err(dx.cpu().numpy(), port.conv_backward(d, wt[0], zb, (C, H, W), k, k, s, s, p, p),
+                           port.conv_backward(ad, aw[0], zb, (C, H, W), k, k, s, s, p, p)) <= tol
+        z = np.zeros((B, K, C * k * k), np.float32)
+        dko, dbo = port.conv_wgrad(z, np.zeros((B, K), np.float32), x, d, k, k, s, s, p, p)
+        mk, mb = port.conv_wgrad(z, np.zeros((B, K), np.float32), ax, ad, k, k, s, s, p, p)
+        assert dot_rel_err(dk.cpu().numpy().reshape(K, -1), base_k.reshape(K, -1) + dko.astype(np.float64).sum(0),
+                           np.abs(base_k.reshape(K, -1)) + mk.astype(np.float64).sum(0)) <= tol
+        assert dot_rel_err(db.cpu().numpy().reshape(K), base_b.reshape(K) + dbo.astype(np.float64).sum(0),
+                           np.abs(base_b.reshape(K)) + mb.astype(np.float64).sum(0)) <= 1e-5
+    # a backward call without a preceding forward in this mode packs the input itself
+    layer2 = ops.ConvLayer(C, H, W, K, k, k, s, s, p, p, B)
+    dk2 = torch.zeros(1, 1, K, C * k * k, device="cuda")
+    layer2.backward(None, dk2, None, D, X, WT, accumulate=False)
+    ops.stream_status()
+    assert dot_rel_err(dk2.cpu().numpy().reshape(K, -1), dko.astype(np.float64).sum(0), mk.astype(np.float64).sum(0)) <= tol
+    layer.close()
+    layer2.close()
+
+
+@pytest.mark.parametrize("case", [(4, 64, 16, 16, 128, 4, 2, 1), (4, 3, 64, 64, 64, 4, 2, 1), (3, 24, 12, 12, 40, 3, 1, 1)])
+@pytest.mark.parametrize("mode", ["x3", "fp32"])
+def test_transposed_convolution_layer(ops, port, case, mode):
+    """cnetlayerbackconvolution.cu.h: Forward = BackwardConvolution of the layer input; TrainingBackward =
+    ForwardConvolution of the output error (zero bias) + CreateBackDeltaWeightAndBias (bias gradient cleared).
+    case = geometry of the underlying convolution: the layer maps K x oy x ox -> C x H x W."""
+    B, C, H, W, K, k, s, p = case
+    ops.set_precision(ops.TF32X3 if mode == "x3" else ops.FP32)
+    tol = TOL_X3 if mode == "x3" else 1e-5
+    big, wt, b, small = conv_inputs(sum(case) + 2, B, C, H, W, K, k, s, p)     # small: layer input, big: layer output error
+    layer = ops.ConvLayer(C, H, W, K, k, k, s, s, p, p, B, transposed=True)
+    S, WT, G = dev(small), dev(wt), dev(big)
+    zb = np.zeros((1, K), np.float32)
+    out = torch.full(big.shape, float("nan"), device="cuda")
+    layer.forward(out, S, WT)
+    d_in = torch.full(small.shape, float("nan"), device="cuda")
+    dk = torch.full((1, 1, K, C * k * k), float("nan"), device="cuda")
+    db = torch.full((1, K, 1, 1), 3.0, device="cuda")
+    layer.backward(d_in, dk, db, G, S, WT, accumulate=False)
+    ops.stream_status()
+    a_s, a_w, a_g = np.abs(small), np.abs(wt), np.abs(big)
+    assert dot_rel_err(out.cpu().numpy(), port.conv_backward(small, wt[0], zb, (C, H, W), k, k, s, s, p, p),
+                       port.conv_backward(a_s, a_w[0], zb, (C, H, W), k, k, s, s, p, p)) <= tol
+    assert dot_rel_err(d_in.cpu().numpy(), port.conv_forward(big, wt[0], zb, k, k, s, s, p, p),
+                       port.conv_forward(a_g, a_w[0], zb, k, k, s, s, p, p)) <= tol
+    z = np.zeros((B, K, C * k * k), np.float32)
+    dko, dbo = port.conv_wgrad(z, np.ones((B, K), np.float32), small, big, k, k, s, s, p, p, back_variant=True)
+    mk, _ = port.conv_wgrad(z, np.ones((B, K), np.float32), a_s, a_g, k, k, s, s, p, p, back_variant=True)
+    assert dot_rel_err(dk.cpu().numpy().reshape(K, -1), dko.astype(np.float64).sum(0), mk.astype(np.float64).sum(0)) <= tol
+    assert not db.cpu().numpy().any() and not dbo.any()
+    layer.close()

@@ -220,9 +220,9 @@ def main():
         dist.broadcast(wt, 0)                       # weights replicated from rank 0 at start-up
     y = torch.empty(B, K, H, W, device="cuda")
     dx = torch.empty(B, Cc, H, W, device="cuda")
-    arena = torch.zeros(K * Cc * k * k + K, device="cuda")      # contiguous dW | dB gradient arena (all-reduced as one buffer)
-    dk = arena[: K * Cc * k * k].view(1, 1, K, Cc * k * k)
-    db = arena[K * Cc * k * k:].view(1, K, 1, 1)
+    from cuda_cnn_gan_vae_b200.dp import GradArena
+    grads = GradArena({"dW": (1, 1, K, Cc * k * k), "dB": (1, K, 1, 1)}, "cuda")   # contiguous dW | dB, all-reduced as one buffer
+    arena, dk, db = grads.buffer, grads.views["dW"], grads.views["dB"]
     step_flops = flops_per_sample(c) * c["batch"]
 
     layer = ops.ConvLayer(Cc, H, W, K, k, k, 1, 1, 1, 1, B)
@@ -232,8 +232,7 @@ def main():
         # convolution, then backward-data and the batch-summed weight/bias gradient written into the arena
         layer.forward(y, x, wt, bias)
         layer.backward(dx, dk, db, delta, x, wt, accumulate=False)
-        if world > 1:
-            dist.all_reduce(arena)
+        grads.all_reduce()
 
     def barrier():
         if world > 1:
@@ -274,11 +273,13 @@ def main():
         lib.b200_profile_tensor_core(0)
         ops.stream_status()
         per_launch_flops = step_flops / world / 3.0
+        # dram__bytes_read+write per tc_kernel launch from the ncu capture at batch 128 (profiles/), scaled by units
+        traffic = 1.886e6 * B
         achieved = per_launch_flops / (kernel_ms * 1e-3) / 1e12 if kernel_ms else None
         results[mode_name] = dict(
             value=step_flops / (ms * 1e-3) / 1e12, ms_per_step=ms, clocks=clocks, gpu_launches=int(launches),
             roofline=dict(bound="tensor", achieved=achieved, peak=tf32_peak, unit="TFLOP/s",
-                          frac=(achieved / tf32_peak) if achieved else None, traffic=None,
+                          frac=(achieved / tf32_peak) if achieved else None, traffic=traffic if mode == ops.TF32 else None,
                           kernel="tc_kernel (tcgen05 implicit GEMM), mean of the forward, backward-data and weight-gradient launches",
                           kernel_ms=kernel_ms, mma_per_product=3 if mode == ops.TF32X3 else 1,
                           tensor_pipe_frac=(achieved * (3 if mode == ops.TF32X3 else 1) / tf32_peak) if achieved else None,

@@ -23,6 +23,7 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "tc_ptx.cuh"
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -40,6 +41,7 @@ struct TapEntry { int8_t dy, dx; uint8_t in_phase, wtap; };
 
 struct PhaseInfo {
     int tile_begin;            // first M-tile of this output phase
+    int pair_begin;            // first M-tile pair of this phase (CTA-pair kernels)
     int tiles_x, tiles_y, tiles_i;
     int ext_y, ext_x;          // output extent of the phase (rows / columns it owns)
     int off_y, off_x;          // position of the phase inside the full output
@@ -51,7 +53,7 @@ struct TcParams {
     int a_boxes, b_boxes;
     uint32_t a_box_bytes, b_box_bytes, b_bytes, stage_bytes;
     uint32_t a_lbo, a_sbo, a_kadv, a_layout, b_lbo, b_sbo, b_kadv, b_layout, idesc;
-    int num_tiles;
+    int num_tiles;             // work items of the kernel: tiles, or tile pairs for the CTA-pair kernel
     unsigned *status;
     // CONV
     int n_tiles_n, c_chunks, phases, BW, BH, BI, n_img, k_out, OH, OW, out_stride_y, out_stride_x;
@@ -75,6 +77,30 @@ struct TileCtx {
     long long chunk_begin;     // WGRAD
     int mt;                    // GEMM
 };
+
+// CTA-pair convolution: work item `pair` = two neighbouring M-tiles of one output phase, CTA `rank`
+// takes the rank-th of them.  A phase with an odd tile count ends in a pair whose second tile lies
+// outside the batch: its loads are zero-filled and its stores masked.
+__device__ __forceinline__ TileCtx decode_pair(const TcParams &p, int pair, int rank)
+{
+    TileCtx c;
+    c.nt = pair % p.n_tiles_n;
+    int mp = pair / p.n_tiles_n;
+    int ph = 0;
+    while (ph + 1 < p.phases && mp >= p.phase[ph + 1].pair_begin) ph++;
+    const PhaseInfo &pi = p.phase[ph];
+    int local = (mp - pi.pair_begin) * 2 + rank;
+    c.ph = ph;
+    c.nsteps = pi.tap_count * p.c_chunks;
+    if (local < pi.tiles_x * pi.tiles_y * pi.tiles_i) {
+        c.tx = local % pi.tiles_x;
+        c.ty = (local / pi.tiles_x) % pi.tiles_y;
+        c.ig = local / (pi.tiles_x * pi.tiles_y);
+    } else {
+        c.tx = 0; c.ty = 0; c.ig = pi.tiles_i;
+    }
+    return c;
+}
 
 template <int MODE>
 __device__ __forceinline__ TileCtx decode_tile(const TcParams &p, int tile)
@@ -128,7 +154,7 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
     }
 }
 
-template <int MODE, bool X3>
+template <int MODE, bool X3, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ CUtensorMap mapA_lo,
           const __grid_constant__ CUtensorMap mapB_hi, const __grid_constant__ CUtensorMap mapB_lo,
@@ -147,10 +173,16 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // CTA pair: both CTAs run the producer and the epilogue on their own 128 rows; the leader (rank 0)
+    // alone issues the 256-row MMAs.  full[] and tempty[] live in the leader, empty[] and tfull[] in
+    // each CTA (signalled in both by the leader's tcgen05.commit).
+    const uint32_t rank = CTAS == 2 ? ptx::cluster_ctarank() : 0u;
+    const int work_begin = CTAS == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int work_step = CTAS == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; s++) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
-        for (int a = 0; a < 2; a++) { ptx::mbar_init(tfull_bar(a), 1); ptx::mbar_init(tempty_bar(a), 4); }
+        for (int a = 0; a < 2; a++) { ptx::mbar_init(tfull_bar(a), 1); ptx::mbar_init(tempty_bar(a), 4 * CTAS); }
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::prefetch_tensormap(&mapA_hi);
@@ -158,11 +190,12 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
         if (X3) { ptx::prefetch_tensormap(&mapA_lo); ptx::prefetch_tensormap(&mapB_lo); }
     }
     if (warp == 1) {
-        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), (uint32_t)p.tmem_cols);
-        ptx::tmem_relinquish();
+        if (CTAS == 2) { ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), (uint32_t)p.tmem_cols); ptx::tmem_relinquish_pair(); }
+        else { ptx::tmem_alloc(ptx::smem_u32(tmem_slot), (uint32_t)p.tmem_cols); ptx::tmem_relinquish(); }
     }
     ptx::tc_fence_before();
     __syncthreads();
+    if (CTAS == 2) ptx::cluster_sync();      // the peer's barriers are initialised before anything signals them
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -170,7 +203,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
     const uint32_t off_a_lo = a_bytes;
     const uint32_t off_b_hi = X3 ? 2 * a_bytes : a_bytes;
     const uint32_t off_b_lo = off_b_hi + p.b_bytes;
-    const uint32_t stage_tx = (a_bytes + p.b_bytes) * (X3 ? 2u : 1u);
+    const uint32_t stage_tx = (a_bytes + p.b_bytes) * (X3 ? 2u : 1u) * (uint32_t)CTAS;    // bytes of both CTAs land on the leader's barrier
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -182,14 +215,14 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
         bool ok = true;
         const int planes = X3 ? 2 : 1;
         const int n_a = p.a_boxes * planes, n_boxes = (p.a_boxes + p.b_boxes) * planes;
-        for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
-            const TileCtx c = decode_tile<MODE>(p, tile);
+        for (int tile = work_begin; ok && tile < p.num_tiles; tile += work_step) {
+            const TileCtx c = CTAS == 2 ? decode_pair(p, tile, (int)rank) : decode_tile<MODE>(p, tile);
             for (int step = 0; step < c.nsteps; step++) {
                 if (lane == 0) ok = wait_bar(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 0x100u + B200_E_TIMEOUT);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
                 const uint32_t fb = full_bar(stage);
-                if (lane == 0) ptx::mbar_arrive_expect_tx(fb, stage_tx);
+                if (lane == 0 && rank == 0) ptx::mbar_arrive_expect_tx(fb, stage_tx);
                 __syncwarp();
                 const uint32_t sbase = ptx::smem_u32(smem + (size_t)stage * p.stage_bytes);
                 int a0, a1, a2, a3, a4, b0, b1, b2, b3, b4;
@@ -199,7 +232,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
                     const int ti = step / p.c_chunks, cc = step - ti * p.c_chunks;
                     const TapEntry t = p.taps[pi.tap_begin + ti];
                     a0 = cc * 32; a1 = c.tx * p.BW + t.dx; a2 = c.ty * p.BH + t.dy; a3 = c.ig * p.BI; a4 = t.in_phase;
-                    b0 = cc * 32; b1 = t.wtap; b2 = c.nt * p.BN; b3 = 0; b4 = 0;
+                    b0 = cc * 32; b1 = t.wtap; b2 = c.nt * p.BN + (int)rank * (p.BN / 2) * (CTAS - 1); b3 = 0; b4 = 0;
                 } else if (MODE == MODE_WGRAD) {
                     const long long q = c.chunk_begin + step;
                     const int cx = (int)(q % p.chunks_x);
@@ -219,13 +252,15 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
                 for (int box = lane; box < n_boxes; box += 32) {
                     if (box < n_a) {
                         const int j = box / planes, lo = box - j * planes;
-                        ptx::tma_load_5d(sbase + (lo ? off_a_lo : 0u) + j * p.a_box_bytes, lo ? &mapA_lo : &mapA_hi, fb,
-                                         a0 + j * a_step0, a1, a2, a3, a4);
+                        const uint32_t dst = sbase + (lo ? off_a_lo : 0u) + j * p.a_box_bytes;
+                        if (CTAS == 2) ptx::tma_load_5d_pair(dst, lo ? &mapA_lo : &mapA_hi, fb, a0 + j * a_step0, a1, a2, a3, a4);
+                        else ptx::tma_load_5d(dst, lo ? &mapA_lo : &mapA_hi, fb, a0 + j * a_step0, a1, a2, a3, a4);
                     } else {
                         const int bb = box - n_a;
                         const int j = bb / planes, lo = bb - j * planes;
-                        ptx::tma_load_5d(sbase + (lo ? off_b_lo : off_b_hi) + j * p.b_box_bytes, lo ? &mapB_lo : &mapB_hi, fb,
-                                         b0 + j * b_step0, b1, b2, b3, b4);
+                        const uint32_t dst = sbase + (lo ? off_b_lo : off_b_hi) + j * p.b_box_bytes;
+                        if (CTAS == 2) ptx::tma_load_5d_pair(dst, lo ? &mapB_lo : &mapB_hi, fb, b0 + j * b_step0, b1, b2, b3, b4);
+                        else ptx::tma_load_5d(dst, lo ? &mapB_lo : &mapB_hi, fb, b0 + j * b_step0, b1, b2, b3, b4);
                     }
                 }
                 if (++stage == p.stages) { stage = 0; phase ^= 1u; }
@@ -233,13 +268,13 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        if (lane == 0 && rank == 0) {
             int stage = 0;
             uint32_t phase = 0;
             int tile_iter = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, tile_iter++) {
-                const TileCtx c = decode_tile<MODE>(p, tile);
+            for (int tile = work_begin; ok && tile < p.num_tiles; tile += work_step, tile_iter++) {
+                const TileCtx c = CTAS == 2 ? decode_pair(p, tile, 0) : decode_tile<MODE>(p, tile);
                 const int acc = tile_iter & 1;
                 const uint32_t acc_phase = (uint32_t)(tile_iter >> 1) & 1u;
                 if (!wait_bar(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 0x200u + B200_E_TIMEOUT)) break;
@@ -257,17 +292,25 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
                         if (X3) {
                             const uint64_t a_lo = ptx::smem_desc(sbase + off_a_lo + k * p.a_kadv, p.a_lbo, p.a_sbo, p.a_layout);
                             const uint64_t b_lo = ptx::smem_desc(sbase + off_b_lo + k * p.b_kadv, p.b_lbo, p.b_sbo, p.b_layout);
-                            ptx::mma_tf32(d, a_lo, b_hi, p.idesc, first);   // small terms first
-                            ptx::mma_tf32(d, a_hi, b_lo, p.idesc, 1u);
-                            ptx::mma_tf32(d, a_hi, b_hi, p.idesc, 1u);
+                            if (CTAS == 2) {
+                                ptx::mma_tf32_pair(d, a_lo, b_hi, p.idesc, first);   // small terms first
+                                ptx::mma_tf32_pair(d, a_hi, b_lo, p.idesc, 1u);
+                                ptx::mma_tf32_pair(d, a_hi, b_hi, p.idesc, 1u);
+                            } else {
+                                ptx::mma_tf32(d, a_lo, b_hi, p.idesc, first);
+                                ptx::mma_tf32(d, a_hi, b_lo, p.idesc, 1u);
+                                ptx::mma_tf32(d, a_hi, b_hi, p.idesc, 1u);
+                            }
+                        } else if (CTAS == 2) {
+                            ptx::mma_tf32_pair(d, a_hi, b_hi, p.idesc, first);
                         } else {
                             ptx::mma_tf32(d, a_hi, b_hi, p.idesc, first);
                         }
                     }
-                    ptx::mma_commit(empty_bar(stage));
+                    if (CTAS == 2) ptx::mma_commit_pair(empty_bar(stage)); else ptx::mma_commit(empty_bar(stage));
                     if (++stage == p.stages) { stage = 0; phase ^= 1u; }
                 }
-                if (ok) ptx::mma_commit(tfull_bar(acc));
+                if (ok) { if (CTAS == 2) ptx::mma_commit_pair(tfull_bar(acc)); else ptx::mma_commit(tfull_bar(acc)); }
             }
         }
     } else {
@@ -275,8 +318,8 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
         const int q = warp & 3;
         const int row = q * 32 + lane;
         int tile_iter = 0;
-        for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, tile_iter++) {
-            const TileCtx c = decode_tile<MODE>(p, tile);
+        for (int tile = work_begin; tile < p.num_tiles; tile += work_step, tile_iter++) {
+            const TileCtx c = CTAS == 2 ? decode_pair(p, tile, (int)rank) : decode_tile<MODE>(p, tile);
             const int acc = tile_iter & 1;
             const uint32_t acc_phase = (uint32_t)(tile_iter >> 1) & 1u;
             bool ok = wait_bar(tfull_bar(acc), acc_phase, abort_flag, p.status, 0x400u + B200_E_TIMEOUT);
@@ -326,7 +369,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
             }
             ptx::tc_fence_before();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+            if (lane == 0) { if (CTAS == 2) ptx::mbar_arrive_remote(tempty_bar(acc), 0u); else ptx::mbar_arrive(tempty_bar(acc)); }
         }
     }
 
@@ -336,9 +379,11 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
     }
     ptx::tc_fence_before();
     __syncthreads();
+    if (CTAS == 2) ptx::cluster_sync();      // neither CTA leaves while its partner may still touch its shared memory or barriers
     if (warp == 1) {
         ptx::tc_fence_after();
-        ptx::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+        if (CTAS == 2) ptx::tmem_dealloc_pair(tmem_base, (uint32_t)p.tmem_cols);
+        else ptx::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
     }
 }
 
@@ -598,8 +643,30 @@ static int profile_begin(EventPair *e, cudaStream_t s)
     return B200_OK;
 }
 
+template <int MODE, bool X3, int CTAS>
+static int launch_one(const CUtensorMap maps[4], const TcParams &p, int grid, size_t smem, cudaStream_t s)
+{
+    B200_CUDA(cudaFuncSetAttribute(tc_kernel<MODE, X3, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CTAS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = CTAS > 1 ? 1 : 0;
+    B200_CUDA(cudaLaunchKernelEx(&cfg, tc_kernel<MODE, X3, CTAS>, maps[0], maps[X3 ? 1 : 0], maps[2], maps[X3 ? 3 : 2], p));
+    return B200_OK;
+}
+
+// p.num_tiles counts work items: tiles (ctas == 1) or tile pairs (ctas == 2, one cluster of two CTAs each).
 template <int MODE>
-static int launch_tc(const CUtensorMap maps[4], TcParams &p, bool x3, cudaStream_t s)
+static int launch_tc(const CUtensorMap maps[4], TcParams &p, bool x3, cudaStream_t s, int ctas = 1)
 {
     if (!g_smem_optin) {
         int d = 0, v = 0;
@@ -620,23 +687,35 @@ static int launch_tc(const CUtensorMap maps[4], TcParams &p, bool x3, cudaStream
     int r = status_word(&p.status);
     if (r) return r;
     const size_t smem = (size_t)stages * p.stage_bytes + fixed;
-    int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+    const int slots = sm_count() / ctas;
+    int grid = (p.num_tiles < slots ? p.num_tiles : slots) * ctas;
     if (grid < 1) return B200_OK;
     EventPair ev;
     if (g_profile && (r = profile_begin(&ev, s))) return r;
-    if (x3) {
-        B200_CUDA(cudaFuncSetAttribute(tc_kernel<MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        tc_kernel<MODE, true><<<grid, kThreads, smem, s>>>(maps[0], maps[1], maps[2], maps[3], p);
+    if (ctas == 2) {
+        if (MODE != MODE_CONV) return fail(B200_E_ARG, "CTA-pair kernel exists for the convolution mode only");
+        r = x3 ? launch_one<MODE_CONV, true, 2>(maps, p, grid, smem, s) : launch_one<MODE_CONV, false, 2>(maps, p, grid, smem, s);
     } else {
-        B200_CUDA(cudaFuncSetAttribute(tc_kernel<MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        tc_kernel<MODE, false><<<grid, kThreads, smem, s>>>(maps[0], maps[0], maps[2], maps[2], p);
+        r = x3 ? launch_one<MODE, true, 1>(maps, p, grid, smem, s) : launch_one<MODE, false, 1>(maps, p, grid, smem, s);
     }
+    if (r) return r;
     B200_LAUNCH_CHECK();
     if (g_profile) {
         B200_CUDA(cudaEventRecord(ev.b, s));
         g_pending.push_back(ev);
     }
     return B200_OK;
+}
+
+// Debug switch: B200CONV_CTA_PAIRS=0 in the environment keeps the convolution on single-CTA tiles.
+static bool cta_pairs_enabled()
+{
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("B200CONV_CTA_PAIRS");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
 }
 
 static void set_kmajor(TcParams &p, bool a_side, int rows)
@@ -748,9 +827,12 @@ int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack 
     memset(&p, 0, sizeof(p));
     p.BN = (int)align_up(k_out < 256 ? k_out : 256, 16);
     p.acc_stride = pow2_ceil(p.BN);
+    // CTA pairs (two CTAs share one 256-row MMA, each stages half of the filter rows): less shared-memory
+    // traffic per flop; used when there are enough M-tiles to pair up
+    const int ctas = (cta_pairs_enabled() && p.BN >= 32) ? 2 : 1;
     set_kmajor(p, true, 128);
-    set_kmajor(p, false, p.BN);
-    p.idesc = make_idesc_tf32(p.BN, 0, 0);
+    set_kmajor(p, false, p.BN / ctas);
+    p.idesc = make_idesc_tf32(p.BN, 0, 0, 128 * ctas);
     p.n_tiles_n = ceil_div(k_out, p.BN);
     p.c_chunks = ceil_div(act_c, 32);
     p.n_img = batch; p.k_out = k_out; p.OH = OH; p.OW = OW; p.out_stride_y = osy; p.out_stride_x = osx;
@@ -761,7 +843,7 @@ int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack 
     const int pad_x = backward ? g.kernel_x - 1 - g.padding_x : g.padding_x;
     const int ext_y0 = ceil_div(OH, osy), ext_x0 = ceil_div(OW, osx);
     tile_shape(ext_y0, ext_x0, 128, &p.BW, &p.BH, &p.BI);
-    int ntaps = 0, mtiles = 0, nph = 0;
+    int ntaps = 0, mtiles = 0, mpairs = 0, nph = 0;
     bool any_empty = false;
     for (int ry = 0; ry < osy; ry++)
         for (int rx = 0; rx < osx; rx++) {
@@ -791,13 +873,15 @@ int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack 
             if (pi.tap_count == 0) { any_empty = true; ntaps = pi.tap_begin; continue; }
             pi.tiles_x = ceil_div(pi.ext_x, p.BW); pi.tiles_y = ceil_div(pi.ext_y, p.BH); pi.tiles_i = ceil_div(batch, p.BI);
             pi.tile_begin = mtiles;
+            pi.pair_begin = mpairs;
             mtiles += pi.tiles_x * pi.tiles_y * pi.tiles_i;
+            mpairs += (pi.tiles_x * pi.tiles_y * pi.tiles_i + 1) / 2;
             p.phase[nph++] = pi;
         }
     if (any_empty) B200_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * (size_t)batch * k_out * OH * OW, s));
     if (nph == 0) return B200_OK;
     p.phases = nph;
-    p.num_tiles = mtiles * p.n_tiles_n;
+    p.num_tiles = (ctas == 2 ? mpairs : mtiles) * p.n_tiles_n;
 
     CUtensorMap maps[4];
     {
@@ -810,11 +894,11 @@ int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack 
     {
         const long long dims[5] = {act_c, taps, k_out, 1, 1};
         const long long pitch[4] = {Cp, (long long)taps * Cp, (long long)k_out * taps * Cp, (long long)k_out * taps * Cp};
-        const int box[5] = {32, 1, p.BN, 1, 1};
+        const int box[5] = {32, 1, p.BN / ctas, 1, 1};
         if ((r = make_map(&maps[2], w_hi, dims, pitch, box))) return r;
         if (x3 && (r = make_map(&maps[3], w_lo, dims, pitch, box))) return r;
     }
-    return launch_tc<MODE_CONV>(maps, p, x3, s);
+    return launch_tc<MODE_CONV>(maps, p, x3, s, ctas);
 }
 
 static int run_conv(bool backward, const b200_conv_geom &g, float *out, const float *act, const float *kernel, const float *bias,

@@ -95,6 +95,64 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float *v)
     for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
 }
 
+// ---- CTA-pair (cta_group::2) forms: two CTAs of a cluster share one 256-row MMA ------------------
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrive on the mbarrier at the same shared-memory offset in CTA `cta` of the cluster
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t bar, uint32_t cta)
+{
+    asm volatile(
+        "{\n\t.reg .b32 ra;\n\t"
+        "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+        "mbarrier.arrive.shared::cluster.b64 _, [ra];\n\t}"
+        ::"r"(bar), "r"(cta)
+        : "memory");
+}
+// TMA load issued by either CTA of a pair into its own shared memory; the byte count is credited to
+// the mbarrier of the pair's leader (even-ranked) CTA: the peer bit of the address is cleared.
+__device__ __forceinline__ void tma_load_5d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3, int c4)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.5d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar & 0xFEFFFFFFu), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols)
+{
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// 256 x N x 8 MMA over the pair: rows 0-127 of A and the first half of B's rows come from the leader's
+// shared memory, rows 128-255 and the second half from the peer's, at the same offsets.
+__device__ __forceinline__ void mma_tf32_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrive on the mbarrier at this offset in both CTAs of the pair once the issued MMAs have completed
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar)
+{
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(both)
+                 : "memory");
+}
+
 // Shared-memory matrix descriptor (descriptor version 1).  Offsets in bytes.  layout: 2 = 128-byte
 // swizzle with 16-byte atoms (K-major operands), 1 = 128-byte swizzle with 32-byte atoms (the only
 // swizzled layout the hardware accepts for MN-major 32-bit operands).
@@ -118,8 +176,9 @@ __device__ __forceinline__ float to_tf32(float x)
 
 }  // namespace ptx
 
-// Instruction descriptor of tcgen05.mma kind::tf32: fp32 accumulator, TF32 A and B, M = 128.
-inline uint32_t make_idesc_tf32(int n, int a_mn_major, int b_mn_major)
+// Instruction descriptor of tcgen05.mma kind::tf32: fp32 accumulator, TF32 A and B, M = 128 (one CTA)
+// or 256 (CTA pair).
+inline uint32_t make_idesc_tf32(int n, int a_mn_major, int b_mn_major, int m = 128)
 {
     uint32_t d = 0;
     d |= 1u << 4;                        // accumulator format: F32
@@ -128,7 +187,7 @@ inline uint32_t make_idesc_tf32(int n, int a_mn_major, int b_mn_major)
     d |= (uint32_t)(a_mn_major ? 1 : 0) << 15;
     d |= (uint32_t)(b_mn_major ? 1 : 0) << 16;
     d |= (uint32_t)(n >> 3) << 17;
-    d |= (uint32_t)(128 >> 4) << 24;
+    d |= (uint32_t)(m >> 4) << 24;
     return d;
 }
 

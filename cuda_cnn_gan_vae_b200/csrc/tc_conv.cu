@@ -1,8 +1,8 @@
 // tcgen05 implicit-GEMM kernels for sm_100a: forward convolution, backward-data convolution
 // (= transposed convolution), batch-summed weight gradient and the dense GEMM of the Linear layer.
 //
-// One warp-specialised persistent kernel serves all four problems.  Per CTA (one per SM):
-//   warp 0      TMA producer: streams 128 x 32 (A) and BN x 32 (B) TF32 tiles into a ring of
+// One warp-specialised persistent kernel serves all four problems.  Per CTA (one per SM, 224 threads):
+//   warps 0, 6  TMA producers (alternate stages): stream 128 x 32 (A) and BN x 32 (B) TF32 tiles into a ring of
 //               shared-memory stages with cp.async.bulk.tensor (128-byte swizzle); zero fill of
 //               out-of-range coordinates implements the convolution padding and every ragged edge;
 //   warp 1      MMA issuer: one thread issues tcgen05.mma kind::tf32 (M=128, N=BN, K=8), four per
@@ -31,7 +31,7 @@ namespace b200 {
 
 enum { MODE_CONV = 0, MODE_WGRAD = 1, MODE_GEMM = 2 };
 
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;            // warps: 0 and 6 TMA producers, 1 MMA issuer, 2-5 epilogue
 constexpr int kABytes = 128 * 128;        // 128 rows x 32 tf32
 constexpr int kMaxTaps = 64;
 constexpr int kMaxPhases = 16;
@@ -51,7 +51,8 @@ struct PhaseInfo {
 struct TcParams {
     int stages, BN, acc_stride, tmem_cols;
     int a_boxes, b_boxes;
-    uint32_t a_box_bytes, b_box_bytes, b_bytes, stage_bytes;
+    uint32_t a_box_bytes, b_box_bytes, b_bytes, mini_bytes, stage_bytes;
+    int ksub;                  // 32-wide K blocks per pipeline stage (each block = one set of operand boxes)
     uint32_t a_lbo, a_sbo, a_kadv, a_layout, b_lbo, b_sbo, b_kadv, b_layout, idesc;
     int num_tiles;             // work items of the kernel: tiles, or tile pairs for the CTA-pair kernel
     unsigned *status;
@@ -67,6 +68,9 @@ struct TcParams {
     float *partial;
     // GEMM
     int M, N, K, ldc, a_mn, b_mn;
+#ifdef B200_TC_TIMING
+    long long *dbg;            // per-CTA cycle counters: [0] producer waiting, [1] issuer waiting for data, [2] issuer waiting for TMEM, [3] issuer total, [4] epilogue waiting, [5] epilogue total
+#endif
 };
 
 struct TileCtx {
@@ -203,69 +207,104 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
     const uint32_t off_a_lo = a_bytes;
     const uint32_t off_b_hi = X3 ? 2 * a_bytes : a_bytes;
     const uint32_t off_b_lo = off_b_hi + p.b_bytes;
-    const uint32_t stage_tx = (a_bytes + p.b_bytes) * (X3 ? 2u : 1u) * (uint32_t)CTAS;    // bytes of both CTAs land on the leader's barrier
+    const uint32_t stage_tx = p.stage_bytes * (uint32_t)CTAS;    // bytes of both CTAs land on the leader's barrier
 
-    if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producer
+    if (warp == 0 || warp == 6) {
+        // ------------------------------------------------------------------ TMA producers
+        // Two producer warps take alternate stages (a stage hand-shake plus its TMA issue keeps one warp
+        // busy for several hundred cycles, more than the MMAs of a stage take).
         // The whole warp walks the tile/step sequence; lane 0 owns the barrier handshake and each box
         // of a stage is issued by its own lane, so a stage of many small boxes (MN-major operands,
         // 3xTF32 planes) costs one issue slot instead of one per box.
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
+        // Fixed role of this lane: which K block of a stage (my_m), which operand and plane, where in the
+        // stage it lands.  One warp-wide TMA instruction then fills a whole stage.
         const int planes = X3 ? 2 : 1;
-        const int n_a = p.a_boxes * planes, n_boxes = (p.a_boxes + p.b_boxes) * planes;
+        const int n_boxes = 2 * planes;                          // A and B, high (and low) plane
+        const bool active = lane < n_boxes * p.ksub;
+        const int my_m = lane / n_boxes, my_box = lane - my_m * n_boxes;
+        const bool is_a = my_box < planes;
+        const bool is_lo = (my_box & 1) && X3;
+        const uint32_t my_off = (uint32_t)my_m * p.mini_bytes + (is_a ? (is_lo ? off_a_lo : 0u) : (is_lo ? off_b_lo : off_b_hi));
+        const CUtensorMap *my_map = is_a ? (is_lo ? &mapA_lo : &mapA_hi) : (is_lo ? &mapB_lo : &mapB_hi);
+        const uint32_t smem0 = ptx::smem_u32(smem);
+        const uint32_t my_turn = warp == 0 ? 0u : 1u;
+        uint32_t iter = 0;
+#ifdef B200_TC_TIMING
+        long long dbg_pw = 0;
+#endif
         for (int tile = work_begin; ok && tile < p.num_tiles; tile += work_step) {
             const TileCtx c = CTAS == 2 ? decode_pair(p, tile, (int)rank) : decode_tile<MODE>(p, tile);
-            for (int step = 0; step < c.nsteps; step++) {
+            // running decomposition of this lane's K-block index st = step + my_m
+            int st = my_m, ti = 0, cc = 0, cx = 0, cy = 0, ci = 0;
+            int tap_begin = 0, base1 = 0, base2 = 0, base3 = 0, bcoord = 0;
+            if (MODE == MODE_CONV) {
+                const PhaseInfo &pi = p.phase[c.ph];
+                ti = my_m / p.c_chunks; cc = my_m - ti * p.c_chunks;
+                tap_begin = pi.tap_begin;
+                base1 = c.tx * p.BW; base2 = c.ty * p.BH; base3 = c.ig * p.BI;
+                bcoord = c.nt * p.BN + (int)rank * (p.BN / 2) * (CTAS - 1);
+            } else if (MODE == MODE_WGRAD) {
+                const long long q = c.chunk_begin + my_m;
+                cx = (int)(q % p.chunks_x);
+                const long long r = q / p.chunks_x;
+                cy = (int)(r % p.chunks_y);
+                ci = (int)(r / p.chunks_y);
+            }
+            for (int step = 0; step < c.nsteps; step += p.ksub, iter++) {
+              if ((iter & 1u) == my_turn) {
+#ifdef B200_TC_TIMING
+                const long long tw0 = clock64();
+#endif
                 if (lane == 0) ok = wait_bar(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 0x100u + B200_E_TIMEOUT);
+#ifdef B200_TC_TIMING
+                if (lane == 0) dbg_pw += clock64() - tw0;
+#endif
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
                 const uint32_t fb = full_bar(stage);
                 if (lane == 0 && rank == 0) ptx::mbar_arrive_expect_tx(fb, stage_tx);
                 __syncwarp();
-                const uint32_t sbase = ptx::smem_u32(smem + (size_t)stage * p.stage_bytes);
-                int a0, a1, a2, a3, a4, b0, b1, b2, b3, b4;
-                int a_step0 = 0, b_step0 = 0;   // advance of coordinate 0 from one box of an operand to the next
-                if (MODE == MODE_CONV) {
-                    const PhaseInfo &pi = p.phase[c.ph];
-                    const int ti = step / p.c_chunks, cc = step - ti * p.c_chunks;
-                    const TapEntry t = p.taps[pi.tap_begin + ti];
-                    a0 = cc * 32; a1 = c.tx * p.BW + t.dx; a2 = c.ty * p.BH + t.dy; a3 = c.ig * p.BI; a4 = t.in_phase;
-                    b0 = cc * 32; b1 = t.wtap; b2 = c.nt * p.BN + (int)rank * (p.BN / 2) * (CTAS - 1); b3 = 0; b4 = 0;
-                } else if (MODE == MODE_WGRAD) {
-                    const long long q = c.chunk_begin + step;
-                    const int cx = (int)(q % p.chunks_x);
-                    const long long r = q / p.chunks_x;
-                    const int cy = (int)(r % p.chunks_y);
-                    const int ci = (int)(r / p.chunks_y);
-                    const TapEntry t = p.taps[c.tap];
-                    // coordinate 4 walks the 32-channel blocks, so one box brings all blocks of the operand
-                    a0 = 0; a1 = cx * p.BW; a2 = cy * p.BH; a3 = ci * p.BI; a4 = c.ft * 4;
-                    b0 = 0; b1 = cx * p.BW + t.dx; b2 = cy * p.BH + t.dy; b3 = t.in_phase * p.n_img + ci * p.BI; b4 = c.ct * (p.BN / 32);
-                } else {
-                    const int k0 = step * 32;
-                    a2 = a3 = a4 = b2 = b3 = b4 = 0;
-                    if (p.a_mn) { a0 = 0; a1 = k0; a4 = c.mt * 4; } else { a0 = k0; a1 = c.mt * 128; }
-                    if (p.b_mn) { b0 = 0; b1 = k0; b4 = c.nt * (p.BN / 32); } else { b0 = k0; b1 = c.nt * p.BN; }
-                }
-                for (int box = lane; box < n_boxes; box += 32) {
-                    if (box < n_a) {
-                        const int j = box / planes, lo = box - j * planes;
-                        const uint32_t dst = sbase + (lo ? off_a_lo : 0u) + j * p.a_box_bytes;
-                        if (CTAS == 2) ptx::tma_load_5d_pair(dst, lo ? &mapA_lo : &mapA_hi, fb, a0 + j * a_step0, a1, a2, a3, a4);
-                        else ptx::tma_load_5d(dst, lo ? &mapA_lo : &mapA_hi, fb, a0 + j * a_step0, a1, a2, a3, a4);
+                if (active) {
+                    const bool pad = st >= c.nsteps;      // filler block of the last stage: coordinates out of range => zeros
+                    int c0, c1, c2, c3, c4;
+                    if (MODE == MODE_CONV) {
+                        const TapEntry t = p.taps[tap_begin + (pad ? 0 : ti)];
+                        if (is_a) { c0 = cc * 32; c1 = base1 + t.dx; c2 = base2 + t.dy; c3 = pad ? p.n_img + p.BI : base3; c4 = t.in_phase; }
+                        else { c0 = cc * 32; c1 = t.wtap; c2 = bcoord; c3 = 0; c4 = 0; }
+                    } else if (MODE == MODE_WGRAD) {
+                        const TapEntry t = p.taps[c.tap];
+                        // coordinate 4 walks the 32-channel blocks, so one box brings all blocks of the operand
+                        if (is_a) { c0 = 0; c1 = cx * p.BW; c2 = cy * p.BH; c3 = pad ? (p.chunks_i + 1) * p.BI : ci * p.BI; c4 = c.ft * 4; }
+                        else { c0 = 0; c1 = cx * p.BW + t.dx; c2 = cy * p.BH + t.dy; c3 = t.in_phase * p.n_img + ci * p.BI; c4 = c.ct * (p.BN / 32); }
                     } else {
-                        const int bb = box - n_a;
-                        const int j = bb / planes, lo = bb - j * planes;
-                        const uint32_t dst = sbase + (lo ? off_b_lo : off_b_hi) + j * p.b_box_bytes;
-                        if (CTAS == 2) ptx::tma_load_5d_pair(dst, lo ? &mapB_lo : &mapB_hi, fb, b0 + j * b_step0, b1, b2, b3, b4);
-                        else ptx::tma_load_5d(dst, lo ? &mapB_lo : &mapB_hi, fb, b0 + j * b_step0, b1, b2, b3, b4);
+                        const int k0 = st * 32;           // beyond K for a filler block: zero-filled
+                        c2 = c3 = c4 = 0;
+                        if (is_a) { if (p.a_mn) { c0 = 0; c1 = k0; c4 = c.mt * 4; } else { c0 = k0; c1 = c.mt * 128; } }
+                        else { if (p.b_mn) { c0 = 0; c1 = k0; c4 = c.nt * (p.BN / 32); } else { c0 = k0; c1 = c.nt * p.BN; } }
                     }
+                    const uint32_t dst = smem0 + (uint32_t)stage * p.stage_bytes + my_off;
+                    if (CTAS == 2) ptx::tma_load_5d_pair(dst, my_map, fb, c0, c1, c2, c3, c4);
+                    else ptx::tma_load_5d(dst, my_map, fb, c0, c1, c2, c3, c4);
+                }
+              }
+                // advance this lane's K-block index by the blocks of one stage
+                st += p.ksub;
+                if (MODE == MODE_CONV) {
+                    cc += p.ksub;
+                    while (cc >= p.c_chunks) { cc -= p.c_chunks; ti++; }
+                } else if (MODE == MODE_WGRAD) {
+                    cx += p.ksub;
+                    while (cx >= p.chunks_x) { cx -= p.chunks_x; if (++cy == p.chunks_y) { cy = 0; ci++; } }
                 }
                 if (++stage == p.stages) { stage = 0; phase ^= 1u; }
             }
         }
+#ifdef B200_TC_TIMING
+        if (lane == 0 && p.dbg) p.dbg[blockIdx.x * 8 + (warp == 0 ? 0 : 6)] = dbg_pw;
+#endif
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0 && rank == 0) {
@@ -273,38 +312,58 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
             uint32_t phase = 0;
             int tile_iter = 0;
             bool ok = true;
+            const uint32_t s0 = ptx::smem_u32(smem);
+            const uint64_t a_hi0 = ptx::smem_desc(s0, p.a_lbo, p.a_sbo, p.a_layout);
+            const uint64_t a_lo0 = ptx::smem_desc(s0 + off_a_lo, p.a_lbo, p.a_sbo, p.a_layout);
+            const uint64_t b_hi0 = ptx::smem_desc(s0 + off_b_hi, p.b_lbo, p.b_sbo, p.b_layout);
+            const uint64_t b_lo0 = ptx::smem_desc(s0 + off_b_lo, p.b_lbo, p.b_sbo, p.b_layout);
+            const uint64_t stage16 = p.stage_bytes >> 4, mini16 = p.mini_bytes >> 4, ak16 = p.a_kadv >> 4, bk16 = p.b_kadv >> 4;
+            const uint32_t idesc = p.idesc;
+#ifdef B200_TC_TIMING
+            long long dbg_mw = 0, dbg_mt = 0;
+            const long long dbg_m0 = clock64();
+#endif
+            auto issue = [&](uint32_t dd, uint64_t ad, uint64_t bd, uint32_t acc_in) {
+                if (CTAS == 2) ptx::mma_tf32_pair(dd, ad, bd, idesc, acc_in); else ptx::mma_tf32(dd, ad, bd, idesc, acc_in);
+            };
             for (int tile = work_begin; ok && tile < p.num_tiles; tile += work_step, tile_iter++) {
                 const TileCtx c = CTAS == 2 ? decode_pair(p, tile, 0) : decode_tile<MODE>(p, tile);
                 const int acc = tile_iter & 1;
                 const uint32_t acc_phase = (uint32_t)(tile_iter >> 1) & 1u;
+#ifdef B200_TC_TIMING
+                const long long te0 = clock64();
+#endif
                 if (!wait_bar(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 0x200u + B200_E_TIMEOUT)) break;
+#ifdef B200_TC_TIMING
+                dbg_mt += clock64() - te0;
+#endif
                 ptx::tc_fence_after();
                 const uint32_t d = tmem_base + (uint32_t)(acc * p.acc_stride);
-                for (int step = 0; step < c.nsteps; step++) {
+                for (int step = 0; step < c.nsteps; step += p.ksub) {
+#ifdef B200_TC_TIMING
+                    const long long tf0 = clock64();
+#endif
                     if (!wait_bar(full_bar(stage), phase, abort_flag, p.status, 0x300u + B200_E_TIMEOUT)) { ok = false; break; }
+#ifdef B200_TC_TIMING
+                    dbg_mw += clock64() - tf0;
+#endif
                     ptx::tc_fence_after();
-                    const uint32_t sbase = ptx::smem_u32(smem + (size_t)stage * p.stage_bytes);
+                    // descriptors of this stage: the precomputed stage-0 descriptors plus the stage offset; only
+                    // the 14-bit address field changes (shared memory ends below 256 KB, so it cannot carry out)
+                    for (int m = 0; m < p.ksub; m++) {
+                        const uint64_t so = (uint64_t)stage * stage16 + (uint64_t)m * mini16;
+                        const uint64_t a_hi = a_hi0 + so, b_hi = b_hi0 + so;
 #pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        const uint64_t a_hi = ptx::smem_desc(sbase + k * p.a_kadv, p.a_lbo, p.a_sbo, p.a_layout);
-                        const uint64_t b_hi = ptx::smem_desc(sbase + off_b_hi + k * p.b_kadv, p.b_lbo, p.b_sbo, p.b_layout);
-                        const uint32_t first = (step > 0 || k > 0) ? 1u : 0u;
-                        if (X3) {
-                            const uint64_t a_lo = ptx::smem_desc(sbase + off_a_lo + k * p.a_kadv, p.a_lbo, p.a_sbo, p.a_layout);
-                            const uint64_t b_lo = ptx::smem_desc(sbase + off_b_lo + k * p.b_kadv, p.b_lbo, p.b_sbo, p.b_layout);
-                            if (CTAS == 2) {
-                                ptx::mma_tf32_pair(d, a_lo, b_hi, p.idesc, first);   // small terms first
-                                ptx::mma_tf32_pair(d, a_hi, b_lo, p.idesc, 1u);
-                                ptx::mma_tf32_pair(d, a_hi, b_hi, p.idesc, 1u);
+                        for (int k = 0; k < 4; k++) {
+                            const uint32_t acc_in = (step > 0 || m > 0 || k > 0) ? 1u : 0u;
+                            if (X3) {
+                                const uint64_t a_lo = a_lo0 + so, b_lo = b_lo0 + so;
+                                issue(d, a_lo + k * ak16, b_hi + k * bk16, acc_in);   // small terms first
+                                issue(d, a_hi + k * ak16, b_lo + k * bk16, 1u);
+                                issue(d, a_hi + k * ak16, b_hi + k * bk16, 1u);
                             } else {
-                                ptx::mma_tf32(d, a_lo, b_hi, p.idesc, first);
-                                ptx::mma_tf32(d, a_hi, b_lo, p.idesc, 1u);
-                                ptx::mma_tf32(d, a_hi, b_hi, p.idesc, 1u);
+                                issue(d, a_hi + k * ak16, b_hi + k * bk16, acc_in);
                             }
-                        } else if (CTAS == 2) {
-                            ptx::mma_tf32_pair(d, a_hi, b_hi, p.idesc, first);
-                        } else {
-                            ptx::mma_tf32(d, a_hi, b_hi, p.idesc, first);
                         }
                     }
                     if (CTAS == 2) ptx::mma_commit_pair(empty_bar(stage)); else ptx::mma_commit(empty_bar(stage));
@@ -312,17 +371,30 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
                 }
                 if (ok) { if (CTAS == 2) ptx::mma_commit_pair(tfull_bar(acc)); else ptx::mma_commit(tfull_bar(acc)); }
             }
+#ifdef B200_TC_TIMING
+            if (p.dbg) { p.dbg[blockIdx.x * 8 + 1] = dbg_mw; p.dbg[blockIdx.x * 8 + 2] = dbg_mt; p.dbg[blockIdx.x * 8 + 3] = clock64() - dbg_m0; }
+#endif
         }
     } else {
         // ------------------------------------------------------------------ epilogue (warps 2..5)
         const int q = warp & 3;
         const int row = q * 32 + lane;
         int tile_iter = 0;
+#ifdef B200_TC_TIMING
+        long long dbg_ew = 0;
+        const long long dbg_e0 = clock64();
+#endif
         for (int tile = work_begin; tile < p.num_tiles; tile += work_step, tile_iter++) {
             const TileCtx c = CTAS == 2 ? decode_pair(p, tile, (int)rank) : decode_tile<MODE>(p, tile);
             const int acc = tile_iter & 1;
             const uint32_t acc_phase = (uint32_t)(tile_iter >> 1) & 1u;
+#ifdef B200_TC_TIMING
+            const long long tq0 = clock64();
+#endif
             bool ok = wait_bar(tfull_bar(acc), acc_phase, abort_flag, p.status, 0x400u + B200_E_TIMEOUT);
+#ifdef B200_TC_TIMING
+            dbg_ew += clock64() - tq0;
+#endif
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             ptx::tc_fence_after();
@@ -371,6 +443,9 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
             __syncwarp();
             if (lane == 0) { if (CTAS == 2) ptx::mbar_arrive_remote(tempty_bar(acc), 0u); else ptx::mbar_arrive(tempty_bar(acc)); }
         }
+#ifdef B200_TC_TIMING
+        if (threadIdx.x == 64 && p.dbg) { p.dbg[blockIdx.x * 8 + 4] = dbg_ew; p.dbg[blockIdx.x * 8 + 5] = clock64() - dbg_e0; }
+#endif
     }
 
     if (*abort_flag) {   // give TMA copies still in flight time to land before the CTA's shared memory is released
@@ -643,6 +718,17 @@ static int profile_begin(EventPair *e, cudaStream_t s)
     return B200_OK;
 }
 
+// Debug switch: B200CONV_DEEP_STAGES=0 keeps one 32-wide K block per pipeline stage.
+static bool deep_stages_enabled()
+{
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("B200CONV_DEEP_STAGES");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
 template <int MODE, bool X3, int CTAS>
 static int launch_one(const CUtensorMap maps[4], const TcParams &p, int grid, size_t smem, cudaStream_t s)
 {
@@ -675,8 +761,11 @@ static int launch_tc(const CUtensorMap maps[4], TcParams &p, bool x3, cudaStream
         g_smem_optin = (size_t)v;
     }
     p.b_bytes = (uint32_t)p.b_boxes * p.b_box_bytes;
-    p.stage_bytes = (uint32_t)((kABytes + p.b_bytes) * (x3 ? 2 : 1));
+    p.mini_bytes = (uint32_t)((kABytes + p.b_bytes) * (x3 ? 2 : 1));
     const size_t fixed = 1024 /*alignment slack*/ + 256 /*barriers*/;
+    // two K blocks per stage halve the per-stage hand-shakes; taken when at least three such stages fit
+    p.ksub = (deep_stages_enabled() && (g_smem_optin - fixed) / (2 * (size_t)p.mini_bytes) >= 3) ? 2 : 1;
+    p.stage_bytes = p.mini_bytes * (uint32_t)p.ksub;
     int stages = (int)((g_smem_optin - fixed) / p.stage_bytes);
     if (stages > 8) stages = 8;
     if (stages < 2) return TC_UNSUPPORTED;
@@ -686,6 +775,12 @@ static int launch_tc(const CUtensorMap maps[4], TcParams &p, bool x3, cudaStream
     p.tmem_cols = cols;
     int r = status_word(&p.status);
     if (r) return r;
+#ifdef B200_TC_TIMING
+    static long long *dbg_dev = nullptr;
+    if (!dbg_dev) { cudaMalloc(&dbg_dev, 8 * 256 * sizeof(long long)); }
+    cudaMemsetAsync(dbg_dev, 0, 8 * 256 * sizeof(long long), s);
+    p.dbg = dbg_dev;
+#endif
     const size_t smem = (size_t)stages * p.stage_bytes + fixed;
     const int slots = sm_count() / ctas;
     int grid = (p.num_tiles < slots ? p.num_tiles : slots) * ctas;
@@ -704,6 +799,17 @@ static int launch_tc(const CUtensorMap maps[4], TcParams &p, bool x3, cudaStream
         B200_CUDA(cudaEventRecord(ev.b, s));
         g_pending.push_back(ev);
     }
+#ifdef B200_TC_TIMING
+    if (getenv("B200_TC_TIMING_DUMP")) {
+        static long long h[8 * 256];
+        cudaStreamSynchronize(s);
+        cudaMemcpy(h, dbg_dev, sizeof(h), cudaMemcpyDeviceToHost);
+        double sum[6] = {0, 0, 0, 0, 0, 0};
+        for (int b = 0; b < grid; b++) for (int i = 0; i < 6; i++) sum[i] += (double)h[b * 8 + i];
+        fprintf(stderr, "tc timing mode=%d ctas=%d ksub=%d stages=%d grid=%d tiles=%d: producer wait %.0f | issuer: wait data %.0f, wait tmem %.0f, total %.0f | epilogue: wait %.0f total %.0f (cycles, mean per CTA)\n",
+                MODE, ctas, p.ksub, p.stages, grid, p.num_tiles, sum[0] / grid * (ctas == 2 ? 1 : 1), sum[1] / (grid / ctas), sum[2] / (grid / ctas), sum[3] / (grid / ctas), sum[4] / grid, sum[5] / grid);
+    }
+#endif
     return B200_OK;
 }
 

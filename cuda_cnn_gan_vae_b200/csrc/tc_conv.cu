@@ -63,7 +63,7 @@ struct TcParams {
     float *out;
     const float *bias;
     // WGRAD
-    int ft_n, ct_n, taps_n, splits, chunks_x, chunks_y, chunks_i, k_rows, c_cols;
+    int ft_n, ct_n, taps_n, splits, chunks_x, chunks_y, chunks_i, k_rows, c_cols, wg_ctas;
     long long chunks_total;
     float *partial;
     // GEMM
@@ -107,7 +107,7 @@ __device__ __forceinline__ TileCtx decode_pair(const TcParams &p, int pair, int 
 }
 
 template <int MODE>
-__device__ __forceinline__ TileCtx decode_tile(const TcParams &p, int tile)
+__device__ __forceinline__ TileCtx decode_tile(const TcParams &p, int tile, int rank = 0)
 {
     TileCtx c;
     if (MODE == MODE_CONV) {
@@ -127,7 +127,7 @@ __device__ __forceinline__ TileCtx decode_tile(const TcParams &p, int tile)
         int rest = tile / p.splits;
         c.ct = rest % p.ct_n; rest /= p.ct_n;
         c.tap = rest % p.taps_n;
-        c.ft = rest / p.taps_n;
+        c.ft = (rest / p.taps_n) * p.wg_ctas + rank;     // CTA pair: the pair owns two neighbouring filter tiles
         long long b = p.chunks_total * c.split / p.splits;
         long long e = p.chunks_total * (c.split + 1) / p.splits;
         c.chunk_begin = b;
@@ -236,7 +236,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
         long long dbg_pw = 0;
 #endif
         for (int tile = work_begin; ok && tile < p.num_tiles; tile += work_step) {
-            const TileCtx c = CTAS == 2 ? decode_pair(p, tile, (int)rank) : decode_tile<MODE>(p, tile);
+            const TileCtx c = (CTAS == 2 && MODE == MODE_CONV) ? decode_pair(p, tile, (int)rank) : decode_tile<MODE>(p, tile, (int)rank);
             // running decomposition of this lane's K-block index st = step + my_m
             int st = my_m, ti = 0, cc = 0, cx = 0, cy = 0, ci = 0;
             int tap_begin = 0, base1 = 0, base2 = 0, base3 = 0, bcoord = 0;
@@ -278,7 +278,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
                         const TapEntry t = p.taps[c.tap];
                         // coordinate 4 walks the 32-channel blocks, so one box brings all blocks of the operand
                         if (is_a) { c0 = 0; c1 = cx * p.BW; c2 = cy * p.BH; c3 = pad ? (p.chunks_i + 1) * p.BI : ci * p.BI; c4 = c.ft * 4; }
-                        else { c0 = 0; c1 = cx * p.BW + t.dx; c2 = cy * p.BH + t.dy; c3 = t.in_phase * p.n_img + ci * p.BI; c4 = c.ct * (p.BN / 32); }
+                        else { c0 = 0; c1 = cx * p.BW + t.dx; c2 = cy * p.BH + t.dy; c3 = t.in_phase * p.n_img + ci * p.BI; c4 = c.ct * (p.BN / 32) + (int)rank * (p.BN / 64) * (CTAS - 1); }
                     } else {
                         const int k0 = st * 32;           // beyond K for a filler block: zero-filled
                         c2 = c3 = c4 = 0;
@@ -327,7 +327,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
                 if (CTAS == 2) ptx::mma_tf32_pair(dd, ad, bd, idesc, acc_in); else ptx::mma_tf32(dd, ad, bd, idesc, acc_in);
             };
             for (int tile = work_begin; ok && tile < p.num_tiles; tile += work_step, tile_iter++) {
-                const TileCtx c = CTAS == 2 ? decode_pair(p, tile, 0) : decode_tile<MODE>(p, tile);
+                const TileCtx c = (CTAS == 2 && MODE == MODE_CONV) ? decode_pair(p, tile, 0) : decode_tile<MODE>(p, tile, 0);
                 const int acc = tile_iter & 1;
                 const uint32_t acc_phase = (uint32_t)(tile_iter >> 1) & 1u;
 #ifdef B200_TC_TIMING
@@ -385,7 +385,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
         const long long dbg_e0 = clock64();
 #endif
         for (int tile = work_begin; tile < p.num_tiles; tile += work_step, tile_iter++) {
-            const TileCtx c = CTAS == 2 ? decode_pair(p, tile, (int)rank) : decode_tile<MODE>(p, tile);
+            const TileCtx c = (CTAS == 2 && MODE == MODE_CONV) ? decode_pair(p, tile, (int)rank) : decode_tile<MODE>(p, tile, (int)rank);
             const int acc = tile_iter & 1;
             const uint32_t acc_phase = (uint32_t)(tile_iter >> 1) & 1u;
 #ifdef B200_TC_TIMING
@@ -788,8 +788,9 @@ static int launch_tc(const CUtensorMap maps[4], TcParams &p, bool x3, cudaStream
     EventPair ev;
     if (g_profile && (r = profile_begin(&ev, s))) return r;
     if (ctas == 2) {
-        if (MODE != MODE_CONV) return fail(B200_E_ARG, "CTA-pair kernel exists for the convolution mode only");
-        r = x3 ? launch_one<MODE_CONV, true, 2>(maps, p, grid, smem, s) : launch_one<MODE_CONV, false, 2>(maps, p, grid, smem, s);
+        if (MODE == MODE_GEMM) return fail(B200_E_ARG, "no CTA-pair kernel for the plain GEMM");
+        constexpr int M2 = MODE == MODE_GEMM ? MODE_CONV : MODE;
+        r = x3 ? launch_one<M2, true, 2>(maps, p, grid, smem, s) : launch_one<M2, false, 2>(maps, p, grid, smem, s);
     } else {
         r = x3 ? launch_one<MODE, true, 1>(maps, p, grid, smem, s) : launch_one<MODE, false, 1>(maps, p, grid, smem, s);
     }
@@ -1077,16 +1078,18 @@ int wgrad_gemm(const b200_conv_geom &g, float *dkernel, int accumulate, const Ac
     memset(&p, 0, sizeof(p));
     p.BN = (int)align_up(C < 256 ? C : 256, 32);
     p.acc_stride = pow2_ceil(p.BN);
+    // CTA pairs: two neighbouring filter tiles share one 256-row MMA, each CTA stages half of the channels
+    const int ctas = (cta_pairs_enabled() && K > 128 && p.BN % 64 == 0) ? 2 : 1;
     set_mnmajor(p, true, 128);
-    set_mnmajor(p, false, p.BN);
-    p.idesc = make_idesc_tf32(p.BN, 1, 1);
-    p.ft_n = ceil_div(K, 128); p.ct_n = ceil_div(C, p.BN); p.taps_n = taps;
+    set_mnmajor(p, false, p.BN / ctas);
+    p.idesc = make_idesc_tf32(p.BN, 1, 1, 128 * ctas);
+    p.ft_n = ceil_div(K, 128); p.ct_n = ceil_div(C, p.BN); p.taps_n = taps; p.wg_ctas = ctas;
     p.k_rows = K; p.c_cols = C; p.n_img = batch;
     tile_shape(g.out_y, g.out_x, 32, &p.BW, &p.BH, &p.BI);
     p.chunks_x = ceil_div(g.out_x, p.BW); p.chunks_y = ceil_div(g.out_y, p.BH); p.chunks_i = ceil_div(batch, p.BI);
     p.chunks_total = (long long)p.chunks_x * p.chunks_y * p.chunks_i;
     p.splits = wgrad_splits(g, batch);
-    p.num_tiles = p.ft_n * p.ct_n * taps * p.splits;
+    p.num_tiles = ceil_div(p.ft_n, ctas) * p.ct_n * taps * p.splits;        // work items: tiles, or pairs of filter tiles
     p.partial = partial;
     for (int ky = 0; ky < g.kernel_y; ky++)
         for (int kx = 0; kx < g.kernel_x; kx++) {
@@ -1110,10 +1113,10 @@ int wgrad_gemm(const b200_conv_geom &g, float *dkernel, int accumulate, const Ac
         const long long dims[3] = {x.ws, x.hs, (long long)batch * sy * sx};
         const long long pitch[3] = {x.cp, (long long)x.ws * x.cp, (long long)x.hs * x.ws * x.cp};
         const int box[3] = {p.BW, p.BH, p.BI};
-        if ((r = make_blocked_map(&maps[2], x.hi, C, dims, pitch, box, p.BN / 32))) return r;
-        if (x3 && (r = make_blocked_map(&maps[3], x.lo, C, dims, pitch, box, p.BN / 32))) return r;
+        if ((r = make_blocked_map(&maps[2], x.hi, C, dims, pitch, box, p.BN / 32 / ctas))) return r;
+        if (x3 && (r = make_blocked_map(&maps[3], x.lo, C, dims, pitch, box, p.BN / 32 / ctas))) return r;
     }
-    if ((r = launch_tc<MODE_WGRAD>(maps, p, x3, s))) return r;
+    if ((r = launch_tc<MODE_WGRAD>(maps, p, x3, s, ctas))) return r;
     size_t total = (size_t)K * C * taps;
     int grid = (int)((total + 255) / 256);
     if (grid > sm_count() * 16) grid = sm_count() * 16;

@@ -24,6 +24,24 @@ static inline bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 struct OpAdd { float ls, rs; __device__ float operator()(float l, float r) const { return __fadd_rn(__fmul_rn(ls, l), __fmul_rn(rs, r)); } };
 struct OpSub { float ls, rs; __device__ float operator()(float l, float r) const { return __fsub_rn(__fmul_rn(ls, l), __fmul_rn(rs, r)); } };
 struct OpMul { __device__ float operator()(float l, float r) const { return __fmul_rn(l, r); } };
+struct OpDiv { float ls, rs; __device__ float operator()(float l, float r) const { return __fdiv_rn(__fmul_rn(l, ls), __fmul_rn(r, rs)); } };
+
+// out[p] (cols x rows) = in[p]^T (rows x cols) for every (w,z) plane p; 32x32 shared-memory tiles
+__global__ void transpose_kernel(float *__restrict__ out, const float *__restrict__ in, int rows, int cols)
+{
+    __shared__ float tile[32][33];
+    const size_t plane = (size_t)blockIdx.z * rows * cols;
+    const int x0 = blockIdx.x * 32, y0 = blockIdx.y * 32;
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        int y = y0 + i, x = x0 + threadIdx.x;
+        tile[i][threadIdx.x] = (y < rows && x < cols) ? in[plane + (size_t)y * cols + x] : 0.f;
+    }
+    __syncthreads();
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        int x = x0 + i, y = y0 + threadIdx.x;
+        if (x < cols && y < rows) out[plane + (size_t)x * rows + y] = tile[threadIdx.x][i];
+    }
+}
 
 template <class F, bool VEC>
 __global__ void binary_kernel(float *__restrict__ out, int out_w, const float *left, int left_w,
@@ -68,7 +86,10 @@ __device__ __forceinline__ float unary_apply(float v, int op, float a, float b)
     case 0: return __fmul_rn(__fmul_rn(v, v), a);
     case 1: return __fmul_rn(__fsqrt_rn(__fadd_rn(v, b)), a);
     case 2: return __fdiv_rn(1.0f, v);
-    default: return __fmul_rn(v, a);
+    case 3: return __fmul_rn(v, a);
+    case 4: return __fadd_rn(__fmul_rn(v, a), b);
+    case 5: return v > b ? b : (v < a ? a : v);
+    default: return v > 0.f ? 1.f : (v < 0.f ? -1.f : v);
     }
 }
 
@@ -491,6 +512,23 @@ int b200_add(float *out, int out_w, const float *left, int left_w, const float *
     return launch_binary(out, out_w, left, left_w, right, right_w, n, OpAdd{ls, rs}, ST(stream));
 }
 
+int b200_div(float *out, int out_w, const float *left, int left_w, const float *right, int right_w,
+             size_t n, float ls, float rs, void *stream)
+{
+    return launch_binary(out, out_w, left, left_w, right, right_w, n, OpDiv{ls, rs}, ST(stream));
+}
+
+int b200_transpose(float *out, const float *in, int planes, int rows, int cols, void *stream)
+{
+    if (!out || !in) return fail(B200_E_ARG, "null tensor pointer");
+    if (planes <= 0 || rows <= 0 || cols <= 0) return fail(B200_E_SHAPE, "non-positive matrix size");
+    if (planes > 65535) return fail(B200_E_SHAPE, "too many planes for one transpose call");
+    dim3 grid((cols + 31) / 32, (rows + 31) / 32, planes), block(32, 8);
+    transpose_kernel<<<grid, block, 0, ST(stream)>>>(out, in, rows, cols);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
 int b200_item_product(float *out, int out_w, const float *left, int left_w, const float *right, int right_w,
                       size_t n, void *stream)
 {
@@ -549,7 +587,7 @@ int b200_summ_xy(float *out, int out_w, const float *in, int in_w, int z, size_t
 int b200_unary(float *out, int out_w, const float *in, int in_w, size_t n, int op, float a, float b, void *stream)
 {
     if (!out || !in) return fail(B200_E_ARG, "null tensor pointer");
-    if (out_w <= 0 || in_w <= 0 || op < 0 || op > 3) return fail(B200_E_ARG, "bad unary arguments");
+    if (out_w <= 0 || in_w <= 0 || op < 0 || op > 6) return fail(B200_E_ARG, "bad unary arguments");
     if (!n) return B200_OK;
     unary_kernel<<<stream_grid(n * out_w, 256), 256, 0, ST(stream)>>>(out, out_w, in, in_w, n, op, a, b);
     B200_LAUNCH_CHECK();

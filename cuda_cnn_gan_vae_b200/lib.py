@@ -44,6 +44,8 @@ SIGNATURES = {
     "b200_add_bias": (_i, [_fp, _i, _i, _sz, _fp, _i, _vp]),
     "b200_summ_xy": (_i, [_fp, _i, _fp, _i, _i, _sz, _vp]),
     "b200_unary": (_i, [_fp, _i, _fp, _i, _sz, _i, _f, _f, _vp]),
+    "b200_div": (_i, [_fp, _i, _fp, _i, _fp, _i, _sz, _f, _f, _vp]),
+    "b200_transpose": (_i, [_fp, _fp, _i, _i, _i, _vp]),
     "b200_item_product": (_i, [_fp, _i, _fp, _i, _fp, _i, _sz, _vp]),
     "b200_fill": (_i, [_fp, _sz, _f, _vp]),
     "b200_activation": (_i, [_fp, _fp, _sz, _i, _i, _d, _vp]),

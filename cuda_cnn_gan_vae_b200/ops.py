@@ -234,6 +234,35 @@ class CTensorMath:
         CTensorMath._unary(2, output, inp, 0.0, 0.0)
 
     @staticmethod
+    def Set(output, inp, scale=1.0, add_value=0.0):
+        """output = input*scale + add_value (cuda/ctensormath.cu.h: Set, AddValue, SubValue)."""
+        CTensorMath._unary(4, output, inp, scale, add_value)
+
+    @staticmethod
+    def Clip(tensor, min_value, max_value):
+        CTensorMath._unary(5, tensor, tensor, min_value, max_value)
+
+    @staticmethod
+    def Signum(tensor):
+        CTensorMath._unary(6, tensor, tensor, 0.0, 0.0)
+
+    @staticmethod
+    def Div(output, left, right, left_scale=1.0, right_scale=1.0):
+        """output = (left*left_scale) / (right*right_scale), W broadcast per operand."""
+        _t(output), _t(left), _t(right)
+        _same_zyx(output, left, right)
+        _check(load().b200_div(_ptr(output), output.shape[0], _ptr(left), left.shape[0], _ptr(right), right.shape[0],
+                               _n(output), left_scale, right_scale, _stream()))
+
+    @staticmethod
+    def Transponse(output, inp):
+        """Every (w,z) plane transposed: output is [W,Z,X,Y] for an input [W,Z,Y,X]."""
+        _t(output), _t(inp)
+        if output.shape[0] != inp.shape[0] or output.shape[1] != inp.shape[1] or output.shape[2] != inp.shape[3] or output.shape[3] != inp.shape[2]:
+            raise B200Error("CTensorMath::Transponse: tensor sizes do not match!")
+        _check(load().b200_transpose(_ptr(output), _ptr(inp), inp.shape[0] * inp.shape[1], inp.shape[2], inp.shape[3], _stream()))
+
+    @staticmethod
     def TensorItemProduction(output, left, right):
         _t(output), _t(left), _t(right)
         _same_zyx(output, left, right)

@@ -195,8 +195,14 @@ int b200_add_bias(float *t, int t_w, int z, size_t yx, const float *bias, int bi
 /* CTensorMath::SummXY (cuda :1396, cpu :455): out[w,z] = sum_{y,x} in[w%Iw,z,:,:]. */
 int b200_summ_xy(float *out, int out_w, const float *in, int in_w, int z, size_t yx, void *stream);
 /* CTensorMath::Pow2 (op 0: i*i*a), SQRT (op 1: sqrt(i+b)*a), Inv (op 2: 1/i), Mul by scalar (op 3: i*a)
- * (cuda :1196,1262,702,2291; cpu :387,421,163,721), input W-broadcast. */
+ * (cuda :1196,1262,702,2291; cpu :387,421,163,721); AddValue / SubValue / Set (op 4: i*a+b; cuda :986,1061,1127),
+ * Clip (op 5: min(max(i,a),b); cuda :2807), Signum (op 6; cuda :2865); input W-broadcast. */
 int b200_unary(float *out, int out_w, const float *in, int in_w, size_t n, int op, float a, float b, void *stream);
+/* CTensorMath::Div (cuda :738-800, cpu :197): out[w] = (ls*left[w%Lw]) / (rs*right[w%Rw]). */
+int b200_div(float *out, int out_w, const float *left, int left_w, const float *right, int right_w,
+             size_t n, float ls, float rs, void *stream);
+/* CTensorMath::Transponse (cuda :2345-2390, cpu :787): every (w,z) plane rows x cols -> cols x rows. */
+int b200_transpose(float *out, const float *in, int planes, int rows, int cols, void *stream);
 /* CTensorMath::TensorItemProduction (cuda :2425, cpu :822). */
 int b200_item_product(float *out, int out_w, const float *left, int left_w, const float *right, int right_w,
                       size_t n, void *stream);

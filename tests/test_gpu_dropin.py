@@ -1,0 +1,77 @@
+"""The C++ drop-in on the GPU: the reference's own programs compiled against this package's headers.
+
+oracle/_ref/dropin/ holds (built by cuda_cnn_gan_vae_b200/host/build_dropin.py where the reference tree exists)
+  dropin_kat         the reference's known-answer suite cuda/ctensortest.cu.h, unmodified, over host/cuda/*.cu.h
+  dropin_layers      the reference's unmodified layer classes (convolution input, convolution, function, linear)
+                     running forward / backward / Adam / forward through libb200conv.so
+  dump_cpu.txt       the same program built with -DUSE_CPU against the reference's CPU backend (the expectation)
+"""
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from util import TOL_X3, TOL_TF32
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DROPIN = os.path.join(ROOT, "oracle", "_ref", "dropin")
+
+pytestmark = pytest.mark.gpu
+
+
+def _need(name):
+    path = os.path.join(DROPIN, name)
+    if not os.path.exists(path):
+        pytest.skip("drop-in artefact not built: " + name)
+    return path
+
+
+def _read_dump(path):
+    tensors = {}
+    with open(path) as f:
+        lines = f.read().split("\n")
+    i = 0
+    while i < len(lines):
+        if lines[i].startswith("tensor "):
+            _, name, count = lines[i].split()
+            count = int(count)
+            tensors[name] = np.array([float(v) for v in lines[i + 1:i + 1 + count]], dtype=np.float64)
+            i += 1 + count
+        else:
+            i += 1
+    return tensors
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_reference_known_answer_suite_over_the_c_abi(mode):
+    """cuda/ctensortest.cu.h:CTensorTest<float>::Test() passes in every precision mode (its inputs are small integers)."""
+    exe = _need("dropin_kat")
+    r = subprocess.run([exe, str(mode)], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+    assert "PASS" in r.stdout
+
+
+@pytest.mark.parametrize("mode,tol", [(0, TOL_X3), (1, TOL_TF32), (2, 1e-5)])
+def test_reference_layers_match_the_cpu_backend(tmp_path, mode, tol):
+    """Forward, backward, Adam step and second forward of the reference's own layer classes agree with its CPU backend."""
+    exe = _need("dropin_layers")
+    want = _read_dump(_need("dump_cpu.txt"))
+    out = str(tmp_path / "dump_gpu.txt")
+    r = subprocess.run([exe, "run", _need("w0.net"), out, str(mode)], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+    got = _read_dump(out)
+    assert set(got) == set(want)
+    for name in ("output_1", "conv1_output", "conv2_output", "linear_delta", "conv2_delta", "conv1_delta", "output_2"):
+        assert got[name].shape == want[name].shape, name
+        scale = np.sqrt(np.mean(want[name] ** 2)) + 1e-30
+        diff = np.abs(got[name] - want[name])
+        if name == "conv1_delta":
+            # this delta has passed the derivative of LeakyReLU, a step from 0.1 to 1 at zero: where the
+            # layer's output lies within the rounding error of zero either side of the step is right
+            out = want["conv1_output"]
+            diff = diff[np.abs(out) > 16 * tol * np.sqrt(np.mean(out ** 2))]
+            assert diff.size > 0.9 * out.size
+        err = np.max(diff) / scale
+        # deltas pass through up to three contractions of TF32 operands: allow their errors to add up
+        assert err <= 4 * tol, (name, err)

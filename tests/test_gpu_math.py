@@ -259,6 +259,32 @@ def test_adam(ops, port):
     assert np.allclose(M.cpu().numpy(), mo, rtol=1e-6, atol=1e-8) and np.allclose(V.cpu().numpy(), vo, rtol=1e-6, atol=1e-9)
 
 
+def test_set_clip_signum_div_transpose_bit_exact(ops):
+    """Element-wise operations without an oracle entry: single IEEE operations, so numpy float32 is the expectation."""
+    rng = np.random.default_rng(11)
+    a = rng.standard_normal((3, 2, 37, 45)).astype(np.float32)
+    b = (rng.standard_normal((1, 2, 37, 45)).astype(np.float32) + np.float32(3.0))
+    A, B = dev(a), dev(b)
+    out = torch.empty_like(A)
+    ops.CTensorMath.Set(out, A, 1.5, -0.25)
+    assert np.array_equal(out.cpu().numpy(), a * np.float32(1.5) + np.float32(-0.25))
+    ops.CTensorMath.Div(out, A, B, 2.0, 0.5)
+    assert np.array_equal(out.cpu().numpy(), (a * np.float32(2.0)) / (b * np.float32(0.5)))
+    c = A.clone()
+    ops.CTensorMath.Clip(c, -0.5, 0.75)
+    assert np.array_equal(c.cpu().numpy(), np.clip(a, np.float32(-0.5), np.float32(0.75)))
+    c = A.clone()
+    c[0, 0, 0, 0] = 0.0
+    ops.CTensorMath.Signum(c)
+    want = np.sign(a)
+    want[0, 0, 0, 0] = 0.0
+    assert np.array_equal(c.cpu().numpy(), want)
+    t = torch.empty(3, 2, 45, 37, device="cuda")
+    ops.CTensorMath.Transponse(t, A)
+    assert np.array_equal(t.cpu().numpy(), a.transpose(0, 1, 3, 2))
+    ops.stream_status()
+
+
 def test_shape_errors_raise(ops):
     a = torch.zeros(2, 3, 4, 4, device="cuda")
     with pytest.raises(ops.B200Error):

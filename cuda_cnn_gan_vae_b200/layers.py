@@ -1,0 +1,274 @@
+"""Host-side mirrors of the reference's layer classes on torch CUDA tensors, each a thin sequence of calls into
+libb200conv.so.  A layer keeps the reference's tensors (output H, delta, weights, weight gradients) and its
+three training entry points:
+
+    Forward()                          netlayer/*.cu.h  Forward
+    TrainingBackward(create_dw)        netlayer/*.cu.h  SetOutputError + TrainingBackward
+    TrainingResetDeltaWeight / TrainingUpdateWeight are done for the whole net at once on the arenas (Net).
+
+Tensors are [W=batch, Z, Y, X] fp32 like CTensor.  Weights, gradients and the two Adam moments of all layers of a
+net live in four contiguous arenas (weights / gradients / m / v) with identical offsets: the gradient arena is what
+a data-parallel step all-reduces, and one b200_adam call updates every parameter of the net.
+"""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import ops
+from .dp import GradArena
+from .lib import load
+from .ops import ACT, _check, _ptr, _stream
+
+
+class _Layer:
+    """Common part: shapes, parameter declaration, binding of arena views."""
+    params = ()                     # names of this layer's parameter tensors
+
+    def param_shapes(self):
+        return {}
+
+    def bind(self, weights, grads):
+        self.w, self.g = weights, grads
+
+    def init(self, rng):
+        pass
+
+    def host_params(self):
+        return {k: v.detach().cpu().numpy() for k, v in self.w.items()}
+
+
+class NetLayerConvolution(_Layer):
+    """netlayer/cnetlayerconvolution.cu.h: Forward :310 (ForwardConvolution with bias), TrainingBackward :484
+    (BackwardConvolution with a zero bias, per-sample CreateDeltaWeightAndBias reduced over W into dKernel/dBias)."""
+    transposed = False
+
+    def __init__(self, in_shape, batch, kernel_amount, kernel_size, stride, padding):
+        z, y, x = in_shape
+        self.in_shape, self.batch = tuple(in_shape), batch
+        self.K, self.k, self.s, self.p = kernel_amount, kernel_size, stride, padding
+        if self.transposed:
+            oy, ox = (y - 1) * stride - 2 * padding + kernel_size, (x - 1) * stride - 2 * padding + kernel_size
+            # the layer's kernel tensor is that of the convolution it transposes: [in_z filters][out_z*k*k]
+            self.ctx = ops.ConvLayer(kernel_amount, oy, ox, z, kernel_size, kernel_size, stride, stride, padding, padding, batch,
+                                     transposed=True)
+            self.kernel_shape, self.bias_shape = (1, 1, z, kernel_amount * kernel_size * kernel_size), (1, z, 1, 1)
+        else:
+            oy, ox = (y - kernel_size + 2 * padding) // stride + 1, (x - kernel_size + 2 * padding) // stride + 1
+            self.ctx = ops.ConvLayer(z, y, x, kernel_amount, kernel_size, kernel_size, stride, stride, padding, padding, batch)
+            self.kernel_shape, self.bias_shape = (1, 1, kernel_amount, z * kernel_size * kernel_size), (1, kernel_amount, 1, 1)
+        self.out_shape = (kernel_amount, oy, ox)
+        self.H = torch.empty((batch,) + self.out_shape, device="cuda")
+        self.prev_error = torch.empty((batch,) + self.in_shape, device="cuda")
+
+    def param_shapes(self):
+        return {"kernel": self.kernel_shape, "bias": self.bias_shape}
+
+    def init(self, rng):
+        # He-normal on the fan-in of one output element, zero bias
+        fan_in = self.kernel_shape[3] if not self.transposed else self.in_shape[0] * self.k * self.k
+        self.w["kernel"].copy_(torch.from_numpy((rng.standard_normal(self.kernel_shape) * np.sqrt(2.0 / fan_in)).astype(np.float32)))
+        self.w["bias"].zero_()
+
+    def Forward(self, x):
+        self.x = x
+        self.ctx.forward(self.H, x, self.w["kernel"], None if self.transposed else self.w["bias"])
+        return self.H
+
+    def TrainingBackward(self, delta, create_delta_weight=True, need_prev=True):
+        self.ctx.backward(self.prev_error if need_prev else None,
+                          self.g["kernel"] if create_delta_weight else None,
+                          self.g["bias"] if create_delta_weight else None,
+                          delta, self.x, self.w["kernel"], accumulate=True)
+        return self.prev_error if need_prev else None
+
+
+class NetLayerBackConvolution(NetLayerConvolution):
+    """netlayer/cnetlayerbackconvolution.cu.h: Forward :303 is BackwardConvolution of the layer input, TrainingBackward
+    :475 is ForwardConvolution of the delta plus CreateBackDeltaWeightAndBias (which clears the bias gradient)."""
+    transposed = True
+
+
+class NetLayerLinear(_Layer):
+    """netlayer/cnetlayerlinear.cu.h: Forward :262 (H = W*x + B per sample), TrainingBackward :415 (prev error =
+    W^T*delta; dW += sum over samples of delta*x^T; dB += sum of delta).  The three products are one GEMM each over the
+    whole batch; the reference's [batch, out, in] scratch of per-sample outer products is not materialised."""
+
+    def __init__(self, in_shape, batch, neurons):
+        self.in_shape, self.batch, self.neurons = tuple(in_shape), batch, neurons
+        self.n_in = int(np.prod(in_shape))
+        self.out_shape = (1, neurons, 1)
+        self.H = torch.empty((batch, 1, neurons, 1), device="cuda")
+        self.prev_error = torch.empty((batch,) + self.in_shape, device="cuda")
+        self.tmp_dw = torch.empty((1, 1, neurons, self.n_in), device="cuda")
+
+    def param_shapes(self):
+        return {"w": (1, 1, self.neurons, self.n_in), "b": (1, 1, self.neurons, 1)}
+
+    def init(self, rng):
+        self.w["w"].copy_(torch.from_numpy((rng.standard_normal((1, 1, self.neurons, self.n_in)) * np.sqrt(2.0 / self.n_in)).astype(np.float32)))
+        self.w["b"].zero_()
+
+    def Forward(self, x):
+        self.x = x
+        ops.CTensorMath.Mul(self.H, self.w["w"], x.view(self.batch, 1, self.n_in, 1))
+        ops.CTensorMath.Add(self.H, self.H, self.w["b"])
+        return self.H
+
+    def TrainingBackward(self, delta, create_delta_weight=True, need_prev=True):
+        delta = delta.view(self.batch, 1, self.neurons, 1)
+        if need_prev:
+            ops.CTensorMath.TransponseMul(self.prev_error.view(self.batch, 1, self.n_in, 1), self.w["w"], delta)
+        if create_delta_weight:
+            # sum_b delta_b * x_b^T = D^T * X with D = [batch, out] and X = [batch, in] as stored
+            ops.CTensorMath.TransponseMul(self.tmp_dw, delta.view(1, 1, self.batch, self.neurons), self.x.view(1, 1, self.batch, self.n_in))
+            ops.CTensorMath.Add(self.g["w"], self.g["w"], self.tmp_dw)
+            ops.CTensorMath.AddSumW(self.g["b"], self.g["b"], delta)
+        return self.prev_error if need_prev else None
+
+
+class NetLayerFunction(_Layer):
+    """netlayer/cnetlayerfunction.cu.h: Forward applies the neuron function; SetOutputError :347-358 forms
+    delta = f'(layer input) * error, which TrainingBackward hands to the previous layer."""
+
+    def __init__(self, in_shape, batch, func, leaky_slope=0.1):
+        self.in_shape = self.out_shape = tuple(in_shape)
+        self.batch, self.func, self.slope = batch, func, leaky_slope
+        self.H = torch.empty((batch,) + self.in_shape, device="cuda")
+        self.delta = torch.empty((batch,) + self.in_shape, device="cuda")
+
+    def Forward(self, x):
+        self.x = x
+        ops.CTensorApplyFunc.Apply(self.H, x, self.func, self.slope)
+        return self.H
+
+    def TrainingBackward(self, error, create_delta_weight=True, need_prev=True):
+        ops.CTensorApplyFunc.Backward(self.delta, self.x, error, self.func, self.slope)
+        return self.delta
+
+
+class NetLayerBatchNormalization(_Layer):
+    """netlayer/cnetlayerbatchnormalization.cu.h: Forward (training) :301-379 and TrainingBackward :578-604, statistics per
+    (z,y,x) element over the batch; one fused kernel each instead of about a dozen element-wise launches."""
+
+    def __init__(self, in_shape, batch, momentum=0.9, eps=1e-6):
+        self.in_shape = self.out_shape = tuple(in_shape)
+        self.batch, self.momentum, self.eps = batch, momentum, eps
+        self.n = int(np.prod(in_shape))
+        full, stat = (batch,) + self.in_shape, (1,) + self.in_shape
+        self.H, self.xhat, self.prev_error = (torch.empty(full, device="cuda") for _ in range(3))
+        self.ivar, self.mean, self.var = (torch.empty(stat, device="cuda") for _ in range(3))
+        self.new_mean, self.new_var = torch.zeros(stat, device="cuda"), torch.ones(stat, device="cuda")
+
+    def param_shapes(self):
+        return {"gamma": (1,) + self.in_shape, "beta": (1,) + self.in_shape}
+
+    def init(self, rng):
+        self.w["gamma"].fill_(1.0)
+        self.w["beta"].zero_()
+
+    def Forward(self, x):
+        _check(load().b200_bn_forward(_ptr(self.H), _ptr(self.xhat), _ptr(self.ivar), _ptr(self.mean), _ptr(self.var),
+                                      _ptr(self.new_mean), _ptr(self.new_var), _ptr(x), _ptr(self.w["gamma"]), _ptr(self.w["beta"]),
+                                      self.batch, self.n, self.momentum, self.eps, _stream()))
+        return self.H
+
+    def TrainingBackward(self, delta, create_delta_weight=True, need_prev=True):
+        _check(load().b200_bn_backward(_ptr(self.prev_error), _ptr(self.g["gamma"]), _ptr(self.g["beta"]), _ptr(delta), _ptr(self.xhat),
+                                       _ptr(self.ivar), _ptr(self.w["gamma"]), self.batch, self.n, int(create_delta_weight), _stream()))
+        return self.prev_error
+
+
+class NetLayerMaxPooling(_Layer):
+    """netlayer/cnetlayermaxpooling.cu.h: Forward :246 (window maximum and its absolute position), TrainingBackward :367."""
+
+    def __init__(self, in_shape, batch, pooling):
+        z, y, x = in_shape
+        self.in_shape, self.out_shape, self.batch, self.pool = tuple(in_shape), (z, y // pooling, x // pooling), batch, pooling
+        self.H = torch.empty((batch,) + self.out_shape, device="cuda")
+        self.P = torch.empty((batch,) + self.out_shape + (2,), dtype=torch.int32, device="cuda")     # SPos {X, Y}
+        self.prev_error = torch.empty((batch,) + self.in_shape, device="cuda")
+
+    def Forward(self, x):
+        ops.CTensorMath.MaxPooling(self.H, self.P, x, self.pool, self.pool)
+        return self.H
+
+    def TrainingBackward(self, delta, create_delta_weight=True, need_prev=True):
+        ops.CTensorMath.MaxPoolingBackward(self.prev_error, self.P, delta, self.pool, self.pool)
+        return self.prev_error
+
+
+class NetLayerUpSampling(_Layer):
+    """netlayer/cnetlayerupsampling.cu.h: Forward :249 (nearest-neighbour replication), TrainingBackward :366 (DownSampling)."""
+
+    def __init__(self, in_shape, batch, factor):
+        z, y, x = in_shape
+        self.in_shape, self.out_shape, self.batch, self.f = tuple(in_shape), (z, y * factor, x * factor), batch, factor
+        self.H = torch.empty((batch,) + self.out_shape, device="cuda")
+        self.prev_error = torch.empty((batch,) + self.in_shape, device="cuda")
+
+    def Forward(self, x):
+        ops.CTensorMath.UpSampling(self.H, x, self.f, self.f)
+        return self.H
+
+    def TrainingBackward(self, delta, create_delta_weight=True, need_prev=True):
+        ops.CTensorMath.DownSampling(self.prev_error, delta, self.f, self.f)
+        return self.prev_error
+
+
+class Net:
+    """A chain of layers with the reference's training protocol (model/cmodelmain.cu.h drives every net the same way:
+    TrainingResetDeltaWeight, Forward of all layers, SetOutputError on the last, TrainingBackward in reverse order,
+    TrainingUpdateWeight) on four arenas: weights, gradients, Adam m and v."""
+
+    def __init__(self, in_shape, batch, spec, seed=0):
+        """spec: list of (class, kwargs).  The input of layer i is the output of layer i-1."""
+        self.batch, self.in_shape = batch, tuple(in_shape)
+        self.layers, shape = [], tuple(in_shape)
+        for cls, kw in spec:
+            if cls == "reshape":             # ReinterpretSize of the previous output (cuda/ctensor.cu.h): no data moves
+                shape = tuple(kw)
+                continue
+            layer = cls(shape, batch, **kw)
+            self.layers.append(layer)
+            shape = layer.out_shape
+        self.out_shape = shape
+        shapes = {}
+        for i, layer in enumerate(self.layers):
+            for name, s in layer.param_shapes().items():
+                shapes["%d.%s" % (i, name)] = s
+        self.weights, self.grads, self.m, self.v = (GradArena(shapes, "cuda") for _ in range(4))
+        rng = np.random.default_rng(seed)
+        for i, layer in enumerate(self.layers):
+            names = list(layer.param_shapes())
+            layer.bind({n: self.weights.views["%d.%s" % (i, n)] for n in names}, {n: self.grads.views["%d.%s" % (i, n)] for n in names})
+            layer.init(rng)
+
+    @property
+    def parameter_count(self):
+        return self.weights.buffer.numel()
+
+    def TrainingResetDeltaWeight(self):
+        ops.CTensorMath.Fill(self.grads.buffer.view(1, 1, 1, -1), 0.0)
+
+    def Forward(self, x):
+        for layer in self.layers:
+            x = layer.Forward(x.view((self.batch,) + layer.in_shape))
+        return x
+
+    def TrainingBackward(self, error, create_delta_weight=True, need_input_error=False):
+        for i in range(len(self.layers) - 1, -1, -1):
+            layer = self.layers[i]
+            error = layer.TrainingBackward(error.view((self.batch,) + layer.out_shape), create_delta_weight, need_prev=(i > 0 or need_input_error))
+        return error
+
+    def TrainingUpdateWeight(self, speed, iteration, batch_scale=1, beta1=0.9, beta2=0.999, epsilon=1e-8):
+        """CTensorMath::Adam over every parameter of the net in one launch; batch_size = batch*batch_scale divides the
+        summed gradient (netlayer/cnetlayerconvolution.cu.h:533-552)."""
+        w, g, m, v = (a.buffer.view(1, 1, 1, -1) for a in (self.weights, self.grads, self.m, self.v))
+        ops.CTensorMath.Adam(w, g, m, v, int(self.batch * batch_scale), speed, beta1, beta2, epsilon, iteration)
+
+    def broadcast_weights(self):
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            dist.broadcast(self.weights.buffer, src=0)

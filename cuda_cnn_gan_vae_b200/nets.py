@@ -1,0 +1,66 @@
+"""The networks of the benchmark configurations, assembled from the layer mirrors (layers.py) the way the reference's
+models assemble its layer classes (model/cmodel_basicgan.cu.h:CreateGenerator/CreateDiscriminator build the same
+chains from CNetLayerLinear, CNetLayerBackConvolution / CNetLayerConvolution, CNetLayerBatchNormalization and
+CNetLayerFunction)."""
+import torch
+
+from . import ops
+from .layers import (Net, NetLayerBackConvolution, NetLayerBatchNormalization, NetLayerConvolution, NetLayerFunction,
+                     NetLayerLinear)
+
+
+def dcgan_generator(batch, noise=100, base=512, widths=(256, 128, 64, 3), leaky_slope=0.2, seed=2):
+    """z[noise] -> Linear to base x 4 x 4 -> 4x4 stride-2 transposed convolutions to widths[-1] x 64 x 64; batch
+    normalisation and LeakyReLU after every stage but the last, tanh at the output."""
+    spec = [(NetLayerLinear, dict(neurons=base * 16)), ("reshape", (base, 4, 4))]
+    for i, width in enumerate(widths):
+        spec.append((NetLayerBackConvolution, dict(kernel_amount=width, kernel_size=4, stride=2, padding=1)))
+        if i + 1 < len(widths):
+            spec.append((NetLayerBatchNormalization, {}))
+            spec.append((NetLayerFunction, dict(func="leaky_relu", leaky_slope=leaky_slope)))
+    spec.append((NetLayerFunction, dict(func="tanh")))
+    return Net((1, noise, 1), batch, spec, seed=seed)
+
+
+def dcgan_discriminator(batch, image=(3, 64, 64), widths=(64, 128, 256, 512), leaky_slope=0.2, seed=3):
+    """image -> 4x4 stride-2 convolutions with batch normalisation and LeakyReLU -> Linear to one logit -> sigmoid."""
+    spec = []
+    for width in widths:
+        spec.append((NetLayerConvolution, dict(kernel_amount=width, kernel_size=4, stride=2, padding=1)))
+        spec.append((NetLayerBatchNormalization, {}))
+        spec.append((NetLayerFunction, dict(func="leaky_relu", leaky_slope=leaky_slope)))
+    spec.append((NetLayerLinear, dict(neurons=1)))
+    spec.append((NetLayerFunction, dict(func="sigmoid")))
+    return Net(image, batch, spec, seed=seed)
+
+
+class DCGANStep:
+    """One combined training step of the two networks on a rank's shard of the mini-batch: generator forward, discriminator
+    forward on the generated images, the discriminator's backward pass with its weight gradients and the error at its
+    input, the generator's backward pass with its weight gradients, one all-reduce per gradient arena and one Adam
+    launch per net.  The error at the discriminator's output is output - label (the gradient of binary cross-entropy with
+    respect to the logit, formed as in model/cmodel_basicgan.cu.h:352-376 but on the device)."""
+
+    def __init__(self, batch, world=1, widths_g=(256, 128, 64, 3), widths_d=(64, 128, 256, 512), base=512, noise=100, leaky_slope=0.2):
+        self.batch, self.world = batch, world
+        self.G = dcgan_generator(batch, noise, base, widths_g, leaky_slope)
+        self.D = dcgan_discriminator(batch, self.G.out_shape, widths_d, leaky_slope)
+        self.G.broadcast_weights()
+        self.D.broadcast_weights()
+        self.error = torch.empty((batch, 1, 1, 1), device="cuda")
+        self.iteration = 0
+
+    def __call__(self, z, labels, speed=2e-4):
+        self.iteration += 1
+        self.G.TrainingResetDeltaWeight()
+        self.D.TrainingResetDeltaWeight()
+        fake = self.G.Forward(z)
+        out = self.D.Forward(fake)
+        ops.CTensorMath.Sub(self.error, out, labels)
+        d_image = self.D.TrainingBackward(self.error, True, need_input_error=True)
+        self.G.TrainingBackward(d_image, True)
+        self.D.grads.all_reduce()
+        self.G.grads.all_reduce()
+        self.D.TrainingUpdateWeight(speed, self.iteration, batch_scale=self.world)
+        self.G.TrainingUpdateWeight(speed, self.iteration, batch_scale=self.world)
+        return out

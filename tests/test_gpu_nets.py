@@ -1,0 +1,148 @@
+"""The layer chains of the DCGAN configurations (generator: Linear + transposed convolutions, discriminator:
+convolutions + Linear, both with batch normalisation and activations) on the GPU against the CPU twin built from the
+oracle's tensor routines (tests/net_oracle.py), layer by layer: outputs, errors handed down, weight gradients, and the
+Adam update of the whole parameter arena."""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from tests.net_oracle import OracleNet  # noqa: E402
+from tests.util import TOL_X3  # noqa: E402
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from cuda_cnn_gan_vae_b200 import ops as o
+    assert torch.cuda.is_available()
+    yield o
+    o.set_precision(o.TF32X3)
+
+
+def check(name, got, want, tol, strict, mag=None):
+    """mag: the same sum over absolute values, the scale of the error when the sum itself cancels.  strict: every
+    element within tol of the RMS-scaled expectation.  Otherwise (batch normalisation over a handful of samples can
+    turn a 1e-6 difference into a large one at isolated elements of small variance): RMS error within tol and at most
+    0.01 % of elements beyond 10 tol."""
+    got, want = np.asarray(got, np.float64).ravel(), np.asarray(want, np.float64).ravel()
+    assert got.shape == want.shape, name
+    assert np.isfinite(got).all(), name
+    scale = np.sqrt(np.mean(want ** 2)) + 1e-30
+    if mag is not None:
+        scale = max(scale, np.sqrt(np.mean(np.asarray(mag, np.float64) ** 2)))
+    err = np.abs(got - want) / scale
+    if strict:
+        assert err.max() <= tol, (name, err.max())
+    else:
+        assert np.sqrt(np.mean(err ** 2)) <= tol, (name, np.sqrt(np.mean(err ** 2)))
+        assert np.mean(err > 10 * tol) <= 1e-4, (name, np.mean(err > 10 * tol), err.max())
+
+
+def run_and_compare(ops, port, net, x, error, tol, strict, need_input_error=False):
+    """Every layer of the chain is compared on the operands the GPU chain actually fed it (its input on the way up, the
+    error from above on the way down), so each comparison is one layer operation against the oracle's, and a LeakyReLU
+    input that rounding puts on the other side of zero cannot carry a step of the derivative into the layers below.
+    The free-running twin is compared at the net's output (the forward pass is continuous)."""
+    twin = OracleNet(port, net)
+    B = x.shape[0]
+    net.TrainingResetDeltaWeight()
+    inputs, cur = [], torch.from_numpy(x).cuda()
+    for layer in net.layers:
+        cur = cur.view((B,) + layer.in_shape)
+        inputs.append(cur.cpu().numpy())
+        cur = layer.Forward(cur)
+    out = cur.cpu().numpy()
+    errors_in, errors_out, cur = [None] * len(net.layers), [None] * len(net.layers), torch.from_numpy(error).cuda()
+    for i in range(len(net.layers) - 1, -1, -1):
+        layer = net.layers[i]
+        cur = cur.view((B,) + layer.out_shape)
+        errors_in[i] = cur.cpu().numpy()
+        cur = layer.TrainingBackward(cur, True, need_prev=(i > 0 or need_input_error))
+        errors_out[i] = cur.cpu().numpy() if cur is not None else None
+    ops.stream_status()
+    check("net output, free-running twin", out, twin.forward(x), 10 * tol, False)
+    # the same contractions on absolute values: sum |a||b|, the scale the rounding error of a dot product is bounded by
+    # (the tensor core's fp32 accumulator adds an error that grows with the length of the contraction)
+    mags = OracleNet(port, net, absolute=True)
+    contraction = lambda layer: type(layer).__name__ in ("NetLayerConvolution", "NetLayerBackConvolution", "NetLayerLinear")
+    for i, layer in enumerate(net.layers):
+        name = "layer %d %s" % (i, type(layer).__name__)
+        want = twin.forward_layer(i, inputs[i])
+        mag = mags.forward_layer(i, np.abs(inputs[i])) if contraction(layer) else None
+        check("output of " + name, layer.H.cpu().numpy(), want, tol, strict, mag)
+    for i in range(len(net.layers) - 1, -1, -1):
+        layer = net.layers[i]
+        name = "layer %d %s" % (i, type(layer).__name__)
+        need = i > 0 or need_input_error
+        want = twin.backward_layer(i, errors_in[i], need)
+        mag = mags.backward_layer(i, np.abs(errors_in[i]), need) if contraction(layer) else None
+        if need:
+            check("error below " + name, errors_out[i], want, tol, strict, mag)
+        for pname in layer.param_shapes():
+            want = twin.grads[i][pname]
+            if not want.any():
+                assert not layer.g[pname].cpu().numpy().any(), (name, pname)
+                continue
+            mag = mags.grads[i][pname] if contraction(layer) else twin.grad_mag[i].get(pname)
+            check("gradient %s of %s" % (pname, name), layer.g[pname].cpu().numpy(), want, tol, strict, mag)
+    return twin
+
+
+@pytest.mark.parametrize("mode", ["fp32", "x3"])
+def test_dcgan_discriminator_chain(ops, port, mode):
+    from cuda_cnn_gan_vae_b200.nets import dcgan_discriminator
+    ops.set_precision(ops.FP32 if mode == "fp32" else ops.TF32X3)
+    B = 8
+    net = dcgan_discriminator(B, image=(3, 32, 32), widths=(16, 32, 64), leaky_slope=0.1 if mode == "fp32" else 0.2)
+    rng = np.random.default_rng(3)
+    x = rng.uniform(-1, 1, (B, 3, 32, 32)).astype(np.float32)
+    labels = rng.integers(0, 2, (B, 1, 1, 1)).astype(np.float32)
+    out = net.Forward(torch.from_numpy(x).cuda()).cpu().numpy()
+    error = (out - labels).astype(np.float32)
+    run_and_compare(ops, port, net, x, error, 2e-5 if mode == "fp32" else TOL_X3, True, need_input_error=True)
+
+
+@pytest.mark.parametrize("mode", ["fp32", "x3"])
+def test_dcgan_generator_chain(ops, port, mode):
+    from cuda_cnn_gan_vae_b200.nets import dcgan_generator
+    ops.set_precision(ops.FP32 if mode == "fp32" else ops.TF32X3)
+    B = 8
+    net = dcgan_generator(B, noise=20, base=64, widths=(32, 16, 3), leaky_slope=0.1 if mode == "fp32" else 0.2)
+    assert net.out_shape == (3, 32, 32)
+    rng = np.random.default_rng(2)
+    z = rng.standard_normal((B, 1, 20, 1)).astype(np.float32)
+    error = rng.standard_normal((B, 3, 32, 32)).astype(np.float32)
+    run_and_compare(ops, port, net, z, error, 2e-5 if mode == "fp32" else TOL_X3, True)
+
+
+def test_dcgan_full_width_layers_x3(ops, port):
+    """The discriminator at the widths of the benchmark configuration (64..512 channels, 64x64 images), batch 16."""
+    from cuda_cnn_gan_vae_b200.nets import dcgan_discriminator
+    ops.set_precision(ops.TF32X3)
+    B = 16
+    net = dcgan_discriminator(B)
+    rng = np.random.default_rng(33)
+    x = rng.uniform(-1, 1, (B, 3, 64, 64)).astype(np.float32)
+    error = rng.standard_normal((B, 1, 1, 1)).astype(np.float32)
+    run_and_compare(ops, port, net, x, error, TOL_X3, True, need_input_error=True)
+
+
+def test_adam_over_the_parameter_arena(ops, port):
+    from cuda_cnn_gan_vae_b200.nets import dcgan_generator
+    ops.set_precision(ops.TF32X3)
+    B = 4
+    net = dcgan_generator(B, noise=20, base=64, widths=(32, 16, 3))
+    rng = np.random.default_rng(5)
+    net.TrainingResetDeltaWeight()
+    net.Forward(torch.from_numpy(rng.standard_normal((B, 1, 20, 1)).astype(np.float32)).cuda())
+    net.TrainingBackward(torch.from_numpy(rng.standard_normal((B, 3, 32, 32)).astype(np.float32)).cuda(), True)
+    w0, g = net.weights.buffer.cpu().numpy().copy(), net.grads.buffer.cpu().numpy().copy()
+    zeros = np.zeros_like(w0)
+    net.TrainingUpdateWeight(2e-4, 1, batch_scale=2)
+    ops.stream_status()
+    want_w, want_m, want_v = port.adam(w0, g, zeros, zeros, B * 2, 2e-4, 0.9, 0.999, 1e-8, 1)
+    assert np.allclose(net.weights.buffer.cpu().numpy(), want_w, rtol=0, atol=1e-7)
+    assert np.allclose(net.m.buffer.cpu().numpy(), want_m, rtol=1e-6, atol=1e-12)
+    assert np.allclose(net.v.buffer.cpu().numpy(), want_v, rtol=1e-6, atol=1e-20)
+    assert np.abs(net.weights.buffer.cpu().numpy() - w0).max() > 1e-5

@@ -182,6 +182,31 @@ def cpu_baseline(seconds_budget=25.0):
                 sample=f"{n} of {c['batch']} samples of the workload, fwd+bwd+wgrad, single thread, {dt:.1f} s")
 
 
+def dcgan_cpu_baseline(images=2):
+    """The combined DCGAN step (generator and discriminator chains, forward + backward + weight gradients) on the CPU twin
+    built from the reference CPU backend's tensor routines, single thread, on a few images."""
+    import numpy as np
+    import torch
+    from cuda_cnn_gan_vae_b200.nets import dcgan_discriminator, dcgan_generator
+    from oracle import Oracle
+    from oracle.net_twin import OracleNet
+    port = Oracle("port")
+    G, D = dcgan_generator(images), dcgan_discriminator(images)
+    tg, td = OracleNet(port, G), OracleNet(port, D)
+    r = np.random.default_rng(7)
+    z = r.standard_normal((images, 1, 100, 1)).astype(np.float32)
+    labels = r.integers(0, 2, (images, 1, 1, 1)).astype(np.float32)
+    t0 = time.perf_counter()
+    fake = tg.forward(z)
+    out = td.forward(fake)
+    d_image = td.backward((out.reshape(labels.shape) - labels).astype(np.float32), need_input_error=True)
+    tg.backward(d_image)
+    dt = time.perf_counter() - t0
+    del torch
+    return dict(value=images / dt, unit="img/s", cores=1, kind="port", host_cores=os.cpu_count(),
+                sample=f"{images} images through generator + discriminator fwd+bwd+dW (no optimiser), single thread, {dt:.1f} s")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -192,6 +217,8 @@ def main():
     ap.add_argument("--cpu-threads", type=int, default=64)
     ap.add_argument("--skip-cpu", action="store_true", help="leave out the cpu_baseline leg")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-dcgan", action="store_true", help="leave out the DCGAN training-step measurement")
+    ap.add_argument("--dcgan-batch", type=int, default=64, help="images per GPU in the DCGAN step")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "b200":
         args.warmup = 3
@@ -315,6 +342,47 @@ def main():
                    note="image and delta copied from pinned host memory, dW|dB read back, every step; plain-TF32 mode")
         ops.stream_status()
 
+    # ---- DCGAN training step (generator + discriminator chains), 64 images per GPU -------------------------------
+    dcgan = None
+    if not args.skip_dcgan:
+        from cuda_cnn_gan_vae_b200.nets import DCGANStep
+        gb = args.dcgan_batch
+        hz = torch.randn(gb, 1, 100, 1, generator=torch.Generator().manual_seed(11 + rank)).pin_memory()
+        hl = (torch.rand(gb, 1, 1, 1, generator=torch.Generator().manual_seed(13 + rank)) < 0.5).float().pin_memory()
+        z, labels = hz.cuda(), hl.cuda()
+        hout = torch.empty(gb, 1, 1, 1).pin_memory()
+        dcgan = dict(unit="img/s", per_gpu_batch=gb, global_batch=gb * world, scaling="weak",
+                     step="G forward, D forward on the generated images, D backward + dW, G backward + dW, all-reduce of both "
+                          "gradient arenas, Adam on both nets; LeakyReLU slope 0.2, per-element batch normalisation; the launches "
+                          "up to the all-reduce are replayed from a CUDA graph captured after two eager steps")
+        for mode_name, mode in (("tf32x3", ops.TF32X3), ("tf32", ops.TF32)):
+            ops.set_precision(mode)
+            trainer = DCGANStep(gb, world=world)          # a graph is captured in the precision mode of its first steps
+            dcgan["parameters"] = dict(generator=trainer.G.parameter_count, discriminator=trainer.D.parameter_count)
+            n0 = lib.b200_launch_count()
+            trainer(z, labels)                            # eager: every launch of the step is counted once
+            per_step = lib.b200_launch_count() - n0
+
+            def dcgan_step():
+                trainer(z, labels)
+
+            ms, clocks, _, _ = timed(dcgan_step, args.steps, max(args.warmup, 3), sample_clocks=True)
+            ops.stream_status()
+            dcgan[mode_name] = dict(value=gb * world / (ms * 1e-3), ms_per_step=ms, gpu_launches=int(per_step), clocks=clocks,
+                                    cuda_graph=trainer.graph is not None)
+
+        def dcgan_e2e_step():
+            z.copy_(hz, non_blocking=True)
+            labels.copy_(hl, non_blocking=True)
+            hout.copy_(trainer(z, labels).view(gb, 1, 1, 1), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        ms, _, _, _ = timed(dcgan_e2e_step, args.steps, 2)
+        ops.stream_status()
+        dcgan["e2e"] = dict(value=gb * world / (ms * 1e-3), unit="img/s", ms_per_step=ms, h2d_bytes_per_step=int((hz.numel() + hl.numel()) * 4 * world),
+                            d2h_bytes_per_step=int(hout.numel() * 4 * world), note="noise and labels from pinned host memory, discriminator outputs read back; plain-TF32 mode")
+        dcgan["value"] = dcgan["tf32"]["value"]
+
     if rank == 0:
         head = results["tf32"]
         line = dict(metric=METRIC, value=head["value"], unit="TFLOP/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
@@ -326,9 +394,11 @@ def main():
                                 parity="tf32: 2e-3, tf32x3: 1e-4 vs the reference CPU backend (tests/test_gpu_conv.py)",
                                 flops_per_step=step_flops),
                     clocks=head["clocks"], gpu_launches=head["gpu_launches"], roofline=head["roofline"], e2e=e2e,
-                    tf32x3=results["tf32x3"])
+                    tf32x3=results["tf32x3"], dcgan=dcgan)
         if not args.skip_cpu and world == 1:
             line["cpu_baseline"] = cpu_baseline()
+            if dcgan is not None:
+                dcgan["cpu_baseline"] = dcgan_cpu_baseline()
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -5,6 +5,7 @@ CNetLayerFunction)."""
 import torch
 
 from . import ops
+from .lib import load
 from .layers import (Net, NetLayerBackConvolution, NetLayerBatchNormalization, NetLayerConvolution, NetLayerFunction,
                      NetLayerLinear)
 
@@ -41,26 +42,56 @@ class DCGANStep:
     launch per net.  The error at the discriminator's output is output - label (the gradient of binary cross-entropy with
     respect to the logit, formed as in model/cmodel_basicgan.cu.h:352-376 but on the device)."""
 
-    def __init__(self, batch, world=1, widths_g=(256, 128, 64, 3), widths_d=(64, 128, 256, 512), base=512, noise=100, leaky_slope=0.2):
+    def __init__(self, batch, world=1, widths_g=(256, 128, 64, 3), widths_d=(64, 128, 256, 512), base=512, noise=100, leaky_slope=0.2,
+                 use_graph=True):
         self.batch, self.world = batch, world
         self.G = dcgan_generator(batch, noise, base, widths_g, leaky_slope)
         self.D = dcgan_discriminator(batch, self.G.out_shape, widths_d, leaky_slope)
         self.G.broadcast_weights()
         self.D.broadcast_weights()
         self.error = torch.empty((batch, 1, 1, 1), device="cuda")
+        self.z = torch.empty((batch, 1, noise, 1), device="cuda")
+        self.labels = torch.empty((batch, 1, 1, 1), device="cuda")
         self.iteration = 0
+        self.use_graph, self.graph, self.eager_steps = use_graph, None, 0
+        self.out = None
 
-    def __call__(self, z, labels, speed=2e-4):
-        self.iteration += 1
+    def _gradients(self):
+        """Everything of the step up to the all-reduced gradients (all launches have fixed arguments: capturable)."""
         self.G.TrainingResetDeltaWeight()
         self.D.TrainingResetDeltaWeight()
-        fake = self.G.Forward(z)
+        fake = self.G.Forward(self.z)
         out = self.D.Forward(fake)
-        ops.CTensorMath.Sub(self.error, out, labels)
+        ops.CTensorMath.Sub(self.error, out, self.labels)
         d_image = self.D.TrainingBackward(self.error, True, need_input_error=True)
         self.G.TrainingBackward(d_image, True)
         self.D.grads.all_reduce()
         self.G.grads.all_reduce()
+        return out
+
+    def __call__(self, z, labels, speed=2e-4):
+        """The step is launch-bound at 64 images (over a hundred launches of a few microseconds each), so after two eager
+        steps (which size every scratch buffer of the library) its launches up to the all-reduce are captured once in a
+        CUDA graph and replayed; the two Adam launches take the step number as a host argument and stay outside."""
+        self.iteration += 1
+        if z.data_ptr() != self.z.data_ptr():
+            self.z.copy_(z, non_blocking=True)
+        if labels.data_ptr() != self.labels.data_ptr():
+            self.labels.copy_(labels, non_blocking=True)
+        if self.graph is not None and load().b200_scratch_bytes() != self.scratch_bytes:
+            self.graph, self.eager_steps = None, 0      # the library's scratch arena was re-allocated: the graph holds stale addresses
+        if self.use_graph and self.graph is None and self.eager_steps >= 2:
+            ops.stream_status()
+            self.scratch_bytes = load().b200_scratch_bytes()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                self.out = self._gradients()
+            self.graph = graph
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.out = self._gradients()
+            self.eager_steps += 1
         self.D.TrainingUpdateWeight(speed, self.iteration, batch_scale=self.world)
         self.G.TrainingUpdateWeight(speed, self.iteration, batch_scale=self.world)
-        return out
+        return self.out

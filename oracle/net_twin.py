@@ -1,4 +1,5 @@
-"""CPU twin of a layers.Net for the parity tests: the same chain of layers evaluated with the oracle's tensor routines
+"""Test infrastructure, not product code.  CPU twin of a layers.Net for the parity tests and the CPU baseline of the
+benchmark: the same chain of layers evaluated with the oracle's tensor routines
 in the order the reference's layer classes call them (netlayer/cnetlayerconvolution.cu.h:310,484;
 cnetlayerbackconvolution.cu.h:303,475; cnetlayerlinear.cu.h:262,415; cnetlayerfunction.cu.h:347-358;
 cnetlayerbatchnormalization.cu.h:301-379,578-604; cnetlayermaxpooling.cu.h:246,367; cnetlayerupsampling.cu.h:249,366).

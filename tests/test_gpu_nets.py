@@ -1,6 +1,6 @@
 """The layer chains of the DCGAN configurations (generator: Linear + transposed convolutions, discriminator:
 convolutions + Linear, both with batch normalisation and activations) on the GPU against the CPU twin built from the
-oracle's tensor routines (tests/net_oracle.py), layer by layer: outputs, errors handed down, weight gradients, and the
+oracle's tensor routines (oracle/net_twin.py), layer by layer: outputs, errors handed down, weight gradients, and the
 Adam update of the whole parameter arena."""
 import numpy as np
 import pytest
@@ -8,7 +8,7 @@ import pytest
 torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
 
-from tests.net_oracle import OracleNet  # noqa: E402
+from oracle.net_twin import OracleNet  # noqa: E402
 from tests.util import TOL_X3  # noqa: E402
 
 
@@ -146,3 +146,27 @@ def test_adam_over_the_parameter_arena(ops, port):
     assert np.allclose(net.m.buffer.cpu().numpy(), want_m, rtol=1e-6, atol=1e-12)
     assert np.allclose(net.v.buffer.cpu().numpy(), want_v, rtol=1e-6, atol=1e-20)
     assert np.abs(net.weights.buffer.cpu().numpy() - w0).max() > 1e-5
+
+
+def test_dcgan_step_graph_replay_matches_eager(ops):
+    """The combined step replayed from its CUDA graph gives the same weights and outputs as the eager launches."""
+    from cuda_cnn_gan_vae_b200.nets import DCGANStep
+    ops.set_precision(ops.TF32X3)
+    B = 8
+    kw = dict(widths_g=(32, 16, 3), widths_d=(16, 32, 64), base=64, noise=20)
+    rng = np.random.default_rng(9)
+    z = torch.from_numpy(rng.standard_normal((B, 1, 20, 1)).astype(np.float32)).cuda()
+    labels = torch.from_numpy(rng.integers(0, 2, (B, 1, 1, 1)).astype(np.float32)).cuda()
+    results = []
+    for use_graph in (False, True):
+        step = DCGANStep(B, use_graph=use_graph, **kw)
+        assert step.G.out_shape == (3, 32, 32)
+        outs = [step(z, labels).cpu().numpy().copy() for _ in range(6)]
+        ops.stream_status()
+        assert (step.graph is not None) == use_graph
+        results.append((outs, step.G.weights.buffer.cpu().numpy(), step.D.weights.buffer.cpu().numpy()))
+    (eo, eg, ed), (go, gg, gd) = results
+    assert not np.array_equal(eo[0], eo[5])                    # the weights do move
+    for a, b in zip(eo, go):
+        assert np.array_equal(a, b)
+    assert np.array_equal(eg, gg) and np.array_equal(ed, gd)

@@ -34,6 +34,23 @@ CFG = dict(C=256, H=32, W=32, K=256, k=3, s=1, p=1, batch=1024)
 METRIC = "conv_fwd_bwd_wgrad_tflops"
 
 
+_RESULT_FD = None
+
+
+def keep_stdout_clean():
+    """The one JSON line must be all that reaches stdout: libraries (NCCL's version banner) write there too, so the
+    process's stdout is pointed at stderr and the result goes to a private copy of the original descriptor."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(text):
+    os.write(_RESULT_FD if _RESULT_FD is not None else 1, (text + "\n").encode())
+
+
 def flops_per_sample(c):
     oh = (c["H"] - c["k"] + 2 * c["p"]) // c["s"] + 1
     ow = (c["W"] - c["k"] + 2 * c["p"]) // c["s"] + 1
@@ -149,7 +166,7 @@ def reference_arm(args, rank, world):
                 data="synthetic", config=dict(workload="dp_conv_sweep_256x32x32_k256_3x3 (CPU sample)", sample=sample),
                 cpu_baseline=dict(value=val, unit="TFLOP/s", cores=T, kind=kind, sample=sample, host_cores=os.cpu_count()),
                 e2e=dict(value=val, unit="TFLOP/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
-    print(json.dumps(line), flush=True)
+    emit(json.dumps(line))
 
 
 def cpu_baseline(seconds_budget=25.0):
@@ -220,6 +237,7 @@ def main():
     ap.add_argument("--skip-dcgan", action="store_true", help="leave out the DCGAN training-step measurement")
     ap.add_argument("--dcgan-batch", type=int, default=64, help="images per GPU in the DCGAN step")
     args = ap.parse_args()
+    keep_stdout_clean()
     if args.warmup < 3 and args.impl == "b200":
         args.warmup = 3
     rank = int(os.environ.get("RANK", "0"))
@@ -399,9 +417,14 @@ def main():
             line["cpu_baseline"] = cpu_baseline()
             if dcgan is not None:
                 dcgan["cpu_baseline"] = dcgan_cpu_baseline()
-        print(json.dumps(line), flush=True)
+        emit(json.dumps(line))
     if world > 1:
-        dist.destroy_process_group()
+        # Leave without tearing the process group down: destroying NCCL communicators while CUDA graphs that hold
+        # captured collectives are alive can block for minutes; every rank has finished its work at this barrier.
+        barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -278,6 +278,9 @@ int b200_mul(float *out, int out_w, const float *left, int left_w, const float *
         if (r != TC_UNSUPPORTED) return r;
     }
     set_path(B200_PATH_SIMT);
+    // too few outputs for a tensor-core tile: long dot products go one warp per output (outside the bit-exact mode)
+    if (g_precision != B200_FP32 && rx == 1 && !transpose_left && lx >= 256)
+        return warp_dot_mul(out, out_w, left, left_w, right, right_w, z, ly, lx, ST(stream));
     return simt_mul(out, out_w, left, left_w, right, right_w, z, ly, lx, rx, transpose_left, ST(stream));
 }
 

@@ -16,6 +16,9 @@ int simt_conv_wgrad(const b200_conv_geom &g, float *dkernel, int dkernel_w, floa
 // simt_math.cu
 int simt_mul(float *out, int out_w, const float *left, int left_w, const float *right, int right_w,
              int z, int ly, int lx, int rx, int transpose_left, cudaStream_t s);
+// matrix times column (rx == 1, not transposed), one warp per output element; not in the CPU backend's summation order
+int warp_dot_mul(float *out, int out_w, const float *left, int left_w, const float *right, int right_w, int z, int ly, int lx,
+                 cudaStream_t s);
 
 // tc_conv.cu -- tcgen05 implicit-GEMM convolution and dense GEMM.  Each returns B200_OK when it ran,
 // a negative value (TC_UNSUPPORTED) when the shape is not covered so the caller falls through to the

@@ -487,6 +487,50 @@ __global__ void simt_mul_kernel(float *__restrict__ out, int out_w, const float 
     }
 }
 
+// Matrix-times-column products (RX == 1, not transposed: out[w,z,y] = <row y of left, right>), one warp per output
+// element: both operands are contiguous along the contraction, the lanes stride over it with 16-byte loads and combine
+// with a shuffle tree.  The order of the additions differs from the CPU backend's, so the bit-exact FP32 mode does
+// not use it; it serves the tensor-core modes when a product has too few outputs for a tensor-core tile (a Linear
+// layer with a handful of neurons).
+__global__ void warp_dot_kernel(float *__restrict__ out, int out_w, const float *__restrict__ left, int left_w,
+                                const float *__restrict__ right, int right_w, int Z, int LY, int LX)
+{
+    const int lane = threadIdx.x & 31;
+    const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    const size_t total = (size_t)out_w * Z * LY;
+    const bool vec = (LX % 4 == 0) && ((((uintptr_t)left) | ((uintptr_t)right)) % 16 == 0);
+    for (size_t idx = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; idx < total; idx += warps) {
+        const int y = idx % LY;
+        size_t t = idx / LY;
+        const int z = t % Z;
+        const int w = t / Z;
+        const float *a = left + (((size_t)(w % left_w) * Z + z) * LY + y) * LX;
+        const float *b = right + ((size_t)(w % right_w) * Z + z) * LX;
+        float acc = 0.f;
+        if (vec) {
+            const float4 *a4 = reinterpret_cast<const float4 *>(a), *b4 = reinterpret_cast<const float4 *>(b);
+            for (int k = lane; k < LX / 4; k += 32) {
+                const float4 u = a4[k], v = b4[k];
+                acc += u.x * v.x + u.y * v.y + u.z * v.z + u.w * v.w;
+            }
+        } else {
+            for (int k = lane; k < LX; k += 32) acc += a[k] * b[k];
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) out[idx] = acc;
+    }
+}
+
+int warp_dot_mul(float *out, int out_w, const float *left, int left_w, const float *right, int right_w, int z, int ly, int lx,
+                 cudaStream_t s)
+{
+    const size_t total = (size_t)out_w * z * ly;
+    if (!total) return B200_OK;
+    warp_dot_kernel<<<stream_grid(total * 32, 256), 256, 0, s>>>(out, out_w, left, left_w, right, right_w, z, ly, lx);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
 int simt_mul(float *out, int out_w, const float *left, int left_w, const float *right, int right_w,
              int z, int ly, int lx, int rx, int transpose_left, cudaStream_t s)
 {

@@ -588,6 +588,36 @@ __global__ void wgrad_reduce_kernel(float *__restrict__ dkernel, const float *__
     }
 }
 
+// The same reduction through a shared-memory tile, so that both sides are coalesced: a block owns 32 filters x
+// c_run channels x all taps; it reads runs of 32 consecutive filters (128 bytes) per (tap, channel) and writes, per
+// filter, the run of c_run*taps consecutive weights.  Splits are added in increasing order as above.
+__global__ void wgrad_reduce_tiled_kernel(float *__restrict__ dkernel, const float *__restrict__ partial, int splits, int taps,
+                                          int C, int K, int c_run, int accumulate)
+{
+    extern __shared__ float tile[];                       // [tap][c_run][33]
+    const int c_tiles = (C + c_run - 1) / c_run;
+    const int f0 = (blockIdx.x / c_tiles) * 32, c0 = (blockIdx.x % c_tiles) * c_run;
+    const int cn = min(c_run, C - c0), fn = min(32, K - f0);
+    const size_t split_stride = (size_t)taps * C * K;
+    for (int e = threadIdx.x; e < taps * cn * 32; e += blockDim.x) {
+        const int fl = e & 31, r = e >> 5, cl = r % cn, tap = r / cn;
+        if (fl < fn) {
+            const float *src = partial + ((size_t)tap * C + c0 + cl) * K + f0 + fl;
+            float sum = 0.f;
+            for (int sp = 0; sp < splits; sp++) sum += src[sp * split_stride];
+            tile[(tap * c_run + cl) * 33 + fl] = sum;
+        }
+    }
+    __syncthreads();
+    const int run = cn * taps;
+    for (int e = threadIdx.x; e < fn * run; e += blockDim.x) {
+        const int j = e % run, fl = e / run, cl = j / taps, tap = j - cl * taps;
+        const size_t o = ((size_t)(f0 + fl) * C + c0) * taps + j;
+        const float v = tile[(tap * c_run + cl) * 33 + fl];
+        dkernel[o] = accumulate ? dkernel[o] + v : v;
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------------
@@ -932,15 +962,6 @@ int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack 
 
     TcParams p;
     memset(&p, 0, sizeof(p));
-    p.BN = (int)align_up(k_out < 256 ? k_out : 256, 16);
-    p.acc_stride = pow2_ceil(p.BN);
-    // CTA pairs (two CTAs share one 256-row MMA, each stages half of the filter rows): less shared-memory
-    // traffic per flop; used when there are enough M-tiles to pair up
-    const int ctas = (cta_pairs_enabled() && p.BN >= 32) ? 2 : 1;
-    set_kmajor(p, true, 128);
-    set_kmajor(p, false, p.BN / ctas);
-    p.idesc = make_idesc_tf32(p.BN, 0, 0, 128 * ctas);
-    p.n_tiles_n = ceil_div(k_out, p.BN);
     p.c_chunks = ceil_div(act_c, 32);
     p.n_img = batch; p.k_out = k_out; p.OH = OH; p.OW = OW; p.out_stride_y = osy; p.out_stride_x = osx;
     p.out = out; p.bias = bias;
@@ -988,6 +1009,35 @@ int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack 
     if (any_empty) B200_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * (size_t)batch * k_out * OH * OW, s));
     if (nph == 0) return B200_OK;
     p.phases = nph;
+    // Column tile (BN) and CTA pairing.  The widest tile with CTA pairs (two CTAs share one 256-row MMA, each stages half
+    // of the filter rows) moves the fewest operand bytes per flop, but a layer with few output pixels then yields only a
+    // handful of work items for 148 SMs.  Model: time ~ waves x K-steps x (A bytes + B bytes per CTA and K-step), with A
+    // = 128 rows and B = BN (or BN/2) rows; take the candidate with the least modelled time, the wider one on a tie.
+    int ctas = 1;
+    {
+        const int bn_max = (int)align_up(k_out < 256 ? k_out : 256, 16);
+        long long best = -1;
+        for (int bn = bn_max; bn >= 16; bn = (bn > 32 ? (int)align_up(bn / 2, 16) : bn - 16)) {
+            for (int c = 2; c >= 1; c--) {
+                if (c == 2 && !(cta_pairs_enabled() && bn >= 32)) continue;
+                const long long items = (long long)(c == 2 ? mpairs : mtiles) * ceil_div(k_out, bn);
+                const long long waves = (items * c + sm_count() - 1) / sm_count();
+                const long long cost = waves * (128 + bn / c);
+                if (best < 0 || cost < best) { best = cost; p.BN = bn; ctas = c; }
+            }
+            if (bn == 16) break;
+        }
+        // tuning aid: B200CONV_TILE="<BN>,<CTAs>" overrides the choice (read on every call)
+        if (const char *e = getenv("B200CONV_TILE")) {
+            int bn = 0, c = 0;
+            if (sscanf(e, "%d,%d", &bn, &c) == 2 && bn >= 16 && bn <= bn_max && bn % 16 == 0 && (c == 1 || (c == 2 && bn >= 32))) { p.BN = bn; ctas = c; }
+        }
+    }
+    p.acc_stride = pow2_ceil(p.BN);
+    set_kmajor(p, true, 128);
+    set_kmajor(p, false, p.BN / ctas);
+    p.idesc = make_idesc_tf32(p.BN, 0, 0, 128 * ctas);
+    p.n_tiles_n = ceil_div(k_out, p.BN);
     p.num_tiles = (ctas == 2 ? mpairs : mtiles) * p.n_tiles_n;
 
     CUtensorMap maps[4];
@@ -1117,6 +1167,16 @@ int wgrad_gemm(const b200_conv_geom &g, float *dkernel, int accumulate, const Ac
         if (x3 && (r = make_blocked_map(&maps[3], x.lo, C, dims, pitch, box, p.BN / 32 / ctas))) return r;
     }
     if ((r = launch_tc<MODE_WGRAD>(maps, p, x3, s, ctas))) return r;
+    // channels per block: runs of about 128 consecutive weights per filter on the output side
+    int c_run = (128 + taps - 1) / taps;
+    if (c_run > C) c_run = C;
+    const size_t tile_bytes = sizeof(float) * (size_t)taps * c_run * 33;
+    if (tile_bytes <= 48 * 1024) {
+        const int blocks = ceil_div(K, 32) * ceil_div(C, c_run);
+        wgrad_reduce_tiled_kernel<<<blocks, 256, tile_bytes, s>>>(dkernel, p.partial, p.splits, taps, C, K, c_run, accumulate);
+        B200_LAUNCH_CHECK();
+        return B200_OK;
+    }
     size_t total = (size_t)K * C * taps;
     int grid = (int)((total + 255) / 256);
     if (grid > sm_count() * 16) grid = sm_count() * 16;

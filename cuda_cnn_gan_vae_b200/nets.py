@@ -7,7 +7,7 @@ import torch
 from . import ops
 from .lib import load
 from .layers import (Net, NetLayerBackConvolution, NetLayerBatchNormalization, NetLayerConvolution, NetLayerFunction,
-                     NetLayerLinear)
+                     NetLayerLinear, NetLayerMaxPooling, NetLayerUpSampling)
 
 
 def dcgan_generator(batch, noise=100, base=512, widths=(256, 128, 64, 3), leaky_slope=0.2, seed=2):
@@ -95,3 +95,67 @@ class DCGANStep:
         self.D.TrainingUpdateWeight(speed, self.iteration, batch_scale=self.world)
         self.G.TrainingUpdateWeight(speed, self.iteration, batch_scale=self.world)
         return self.out
+
+
+def vae_encoder(batch, image=(3, 128, 128), widths=(32, 64, 128, 256), leaky_slope=0.1, seed=4):
+    """image -> 4 x (3x3 convolution, LeakyReLU, 2x2 max-pooling)."""
+    spec = []
+    for width in widths:
+        spec.append((NetLayerConvolution, dict(kernel_amount=width, kernel_size=3, stride=1, padding=1)))
+        spec.append((NetLayerFunction, dict(func="leaky_relu", leaky_slope=leaky_slope)))
+        spec.append((NetLayerMaxPooling, dict(pooling=2)))
+    return Net(image, batch, spec, seed=seed)
+
+
+def vae_decoder(batch, latent=256, start=(256, 8, 8), widths=(128, 64, 32, 3), leaky_slope=0.1, seed=5):
+    """latent -> Linear to start -> 4 x (2x upsampling, 3x3 convolution), LeakyReLU between, sigmoid at the output."""
+    spec = [(NetLayerLinear, dict(neurons=start[0] * start[1] * start[2])), ("reshape", tuple(start)),
+            (NetLayerFunction, dict(func="leaky_relu", leaky_slope=leaky_slope))]
+    for i, width in enumerate(widths):
+        spec.append((NetLayerUpSampling, dict(factor=2)))
+        spec.append((NetLayerConvolution, dict(kernel_amount=width, kernel_size=3, stride=1, padding=1)))
+        spec.append((NetLayerFunction, dict(func="leaky_relu", leaky_slope=leaky_slope) if i + 1 < len(widths) else dict(func="sigmoid")))
+    return Net((1, latent, 1), batch, spec, seed=seed)
+
+
+class VAEStep:
+    """One training step of the convolutional VAE on a rank's shard: encoder, the two Linear heads (mean and log-variance),
+    the reparameterised latent with caller-supplied noise (netlayer/cnetlayervaecoderoutput.cu.h:244-287), decoder; error
+    2(x_hat - x)/numel at the output plus the Kullback-Leibler terms at the heads (:424-460); backward through all four
+    nets with weight gradients, one all-reduce per gradient arena, Adam on every net."""
+
+    def __init__(self, batch, world=1, image=(3, 128, 128), widths=(32, 64, 128, 256), latent=256, kl_speed=1.0, leaky_slope=0.1):
+        self.batch, self.world, self.kl_speed = batch, world, kl_speed
+        self.encoder = vae_encoder(batch, image, widths, leaky_slope)
+        feat = self.encoder.out_shape
+        self.mu = Net(feat, batch, [(NetLayerLinear, dict(neurons=latent))], seed=6)
+        self.logvar = Net(feat, batch, [(NetLayerLinear, dict(neurons=latent))], seed=7)
+        self.decoder = vae_decoder(batch, latent, feat, tuple(widths[-2::-1]) + (image[0],), leaky_slope)
+        assert self.decoder.out_shape == tuple(image), (self.decoder.out_shape, image)
+        self.nets = (self.encoder, self.mu, self.logvar, self.decoder)
+        for net in self.nets:
+            net.broadcast_weights()
+        self.error = torch.empty((batch,) + tuple(image), device="cuda")
+        self.feat_error = torch.empty((batch,) + feat, device="cuda")
+        self.iteration = 0
+        self.kl = None
+
+    def __call__(self, x, eps, speed=1e-3, want_kl=False):
+        self.iteration += 1
+        for net in self.nets:
+            net.TrainingResetDeltaWeight()
+        feat = self.encoder.Forward(x)
+        mu, logvar = self.mu.Forward(feat), self.logvar.Forward(feat)
+        z, self.kl = ops.vae_forward(mu, logvar, eps.view(mu.shape), want_kl=want_kl)
+        x_hat = self.decoder.Forward(z)
+        ops.CTensorMath.Sub(self.error, x_hat, x, 2.0 / x[0].numel(), 2.0 / x[0].numel())
+        d_z = self.decoder.TrainingBackward(self.error, True, need_input_error=True)
+        d_mu, d_logvar = ops.vae_backward(d_z.view(mu.shape), mu, logvar, eps.view(mu.shape), self.kl_speed)
+        e_mu = self.mu.TrainingBackward(d_mu, True, need_input_error=True)
+        e_lv = self.logvar.TrainingBackward(d_logvar, True, need_input_error=True)
+        ops.CTensorMath.Add(self.feat_error, e_mu, e_lv)
+        self.encoder.TrainingBackward(self.feat_error, True)
+        for net in self.nets:
+            net.grads.all_reduce()
+            net.TrainingUpdateWeight(speed, self.iteration, batch_scale=self.world)
+        return x_hat

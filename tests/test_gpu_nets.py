@@ -170,3 +170,56 @@ def test_dcgan_step_graph_replay_matches_eager(ops):
     for a, b in zip(eo, go):
         assert np.array_equal(a, b)
     assert np.array_equal(eg, gg) and np.array_equal(ed, gd)
+
+
+@pytest.mark.parametrize("mode", ["fp32", "x3"])
+def test_vae_encoder_and_decoder_chains(ops, port, mode):
+    """Convolution + LeakyReLU + max-pooling (argmax routed back) and Linear + upsampling + convolution chains."""
+    from cuda_cnn_gan_vae_b200.nets import vae_decoder, vae_encoder
+    ops.set_precision(ops.FP32 if mode == "fp32" else ops.TF32X3)
+    tol, B = (2e-5 if mode == "fp32" else TOL_X3), 4
+    rng = np.random.default_rng(4)
+    enc = vae_encoder(B, image=(3, 32, 32), widths=(8, 16, 32))
+    assert enc.out_shape == (32, 4, 4)
+    x = rng.uniform(0, 1, (B, 3, 32, 32)).astype(np.float32)
+    run_and_compare(ops, port, enc, x, rng.standard_normal((B, 32, 4, 4)).astype(np.float32), tol, True, need_input_error=True)
+    dec = vae_decoder(B, latent=24, start=(32, 4, 4), widths=(16, 8, 3))
+    assert dec.out_shape == (3, 32, 32)
+    z = rng.standard_normal((B, 1, 24, 1)).astype(np.float32)
+    run_and_compare(ops, port, dec, z, rng.standard_normal((B, 3, 32, 32)).astype(np.float32), tol, True, need_input_error=True)
+
+
+def test_vae_step_matches_twin(ops, port):
+    """The whole VAE step (two heads on one feature tensor, reparameterisation with supplied noise, reconstruction and
+    Kullback-Leibler errors) against the same composition of oracle routines, free-running, in FP32 mode."""
+    from cuda_cnn_gan_vae_b200.nets import VAEStep
+    ops.set_precision(ops.FP32)
+    B, image = 4, (3, 16, 16)
+    step = VAEStep(B, image=image, widths=(8, 16), latent=12, kl_speed=0.5)
+    twins = [OracleNet(port, net) for net in step.nets]
+    rng = np.random.default_rng(8)
+    x = rng.uniform(0, 1, (B,) + image).astype(np.float32)
+    eps = rng.standard_normal((B, 1, 12, 1)).astype(np.float32)
+    w0 = [net.weights.buffer.cpu().numpy().copy() for net in step.nets]
+    x_hat = step(torch.from_numpy(x).cuda(), torch.from_numpy(eps).cuda(), want_kl=True)
+    ops.stream_status()
+    enc, mu_t, lv_t, dec = twins
+    feat = enc.forward(x)
+    mu, lv = mu_t.forward(feat), lv_t.forward(feat)
+    z, kl = port.vae_forward(mu.reshape(B, -1), lv.reshape(B, -1), eps.reshape(B, -1))
+    want_hat = dec.forward(z.reshape(B, 1, 12, 1))
+    check("reconstruction", x_hat.cpu().numpy(), want_hat, 2e-5, True)
+    assert abs(step.kl - kl) <= 1e-4 * max(1.0, abs(kl))
+    n = float(np.prod(image))
+    err = port.binary("sub", want_hat, x, 2.0 / n, 2.0 / n)
+    d_z = dec.backward(err, need_input_error=True)
+    d_mu, d_lv = port.vae_backward(d_z.reshape(B, -1), mu.reshape(B, -1), lv.reshape(B, -1), eps.reshape(B, -1), 0.5)
+    e = port.binary("add", mu_t.backward(d_mu.reshape(B, 1, 12, 1), need_input_error=True),
+                    lv_t.backward(d_lv.reshape(B, 1, 12, 1), need_input_error=True))
+    enc.backward(e)
+    check("error at the encoder output", step.feat_error.cpu().numpy(), e, 5e-5, True)
+    for net, twin, before in zip(step.nets, twins, w0):
+        for i, layer in enumerate(net.layers):
+            for name in layer.param_shapes():
+                check("gradient %d.%s" % (i, name), layer.g[name].cpu().numpy(), twin.grads[i][name], 1e-4, False, twin.grad_mag[i].get(name))
+        assert np.abs(net.weights.buffer.cpu().numpy() - before).max() > 0      # Adam moved the weights

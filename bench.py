@@ -224,6 +224,63 @@ def dcgan_cpu_baseline(images=2):
                 sample=f"{images} images through generator + discriminator fwd+bwd+dW (no optimiser), single thread, {dt:.1f} s")
 
 
+def hbm_kernels(torch, ops, peak_gbs, iters=5):
+    """The memory-bound kernels around the contractions on tensors well beyond L2 (256 MiB of fp32 activations: the
+    VAE encoder's first feature map, 128 x 32 x 128 x 128): algorithmic bytes (every input read once, every output
+    written once) / CUDA-event time, against the measured HBM copy bandwidth."""
+    W, Z, Y, X = 128, 32, 128, 128
+    n = Z * Y * X
+    gen = torch.Generator(device="cuda").manual_seed(17)
+    a = torch.randn(W, Z, Y, X, device="cuda", generator=gen)
+    b = torch.randn(W, Z, Y, X, device="cuda", generator=gen)
+    o1, o2 = torch.empty_like(a), torch.empty_like(a)
+    stat = [torch.rand(1, Z, Y, X, device="cuda", generator=gen) + 0.5 for _ in range(3)]
+    s_out = [torch.empty(1, Z, Y, X, device="cuda") for _ in range(5)]
+    bias = torch.randn(1, Z, 1, 1, device="cuda", generator=gen)
+    half = torch.empty(W, Z, Y // 2, X // 2, device="cuda")
+    pos = torch.empty(W, Z, Y // 2, X // 2, 2, dtype=torch.int32, device="cuda")
+    planes = torch.empty(W, Z, 1, 1, device="cuda")
+    flat = lambda t: t.view(1, 1, 1, -1)
+    lib = ops.load()
+    P, S, chk = ops._ptr, ops._stream, ops._check
+    F = 4.0 * W * n                                    # bytes of one full activation tensor
+    st = 4.0 * n
+    cases = [
+        ("bn_forward", lambda: chk(lib.b200_bn_forward(P(o1), P(o2), P(s_out[0]), P(s_out[1]), P(s_out[2]), P(s_out[3]), P(s_out[4]), P(a),
+                                                       P(stat[0]), P(stat[1]), W, n, 0.9, 1e-6, S())), 3 * F + 7 * st),
+        ("bn_backward", lambda: chk(lib.b200_bn_backward(P(o1), P(s_out[0]), P(s_out[1]), P(a), P(b), P(stat[0]), P(stat[1]), W, n, 1, S())),
+         3 * F + 6 * st),
+        ("bias_activation", lambda: ops.CTensorApplyFunc.BiasActivation(o1, bias, "leaky_relu", 0.2), 2 * F),
+        ("activation_backward", lambda: ops.CTensorApplyFunc.Backward(o1, a, b, "leaky_relu", 0.2), 3 * F),
+        ("maxpool", lambda: ops.CTensorMath.MaxPooling(half, pos, a, 2, 2), F + F / 4 + 2 * F / 4),
+        ("maxpool_backward", lambda: ops.CTensorMath.MaxPoolingBackward(o1, pos, half, 2, 2), F + F / 4 + 2 * F / 4),
+        ("upsample", lambda: ops.CTensorMath.UpSampling(o1, half, 2, 2), F + F / 4),
+        ("downsample", lambda: ops.CTensorMath.DownSampling(half, a, 2, 2), F + F / 4),
+        ("summ_xy", lambda: ops.CTensorMath.SummXY(planes, a), F),
+        ("add_sum_w", lambda: ops.CTensorMath.AddSumW(s_out[0], s_out[0], a), F + 2 * st),
+        ("add", lambda: ops.CTensorMath.Add(o1, a, b, 0.5, 0.25), 3 * F),
+        ("adam", lambda: ops.CTensorMath.Adam(flat(o1), flat(a), flat(b), flat(o2), 64, 1e-3, 0.9, 0.999, 1e-8, 2), 7 * F),
+    ]
+    out = {}
+    for name, fn, nbytes in cases:
+        if name == "adam":
+            o2.abs_()                                  # the second-moment operand must not be negative
+        for _ in range(2):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = dict(ms=ms, algorithmic_mb=nbytes / 1e6, achieved_gbs=gbs, frac=gbs / peak_gbs)
+    ops.stream_status()
+    return dict(unit="GB/s", peak=peak_gbs, peak_source="hbm_gbs (copy bandwidth), of measured", tensor="128x32x128x128 fp32 (256 MiB), beyond L2",
+                kernels=out)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -235,6 +292,7 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true", help="leave out the cpu_baseline leg")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-dcgan", action="store_true", help="leave out the DCGAN training-step measurement")
+    ap.add_argument("--skip-hbm", action="store_true", help="leave out the memory-bound kernel measurements")
     ap.add_argument("--dcgan-batch", type=int, default=64, help="images per GPU in the DCGAN step")
     args = ap.parse_args()
     keep_stdout_clean()
@@ -401,6 +459,12 @@ def main():
                             d2h_bytes_per_step=int(hout.numel() * 4 * world), note="noise and labels from pinned host memory, discriminator outputs read back; plain-TF32 mode")
         dcgan["value"] = dcgan["tf32"]["value"]
 
+    hbm = None
+    if not args.skip_hbm and world == 1:
+        del x, delta, y, dx
+        torch.cuda.empty_cache()
+        hbm = hbm_kernels(torch, ops, peaks["hbm"])
+
     if rank == 0:
         head = results["tf32"]
         line = dict(metric=METRIC, value=head["value"], unit="TFLOP/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
@@ -412,7 +476,7 @@ def main():
                                 parity="tf32: 2e-3, tf32x3: 1e-4 vs the reference CPU backend (tests/test_gpu_conv.py)",
                                 flops_per_step=step_flops),
                     clocks=head["clocks"], gpu_launches=head["gpu_launches"], roofline=head["roofline"], e2e=e2e,
-                    tf32x3=results["tf32x3"], dcgan=dcgan)
+                    tf32x3=results["tf32x3"], dcgan=dcgan, hbm_kernels=hbm)
         if not args.skip_cpu and world == 1:
             line["cpu_baseline"] = cpu_baseline()
             if dcgan is not None:

@@ -307,6 +307,60 @@ __global__ void maxpool_backward_kernel(float *__restrict__ out, const uint2 *__
     }
 }
 
+// 2x2 windows that tile the plane exactly: one thread per window; it reads its position and delta once and writes the
+// window's two rows as 8-byte stores (consecutive threads write consecutive addresses).
+__global__ void maxpool_backward_2x2_kernel(float *__restrict__ out, const uint2 *__restrict__ pos, const float *__restrict__ delta,
+                                            unsigned rows, unsigned dx)
+{
+    // rows = planes * dy window rows; each owns two output rows of 2*dx floats
+    const size_t total = (size_t)rows * dx;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const unsigned wx = (unsigned)(i % dx);
+        const size_t row = i / dx;
+        const uint2 ps = pos[i];
+        const float d = delta[i];
+        const unsigned px = ps.x - 2 * wx, py = ps.y & 1u;      // position inside the window (y is absolute within the plane, windows start at even rows)
+        float2 r0 = make_float2(0.f, 0.f), r1 = r0;
+        if (py == 0) { if (px == 0) r0.x = d; else r0.y = d; }
+        else { if (px == 0) r1.x = d; else r1.y = d; }
+        float2 *o = reinterpret_cast<float2 *>(out + (row * 2) * (size_t)(2 * dx)) + wx;
+        o[0] = r0;
+        o[dx] = r1;
+    }
+}
+
+// factor 2 in both directions: one thread per input element, two 8-byte stores
+__global__ void upsample_2x2_kernel(float *__restrict__ out, const float *__restrict__ in, unsigned rows, unsigned in_x)
+{
+    const size_t total = (size_t)rows * in_x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const unsigned x = (unsigned)(i % in_x);
+        const size_t row = i / in_x;
+        const float v = in[i];
+        float2 *o = reinterpret_cast<float2 *>(out + (row * 2) * (size_t)(2 * in_x)) + x;
+        o[0] = make_float2(v, v);
+        o[in_x] = make_float2(v, v);
+    }
+}
+
+// factor 2 in both directions, even input sizes: one thread per output, two 8-byte loads; the four values are added in
+// the reference's order (column by column, rows inside)
+__global__ void downsample_2x2_kernel(float *__restrict__ out, const float *__restrict__ in, unsigned rows, unsigned out_x)
+{
+    const size_t total = (size_t)rows * out_x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const unsigned x = (unsigned)(i % out_x);
+        const size_t row = i / out_x;
+        const float2 *p = reinterpret_cast<const float2 *>(in + (row * 2) * (size_t)(2 * out_x)) + x;
+        const float2 a = p[0], b = p[out_x];
+        float s = __fadd_rn(0.f, a.x);
+        s = __fadd_rn(s, b.x);
+        s = __fadd_rn(s, a.y);
+        s = __fadd_rn(s, b.y);
+        out[i] = __fdiv_rn(s, 4.0f);
+    }
+}
+
 __global__ void upsample_kernel(float *__restrict__ out, const float *__restrict__ in, size_t planes, int in_y, int in_x,
                                 int out_y, int out_x, int ux, int uy)
 {
@@ -376,6 +430,84 @@ __global__ void bn_forward_kernel(float *__restrict__ y, float *__restrict__ xha
             float h = __fmul_rn(__fsub_rn(x[(size_t)w * n + i], mu), iv);
             xhat[(size_t)w * n + i] = h;
             y[(size_t)w * n + i] = __fadd_rn(__fmul_rn(g, h), b);
+        }
+    }
+}
+
+// The same arithmetic with the W column of an element held in registers (W <= WMAX): every load of a pass is independent
+// of the others and x is read from HBM exactly once, whatever the tensor's size relative to L2.
+template <int WMAX>
+__global__ void __launch_bounds__(128) bn_forward_reg_kernel(float *__restrict__ y, float *__restrict__ xhat, float *__restrict__ ivar,
+                                      float *__restrict__ mean, float *__restrict__ var, float *new_mean, float *new_var,
+                                      const float *__restrict__ x, const float *__restrict__ gamma, const float *__restrict__ beta,
+                                      int W, size_t n, float momentum, float eps)
+{
+    const float invN = (float)(1.0 / (double)(float)W);
+    const float om = (float)(1.0 - (double)momentum);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float v[WMAX];
+#pragma unroll
+        for (int w = 0; w < WMAX; w++) v[w] = w < W ? x[(size_t)w * n + i] : 0.f;
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < WMAX; w++) if (w < W) s = __fadd_rn(s, v[w]);
+        const float mu = __fadd_rn(0.f, __fmul_rn(s, invN));
+        float q = 0.f;
+#pragma unroll
+        for (int w = 0; w < WMAX; w++) if (w < W) {
+            const float d = __fsub_rn(v[w], mu);
+            q = __fadd_rn(q, __fmul_rn(__fmul_rn(d, d), 1.0f));
+        }
+        const float vr = __fadd_rn(0.f, __fmul_rn(q, invN));
+        const float iv = __fdiv_rn(1.0f, __fmul_rn(__fsqrt_rn(__fadd_rn(vr, eps)), 1.0f));
+        mean[i] = mu; var[i] = vr; ivar[i] = iv;
+        if (new_mean) new_mean[i] = __fadd_rn(__fmul_rn(momentum, new_mean[i]), __fmul_rn(om, mu));
+        if (new_var) new_var[i] = __fadd_rn(__fmul_rn(momentum, new_var[i]), __fmul_rn(om, vr));
+        const float g = gamma[i], b = beta[i];
+#pragma unroll
+        for (int w = 0; w < WMAX; w++) if (w < W) {
+            const float h = __fmul_rn(__fsub_rn(v[w], mu), iv);
+            xhat[(size_t)w * n + i] = h;
+            y[(size_t)w * n + i] = __fadd_rn(__fmul_rn(g, h), b);
+        }
+    }
+}
+
+template <int WMAX>
+__global__ void __launch_bounds__(128) bn_backward_reg_kernel(float *__restrict__ dx, float *dgamma, float *dbeta, const float *__restrict__ dy,
+                                       const float *__restrict__ xhat, const float *__restrict__ ivar, const float *__restrict__ gamma,
+                                       int W, size_t n, int create_delta_weight)
+{
+    const float N = (float)W;
+    const float invN = (float)(1.0 / (double)N);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float d[WMAX], h[WMAX];
+#pragma unroll
+        for (int w = 0; w < WMAX; w++) {
+            d[w] = w < W ? dy[(size_t)w * n + i] : 0.f;
+            h[w] = w < W ? xhat[(size_t)w * n + i] : 0.f;
+        }
+        const float g = gamma[i], iv = ivar[i];
+        float sb = 0.f, sc = 0.f, sg = 0.f, sbeta = 0.f;
+#pragma unroll
+        for (int w = 0; w < WMAX; w++) if (w < W) {
+            const float dh = __fmul_rn(d[w], g);
+            sb = __fadd_rn(sb, dh);
+            sc = __fadd_rn(sc, __fmul_rn(dh, h[w]));
+            sg = __fadd_rn(sg, __fmul_rn(d[w], h[w]));
+            sbeta = __fadd_rn(sbeta, d[w]);
+        }
+        if (create_delta_weight) {
+            dgamma[i] = __fadd_rn(dgamma[i], sg);
+            dbeta[i] = __fadd_rn(dbeta[i], sbeta);
+        }
+#pragma unroll
+        for (int w = 0; w < WMAX; w++) if (w < W) {
+            float v = __fmul_rn(__fmul_rn(d[w], g), N);
+            v = __fsub_rn(v, __fmul_rn(h[w], sc));
+            v = __fsub_rn(v, sb);
+            v = __fmul_rn(v, iv);
+            dx[(size_t)w * n + i] = __fmul_rn(v, invN);
         }
     }
 }
@@ -689,8 +821,12 @@ int b200_maxpool_backward(float *out, const uint32_t *pos, const float *delta, i
     size_t planes = (size_t)w * z;
     size_t total = planes * out_y * out_x;
     if (!total) return B200_OK;
-    maxpool_backward_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(out, reinterpret_cast<const uint2 *>(pos), delta, planes,
-                                                                           out_y, out_x, pool_x, pool_y);
+    if (pool_x == 2 && pool_y == 2 && out_x % 2 == 0 && out_y % 2 == 0 && ((uintptr_t)out % 8) == 0 && planes * (size_t)(out_y / 2) < 0xFFFFFFFFull)
+        maxpool_backward_2x2_kernel<<<stream_grid(total / 4, 256), 256, 0, ST(stream)>>>(out, reinterpret_cast<const uint2 *>(pos), delta,
+                                                                                       (unsigned)(planes * (out_y / 2)), (unsigned)(out_x / 2));
+    else
+        maxpool_backward_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(out, reinterpret_cast<const uint2 *>(pos), delta, planes,
+                                                                               out_y, out_x, pool_x, pool_y);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -702,7 +838,10 @@ int b200_upsample(float *out, const float *in, int w, int z, int in_y, int in_x,
     size_t planes = (size_t)w * z;
     size_t total = planes * in_y * uy * in_x * ux;
     if (!total) return B200_OK;
-    upsample_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(out, in, planes, in_y, in_x, in_y * uy, in_x * ux, ux, uy);
+    if (ux == 2 && uy == 2 && ((uintptr_t)out % 8) == 0 && planes * (size_t)in_y < 0xFFFFFFFFull)
+        upsample_2x2_kernel<<<stream_grid(total / 4, 256), 256, 0, ST(stream)>>>(out, in, (unsigned)(planes * in_y), (unsigned)in_x);
+    else
+        upsample_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(out, in, planes, in_y, in_x, in_y * uy, in_x * ux, ux, uy);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -714,7 +853,10 @@ int b200_downsample(float *out, const float *in, int w, int z, int in_y, int in_
     size_t planes = (size_t)w * z;
     size_t total = planes * (in_y / dy) * (in_x / dx);
     if (!total) return B200_OK;
-    downsample_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(out, in, planes, in_y, in_x, in_y / dy, in_x / dx, dx, dy);
+    if (dx == 2 && dy == 2 && in_x % 2 == 0 && in_y % 2 == 0 && ((uintptr_t)in % 8) == 0 && planes * (size_t)(in_y / 2) < 0xFFFFFFFFull)
+        downsample_2x2_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(out, in, (unsigned)(planes * (in_y / 2)), (unsigned)(in_x / 2));
+    else
+        downsample_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(out, in, planes, in_y, in_x, in_y / dy, in_x / dx, dx, dy);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -726,8 +868,14 @@ int b200_bn_forward(float *y, float *xhat, float *ivar, float *mean, float *var,
     if (!y || !xhat || !ivar || !mean || !var || !x || !gamma || !beta) return fail(B200_E_ARG, "null tensor pointer");
     if (w <= 0) return fail(B200_E_SHAPE, "non-positive batch");
     if (!n) return B200_OK;
-    bn_forward_kernel<<<stream_grid(n, 128), 128, 0, ST(stream)>>>(y, xhat, ivar, mean, var, new_mean, new_var, x, gamma, beta,
-                                                                  w, n, momentum, eps);
+#define B200_BN_FWD(WMAX) bn_forward_reg_kernel<WMAX><<<stream_grid(n, 128), 128, 0, ST(stream)>>>(y, xhat, ivar, mean, var, new_mean, new_var, x, gamma, beta, w, n, momentum, eps)
+    if (w <= 16) B200_BN_FWD(16);
+    else if (w <= 32) B200_BN_FWD(32);
+    else if (w <= 64) B200_BN_FWD(64);
+    else if (w <= 128) B200_BN_FWD(128);
+    else bn_forward_kernel<<<stream_grid(n, 128), 128, 0, ST(stream)>>>(y, xhat, ivar, mean, var, new_mean, new_var, x, gamma, beta,
+                                                                       w, n, momentum, eps);
+#undef B200_BN_FWD
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -739,7 +887,12 @@ int b200_bn_backward(float *dx, float *dgamma, float *dbeta, const float *dy, co
     if (create_delta_weight && (!dgamma || !dbeta)) return fail(B200_E_ARG, "null gradient pointer");
     if (w <= 0) return fail(B200_E_SHAPE, "non-positive batch");
     if (!n) return B200_OK;
-    bn_backward_kernel<<<stream_grid(n, 128), 128, 0, ST(stream)>>>(dx, dgamma, dbeta, dy, xhat, ivar, gamma, w, n, create_delta_weight);
+#define B200_BN_BWD(WMAX) bn_backward_reg_kernel<WMAX><<<stream_grid(n, 128), 128, 0, ST(stream)>>>(dx, dgamma, dbeta, dy, xhat, ivar, gamma, w, n, create_delta_weight)
+    if (w <= 16) B200_BN_BWD(16);
+    else if (w <= 32) B200_BN_BWD(32);
+    else if (w <= 64) B200_BN_BWD(64);
+    else bn_backward_kernel<<<stream_grid(n, 128), 128, 0, ST(stream)>>>(dx, dgamma, dbeta, dy, xhat, ivar, gamma, w, n, create_delta_weight);
+#undef B200_BN_BWD
     B200_LAUNCH_CHECK();
     return B200_OK;
 }

@@ -55,18 +55,26 @@ class DCGANStep:
         self.iteration = 0
         self.use_graph, self.graph, self.eager_steps = use_graph, None, 0
         self.out = None
+        self.side = torch.cuda.Stream() if world > 1 else None
 
     def _gradients(self):
-        """Everything of the step up to the all-reduced gradients (all launches have fixed arguments: capturable)."""
+        """Everything of the step up to the all-reduced gradients (all launches have fixed arguments: capturable).  The
+        discriminator's gradient arena is all-reduced on a side stream while the generator's backward pass runs."""
+        main = torch.cuda.current_stream()
         self.G.TrainingResetDeltaWeight()
         self.D.TrainingResetDeltaWeight()
         fake = self.G.Forward(self.z)
         out = self.D.Forward(fake)
         ops.CTensorMath.Sub(self.error, out, self.labels)
         d_image = self.D.TrainingBackward(self.error, True, need_input_error=True)
+        if self.world > 1:
+            self.side.wait_stream(main)
+            with torch.cuda.stream(self.side):
+                self.D.grads.all_reduce()
         self.G.TrainingBackward(d_image, True)
-        self.D.grads.all_reduce()
         self.G.grads.all_reduce()
+        if self.world > 1:
+            main.wait_stream(self.side)
         return out
 
     def __call__(self, z, labels, speed=2e-4):

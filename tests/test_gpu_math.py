@@ -201,11 +201,21 @@ def test_pooling_and_resampling_bit_exact(ops, port):
     down = torch.empty(2, 3, 2, 4, device="cuda")
     ops.CTensorMath.DownSampling(down, dev(bigx), 2, 3)
     assert down.cpu().numpy().tobytes() == port.downsample(bigx, 2, 3).tobytes()
+    # factor 2 x 2 (the decoder's case: 8-byte vector kernels), even and odd sizes
+    for shape in ((3, 5, 8, 16), (2, 3, 7, 9), (1, 2, 6, 10)):
+        xs = r.normal(0, 1, shape).astype(np.float32)
+        up = torch.empty(shape[0], shape[1], shape[2] * 2, shape[3] * 2, device="cuda")
+        ops.CTensorMath.UpSampling(up, dev(xs), 2, 2)
+        assert up.cpu().numpy().tobytes() == port.upsample(xs, 2, 2).tobytes()
+        down = torch.empty(shape[0], shape[1], shape[2] // 2, shape[3] // 2, device="cuda")
+        ops.CTensorMath.DownSampling(down, dev(xs), 2, 2)
+        assert down.cpu().numpy().tobytes() == port.downsample(xs, 2, 2).tobytes()
 
 
-def test_batchnorm_fused_bit_exact(ops, port):
+@pytest.mark.parametrize("batch", [5, 24, 64, 100, 130])      # every register-resident variant and the general kernel
+def test_batchnorm_fused_bit_exact(ops, port, batch):
     r = np.random.default_rng(3)
-    x = r.normal(1.5, 2.0, (64, 16, 8, 8)).astype(np.float32)
+    x = r.normal(1.5, 2.0, (batch, 16, 8, 8)).astype(np.float32)
     gamma = r.normal(1, 0.1, (1, 16, 8, 8)).astype(np.float32)
     beta = r.normal(0, 0.1, (1, 16, 8, 8)).astype(np.float32)
     nm = r.normal(0, 1, gamma.shape).astype(np.float32)

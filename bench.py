@@ -293,6 +293,7 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-dcgan", action="store_true", help="leave out the DCGAN training-step measurement")
     ap.add_argument("--skip-hbm", action="store_true", help="leave out the memory-bound kernel measurements")
+    ap.add_argument("--hbm-only", action="store_true", help="run only the memory-bound kernel measurements (profiling aid)")
     ap.add_argument("--dcgan-batch", type=int, default=64, help="images per GPU in the DCGAN step")
     args = ap.parse_args()
     keep_stdout_clean()
@@ -318,6 +319,9 @@ def main():
         if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
             os.environ["NCCL_DEBUG"] = "WARN"           # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    if args.hbm_only:
+        emit(json.dumps(dict(hbm_kernels=hbm_kernels(torch, ops, measured_peaks()["hbm"], iters=2))))
+        return
     c = dict(CFG, batch=args.batch)
     assert c["batch"] % world == 0, "global batch must divide over the ranks"
     B = c["batch"] // world

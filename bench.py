@@ -236,6 +236,7 @@ def hbm_kernels(torch, ops, peak_gbs, iters=5):
     o1, o2 = torch.empty_like(a), torch.empty_like(a)
     stat = [torch.rand(1, Z, Y, X, device="cuda", generator=gen) + 0.5 for _ in range(3)]
     s_out = [torch.empty(1, Z, Y, X, device="cuda") for _ in range(5)]
+    bn_s = [torch.rand(1, 2 * Z, Y, X, device="cuda", generator=gen) + 0.5 for _ in range(7)]
     bias = torch.randn(1, Z, 1, 1, device="cuda", generator=gen)
     half = torch.empty(W, Z, Y // 2, X // 2, device="cuda")
     pos = torch.empty(W, Z, Y // 2, X // 2, 2, dtype=torch.int32, device="cuda")
@@ -246,10 +247,11 @@ def hbm_kernels(torch, ops, peak_gbs, iters=5):
     F = 4.0 * W * n                                    # bytes of one full activation tensor
     st = 4.0 * n
     cases = [
-        ("bn_forward", lambda: chk(lib.b200_bn_forward(P(o1), P(o2), P(s_out[0]), P(s_out[1]), P(s_out[2]), P(s_out[3]), P(s_out[4]), P(a),
-                                                       P(stat[0]), P(stat[1]), W, n, 0.9, 1e-6, S())), 3 * F + 7 * st),
-        ("bn_backward", lambda: chk(lib.b200_bn_backward(P(o1), P(s_out[0]), P(s_out[1]), P(a), P(b), P(stat[0]), P(stat[1]), W, n, 1, S())),
-         3 * F + 6 * st),
+        # batch normalisation at the DCGAN batch: the same 256 MiB viewed as 64 x (2 n) elements
+        ("bn_forward", lambda: chk(lib.b200_bn_forward(P(o1), P(o2), P(bn_s[2]), P(bn_s[3]), P(bn_s[4]), P(bn_s[5]), P(bn_s[6]), P(a),
+                                                       P(bn_s[0]), P(bn_s[1]), W // 2, 2 * n, 0.9, 1e-6, S())), 3 * F + 14 * st),
+        ("bn_backward", lambda: chk(lib.b200_bn_backward(P(o1), P(bn_s[2]), P(bn_s[3]), P(a), P(b), P(bn_s[0]), P(bn_s[1]), W // 2, 2 * n, 1, S())),
+         3 * F + 12 * st),
         ("bias_activation", lambda: ops.CTensorApplyFunc.BiasActivation(o1, bias, "leaky_relu", 0.2), 2 * F),
         ("activation_backward", lambda: ops.CTensorApplyFunc.Backward(o1, a, b, "leaky_relu", 0.2), 3 * F),
         ("maxpool", lambda: ops.CTensorMath.MaxPooling(half, pos, a, 2, 2), F + F / 4 + 2 * F / 4),
@@ -295,6 +297,7 @@ def main():
     ap.add_argument("--skip-hbm", action="store_true", help="leave out the memory-bound kernel measurements")
     ap.add_argument("--hbm-only", action="store_true", help="run only the memory-bound kernel measurements (profiling aid)")
     ap.add_argument("--dcgan-batch", type=int, default=64, help="images per GPU in the DCGAN step")
+    ap.add_argument("--dcgan-eager", action="store_true", help="launch the DCGAN step eagerly instead of replaying its CUDA graph (profiling aid)")
     args = ap.parse_args()
     keep_stdout_clean()
     if args.warmup < 3 and args.impl == "b200":
@@ -437,7 +440,7 @@ def main():
                           "up to the all-reduce are replayed from a CUDA graph captured after two eager steps")
         for mode_name, mode in (("tf32x3", ops.TF32X3), ("tf32", ops.TF32)):
             ops.set_precision(mode)
-            trainer = DCGANStep(gb, world=world)          # a graph is captured in the precision mode of its first steps
+            trainer = DCGANStep(gb, world=world, use_graph=not args.dcgan_eager)   # a graph is captured in the precision mode of its first steps
             dcgan["parameters"] = dict(generator=trainer.G.parameter_count, discriminator=trainer.D.parameter_count)
             n0 = lib.b200_launch_count()
             trainer(z, labels)                            # eager: every launch of the step is counted once

@@ -56,6 +56,8 @@ int dbias_batch(float *dbias, int accumulate, const float *delta, int batch, int
 
 // Status word written by device-side waits that gave up (0 = none); clear != 0 resets it.
 unsigned tc_read_status(int clear);
+// device pointer of the per-device status word (pinned, mapped host memory) that bounded device-side waits report into
+int status_word(unsigned **dev);
 
 void tc_profile_enable(int on);
 int tc_profile_read(double *total_ms, int *launches);

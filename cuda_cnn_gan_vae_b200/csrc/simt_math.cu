@@ -4,6 +4,7 @@
 // 128-bit accesses where the alignment allows; grids are sized in multiples of the SM count.
 #include "common.cuh"
 #include "kernels.h"
+#include "tc_ptx.cuh"
 #include <cmath>
 
 namespace b200 {
@@ -512,6 +513,155 @@ __global__ void __launch_bounds__(128) bn_backward_reg_kernel(float *__restrict_
     }
 }
 
+// ---- batch-norm with the W column block staged in shared memory by bulk copies ---------------------------------------
+// One block of TW threads per tile of TW consecutive elements x all W samples.  Thread 0 issues one cp.async.bulk per batch
+// row (TW*4 bytes; all rows of the tile in flight at once) and the block waits on one mbarrier.  Each thread then walks its
+// own column in shared memory in the reference's order (bit-identical results) and stores coalesced rows.  Several blocks
+// are resident per SM, so the loads of one overlap the arithmetic and stores of the others (measured: better than
+// persistent double-buffered blocks, which leave too few threads per SM for the dependent additions of a column).
+// Needs n % 4 == 0 (16-byte aligned rows).  The wait is bounded; on a time-out the block reports through the status word
+// and returns.
+__device__ __forceinline__ void bulk_load_row(uint32_t dst, const float *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, unsigned *status)
+{
+    const long long t0 = clock64();
+    while (!ptx::mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > 2000000000LL) {
+            atomicExch(status, 0x500u + B200_E_TIMEOUT);
+            __threadfence_system();
+            return false;
+        }
+    }
+    return true;
+}
+
+// rows of `arrays` tensors (1 or 2) for the tile starting at element i0 into one stage buffer [array][W][TW]
+template <int TW>
+__device__ __forceinline__ void bn_issue_tile(float *buf, uint32_t bar, const float *a0, const float *a1, int arrays, int W, size_t n, size_t i0)
+{
+    const uint32_t cols = (uint32_t)min((size_t)TW, n - i0);
+    ptx::mbar_arrive_expect_tx(bar, (uint32_t)arrays * (uint32_t)W * cols * 4u);
+    for (int w = 0; w < W; w++) {
+        bulk_load_row(ptx::smem_u32(buf + (size_t)w * TW), a0 + (size_t)w * n + i0, cols * 4u, bar);
+        if (arrays == 2) bulk_load_row(ptx::smem_u32(buf + (size_t)(W + w) * TW), a1 + (size_t)w * n + i0, cols * 4u, bar);
+    }
+}
+
+template <int TW>
+__global__ void __launch_bounds__(TW) bn_forward_smem_kernel(float *__restrict__ y, float *__restrict__ xhat, float *__restrict__ ivar,
+                                      float *__restrict__ mean, float *__restrict__ var, float *new_mean, float *new_var,
+                                      const float *__restrict__ x, const float *__restrict__ gamma, const float *__restrict__ beta,
+                                      int W, size_t n, float momentum, float eps, unsigned *status)
+{
+    extern __shared__ __align__(128) float xs[];          // [W][TW]
+    __shared__ __align__(8) unsigned long long bar_storage;
+    const uint32_t bar0 = ptx::smem_u32(&bar_storage);
+    const int t = threadIdx.x;
+    const size_t tile = blockIdx.x;
+    if (t == 0) {
+        ptx::mbar_init(bar0, 1);
+        ptx::fence_barrier_init();
+        bn_issue_tile<TW>(xs, bar0, x, nullptr, 1, W, n, tile * TW);
+    }
+    __syncthreads();
+    const float invN = (float)(1.0 / (double)(float)W);
+    const float om = (float)(1.0 - (double)momentum);
+    {
+        if (!bounded_wait(bar0, 0, status)) return;
+        const float *col = xs + t;
+        const size_t i = tile * TW + t;
+        if (i < n) {
+            float s = 0.f;
+            for (int w = 0; w < W; w++) s = __fadd_rn(s, col[w * TW]);
+            const float mu = __fadd_rn(0.f, __fmul_rn(s, invN));
+            float q = 0.f;
+            for (int w = 0; w < W; w++) {
+                const float d = __fsub_rn(col[w * TW], mu);
+                q = __fadd_rn(q, __fmul_rn(__fmul_rn(d, d), 1.0f));
+            }
+            const float vr = __fadd_rn(0.f, __fmul_rn(q, invN));
+            const float iv = __fdiv_rn(1.0f, __fmul_rn(__fsqrt_rn(__fadd_rn(vr, eps)), 1.0f));
+            mean[i] = mu; var[i] = vr; ivar[i] = iv;
+            if (new_mean) new_mean[i] = __fadd_rn(__fmul_rn(momentum, new_mean[i]), __fmul_rn(om, mu));
+            if (new_var) new_var[i] = __fadd_rn(__fmul_rn(momentum, new_var[i]), __fmul_rn(om, vr));
+            const float g = gamma[i], b = beta[i];
+#pragma unroll 8
+            for (int w = 0; w < W; w++) {
+                const float h = __fmul_rn(__fsub_rn(col[w * TW], mu), iv);
+                xhat[(size_t)w * n + i] = h;
+                y[(size_t)w * n + i] = __fadd_rn(__fmul_rn(g, h), b);
+            }
+        }
+    }
+}
+
+// Two threads per element (2*TW threads per block): the four sums of the first pass are independent chains, so one thread of
+// the pair forms sum(dxhat) and sum(dxhat*xhat), the other the two weight gradients; the second pass is split by even/odd
+// sample.  Every chain keeps the reference's order of additions.
+template <int TW>
+__global__ void __launch_bounds__(2 * TW) bn_backward_smem_kernel(float *__restrict__ dx, float *dgamma, float *dbeta, const float *__restrict__ dy,
+                                       const float *__restrict__ xhat, const float *__restrict__ ivar, const float *__restrict__ gamma,
+                                       int W, size_t n, int create_delta_weight, unsigned *status)
+{
+    extern __shared__ __align__(128) float xs[];          // dy rows [W][TW], xhat rows [W][TW]
+    __shared__ __align__(8) unsigned long long bar_storage;
+    __shared__ float sums[2][TW];
+    const uint32_t bar0 = ptx::smem_u32(&bar_storage);
+    const int t = threadIdx.x % TW, half = threadIdx.x / TW;
+    const size_t tile = blockIdx.x;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(bar0, 1);
+        ptx::fence_barrier_init();
+        bn_issue_tile<TW>(xs, bar0, dy, xhat, 2, W, n, tile * TW);
+    }
+    __syncthreads();
+    const float N = (float)W;
+    const float invN = (float)(1.0 / (double)N);
+    const bool ok = bounded_wait(bar0, 0, status);
+    const float *ds = xs + t, *hs = ds + (size_t)W * TW;
+    const size_t i = tile * TW + t;
+    const bool live = ok && i < n;
+    float g = 0.f, iv = 0.f;
+    if (live) {
+        g = gamma[i]; iv = ivar[i];
+        if (half == 0) {
+            float sb = 0.f, sc = 0.f;
+            for (int w = 0; w < W; w++) {
+                const float dh = __fmul_rn(ds[w * TW], g);
+                sb = __fadd_rn(sb, dh);
+                sc = __fadd_rn(sc, __fmul_rn(dh, hs[w * TW]));
+            }
+            sums[0][t] = sb; sums[1][t] = sc;
+        } else if (create_delta_weight) {
+            float sg = 0.f, sbeta = 0.f;
+            for (int w = 0; w < W; w++) {
+                const float d = ds[w * TW];
+                sg = __fadd_rn(sg, __fmul_rn(d, hs[w * TW]));
+                sbeta = __fadd_rn(sbeta, d);
+            }
+            dgamma[i] = __fadd_rn(dgamma[i], sg);
+            dbeta[i] = __fadd_rn(dbeta[i], sbeta);
+        }
+    }
+    __syncthreads();
+    if (!live) return;
+    const float sb = sums[0][t], sc = sums[1][t];
+#pragma unroll 8
+    for (int w = half; w < W; w += 2) {
+        const float d = ds[w * TW], h = hs[w * TW];
+        float v = __fmul_rn(__fmul_rn(d, g), N);
+        v = __fsub_rn(v, __fmul_rn(h, sc));
+        v = __fsub_rn(v, sb);
+        v = __fmul_rn(v, iv);
+        dx[(size_t)w * n + i] = __fmul_rn(v, invN);
+    }
+}
+
 __global__ void bn_backward_kernel(float *__restrict__ dx, float *dgamma, float *dbeta, const float *__restrict__ dy,
                                    const float *__restrict__ xhat, const float *__restrict__ ivar, const float *__restrict__ gamma,
                                    int W, size_t n, int create_delta_weight)
@@ -868,6 +1018,20 @@ int b200_bn_forward(float *y, float *xhat, float *ivar, float *mean, float *var,
     if (!y || !xhat || !ivar || !mean || !var || !x || !gamma || !beta) return fail(B200_E_ARG, "null tensor pointer");
     if (w <= 0) return fail(B200_E_SHAPE, "non-positive batch");
     if (!n) return B200_OK;
+    {
+        // staged through shared memory when the rows are 16-byte aligned and the column block fits
+        const size_t smem = (size_t)w * 128 * sizeof(float);
+        if (n % 4 == 0 && aligned16(x) && w >= 8 && smem <= 200 * 1024) {
+            unsigned *status = nullptr;
+            int r = status_word(&status);
+            if (r) return r;
+            B200_CUDA(cudaFuncSetAttribute(bn_forward_smem_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            bn_forward_smem_kernel<128><<<(unsigned)((n + 127) / 128), 128, smem, ST(stream)>>>(
+                y, xhat, ivar, mean, var, new_mean, new_var, x, gamma, beta, w, n, momentum, eps, status);
+            B200_LAUNCH_CHECK();
+            return B200_OK;
+        }
+    }
 #define B200_BN_FWD(WMAX) bn_forward_reg_kernel<WMAX><<<stream_grid(n, 128), 128, 0, ST(stream)>>>(y, xhat, ivar, mean, var, new_mean, new_var, x, gamma, beta, w, n, momentum, eps)
     if (w <= 16) B200_BN_FWD(16);
     else if (w <= 32) B200_BN_FWD(32);
@@ -887,6 +1051,20 @@ int b200_bn_backward(float *dx, float *dgamma, float *dbeta, const float *dy, co
     if (create_delta_weight && (!dgamma || !dbeta)) return fail(B200_E_ARG, "null gradient pointer");
     if (w <= 0) return fail(B200_E_SHAPE, "non-positive batch");
     if (!n) return B200_OK;
+    {
+        // 64-element tiles here: two tensors are staged, and six blocks per SM stay resident at batch 64
+        const size_t smem = 2 * (size_t)w * 64 * sizeof(float);
+        if (n % 4 == 0 && aligned16(dy) && aligned16(xhat) && w >= 8 && smem <= 200 * 1024) {
+            unsigned *status = nullptr;
+            int r = status_word(&status);
+            if (r) return r;
+            B200_CUDA(cudaFuncSetAttribute(bn_backward_smem_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            bn_backward_smem_kernel<64><<<(unsigned)((n + 63) / 64), 128, smem, ST(stream)>>>(
+                dx, dgamma, dbeta, dy, xhat, ivar, gamma, w, n, create_delta_weight, status);
+            B200_LAUNCH_CHECK();
+            return B200_OK;
+        }
+    }
 #define B200_BN_BWD(WMAX) bn_backward_reg_kernel<WMAX><<<stream_grid(n, 128), 128, 0, ST(stream)>>>(dx, dgamma, dbeta, dy, xhat, ivar, gamma, w, n, create_delta_weight)
     if (w <= 16) B200_BN_BWD(16);
     else if (w <= 32) B200_BN_BWD(32);

@@ -599,13 +599,31 @@ __global__ void wgrad_reduce_tiled_kernel(float *__restrict__ dkernel, const flo
     const int f0 = (blockIdx.x / c_tiles) * 32, c0 = (blockIdx.x % c_tiles) * c_run;
     const int cn = min(c_run, C - c0), fn = min(32, K - f0);
     const size_t split_stride = (size_t)taps * C * K;
-    for (int e = threadIdx.x; e < taps * cn * 32; e += blockDim.x) {
-        const int fl = e & 31, r = e >> 5, cl = r % cn, tap = r / cn;
-        if (fl < fn) {
-            const float *src = partial + ((size_t)tap * C + c0 + cl) * K + f0 + fl;
-            float sum = 0.f;
-            for (int sp = 0; sp < splits; sp++) sum += src[sp * split_stride];
-            tile[(tap * c_run + cl) * 33 + fl] = sum;
+    if ((K & 3) == 0) {
+        // 16-byte loads along the filters (rows of K floats are 16-byte aligned when K is a multiple of 4)
+        for (int e = threadIdx.x; e < taps * cn * 8; e += blockDim.x) {
+            const int fl = (e & 7) * 4, r = e >> 3, cl = r % cn, tap = r / cn;
+            if (fl < fn) {
+                const float4 *src = reinterpret_cast<const float4 *>(partial + ((size_t)tap * C + c0 + cl) * K + f0 + fl);
+                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+                for (int sp = 0; sp < splits; sp++) {
+                    const float4 v = src[sp * (split_stride >> 2)];
+                    sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+                }
+                float *t = &tile[(tap * c_run + cl) * 33 + fl];
+                t[0] = sum.x; t[1] = sum.y; t[2] = sum.z; t[3] = sum.w;
+            }
+        }
+    } else {
+        for (int e = threadIdx.x; e < taps * cn * 32; e += blockDim.x) {
+            const int fl = e & 31, r = e >> 5, cl = r % cn, tap = r / cn;
+            if (fl < fn) {
+                const float *src = partial + ((size_t)tap * C + c0 + cl) * K + f0 + fl;
+                float sum = 0.f;
+                for (int sp = 0; sp < splits; sp++) sum += src[sp * split_stride];
+                tile[(tap * c_run + cl) * 33 + fl] = sum;
+            }
         }
     }
     __syncthreads();
@@ -680,7 +698,7 @@ static int pos_mod(int a, int b) { int r = a % b; return r < 0 ? r + b : r; }
 static unsigned *g_status_host[64];
 static unsigned *g_status_dev[64];
 
-static int status_word(unsigned **dev)
+int status_word(unsigned **dev)
 {
     int d = 0;
     cudaGetDevice(&d);
@@ -1167,8 +1185,8 @@ int wgrad_gemm(const b200_conv_geom &g, float *dkernel, int accumulate, const Ac
         if (x3 && (r = make_blocked_map(&maps[3], x.lo, C, dims, pitch, box, p.BN / 32 / ctas))) return r;
     }
     if ((r = launch_tc<MODE_WGRAD>(maps, p, x3, s, ctas))) return r;
-    // channels per block: runs of about 128 consecutive weights per filter on the output side
-    int c_run = (128 + taps - 1) / taps;
+    // channels per block: runs of about 64 consecutive weights (256 bytes) per filter on the output side
+    int c_run = (64 + taps - 1) / taps;
     if (c_run > C) c_run = C;
     const size_t tile_bytes = sizeof(float) * (size_t)taps * c_run * 33;
     if (tile_bytes <= 48 * 1024) {
@@ -1185,14 +1203,29 @@ int wgrad_gemm(const b200_conv_geom &g, float *dkernel, int accumulate, const Ac
     return B200_OK;
 }
 
+// second stage of the bias gradient: dbias[k] (+)= sum over the batch of the plane sums; one warp per filter, the lanes walk the batch and combine
+// in a shuffle tree (a fixed order: reproducible run to run)
+__global__ void dbias_reduce_kernel(float *__restrict__ dbias, const float *__restrict__ plane_sums, int batch, int K, int accumulate)
+{
+    const int lane = threadIdx.x & 31;
+    const int k = (int)((blockIdx.x * blockDim.x + threadIdx.x) >> 5);
+    if (k >= K) return;
+    float s = 0.f;
+    for (int w = lane; w < batch; w += 32) s += plane_sums[(size_t)w * K + k];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) dbias[k] = accumulate ? dbias[k] + s : s;
+}
+
 // Bias gradient: plane sums of delta per (sample, filter), then the reduction over the batch.
 // db_tmp holds batch * K floats.
 int dbias_batch(float *dbias, int accumulate, const float *delta, int batch, int K, size_t plane, float *db_tmp, cudaStream_t s)
 {
     int r;
     if ((r = b200_summ_xy(db_tmp, batch, delta, batch, K, plane, s))) return r;
-    if (!accumulate) B200_CUDA(cudaMemsetAsync(dbias, 0, sizeof(float) * K, s));
-    return b200_add_sum_w(dbias, 1, dbias, 1, db_tmp, batch, (size_t)K, 1.f, 1.f, s);
+    dbias_reduce_kernel<<<ceil_div(K * 32, 256), 256, 0, s>>>(dbias, db_tmp, batch, K, accumulate);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
 }
 
 int tc_conv_wgrad_batch(const b200_conv_geom &g, float *dkernel, float *dbias, int accumulate, const float *image,

@@ -212,12 +212,13 @@ def test_pooling_and_resampling_bit_exact(ops, port):
         assert down.cpu().numpy().tobytes() == port.downsample(xs, 2, 2).tobytes()
 
 
-@pytest.mark.parametrize("batch", [5, 24, 64, 100, 130])      # every register-resident variant and the general kernel
-def test_batchnorm_fused_bit_exact(ops, port, batch):
+@pytest.mark.parametrize("zyx", [(16, 8, 8), (5, 9, 11), (3, 7, 5)])    # rows 16-byte aligned (staged through shared memory) or not, ragged last block
+@pytest.mark.parametrize("batch", [5, 24, 64, 100, 130, 330])            # every register-resident variant and the general kernel
+def test_batchnorm_fused_bit_exact(ops, port, batch, zyx):
     r = np.random.default_rng(3)
-    x = r.normal(1.5, 2.0, (batch, 16, 8, 8)).astype(np.float32)
-    gamma = r.normal(1, 0.1, (1, 16, 8, 8)).astype(np.float32)
-    beta = r.normal(0, 0.1, (1, 16, 8, 8)).astype(np.float32)
+    x = r.normal(1.5, 2.0, (batch,) + zyx).astype(np.float32)
+    gamma = r.normal(1, 0.1, (1,) + zyx).astype(np.float32)
+    beta = r.normal(0, 0.1, (1,) + zyx).astype(np.float32)
     nm = r.normal(0, 1, gamma.shape).astype(np.float32)
     nv = np.abs(r.normal(1, 0.1, gamma.shape)).astype(np.float32)
     want = port.bn_forward(x, gamma[0], beta[0], 0.9, 1e-6, nm[0], nv[0])

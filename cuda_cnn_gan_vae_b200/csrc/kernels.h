@@ -45,6 +45,11 @@ struct ActPack {
 constexpr size_t kPackPad = 256;
 ActPack act_pack_shape(int n, int c, int h, int w, int sy, int sx);
 int act_pack_fill(const ActPack &pk, const float *src, cudaStream_t s);
+// The same pack with the first stage of a bias gradient fused in: rowsum (act_pack_rowsum_elems floats) receives partial
+// plane sums [n][c][runs]; *runs == 0 on return means the shape took the scalar pack kernel and no sums were produced.
+size_t act_pack_rowsum_elems(const ActPack &pk);
+int act_pack_fill_with_sums(const ActPack &pk, const float *src, float *rowsum, int *runs, cudaStream_t s);
+int dbias_from_rowsums(float *dbias, int accumulate, const float *rowsum, int batch, int K, int runs, cudaStream_t s);
 size_t weight_pack_elems(const b200_conv_geom &g, bool backward);
 int weight_pack_fill(const b200_conv_geom &g, bool backward, const float *kernel, float *hi, float *lo, cudaStream_t s);
 int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack &act, const float *w_hi, const float *w_lo,

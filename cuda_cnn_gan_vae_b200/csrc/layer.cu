@@ -6,6 +6,7 @@
 // packed output error is made once for both the input error and the weight gradient.
 #include "common.cuh"
 #include "kernels.h"
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -58,7 +59,8 @@ static ActPack er_shape(const b200_conv_layer *l)
                          : act_pack_shape(l->batch, g.kernel_amount, g.out_y, g.out_x, 1, 1);
 }
 
-static int pack_into(b200_conv_layer *l, int hi_slot, ActPack &pk, const float *src, bool x3, cudaStream_t s)
+// rowsum_runs != NULL: the pack also leaves partial plane sums of src in the DB_TMP buffer (first stage of the bias gradient)
+static int pack_into(b200_conv_layer *l, int hi_slot, ActPack &pk, const float *src, bool x3, cudaStream_t s, int *rowsum_runs = nullptr)
 {
     int r;
     const size_t bytes = sizeof(float) * pk.elems() + kPackPad;
@@ -66,7 +68,9 @@ static int pack_into(b200_conv_layer *l, int hi_slot, ActPack &pk, const float *
     if (x3 && (r = ensure(l, hi_slot + 1, bytes, s))) return r;
     pk.hi = l->buf[hi_slot];
     pk.lo = x3 ? l->buf[hi_slot + 1] : nullptr;
-    return act_pack_fill(pk, src, s);
+    if (!rowsum_runs) return act_pack_fill(pk, src, s);
+    if ((r = ensure(l, b200_conv_layer::DB_TMP, sizeof(float) * act_pack_rowsum_elems(pk), s))) return r;
+    return act_pack_fill_with_sums(pk, src, l->buf[b200_conv_layer::DB_TMP], rowsum_runs, s);
 }
 
 static int pack_weights(b200_conv_layer *l, bool backward, const float *kernel, bool x3, cudaStream_t s)
@@ -153,7 +157,11 @@ int b200_conv_layer_backward(b200_conv_layer *l, float *input_delta, float *dker
     if (prec != B200_FP32) {
         const bool x3 = prec == B200_TF32X3;
         ActPack in = in_shape(l), er = er_shape(l);
-        r = pack_into(l, b200_conv_layer::ER_HI, er, output_delta, x3, s);
+        // a convolution layer's bias gradient is the plane sum of the output error: its first stage rides on the pack
+        int sum_runs = 0;
+        static const bool fuse_sums = !(getenv("B200CONV_FUSE_DBIAS") && getenv("B200CONV_FUSE_DBIAS")[0] == '0');   // debug switch
+        const bool want_sums = fuse_sums && !l->transposed && dkernel && dbias;
+        r = pack_into(l, b200_conv_layer::ER_HI, er, output_delta, x3, s, want_sums ? &sum_runs : nullptr);
         if (r == B200_OK && input_delta) {
             // error of the layer input: BackwardConvolution for a convolution layer, ForwardConvolution
             // (zero bias) for a transposed-convolution layer
@@ -177,6 +185,8 @@ int b200_conv_layer_backward(b200_conv_layer *l, float *input_delta, float *dker
                 if (l->transposed) {
                     // the reference clears the bias gradient of this layer (cuda/ctensorconv.cu.h:1221)
                     if (!accumulate) B200_CUDA(cudaMemsetAsync(dbias, 0, sizeof(float) * g.kernel_amount, s));
+                } else if (sum_runs > 0) {
+                    r = dbias_from_rowsums(dbias, accumulate, l->buf[b200_conv_layer::DB_TMP], l->batch, g.kernel_amount, sum_runs, s);
                 } else if ((r = ensure(l, b200_conv_layer::DB_TMP, sizeof(float) * (size_t)l->batch * g.kernel_amount, s)) == B200_OK) {
                     r = dbias_batch(dbias, accumulate, output_delta, l->batch, g.kernel_amount, (size_t)g.out_y * g.out_x,
                                     l->buf[b200_conv_layer::DB_TMP], s);

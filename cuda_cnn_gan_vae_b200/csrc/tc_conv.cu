@@ -507,35 +507,47 @@ __global__ void pack_act_kernel(const float *__restrict__ src, float *__restrict
 // thread.  Needs W % 4 == 0 and a 16-byte aligned source.
 __global__ void __launch_bounds__(256)
 pack_act_vec_kernel(const float *__restrict__ src, float *__restrict__ hi, float *__restrict__ lo,
-                    int N, int C, int H, int W, int Cp, int sy, int sx, int Hs, int Ws)
+                    int N, int C, int H, int W, int Cp, int sy, int sx, int Hs, int Ws, int rows_per_block, float *__restrict__ rowsum)
 {
     __shared__ float tile[32][33];
-    const int n = blockIdx.z, h = blockIdx.y, w0 = blockIdx.x * 32;
+    const int n = blockIdx.z, h0 = blockIdx.y * rows_per_block, w0 = blockIdx.x * 32;
+    const int h1 = min(h0 + rows_per_block, Hs * sy);
     const int tid = threadIdx.x;
     const int lc = tid >> 3, lq = tid & 7;          // load role: channel lc of the chunk, pixel quad lq
     const int sp = tid >> 3, sq = tid & 7;          // store role: pixel sp of the tile, channel quad sq
-    const bool row_ok = h < H;
-    const int hq = h / sy, hr = h % sy;
     const int wl = w0 + 4 * lq;
     const int ws = w0 + sp;
-    const int ph = hr * sx + (ws % sx);
-    const size_t obase = ((((size_t)ph * N + n) * Hs + hq) * Ws + (ws / sx)) * Cp;
     for (int c0 = 0; c0 < Cp; c0 += 32) {
         const int c = c0 + lc;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (row_ok && c < C && wl < W) v = *reinterpret_cast<const float4 *>(src + (((size_t)n * C + c) * H + h) * W + wl);
-        tile[lc][4 * lq + 0] = v.x; tile[lc][4 * lq + 1] = v.y; tile[lc][4 * lq + 2] = v.z; tile[lc][4 * lq + 3] = v.w;
-        __syncthreads();
         const int cq = c0 + 4 * sq;
-        if (ws < Ws * sx && cq < Cp) {
-            float4 a = make_float4(tile[4 * sq + 0][sp], tile[4 * sq + 1][sp], tile[4 * sq + 2][sp], tile[4 * sq + 3][sp]);
-            float4 b = make_float4(ptx::to_tf32(a.x), ptx::to_tf32(a.y), ptx::to_tf32(a.z), ptx::to_tf32(a.w));
-            *reinterpret_cast<float4 *>(hi + obase + cq) = b;
-            if (lo)
-                *reinterpret_cast<float4 *>(lo + obase + cq) =
-                    make_float4(ptx::to_tf32(a.x - b.x), ptx::to_tf32(a.y - b.y), ptx::to_tf32(a.z - b.z), ptx::to_tf32(a.w - b.w));
+        float acc = 0.f;                            // this thread's share of the plane sum of channel c (bias gradient)
+        for (int h = h0; h < h1; h++) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (h < H && c < C && wl < W) v = *reinterpret_cast<const float4 *>(src + (((size_t)n * C + c) * H + h) * W + wl);
+            acc += (v.x + v.y) + (v.z + v.w);
+            tile[lc][4 * lq + 0] = v.x; tile[lc][4 * lq + 1] = v.y; tile[lc][4 * lq + 2] = v.z; tile[lc][4 * lq + 3] = v.w;
+            __syncthreads();
+            if (ws < Ws * sx && cq < Cp) {
+                const int hq = h / sy, hr = h % sy;
+                const int ph = hr * sx + (ws % sx);
+                const size_t obase = ((((size_t)ph * N + n) * Hs + hq) * Ws + (ws / sx)) * Cp;
+                float4 a = make_float4(tile[4 * sq + 0][sp], tile[4 * sq + 1][sp], tile[4 * sq + 2][sp], tile[4 * sq + 3][sp]);
+                float4 b = make_float4(ptx::to_tf32(a.x), ptx::to_tf32(a.y), ptx::to_tf32(a.z), ptx::to_tf32(a.w));
+                *reinterpret_cast<float4 *>(hi + obase + cq) = b;
+                if (lo)
+                    *reinterpret_cast<float4 *>(lo + obase + cq) =
+                        make_float4(ptx::to_tf32(a.x - b.x), ptx::to_tf32(a.y - b.y), ptx::to_tf32(a.z - b.z), ptx::to_tf32(a.w - b.w));
+            }
+            __syncthreads();
         }
-        __syncthreads();
+        if (rowsum) {
+            // first stage of the bias gradient: the 8 threads that hold channel c are neighbours in a warp; one partial sum
+            // per block and channel goes to rowsum[n][c][row group][x block]
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+            if (lq == 0 && c < C) rowsum[(((size_t)n * C + c) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x] = acc;
+        }
     }
 }
 
@@ -889,15 +901,63 @@ static void set_mnmajor(TcParams &p, bool a_side, int extent)
     else { p.b_boxes = 1; p.b_box_bytes = (uint32_t)(extent / 32) * 4096; p.b_lbo = 4096; p.b_sbo = 512; p.b_kadv = 1024; p.b_layout = 1; }
 }
 
+// rowsum (optional, act_pack_rowsum_elems floats): receives per-block partial plane sums when the vector kernel runs;
+// *rowsum_runs tells the caller how many partial sums each (image, channel) got (0: not produced).
 static int pack_act(const float *src, float *hi, float *lo, int N, int C, int H, int W, int Cp, int sy, int sx, int Hs, int Ws,
-                    cudaStream_t s)
+                    cudaStream_t s, float *rowsum = nullptr, int *rowsum_runs = nullptr)
 {
     dim3 grid(ceil_div(Ws * sx, 32), Hs * sy, N), block(32, 8);
     if (grid.y > 65535 || grid.z > 65535) return TC_UNSUPPORTED;
-    if (W % 4 == 0 && ((uintptr_t)src & 15) == 0)
-        pack_act_vec_kernel<<<grid, 256, 0, s>>>(src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws);
-    else
+    if (rowsum_runs) *rowsum_runs = 0;
+    if (W % 4 == 0 && ((uintptr_t)src & 15) == 0) {
+        // with the bias-gradient sums fused in, a block walks 8 rows so that it leaves one partial sum per 8 rows and channel
+        const int rows_per_block = rowsum ? 8 : 1;
+        dim3 vgrid(grid.x, ceil_div((int)grid.y, rows_per_block), N);
+        pack_act_vec_kernel<<<vgrid, 256, 0, s>>>(src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws, rows_per_block, rowsum);
+        if (rowsum && rowsum_runs) *rowsum_runs = (int)(vgrid.x * vgrid.y);
+    } else
         pack_act_kernel<<<grid, block, 0, s>>>(src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+// dbias[c] (+)= sum over images and partial sums of rowsum[n][c][runs]; one block per channel, its threads stride over the
+// (image, partial sum) pairs and combine in a fixed shuffle / shared-memory tree (reproducible run to run)
+__global__ void __launch_bounds__(256) dbias_from_rowsums_kernel(float *__restrict__ dbias, const float *__restrict__ rowsum, int N, int C, int runs,
+                                                                 int accumulate)
+{
+    __shared__ float part[8];
+    const int c = blockIdx.x;
+    const int total = N * runs;
+    float s = 0.f;
+    for (int j = threadIdx.x; j < total; j += 256) {
+        const int n = j / runs, r = j - n * runs;
+        s += rowsum[((size_t)n * C + c) * runs + r];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = part[0];
+        for (int w = 1; w < 8; w++) t += part[w];
+        dbias[c] = accumulate ? dbias[c] + t : t;
+    }
+}
+
+size_t act_pack_rowsum_elems(const ActPack &pk)
+{
+    return (size_t)pk.n * pk.c * (size_t)(pk.hs * pk.sy) * ceil_div(pk.ws * pk.sx, 32);      // an upper bound: one sum per row
+}
+
+int act_pack_fill_with_sums(const ActPack &pk, const float *src, float *rowsum, int *runs, cudaStream_t s)
+{
+    return pack_act(src, pk.hi, pk.lo, pk.n, pk.c, pk.h, pk.w, pk.cp, pk.sy, pk.sx, pk.hs, pk.ws, s, rowsum, runs);
+}
+
+int dbias_from_rowsums(float *dbias, int accumulate, const float *rowsum, int batch, int K, int runs, cudaStream_t s)
+{
+    dbias_from_rowsums_kernel<<<K, 256, 0, s>>>(dbias, rowsum, batch, K, runs, accumulate);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }

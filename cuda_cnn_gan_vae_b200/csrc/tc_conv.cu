@@ -911,7 +911,8 @@ static int pack_act(const float *src, float *hi, float *lo, int N, int C, int H,
     if (rowsum_runs) *rowsum_runs = 0;
     if (W % 4 == 0 && ((uintptr_t)src & 15) == 0) {
         // with the bias-gradient sums fused in, a block walks 8 rows so that it leaves one partial sum per 8 rows and channel
-        const int rows_per_block = rowsum ? 8 : 1;
+        int rows_per_block = rowsum ? 8 : 1;
+        while (rows_per_block > 1 && (long long)grid.x * ceil_div((int)grid.y, rows_per_block) * N < 8LL * sm_count()) rows_per_block /= 2;
         dim3 vgrid(grid.x, ceil_div((int)grid.y, rows_per_block), N);
         pack_act_vec_kernel<<<vgrid, 256, 0, s>>>(src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws, rows_per_block, rowsum);
         if (rowsum && rowsum_runs) *rowsum_runs = (int)(vgrid.x * vgrid.y);

@@ -59,6 +59,15 @@ int wgrad_gemm(const b200_conv_geom &g, float *dkernel, int accumulate, const Ac
                bool x3, cudaStream_t s);
 int dbias_batch(float *dbias, int accumulate, const float *delta, int batch, int K, size_t plane, float *db_tmp, cudaStream_t s);
 
+// smallc.cu -- layers with very few channels on one side: the taps are folded into the channel dimension (explicit
+// im2col, C' = taps*C) and the contractions run as 1x1 convolutions on the tensor-core kernel
+bool smallc_applies(const b200_conv_geom &g);
+b200_conv_geom smallc_geom(const b200_conv_geom &g);          // in_z = C', 1x1 kernel on the out_y x out_x plane
+int im2col_pack(const b200_conv_geom &g, const ActPack &col, const float *x, int batch, cudaStream_t s);
+int smallc_weights(const b200_conv_geom &g, const float *kernel, float *hi, float *lo, int pitch, bool transposed, cudaStream_t s);
+int col2im_gather(const b200_conv_geom &g, float *dx, const float *t, int batch, cudaStream_t s);
+int smallc_dkernel(const b200_conv_geom &g, float *dkernel, const float *dk, int accumulate, cudaStream_t s);
+
 // Status word written by device-side waits that gave up (0 = none); clear != 0 resets it.
 unsigned tc_read_status(int clear);
 // device pointer of the per-device status word (pinned, mapped host memory) that bounded device-side waits report into

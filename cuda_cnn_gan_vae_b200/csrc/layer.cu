@@ -15,11 +15,13 @@ struct b200_conv_layer {
     int batch;
     int transposed;
     int device;
-    enum { IN_HI, IN_LO, ER_HI, ER_LO, W_HI, W_LO, PARTIAL, DB_TMP, NBUF };
+    enum { IN_HI, IN_LO, ER_HI, ER_LO, W_HI, W_LO, PARTIAL, DB_TMP, COL_HI, COL_LO, TMP, DK_TMP, NBUF };
     float *buf[NBUF];
     size_t cap[NBUF];            // bytes
     int in_valid;                // the kept input pack matches the last forward call
     int in_precision;
+    int col_valid;               // the kept im2col copy of the layer input matches the last forward call (few-channel layers)
+    int col_precision;
 };
 
 namespace b200 {
@@ -82,6 +84,80 @@ static int pack_weights(b200_conv_layer *l, bool backward, const float *kernel, 
     return weight_pack_fill(l->g, backward, kernel, l->buf[b200_conv_layer::W_HI], x3 ? l->buf[b200_conv_layer::W_LO] : nullptr, s);
 }
 
+// ---- few-channel layers (smallc.cu): taps folded into the channel dimension, contractions as 1x1 convolutions ------------
+static bool use_smallc(const b200_conv_layer *l)
+{
+    static const bool enabled = !(getenv("B200CONV_SMALLC") && getenv("B200CONV_SMALLC")[0] == '0');      // debug switch
+    return enabled && smallc_applies(l->g);
+}
+
+static ActPack col_shape(const b200_conv_layer *l)
+{
+    const b200_conv_geom &g = l->g;
+    return act_pack_shape(l->batch, g.in_z * g.kernel_x * g.kernel_y, g.out_y, g.out_x, 1, 1);
+}
+
+// im2col copy of `src` (the tensor with the few channels) into the COL buffers
+static int col_into(b200_conv_layer *l, ActPack &col, const float *src, bool x3, cudaStream_t s)
+{
+    int r;
+    col = col_shape(l);
+    const size_t bytes = sizeof(float) * col.elems() + kPackPad;
+    if ((r = ensure(l, b200_conv_layer::COL_HI, bytes, s))) return r;
+    if (x3 && (r = ensure(l, b200_conv_layer::COL_LO, bytes, s))) return r;
+    col.hi = l->buf[b200_conv_layer::COL_HI];
+    col.lo = x3 ? l->buf[b200_conv_layer::COL_LO] : nullptr;
+    return im2col_pack(l->g, col, src, l->batch, s);
+}
+
+static int smallc_weights_into(b200_conv_layer *l, const float *kernel, int pitch, bool transposed, bool x3, cudaStream_t s)
+{
+    int r;
+    const b200_conv_geom &g = l->g;
+    const size_t rows = transposed ? (size_t)g.in_z * g.kernel_x * g.kernel_y : (size_t)g.kernel_amount;
+    const size_t bytes = sizeof(float) * rows * pitch + kPackPad;
+    if ((r = ensure(l, b200_conv_layer::W_HI, bytes, s))) return r;
+    if (x3 && (r = ensure(l, b200_conv_layer::W_LO, bytes, s))) return r;
+    return smallc_weights(g, kernel, l->buf[b200_conv_layer::W_HI], x3 ? l->buf[b200_conv_layer::W_LO] : nullptr, pitch, transposed, s);
+}
+
+// out[n, k, oy, ox] = sum_c' W'[k][c'] col[n, oy, ox, c'] (+ bias): the convolution of the few-channel tensor
+static int smallc_conv(b200_conv_layer *l, float *out, const ActPack &col, const float *kernel, const float *bias, bool x3, cudaStream_t s)
+{
+    int r;
+    if ((r = smallc_weights_into(l, kernel, col.cp, false, x3, s))) return r;
+    return conv_gemm(false, smallc_geom(l->g), out, col, l->buf[b200_conv_layer::W_HI], l->buf[b200_conv_layer::W_LO], bias, x3, s);
+}
+
+// dx = col2im(W''^T delta): the transposed convolution towards the few-channel tensor; `many` is the pack of the
+// many-channel tensor (kernel_amount channels on the out_y x out_x plane)
+static int smallc_tconv(b200_conv_layer *l, float *dx, const ActPack &many, const float *kernel, bool x3, cudaStream_t s)
+{
+    int r;
+    const b200_conv_geom &g = l->g;
+    const int cc = g.in_z * g.kernel_x * g.kernel_y;
+    if ((r = smallc_weights_into(l, kernel, many.cp, true, x3, s))) return r;
+    if ((r = ensure(l, b200_conv_layer::TMP, sizeof(float) * (size_t)l->batch * cc * g.out_y * g.out_x, s))) return r;
+    b200_conv_geom q = smallc_geom(g);
+    q.in_z = g.kernel_amount;
+    q.kernel_amount = cc;
+    if ((r = conv_gemm(false, q, l->buf[b200_conv_layer::TMP], many, l->buf[b200_conv_layer::W_HI], l->buf[b200_conv_layer::W_LO], nullptr, x3, s)))
+        return r;
+    return col2im_gather(g, dx, l->buf[b200_conv_layer::TMP], l->batch, s);
+}
+
+// dkernel (+)= sum over positions of many x col, re-ordered into the reference's [k][c*taps + tap]
+static int smallc_wgrad(b200_conv_layer *l, float *dkernel, int accumulate, const ActPack &col, const ActPack &many, bool x3, cudaStream_t s)
+{
+    int r;
+    const b200_conv_geom &g = l->g;
+    const b200_conv_geom q = smallc_geom(g);
+    if ((r = ensure(l, b200_conv_layer::PARTIAL, sizeof(float) * wgrad_partial_elems(q, l->batch), s))) return r;
+    if ((r = ensure(l, b200_conv_layer::DK_TMP, sizeof(float) * (size_t)g.kernel_amount * q.in_z, s))) return r;
+    if ((r = wgrad_gemm(q, l->buf[b200_conv_layer::DK_TMP], 0, col, many, l->buf[b200_conv_layer::PARTIAL], x3, s))) return r;
+    return smallc_dkernel(g, dkernel, l->buf[b200_conv_layer::DK_TMP], accumulate, s);
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -125,6 +201,22 @@ int b200_conv_layer_forward(b200_conv_layer *l, float *out, const float *input, 
     const int prec = precision();
     l->in_valid = 0;
     int r = TC_UNSUPPORTED;
+    l->col_valid = 0;
+    if (prec != B200_FP32 && use_smallc(l)) {
+        const bool x3 = prec == B200_TF32X3;
+        if (!l->transposed) {
+            ActPack col;
+            if ((r = col_into(l, col, input, x3, s)) == B200_OK) r = smallc_conv(l, out, col, kernel, bias, x3, s);
+            if (r == B200_OK) { l->col_valid = 1; l->col_precision = prec; }
+        } else {
+            ActPack in = in_shape(l);
+            if ((r = pack_into(l, b200_conv_layer::IN_HI, in, input, x3, s)) == B200_OK) r = smallc_tconv(l, out, in, kernel, x3, s);
+            if (r == B200_OK) { l->in_valid = 1; l->in_precision = prec; }
+        }
+        if (r == B200_OK) { set_path(B200_PATH_TCGEN05); return r; }
+        if (r != TC_UNSUPPORTED) return r;
+        l->in_valid = l->col_valid = 0;
+    }
     if (prec != B200_FP32) {
         const bool x3 = prec == B200_TF32X3;
         ActPack in = in_shape(l);
@@ -154,6 +246,51 @@ int b200_conv_layer_backward(b200_conv_layer *l, float *input_delta, float *dker
     const b200_conv_geom &g = l->g;
     const int prec = precision();
     int r = TC_UNSUPPORTED;
+    if (prec != B200_FP32 && use_smallc(l)) {
+        const bool x3 = prec == B200_TF32X3;
+        if (!l->transposed) {
+            // the output error has the many channels: packed once (with the bias gradient's plane sums) for both products
+            ActPack er = er_shape(l), col;
+            int sum_runs = 0;
+            const bool want_sums = dkernel && dbias;
+            r = pack_into(l, b200_conv_layer::ER_HI, er, output_delta, x3, s, want_sums ? &sum_runs : nullptr);
+            if (r == B200_OK && input_delta) r = smallc_tconv(l, input_delta, er, kernel, x3, s);
+            if (r == B200_OK && dkernel) {
+                if (l->col_valid && l->col_precision == prec) {
+                    col = col_shape(l);
+                    col.hi = l->buf[b200_conv_layer::COL_HI];
+                    col.lo = x3 ? l->buf[b200_conv_layer::COL_LO] : nullptr;
+                } else {
+                    r = col_into(l, col, input, x3, s);
+                }
+                if (r == B200_OK) r = smallc_wgrad(l, dkernel, accumulate, col, er, x3, s);
+                if (r == B200_OK && dbias) {
+                    if (sum_runs > 0) r = dbias_from_rowsums(dbias, accumulate, l->buf[b200_conv_layer::DB_TMP], l->batch, g.kernel_amount, sum_runs, s);
+                    else if ((r = ensure(l, b200_conv_layer::DB_TMP, sizeof(float) * (size_t)l->batch * g.kernel_amount, s)) == B200_OK)
+                        r = dbias_batch(dbias, accumulate, output_delta, l->batch, g.kernel_amount, (size_t)g.out_y * g.out_x,
+                                        l->buf[b200_conv_layer::DB_TMP], s);
+                }
+            }
+        } else {
+            // the output error has the few channels: its im2col copy serves the input error and the weight gradient
+            ActPack col, in = in_shape(l);
+            r = col_into(l, col, output_delta, x3, s);
+            if (r == B200_OK && input_delta) r = smallc_conv(l, input_delta, col, kernel, nullptr, x3, s);
+            if (r == B200_OK && dkernel) {
+                if (l->in_valid && l->in_precision == prec) {
+                    in.hi = l->buf[b200_conv_layer::IN_HI];
+                    in.lo = x3 ? l->buf[b200_conv_layer::IN_LO] : nullptr;
+                } else {
+                    r = pack_into(l, b200_conv_layer::IN_HI, in, input, x3, s);
+                }
+                if (r == B200_OK) r = smallc_wgrad(l, dkernel, accumulate, col, in, x3, s);
+                // the reference clears the bias gradient of this layer (cuda/ctensorconv.cu.h:1221)
+                if (r == B200_OK && dbias && !accumulate) B200_CUDA(cudaMemsetAsync(dbias, 0, sizeof(float) * g.kernel_amount, s));
+            }
+        }
+        if (r == B200_OK) { set_path(B200_PATH_TCGEN05); return r; }
+        if (r != TC_UNSUPPORTED) return r;
+    }
     if (prec != B200_FP32) {
         const bool x3 = prec == B200_TF32X3;
         ActPack in = in_shape(l), er = er_shape(l);

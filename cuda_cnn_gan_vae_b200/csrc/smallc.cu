@@ -1,0 +1,166 @@
+// Layers with very few channels on one side (the RGB end of every network: 3 -> 64 convolutions, 64 -> 3 transposed
+// convolutions).  The implicit GEMM stages 32 channels per tap, so with 3 channels nine tenths of every staged tile and of
+// every MMA are zeros.  Here the taps are folded into the channel dimension instead (explicit im2col of the small-channel
+// tensor: C' = taps x C "channels" per output position) and the three contractions become 1x1 convolutions on the
+// tensor-core kernel:
+//   forward        y[n,k,oy,ox]      = sum_c' W'[k][c'] col[n,oy,ox,c']                       (conv_gemm, 1x1)
+//   backward-data  t[n,c',oy,ox]     = sum_k W''[c'][k] delta[n,k,oy,ox]  then  dx = col2im(t)  (conv_gemm 1x1 + gather)
+//   weight grad.   dW'[k][c']        = sum_{n,oy,ox} delta[n,k,oy,ox] col[n,oy,ox,c']          (wgrad_gemm, 1x1) then re-ordered
+// with c' = tap * C + c.  col is written once per layer call (high and, in 3xTF32 mode, low TF32 planes) and is
+// taps/stride^2 times the size of the small tensor -- a few MB.
+#include "common.cuh"
+#include "kernels.h"
+#include "tc_ptx.cuh"
+
+namespace b200 {
+
+// col[n][oy][ox][tap*C + c] = x[n][c][oy*sy + ky - py][ox*sx + kx - px] (0 outside), pitch cp floats per position
+__global__ void im2col_pack_kernel(float *__restrict__ hi, float *__restrict__ lo, const float *__restrict__ x, int N, int C, int H, int W,
+                                   int OH, int OW, int kh, int kw, int sy, int sx, int py, int px, int cp)
+{
+    const int cc = C * kh * kw;
+    const size_t total = (size_t)N * OH * OW * cp;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int j = (int)(idx % cp);
+        size_t t = idx / cp;
+        const int ox = (int)(t % OW); t /= OW;
+        const int oy = (int)(t % OH);
+        const int n = (int)(t / OH);
+        float v = 0.f;
+        if (j < cc) {
+            const int tap = j / C, c = j - tap * C;
+            const int ky = tap / kw, kx = tap - ky * kw;
+            const int iy = oy * sy + ky - py, ix = ox * sx + kx - px;
+            if (iy >= 0 && iy < H && ix >= 0 && ix < W) v = x[(((size_t)n * C + c) * H + iy) * W + ix];
+        }
+        const float h = ptx::to_tf32(v);
+        hi[idx] = h;
+        if (lo) lo[idx] = ptx::to_tf32(v - h);
+    }
+}
+
+// forward weights  W'[k][tap*C + c] (pitch cp)  = W[k][c*taps + tap]
+// backward weights W''[tap*C + c][k] (pitch kp) = W[k][c*taps + tap]
+__global__ void smallc_weight_kernel(float *__restrict__ hi, float *__restrict__ lo, const float *__restrict__ w, int K, int C, int taps,
+                                     int pitch, int transposed)
+{
+    const int cc = C * taps;
+    const int rows = transposed ? cc : K, inner = transposed ? K : cc;
+    const size_t total = (size_t)rows * pitch;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int i = (int)(idx % pitch), r = (int)(idx / pitch);
+        float v = 0.f;
+        if (i < inner) {
+            const int k = transposed ? i : r, j = transposed ? r : i;
+            const int tap = j / C, c = j - tap * C;
+            v = w[((size_t)k * C + c) * taps + tap];
+        }
+        const float h = ptx::to_tf32(v);
+        hi[idx] = h;
+        if (lo) lo[idx] = ptx::to_tf32(v - h);
+    }
+}
+
+// dx[n][c][y][x] = sum over the taps (ky,kx) with (y + py - ky) % sy == 0 and (x + px - kx) % sx == 0 (and the quotient
+// inside the OH x OW plane) of t[n][(ky*kw + kx)*C + c][(y + py - ky)/sy][(x + px - kx)/sx]
+__global__ void col2im_gather_kernel(float *__restrict__ dx, const float *__restrict__ t, int N, int C, int H, int W, int OH, int OW,
+                                     int kh, int kw, int sy, int sx, int py, int px)
+{
+    const int cc = C * kh * kw;
+    const size_t total = (size_t)N * C * H * W;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int x = (int)(idx % W);
+        size_t r = idx / W;
+        const int y = (int)(r % H); r /= H;
+        const int c = (int)(r % C);
+        const int n = (int)(r / C);
+        float s = 0.f;
+        for (int ky = 0; ky < kh; ky++) {
+            const int ny = y + py - ky;
+            if (ny < 0 || ny % sy) continue;
+            const int oy = ny / sy;
+            if (oy >= OH) continue;
+            for (int kx = 0; kx < kw; kx++) {
+                const int nx = x + px - kx;
+                if (nx < 0 || nx % sx) continue;
+                const int ox = nx / sx;
+                if (ox >= OW) continue;
+                s += t[(((size_t)n * cc + (ky * kw + kx) * C + c) * OH + oy) * OW + ox];
+            }
+        }
+        dx[idx] = s;
+    }
+}
+
+// dkernel[k][c*taps + tap] (+)= dk[k][tap*C + c]
+__global__ void smallc_dkernel_kernel(float *__restrict__ dkernel, const float *__restrict__ dk, int K, int C, int taps, int accumulate)
+{
+    const int cc = C * taps;
+    const int total = K * cc;
+    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+        const int k = idx / cc, j = idx - k * cc;
+        const int c = j / taps, tap = j - c * taps;
+        const float v = dk[(size_t)k * cc + tap * C + c];
+        dkernel[idx] = accumulate ? dkernel[idx] + v : v;
+    }
+}
+
+static inline int grid_for(size_t total)
+{
+    size_t blocks = (total + 255) / 256, cap = (size_t)sm_count() * 16;
+    return (int)(blocks < 1 ? 1 : (blocks < cap ? blocks : cap));
+}
+
+bool smallc_applies(const b200_conv_geom &g)
+{
+    const int cc = g.in_z * g.kernel_x * g.kernel_y;
+    return g.in_z <= 8 && cc <= 256 && g.kernel_x * g.kernel_y > 1;
+}
+
+b200_conv_geom smallc_geom(const b200_conv_geom &g)
+{
+    b200_conv_geom q = g;
+    q.in_z = g.in_z * g.kernel_x * g.kernel_y;
+    q.in_y = g.out_y; q.in_x = g.out_x;
+    q.kernel_x = q.kernel_y = 1;
+    q.stride_x = q.stride_y = 1;
+    q.padding_x = q.padding_y = 0;
+    return q;
+}
+
+int im2col_pack(const b200_conv_geom &g, const ActPack &col, const float *x, int batch, cudaStream_t s)
+{
+    const size_t total = (size_t)batch * g.out_y * g.out_x * col.cp;
+    im2col_pack_kernel<<<grid_for(total), 256, 0, s>>>(col.hi, col.lo, x, batch, g.in_z, g.in_y, g.in_x, g.out_y, g.out_x, g.kernel_y,
+                                                      g.kernel_x, g.stride_y, g.stride_x, g.padding_y, g.padding_x, col.cp);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+int smallc_weights(const b200_conv_geom &g, const float *kernel, float *hi, float *lo, int pitch, bool transposed, cudaStream_t s)
+{
+    const int taps = g.kernel_x * g.kernel_y;
+    const size_t total = (size_t)(transposed ? g.in_z * taps : g.kernel_amount) * pitch;
+    smallc_weight_kernel<<<grid_for(total), 256, 0, s>>>(hi, lo, kernel, g.kernel_amount, g.in_z, taps, pitch, transposed ? 1 : 0);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+int col2im_gather(const b200_conv_geom &g, float *dx, const float *t, int batch, cudaStream_t s)
+{
+    const size_t total = (size_t)batch * g.in_z * g.in_y * g.in_x;
+    col2im_gather_kernel<<<grid_for(total), 256, 0, s>>>(dx, t, batch, g.in_z, g.in_y, g.in_x, g.out_y, g.out_x, g.kernel_y, g.kernel_x,
+                                                        g.stride_y, g.stride_x, g.padding_y, g.padding_x);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+int smallc_dkernel(const b200_conv_geom &g, float *dkernel, const float *dk, int accumulate, cudaStream_t s)
+{
+    const int taps = g.kernel_x * g.kernel_y;
+    smallc_dkernel_kernel<<<grid_for((size_t)g.kernel_amount * g.in_z * taps), 256, 0, s>>>(dkernel, dk, g.kernel_amount, g.in_z, taps, accumulate);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+}  // namespace b200

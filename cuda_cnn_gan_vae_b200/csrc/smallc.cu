@@ -14,28 +14,30 @@
 
 namespace b200 {
 
-// col[n][oy][ox][tap*C + c] = x[n][c][oy*sy + ky - py][ox*sx + kx - px] (0 outside), pitch cp floats per position
+// col[n][oy][ox][tap*C + c] = x[n][c][oy*sy + ky - py][ox*sx + kx - px] (0 outside), pitch cp floats per position.
+// One block per (n, oy) row of positions; its threads walk (ox, c') with c' fastest, so the writes are contiguous.
 __global__ void im2col_pack_kernel(float *__restrict__ hi, float *__restrict__ lo, const float *__restrict__ x, int N, int C, int H, int W,
                                    int OH, int OW, int kh, int kw, int sy, int sx, int py, int px, int cp)
 {
     const int cc = C * kh * kw;
-    const size_t total = (size_t)N * OH * OW * cp;
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-        const int j = (int)(idx % cp);
-        size_t t = idx / cp;
-        const int ox = (int)(t % OW); t /= OW;
-        const int oy = (int)(t % OH);
-        const int n = (int)(t / OH);
-        float v = 0.f;
-        if (j < cc) {
-            const int tap = j / C, c = j - tap * C;
-            const int ky = tap / kw, kx = tap - ky * kw;
-            const int iy = oy * sy + ky - py, ix = ox * sx + kx - px;
-            if (iy >= 0 && iy < H && ix >= 0 && ix < W) v = x[(((size_t)n * C + c) * H + iy) * W + ix];
+    const int row_elems = OW * cp;
+    for (int row = blockIdx.x; row < N * OH; row += gridDim.x) {
+        const int n = row / OH, oy = row - n * OH;
+        const float *xn = x + (size_t)n * C * H * W;
+        const size_t obase = (size_t)row * row_elems;
+        for (int t = threadIdx.x; t < row_elems; t += blockDim.x) {
+            const int ox = t / cp, j = t - ox * cp;
+            float v = 0.f;
+            if (j < cc) {
+                const int tap = j / C, c = j - tap * C;
+                const int ky = tap / kw, kx = tap - ky * kw;
+                const int iy = oy * sy + ky - py, ix = ox * sx + kx - px;
+                if (iy >= 0 && iy < H && ix >= 0 && ix < W) v = xn[((size_t)c * H + iy) * W + ix];
+            }
+            const float h = ptx::to_tf32(v);
+            hi[obase + t] = h;
+            if (lo) lo[obase + t] = ptx::to_tf32(v - h);
         }
-        const float h = ptx::to_tf32(v);
-        hi[idx] = h;
-        if (lo) lo[idx] = ptx::to_tf32(v - h);
     }
 }
 
@@ -62,33 +64,33 @@ __global__ void smallc_weight_kernel(float *__restrict__ hi, float *__restrict__
 }
 
 // dx[n][c][y][x] = sum over the taps (ky,kx) with (y + py - ky) % sy == 0 and (x + px - kx) % sx == 0 (and the quotient
-// inside the OH x OW plane) of t[n][(ky*kw + kx)*C + c][(y + py - ky)/sy][(x + px - kx)/sx]
+// inside the OH x OW plane) of t[n][(ky*kw + kx)*C + c][(y + py - ky)/sy][(x + px - kx)/sx].  One block per (n, c, y) row.
 __global__ void col2im_gather_kernel(float *__restrict__ dx, const float *__restrict__ t, int N, int C, int H, int W, int OH, int OW,
                                      int kh, int kw, int sy, int sx, int py, int px)
 {
     const int cc = C * kh * kw;
-    const size_t total = (size_t)N * C * H * W;
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-        const int x = (int)(idx % W);
-        size_t r = idx / W;
-        const int y = (int)(r % H); r /= H;
-        const int c = (int)(r % C);
-        const int n = (int)(r / C);
-        float s = 0.f;
-        for (int ky = 0; ky < kh; ky++) {
-            const int ny = y + py - ky;
-            if (ny < 0 || ny % sy) continue;
-            const int oy = ny / sy;
-            if (oy >= OH) continue;
-            for (int kx = 0; kx < kw; kx++) {
-                const int nx = x + px - kx;
-                if (nx < 0 || nx % sx) continue;
-                const int ox = nx / sx;
-                if (ox >= OW) continue;
-                s += t[(((size_t)n * cc + (ky * kw + kx) * C + c) * OH + oy) * OW + ox];
+    for (int row = blockIdx.x; row < N * C * H; row += gridDim.x) {
+        const int y = row % H;
+        const int nc = row / H;
+        const int c = nc % C, n = nc / C;
+        const float *tn = t + (size_t)n * cc * OH * OW;
+        for (int x = threadIdx.x; x < W; x += blockDim.x) {
+            float s = 0.f;
+            for (int ky = 0; ky < kh; ky++) {
+                const int ny = y + py - ky;
+                if (ny < 0 || ny % sy) continue;
+                const int oy = ny / sy;
+                if (oy >= OH) continue;
+                for (int kx = 0; kx < kw; kx++) {
+                    const int nx = x + px - kx;
+                    if (nx < 0 || nx % sx) continue;
+                    const int ox = nx / sx;
+                    if (ox >= OW) continue;
+                    s += tn[((size_t)((ky * kw + kx) * C + c) * OH + oy) * OW + ox];
+                }
             }
+            dx[(size_t)row * W + x] = s;
         }
-        dx[idx] = s;
     }
 }
 
@@ -130,8 +132,8 @@ b200_conv_geom smallc_geom(const b200_conv_geom &g)
 
 int im2col_pack(const b200_conv_geom &g, const ActPack &col, const float *x, int batch, cudaStream_t s)
 {
-    const size_t total = (size_t)batch * g.out_y * g.out_x * col.cp;
-    im2col_pack_kernel<<<grid_for(total), 256, 0, s>>>(col.hi, col.lo, x, batch, g.in_z, g.in_y, g.in_x, g.out_y, g.out_x, g.kernel_y,
+    const int rows = batch * g.out_y;
+    im2col_pack_kernel<<<rows < sm_count() * 32 ? rows : sm_count() * 32, 256, 0, s>>>(col.hi, col.lo, x, batch, g.in_z, g.in_y, g.in_x, g.out_y, g.out_x, g.kernel_y,
                                                       g.kernel_x, g.stride_y, g.stride_x, g.padding_y, g.padding_x, col.cp);
     B200_LAUNCH_CHECK();
     return B200_OK;
@@ -148,8 +150,9 @@ int smallc_weights(const b200_conv_geom &g, const float *kernel, float *hi, floa
 
 int col2im_gather(const b200_conv_geom &g, float *dx, const float *t, int batch, cudaStream_t s)
 {
-    const size_t total = (size_t)batch * g.in_z * g.in_y * g.in_x;
-    col2im_gather_kernel<<<grid_for(total), 256, 0, s>>>(dx, t, batch, g.in_z, g.in_y, g.in_x, g.out_y, g.out_x, g.kernel_y, g.kernel_x,
+    const int rows = batch * g.in_z * g.in_y;
+    const int threads = g.in_x >= 128 ? 128 : (g.in_x >= 64 ? 64 : 32);
+    col2im_gather_kernel<<<rows < sm_count() * 64 ? rows : sm_count() * 64, threads, 0, s>>>(dx, t, batch, g.in_z, g.in_y, g.in_x, g.out_y, g.out_x, g.kernel_y, g.kernel_x,
                                                         g.stride_y, g.stride_x, g.padding_y, g.padding_x);
     B200_LAUNCH_CHECK();
     return B200_OK;

@@ -1249,6 +1249,8 @@ int wgrad_gemm(const b200_conv_geom &g, float *dkernel, int accumulate, const Ac
     // channels per block: runs of about 64 consecutive weights (256 bytes) per filter on the output side
     int c_run = (64 + taps - 1) / taps;
     if (c_run > C) c_run = C;
+    // few filters and channels (1x1 products of the few-channel layers): shorter runs so that the splits are summed by more blocks
+    while (c_run > 1 && ceil_div(K, 32) * ceil_div(C, c_run) < 2 * sm_count()) c_run = (c_run + 1) / 2;
     const size_t tile_bytes = sizeof(float) * (size_t)taps * c_run * 33;
     if (tile_bytes <= 48 * 1024) {
         const int blocks = ceil_div(K, 32) * ceil_div(C, c_run);

@@ -346,12 +346,24 @@ def main():
 
     layer = ops.ConvLayer(Cc, H, W, K, k, k, 1, 1, 1, 1, B)
 
+    side = torch.cuda.Stream() if world > 1 else None
+
     def step():
-        # the layer's Forward and TrainingBackward (netlayer/cnetlayerconvolution.cu.h:310,484): forward
-        # convolution, then backward-data and the batch-summed weight/bias gradient written into the arena
+        # the layer's Forward and TrainingBackward (netlayer/cnetlayerconvolution.cu.h:310,484): forward convolution, then the
+        # batch-summed weight/bias gradient written into the arena and the backward-data convolution.  With several ranks
+        # the gradients come first and their all-reduce runs on a side stream while the input error is computed (the
+        # library packs the output error once for the two calls).
         layer.forward(y, x, wt, bias)
-        layer.backward(dx, dk, db, delta, x, wt, accumulate=False)
-        grads.all_reduce()
+        if world > 1:
+            layer.backward(None, dk, db, delta, x, wt, accumulate=False)
+            main = torch.cuda.current_stream()
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                grads.all_reduce()
+            layer.backward(dx, None, None, delta, x, wt)
+            main.wait_stream(side)
+        else:
+            layer.backward(dx, dk, db, delta, x, wt, accumulate=False)
 
     def barrier():
         if world > 1:

@@ -22,6 +22,9 @@ struct b200_conv_layer {
     int in_precision;
     int col_valid;               // the kept im2col copy of the layer input matches the last forward call (few-channel layers)
     int col_precision;
+    int er_valid;                // the packed output error of a weights-only backward call may serve the input-only call that follows
+    int er_precision;
+    const float *er_ptr;
 };
 
 namespace b200 {
@@ -202,6 +205,7 @@ int b200_conv_layer_forward(b200_conv_layer *l, float *out, const float *input, 
     l->in_valid = 0;
     int r = TC_UNSUPPORTED;
     l->col_valid = 0;
+    l->er_valid = 0;
     if (prec != B200_FP32 && use_smallc(l)) {
         const bool x3 = prec == B200_TF32X3;
         if (!l->transposed) {
@@ -246,6 +250,10 @@ int b200_conv_layer_backward(b200_conv_layer *l, float *input_delta, float *dker
     const b200_conv_geom &g = l->g;
     const int prec = precision();
     int r = TC_UNSUPPORTED;
+    // A weights-only call followed by an input-only call on the same output error (the order that lets a caller start the
+    // all-reduce of the gradients while the input error is still being computed) packs the error once.
+    const bool reuse_er = l->er_valid && l->er_ptr == output_delta && l->er_precision == prec && !dkernel && input_delta;
+    l->er_valid = 0;
     if (prec != B200_FP32 && use_smallc(l)) {
         const bool x3 = prec == B200_TF32X3;
         if (!l->transposed) {
@@ -298,7 +306,13 @@ int b200_conv_layer_backward(b200_conv_layer *l, float *input_delta, float *dker
         int sum_runs = 0;
         static const bool fuse_sums = !(getenv("B200CONV_FUSE_DBIAS") && getenv("B200CONV_FUSE_DBIAS")[0] == '0');   // debug switch
         const bool want_sums = fuse_sums && !l->transposed && dkernel && dbias;
-        r = pack_into(l, b200_conv_layer::ER_HI, er, output_delta, x3, s, want_sums ? &sum_runs : nullptr);
+        if (reuse_er) {
+            er.hi = l->buf[b200_conv_layer::ER_HI];
+            er.lo = x3 ? l->buf[b200_conv_layer::ER_LO] : nullptr;
+            r = B200_OK;
+        } else {
+            r = pack_into(l, b200_conv_layer::ER_HI, er, output_delta, x3, s, want_sums ? &sum_runs : nullptr);
+        }
         if (r == B200_OK && input_delta) {
             // error of the layer input: BackwardConvolution for a convolution layer, ForwardConvolution
             // (zero bias) for a transposed-convolution layer
@@ -330,7 +344,11 @@ int b200_conv_layer_backward(b200_conv_layer *l, float *input_delta, float *dker
                 }
             }
         }
-        if (r == B200_OK) { set_path(B200_PATH_TCGEN05); return r; }
+        if (r == B200_OK) {
+            if (dkernel && !input_delta) { l->er_valid = 1; l->er_precision = prec; l->er_ptr = output_delta; }
+            set_path(B200_PATH_TCGEN05);
+            return r;
+        }
         if (r != TC_UNSUPPORTED) return r;
     }
     // general path

@@ -150,7 +150,10 @@ int b200_conv_layer_forward(b200_conv_layer *layer, float *out, const float *inp
 /* input_delta (may be NULL) = error of the layer input; dkernel / dbias (may be NULL) (+)= batch-summed
  * gradients (dbias of a transposed layer is cleared, as the reference does).  `input` must hold what the
  * forward call saw: it is only read when the kept pack cannot be used (no forward call yet, precision
- * mode changed, or the CUDA-core path). */
+ * mode changed, or the CUDA-core path).  The call may be split in two on the same output_delta -- gradients only
+ * (input_delta NULL), then input error only (dkernel and dbias NULL) -- so that the caller can start reducing the
+ * gradients across devices while the input error is computed; the second call then reuses the packed error of the
+ * first, provided nothing else was called on the layer in between and output_delta was not modified. */
 int b200_conv_layer_backward(b200_conv_layer *layer, float *input_delta, float *dkernel, float *dbias, int accumulate,
                              const float *output_delta, const float *input, const float *kernel, void *stream);
 

@@ -99,3 +99,29 @@ def test_transposed_convolution_layer(ops, port, case, mode):
     assert dot_rel_err(dk.cpu().numpy().reshape(K, -1), dko.astype(np.float64).sum(0), mk.astype(np.float64).sum(0)) <= tol
     assert not db.cpu().numpy().any() and not dbo.any()
     layer.close()
+
+
+def test_split_backward_call_reuses_the_packed_error(ops):
+    """Gradients-only then input-error-only calls on the same output error give what the single call gives."""
+    ops.set_precision(ops.TF32X3)
+    B, C, H, W, K, k, s, p = 4, 64, 16, 16, 96, 3, 1, 1
+    x, wt, b, d = conv_inputs(77, B, C, H, W, K, k, s, p)
+    X, WT, BI, D = dev(x), dev(wt), dev(b), dev(d)
+    layer = ops.ConvLayer(C, H, W, K, k, k, s, s, p, p, B)
+    y = torch.empty_like(D)
+    layer.forward(y, X, WT, BI)
+    dx1, dk1, db1 = torch.empty_like(X), torch.empty(1, 1, K, C * k * k, device="cuda"), torch.empty(1, K, 1, 1, device="cuda")
+    layer.backward(dx1, dk1, db1, D, X, WT, accumulate=False)
+    dx2, dk2, db2 = torch.full_like(X, float("nan")), torch.empty_like(dk1), torch.empty_like(db1)
+    layer.forward(y, X, WT, BI)
+    layer.backward(None, dk2, db2, D, X, WT, accumulate=False)
+    layer.backward(dx2, None, None, D, X, WT)
+    ops.stream_status()
+    assert torch.equal(dx1, dx2) and torch.equal(dk1, dk2) and torch.equal(db1, db2)
+    # a changed pointer is packed afresh
+    D2 = D.clone() * 2
+    layer.backward(None, dk2, db2, D, X, WT, accumulate=False)
+    layer.backward(dx2, None, None, D2, X, WT)
+    ops.stream_status()
+    assert torch.allclose(dx2, 2 * dx1, rtol=1e-4, atol=1e-5)
+    layer.close()

@@ -221,3 +221,75 @@ def test_linearity_and_adjointness_at_scale(ops):
     c = (wt.double() * dk.double()).sum().item()
     scale = (y.double().norm() * d.double().norm()).item()
     assert abs(a - b_) <= 1e-6 * scale and abs(a - c) <= 1e-6 * scale, (a, b_, c, scale)
+
+
+# degenerate and tile-boundary geometries: a single pixel, a kernel larger than the image, stride equal to the kernel,
+# channel / filter counts one past a tile boundary (32 channels per K block, 128 filter rows, 256 columns), one image
+EDGE_CASES = [
+    (1, 1, 1, 1, 1, 1, 1, 0),
+    (1, 1, 3, 3, 1, 3, 1, 1),
+    (1, 2, 2, 2, 3, 5, 1, 2),          # 5x5 kernel over a 2x2 image
+    (2, 5, 8, 8, 7, 4, 4, 0),          # stride == kernel size: disjoint windows
+    (1, 33, 5, 5, 257, 3, 1, 1),       # one past 32 channels and 256 filters
+    (3, 129, 6, 6, 129, 3, 1, 1),      # one past 128
+    (130, 4, 4, 4, 4, 3, 1, 1),        # batch one past the 128-row tile
+    (2, 6, 17, 5, 5, 3, 2, 0),         # no padding, stride 2, odd sizes
+]
+
+
+@pytest.mark.parametrize("case", EDGE_CASES)
+@pytest.mark.parametrize("mode", ["x3", "fp32"])
+def test_edge_geometries(ops, port, case, mode):
+    B, C, H, W, K, k, s, p = case
+    ops.set_precision(ops.TF32X3 if mode == "x3" else ops.FP32)
+    x, wt, b, d = conv_inputs(sum(case) + 11, B, C, H, W, K, k, s, p)
+    got, _ = run_trio(ops, x, wt, b, d, k, s, p)
+    want = oracle_trio(port, x, wt, b, d, k, s, p)
+    mag = oracle_trio(port, np.abs(x), np.abs(wt), np.abs(b), np.abs(d), k, s, p)
+    for name, g, w, m in zip(("forward", "backward", "dkernel", "dbias"), got, want, mag):
+        assert not np.isnan(g).any(), name
+        assert g.shape == w.shape
+        assert dot_rel_err(g, w, m) <= (TOL_X3 if mode == "x3" else 1e-5), (name, dot_rel_err(g, w, m))
+
+
+@pytest.mark.parametrize("case", [(4, 3, 16, 16, 32, 3, 1, 1), (4, 3, 32, 32, 64, 4, 2, 1), (3, 1, 12, 10, 20, 5, 1, 2), (2, 8, 9, 9, 16, 3, 2, 1)])
+@pytest.mark.parametrize("transposed", [False, True])
+def test_few_channel_layers(ops, port, case, transposed):
+    """Layers with <= 8 channels on one side run with the taps folded into the channel dimension: same results as the
+    oracle's convolution trio, for the convolution layer and for the transposed-convolution layer."""
+    B, C, H, W, K, k, s, p = case
+    ops.set_precision(ops.TF32X3)
+    big, wt, b, small = conv_inputs(sum(case) + 5, B, C, H, W, K, k, s, p)      # big: C channels H x W; small: K channels oy x ox
+    layer = ops.ConvLayer(C, H, W, K, k, k, s, s, p, p, B, transposed=transposed)
+    zb = np.zeros((1, K), np.float32)
+    zk = np.zeros((B, K, C * k * k), np.float32)
+    if not transposed:
+        out = torch.full(small.shape, float("nan"), device="cuda")
+        layer.forward(out, dev(big), dev(wt), dev(b))
+        assert ops.last_path() == ops.PATH_TCGEN05
+        d_in, dk, db = torch.full(big.shape, float("nan"), device="cuda"), torch.empty(1, 1, K, C * k * k, device="cuda"), torch.empty(1, K, 1, 1, device="cuda")
+        layer.backward(d_in, dk, db, dev(small), dev(big), dev(wt), accumulate=False)
+        want = (port.conv_forward(big, wt[0], b.reshape(1, K), k, k, s, s, p, p),
+                port.conv_backward(small, wt[0], zb, (C, H, W), k, k, s, s, p, p))
+        mag = (port.conv_forward(np.abs(big), np.abs(wt[0]), np.abs(b).reshape(1, K), k, k, s, s, p, p),
+               port.conv_backward(np.abs(small), np.abs(wt[0]), zb, (C, H, W), k, k, s, s, p, p))
+        dko, dbo = port.conv_wgrad(zk, np.zeros((B, K), np.float32), big, small, k, k, s, s, p, p)
+        mk, mb = port.conv_wgrad(zk, np.zeros((B, K), np.float32), np.abs(big), np.abs(small), k, k, s, s, p, p)
+        assert dot_rel_err(db.cpu().numpy().reshape(K), dbo.astype(np.float64).sum(0), mb.astype(np.float64).sum(0)) <= 1e-5
+    else:
+        out = torch.full(big.shape, float("nan"), device="cuda")
+        layer.forward(out, dev(small), dev(wt))
+        assert ops.last_path() == ops.PATH_TCGEN05
+        d_in, dk, db = torch.full(small.shape, float("nan"), device="cuda"), torch.empty(1, 1, K, C * k * k, device="cuda"), torch.full((1, K, 1, 1), 3.0, device="cuda")
+        layer.backward(d_in, dk, db, dev(big), dev(small), dev(wt), accumulate=False)
+        want = (port.conv_backward(small, wt[0], zb, (C, H, W), k, k, s, s, p, p), port.conv_forward(big, wt[0], zb, k, k, s, s, p, p))
+        mag = (port.conv_backward(np.abs(small), np.abs(wt[0]), zb, (C, H, W), k, k, s, s, p, p),
+               port.conv_forward(np.abs(big), np.abs(wt[0]), zb, k, k, s, s, p, p))
+        dko, _ = port.conv_wgrad(zk, np.ones((B, K), np.float32), small, big, k, k, s, s, p, p, back_variant=True)
+        mk, _ = port.conv_wgrad(zk, np.ones((B, K), np.float32), np.abs(small), np.abs(big), k, k, s, s, p, p, back_variant=True)
+        assert not db.cpu().numpy().any()
+    ops.stream_status()
+    assert dot_rel_err(out.cpu().numpy(), want[0], mag[0]) <= TOL_X3
+    assert dot_rel_err(d_in.cpu().numpy(), want[1], mag[1]) <= TOL_X3
+    assert dot_rel_err(dk.cpu().numpy().reshape(K, -1), dko.astype(np.float64).sum(0), mk.astype(np.float64).sum(0)) <= TOL_X3
+    layer.close()

@@ -297,6 +297,7 @@ def main():
     ap.add_argument("--skip-hbm", action="store_true", help="leave out the memory-bound kernel measurements")
     ap.add_argument("--hbm-only", action="store_true", help="run only the memory-bound kernel measurements (profiling aid)")
     ap.add_argument("--dcgan-batch", type=int, default=64, help="images per GPU in the DCGAN step")
+    ap.add_argument("--dcgan-fused", action="store_true", help="batch normalisation and the function layer after it as one fused layer (comparison aid)")
     ap.add_argument("--dcgan-eager", action="store_true", help="launch the DCGAN step eagerly instead of replaying its CUDA graph (profiling aid)")
     args = ap.parse_args()
     keep_stdout_clean()
@@ -452,7 +453,7 @@ def main():
                           "up to the all-reduce are replayed from a CUDA graph captured after two eager steps")
         for mode_name, mode in (("tf32x3", ops.TF32X3), ("tf32", ops.TF32)):
             ops.set_precision(mode)
-            trainer = DCGANStep(gb, world=world, use_graph=not args.dcgan_eager)   # a graph is captured in the precision mode of its first steps
+            trainer = DCGANStep(gb, world=world, use_graph=not args.dcgan_eager, fused=args.dcgan_fused)   # a graph is captured in the precision mode of its first steps
             dcgan["parameters"] = dict(generator=trainer.G.parameter_count, discriminator=trainer.D.parameter_count)
             n0 = lib.b200_launch_count()
             trainer(z, labels)                            # eager: every launch of the step is counted once

@@ -507,7 +507,7 @@ __global__ void __launch_bounds__(128) bn_forward_reg_kernel(float *__restrict__
 }
 
 template <int WMAX>
-__global__ void __launch_bounds__(128) bn_backward_reg_kernel(float *__restrict__ dx, float *dgamma, float *dbeta, const float *__restrict__ dy,
+__global__ void __launch_bounds__(128) bn_backward_reg_kernel(float *dx, float *dgamma, float *dbeta, const float *dy,   // dy may be dx
                                        const float *__restrict__ xhat, const float *__restrict__ ivar, const float *__restrict__ gamma,
                                        int W, size_t n, int create_delta_weight)
 {
@@ -588,8 +588,9 @@ template <int TW>
 __global__ void __launch_bounds__(TW) bn_forward_smem_kernel(float *__restrict__ y, float *__restrict__ xhat, float *__restrict__ ivar,
                                       float *__restrict__ mean, float *__restrict__ var, float *new_mean, float *new_var,
                                       const float *__restrict__ x, const float *__restrict__ gamma, const float *__restrict__ beta,
-                                      int W, size_t n, float momentum, float eps, unsigned *status)
+                                      int W, size_t n, float momentum, float eps, unsigned *status, int func, double slope)
 {
+    // func >= 0: the activation of the function layer that follows is applied to the output (y = f(gamma*xhat + beta))
     extern __shared__ __align__(128) float xs[];          // [W][TW]
     __shared__ __align__(8) unsigned long long bar_storage;
     const uint32_t bar0 = ptx::smem_u32(&bar_storage);
@@ -626,7 +627,8 @@ __global__ void __launch_bounds__(TW) bn_forward_smem_kernel(float *__restrict__
             for (int w = 0; w < W; w++) {
                 const float h = __fmul_rn(__fsub_rn(col[w * TW], mu), iv);
                 xhat[(size_t)w * n + i] = h;
-                y[(size_t)w * n + i] = __fadd_rn(__fmul_rn(g, h), b);
+                const float o = __fadd_rn(__fmul_rn(g, h), b);
+                y[(size_t)w * n + i] = func < 0 ? o : act_apply(o, func, slope);
             }
         }
     }
@@ -638,8 +640,11 @@ __global__ void __launch_bounds__(TW) bn_forward_smem_kernel(float *__restrict__
 template <int TW>
 __global__ void __launch_bounds__(2 * TW) bn_backward_smem_kernel(float *__restrict__ dx, float *dgamma, float *dbeta, const float *__restrict__ dy,
                                        const float *__restrict__ xhat, const float *__restrict__ ivar, const float *__restrict__ gamma,
-                                       int W, size_t n, int create_delta_weight, unsigned *status)
+                                       int W, size_t n, int create_delta_weight, unsigned *status, const float *__restrict__ beta, int func,
+                                       double slope)
 {
+    // func >= 0: dy is the error above the function layer that follows this one; it is first multiplied by f'(gamma*xhat + beta)
+    // (the layer's output, recomputed from xhat), which is what that function layer would have handed down
     extern __shared__ __align__(128) float xs[];          // dy rows [W][TW], xhat rows [W][TW]
     __shared__ __align__(8) unsigned long long bar_storage;
     __shared__ float sums[2][TW];
@@ -659,6 +664,17 @@ __global__ void __launch_bounds__(2 * TW) bn_backward_smem_kernel(float *__restr
     const size_t i = tile * TW + t;
     const bool live = ok && i < n;
     float g = 0.f, iv = 0.f;
+    if (func >= 0) {
+        if (live) {
+            float *dw = xs + t;
+            const float gg = gamma[i], bb = beta[i];
+            for (int w = half; w < W; w += 2) {
+                const float o = __fadd_rn(__fmul_rn(gg, hs[w * TW]), bb);
+                dw[w * TW] = act_derivative(o, func, slope) * dw[w * TW];
+            }
+        }
+        __syncthreads();
+    }
     if (live) {
         g = gamma[i]; iv = ivar[i];
         if (half == 0) {
@@ -694,7 +710,7 @@ __global__ void __launch_bounds__(2 * TW) bn_backward_smem_kernel(float *__restr
     }
 }
 
-__global__ void bn_backward_kernel(float *__restrict__ dx, float *dgamma, float *dbeta, const float *__restrict__ dy,
+__global__ void bn_backward_kernel(float *dx, float *dgamma, float *dbeta, const float *dy,      // dy may be dx (in place)
                                    const float *__restrict__ xhat, const float *__restrict__ ivar, const float *__restrict__ gamma,
                                    int W, size_t n, int create_delta_weight)
 {
@@ -1043,9 +1059,9 @@ int b200_downsample(float *out, const float *in, int w, int z, int in_y, int in_
     return B200_OK;
 }
 
-int b200_bn_forward(float *y, float *xhat, float *ivar, float *mean, float *var, float *new_mean, float *new_var,
-                    const float *x, const float *gamma, const float *beta, int w, size_t n, float momentum, float eps,
-                    void *stream)
+static int bn_forward_impl(float *y, float *xhat, float *ivar, float *mean, float *var, float *new_mean, float *new_var,
+                           const float *x, const float *gamma, const float *beta, int w, size_t n, float momentum, float eps,
+                           int func, double leaky_slope, void *stream)
 {
     if (!y || !xhat || !ivar || !mean || !var || !x || !gamma || !beta) return fail(B200_E_ARG, "null tensor pointer");
     if (w <= 0) return fail(B200_E_SHAPE, "non-positive batch");
@@ -1059,7 +1075,7 @@ int b200_bn_forward(float *y, float *xhat, float *ivar, float *mean, float *var,
             if (r) return r;
             B200_CUDA(cudaFuncSetAttribute(bn_forward_smem_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             bn_forward_smem_kernel<128><<<(unsigned)((n + 127) / 128), 128, smem, ST(stream)>>>(
-                y, xhat, ivar, mean, var, new_mean, new_var, x, gamma, beta, w, n, momentum, eps, status);
+                y, xhat, ivar, mean, var, new_mean, new_var, x, gamma, beta, w, n, momentum, eps, status, func, leaky_slope);
             B200_LAUNCH_CHECK();
             return B200_OK;
         }
@@ -1073,11 +1089,40 @@ int b200_bn_forward(float *y, float *xhat, float *ivar, float *mean, float *var,
                                                                        w, n, momentum, eps);
 #undef B200_BN_FWD
     B200_LAUNCH_CHECK();
+    // the general kernels leave the plain output; the function layer's activation follows as its own pass
+    if (func >= 0) launch_activation(y, y, nullptr, (size_t)w * n, func, 0, leaky_slope, ST(stream));
     return B200_OK;
 }
 
-int b200_bn_backward(float *dx, float *dgamma, float *dbeta, const float *dy, const float *xhat, const float *ivar,
-                     const float *gamma, int w, size_t n, int create_delta_weight, void *stream)
+int b200_bn_forward(float *y, float *xhat, float *ivar, float *mean, float *var, float *new_mean, float *new_var,
+                    const float *x, const float *gamma, const float *beta, int w, size_t n, float momentum, float eps,
+                    void *stream)
+{
+    return bn_forward_impl(y, xhat, ivar, mean, var, new_mean, new_var, x, gamma, beta, w, n, momentum, eps, -1, 0.0, stream);
+}
+
+int b200_bn_act_forward(float *out, float *xhat, float *ivar, float *mean, float *var, float *new_mean, float *new_var,
+                        const float *x, const float *gamma, const float *beta, int w, size_t n, float momentum, float eps,
+                        int func, double leaky_slope, void *stream)
+{
+    if (func < 0 || func > 5) return fail(B200_E_ARG, "unknown activation %d", func);
+    return bn_forward_impl(out, xhat, ivar, mean, var, new_mean, new_var, x, gamma, beta, w, n, momentum, eps, func, leaky_slope, stream);
+}
+
+// dx[w][i] = f'(gamma[i]*xhat[w][i] + beta[i]) * error[w][i]: what the function layer above would hand down
+__global__ void bn_act_delta_kernel(float *dx, const float *error, const float *__restrict__ xhat, const float *__restrict__ gamma,
+                                    const float *__restrict__ beta, size_t total, size_t n, int func, double slope)
+{
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t i = idx % n;
+        const float o = __fadd_rn(__fmul_rn(gamma[i], xhat[idx]), beta[i]);
+        dx[idx] = act_derivative(o, func, slope) * error[idx];
+    }
+}
+
+static int bn_backward_impl(float *dx, float *dgamma, float *dbeta, const float *dy, const float *xhat, const float *ivar,
+                            const float *gamma, int w, size_t n, int create_delta_weight, const float *beta, int func, double leaky_slope,
+                            void *stream)
 {
     if (!dx || !dy || !xhat || !ivar || !gamma) return fail(B200_E_ARG, "null tensor pointer");
     if (create_delta_weight && (!dgamma || !dbeta)) return fail(B200_E_ARG, "null gradient pointer");
@@ -1092,10 +1137,16 @@ int b200_bn_backward(float *dx, float *dgamma, float *dbeta, const float *dy, co
             if (r) return r;
             B200_CUDA(cudaFuncSetAttribute(bn_backward_smem_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             bn_backward_smem_kernel<64><<<(unsigned)((n + 63) / 64), 128, smem, ST(stream)>>>(
-                dx, dgamma, dbeta, dy, xhat, ivar, gamma, w, n, create_delta_weight, status);
+                dx, dgamma, dbeta, dy, xhat, ivar, gamma, w, n, create_delta_weight, status, beta, func, leaky_slope);
             B200_LAUNCH_CHECK();
             return B200_OK;
         }
+    }
+    if (func >= 0) {
+        // general kernels: the error is first turned into the function layer's delta, in place in dx
+        bn_act_delta_kernel<<<stream_grid((size_t)w * n, 256), 256, 0, ST(stream)>>>(dx, dy, xhat, gamma, beta, (size_t)w * n, n, func, leaky_slope);
+        B200_LAUNCH_CHECK();
+        dy = dx;
     }
 #define B200_BN_BWD(WMAX) bn_backward_reg_kernel<WMAX><<<stream_grid(n, 128), 128, 0, ST(stream)>>>(dx, dgamma, dbeta, dy, xhat, ivar, gamma, w, n, create_delta_weight)
     if (w <= 16) B200_BN_BWD(16);
@@ -1105,6 +1156,21 @@ int b200_bn_backward(float *dx, float *dgamma, float *dbeta, const float *dy, co
 #undef B200_BN_BWD
     B200_LAUNCH_CHECK();
     return B200_OK;
+}
+
+int b200_bn_backward(float *dx, float *dgamma, float *dbeta, const float *dy, const float *xhat, const float *ivar,
+                     const float *gamma, int w, size_t n, int create_delta_weight, void *stream)
+{
+    return bn_backward_impl(dx, dgamma, dbeta, dy, xhat, ivar, gamma, w, n, create_delta_weight, nullptr, -1, 0.0, stream);
+}
+
+int b200_bn_act_backward(float *dx, float *dgamma, float *dbeta, const float *error, const float *xhat, const float *ivar,
+                         const float *gamma, const float *beta, int w, size_t n, int create_delta_weight, int func, double leaky_slope,
+                         void *stream)
+{
+    if (func < 0 || func > 5) return fail(B200_E_ARG, "unknown activation %d", func);
+    if (!beta) return fail(B200_E_ARG, "null tensor pointer");
+    return bn_backward_impl(dx, dgamma, dbeta, error, xhat, ivar, gamma, w, n, create_delta_weight, beta, func, leaky_slope, stream);
 }
 
 int b200_vae_forward(float *z, const float *mu, const float *logvar, const float *eps, int batch, size_t n,

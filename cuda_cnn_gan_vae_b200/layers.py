@@ -179,6 +179,30 @@ class NetLayerBatchNormalization(_Layer):
         return self.prev_error
 
 
+class NetLayerBatchNormalizationFunction(NetLayerBatchNormalization):
+    """A batch-normalisation layer and the function layer that follows it as one layer (same arithmetic as the two in
+    sequence, netlayer/cnetlayerbatchnormalization.cu.h:301-379,578-604 + netlayer/cnetlayerfunction.cu.h:347-358): the
+    activation is applied when the normalised values are written, and on the way back the function layer's delta is formed
+    from the recomputed output while the error column is staged, so neither the pre-activation tensor nor the delta is ever
+    stored."""
+
+    def __init__(self, in_shape, batch, func, leaky_slope=0.1, momentum=0.9, eps=1e-6):
+        super().__init__(in_shape, batch, momentum, eps)
+        self.func, self.slope = func, leaky_slope
+
+    def Forward(self, x):
+        _check(load().b200_bn_act_forward(_ptr(self.H), _ptr(self.xhat), _ptr(self.ivar), _ptr(self.mean), _ptr(self.var),
+                                          _ptr(self.new_mean), _ptr(self.new_var), _ptr(x), _ptr(self.w["gamma"]), _ptr(self.w["beta"]),
+                                          self.batch, self.n, self.momentum, self.eps, ACT[self.func], self.slope, _stream()))
+        return self.H
+
+    def TrainingBackward(self, error, create_delta_weight=True, need_prev=True):
+        _check(load().b200_bn_act_backward(_ptr(self.prev_error), _ptr(self.g["gamma"]), _ptr(self.g["beta"]), _ptr(error), _ptr(self.xhat),
+                                           _ptr(self.ivar), _ptr(self.w["gamma"]), _ptr(self.w["beta"]), self.batch, self.n,
+                                           int(create_delta_weight), ACT[self.func], self.slope, _stream()))
+        return self.prev_error
+
+
 class NetLayerMaxPooling(_Layer):
     """netlayer/cnetlayermaxpooling.cu.h: Forward :246 (window maximum and its absolute position), TrainingBackward :367."""
 

@@ -57,6 +57,8 @@ SIGNATURES = {
     "b200_downsample": (_i, [_fp, _fp, _i, _i, _i, _i, _i, _i, _vp]),
     "b200_bn_forward": (_i, [_fp] * 10 + [_i, _sz, _f, _f, _vp]),
     "b200_bn_backward": (_i, [_fp] * 7 + [_i, _sz, _i, _vp]),
+    "b200_bn_act_forward": (_i, [_fp] * 10 + [_i, _sz, _f, _f, _i, _d, _vp]),
+    "b200_bn_act_backward": (_i, [_fp] * 8 + [_i, _sz, _i, _i, _d, _vp]),
     "b200_vae_forward": (_i, [_fp, _fp, _fp, _fp, _i, _sz, C.POINTER(C.c_float), _vp]),
     "b200_vae_backward": (_i, [_fp] * 6 + [_sz, _f, _vp]),
     "b200_adam": (_i, [_fp, _fp, _fp, _fp, _sz, C.c_uint32, _d, _d, _d, _d, _d, _vp]),

@@ -249,6 +249,17 @@ int b200_bn_forward(float *y, float *xhat, float *ivar, float *mean, float *var,
  * dbeta += sum_w dy when create_delta_weight != 0. */
 int b200_bn_backward(float *dx, float *dgamma, float *dbeta, const float *dy, const float *xhat, const float *ivar,
                      const float *gamma, int w, size_t n, int create_delta_weight, void *stream);
+/* The batch-normalisation layer together with the function layer that follows it (CNetLayerFunction::Forward and
+ * SetOutputError, netlayer/cnetlayerfunction.cu.h:347-358), same arithmetic as the two layers in sequence:
+ * forward writes out = f(gamma*xhat + beta) (the normalisation's own output is not stored); backward takes the error
+ * above the function layer, forms f'(gamma*xhat + beta) * error (the output recomputed from xhat) and continues as
+ * b200_bn_backward.  func is a B200_ACT_* code. */
+int b200_bn_act_forward(float *out, float *xhat, float *ivar, float *mean, float *var, float *new_mean, float *new_var,
+                        const float *x, const float *gamma, const float *beta, int w, size_t n, float momentum, float eps,
+                        int func, double leaky_slope, void *stream);
+int b200_bn_act_backward(float *dx, float *dgamma, float *dbeta, const float *error, const float *xhat, const float *ivar,
+                         const float *gamma, const float *beta, int w, size_t n, int create_delta_weight, int func,
+                         double leaky_slope, void *stream);
 /* CNetLayerVAECoderOutput::Forward (netlayer/cnetlayervaecoderoutput.cu.h:251-280) with the noise eps
  * supplied by the caller: z = mu + exp(clamp(logvar,-10,10)/2)*eps; *kl_host (host pointer, may be NULL;
  * the call synchronises the stream if given) receives -0.5/batch * sum(1+lv-mu^2-exp(lv)). */

@@ -130,6 +130,26 @@ class OracleNet:
         self.grads[i]["beta"] += db.reshape(w["beta"].shape)
         return dx
 
+    # ---- batch normalisation + function as one layer: the two layers in sequence ------------------
+    def _f_NetLayerBatchNormalizationFunction(self, i, L, x):
+        y = self._f_NetLayerBatchNormalization(i, L, x)
+        self.cache[i] = (self.cache[i], y)
+        if L.func == "leaky_relu" and L.slope != 0.1:
+            return np.where(y > 0, y, (L.slope * y.astype(np.float64)).astype(np.float32))
+        return self.port.activation(y, L.func)
+
+    def _b_NetLayerBatchNormalizationFunction(self, i, L, e, need_prev):
+        r, y = self.cache[i]
+        if L.func == "leaky_relu" and L.slope != 0.1:
+            diff = np.where(y >= 0, np.float32(1), np.float32(L.slope))
+        else:
+            diff = self.port.activation(y, L.func, derivative=True)
+        d = self.port.binary("item_product", e, diff)
+        self.cache[i] = r
+        out = self._b_NetLayerBatchNormalization(i, L, d, need_prev)
+        self.cache[i] = (r, y)
+        return out
+
     # ---- pooling / resampling ------------------------------------------------------------------
     def _f_NetLayerMaxPooling(self, i, L, x):
         out, pos = self.port.maxpool(x, L.pool, L.pool)

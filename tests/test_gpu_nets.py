@@ -89,12 +89,13 @@ def run_and_compare(ops, port, net, x, error, tol, strict, need_input_error=Fals
     return twin
 
 
+@pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("mode", ["fp32", "x3"])
-def test_dcgan_discriminator_chain(ops, port, mode):
+def test_dcgan_discriminator_chain(ops, port, mode, fused):
     from cuda_cnn_gan_vae_b200.nets import dcgan_discriminator
     ops.set_precision(ops.FP32 if mode == "fp32" else ops.TF32X3)
     B = 8
-    net = dcgan_discriminator(B, image=(3, 32, 32), widths=(16, 32, 64), leaky_slope=0.1 if mode == "fp32" else 0.2)
+    net = dcgan_discriminator(B, image=(3, 32, 32), widths=(16, 32, 64), leaky_slope=0.1 if mode == "fp32" else 0.2, fused=fused)
     rng = np.random.default_rng(3)
     x = rng.uniform(-1, 1, (B, 3, 32, 32)).astype(np.float32)
     labels = rng.integers(0, 2, (B, 1, 1, 1)).astype(np.float32)
@@ -223,3 +224,25 @@ def test_vae_step_matches_twin(ops, port):
             for name in layer.param_shapes():
                 check("gradient %d.%s" % (i, name), layer.g[name].cpu().numpy(), twin.grads[i][name], 1e-4, False, twin.grad_mag[i].get(name))
         assert np.abs(net.weights.buffer.cpu().numpy() - before).max() > 0      # Adam moved the weights
+
+
+@pytest.mark.parametrize("w_n", [(16, (16, 32, 64)), (5, (8, 12, 20))])     # staged kernels (batch >= 8) and the general ones
+def test_fused_normalisation_and_function_layers_are_bit_identical(ops, w_n):
+    """The fused batch-normalisation + function layer gives bit for bit what the two layers give in sequence."""
+    from cuda_cnn_gan_vae_b200.nets import dcgan_discriminator
+    ops.set_precision(ops.FP32)
+    B, widths = w_n
+    rng = np.random.default_rng(21)
+    x = torch.from_numpy(rng.uniform(-1, 1, (B, 3, 32, 32)).astype(np.float32)).cuda()
+    err = torch.from_numpy(rng.standard_normal((B, 1, 1, 1)).astype(np.float32)).cuda()
+    results = []
+    for fused in (False, True):
+        net = dcgan_discriminator(B, image=(3, 32, 32), widths=widths, leaky_slope=0.2, fused=fused)
+        assert (len(net.layers) == 3 * len(widths) + 2) == (not fused)
+        net.TrainingResetDeltaWeight()
+        out = net.Forward(x).clone()
+        d_in = net.TrainingBackward(err, True, need_input_error=True).clone()
+        ops.stream_status()
+        results.append((out, d_in, net.weights.buffer.clone(), net.grads.buffer.clone()))
+    for a, b in zip(*results):
+        assert torch.equal(a, b)

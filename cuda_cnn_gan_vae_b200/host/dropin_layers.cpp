@@ -20,6 +20,7 @@
 #include "netlayer/cnetlayerconvolution.cu.h"
 #include "netlayer/cnetlayerfunction.cu.h"
 #include "netlayer/cnetlayerlinear.cu.h"
+#include "netlayer/cnetlayerupsampling.cu.h"
 
 typedef float type_t;
 static const uint32_t BATCH=6;
@@ -51,11 +52,22 @@ int main(int argc,char **argv)
   net.push_back(std::shared_ptr<INetLayer<type_t> >(new CNetLayerLinear<type_t>(10,net.back().get(),BATCH)));
   net.push_back(std::shared_ptr<INetLayer<type_t> >(new CNetLayerFunction<type_t>(NNeuron::NEURON_FUNCTION_SIGMOID,net.back().get(),BATCH)));
 
+  // a second chain through the upsampling layer (UpSampling forward, DownSampling backward)
+  std::vector<std::shared_ptr<INetLayer<type_t> > > up;
+  up.push_back(std::shared_ptr<INetLayer<type_t> >(new CNetLayerConvolutionInput<type_t>(3,8,8,BATCH)));
+  up.push_back(std::shared_ptr<INetLayer<type_t> >(new CNetLayerUpSampling<type_t>(2,2,up.back().get(),BATCH)));
+  up.push_back(std::shared_ptr<INetLayer<type_t> >(new CNetLayerConvolution<type_t>(16,3,1,1,1,1,up.back().get(),BATCH)));
+  up.push_back(std::shared_ptr<INetLayer<type_t> >(new CNetLayerFunction<type_t>(NNeuron::NEURON_FUNCTION_LEAKY_RELU,up.back().get(),BATCH)));
+  up.push_back(std::shared_ptr<INetLayer<type_t> >(new CNetLayerLinear<type_t>(5,up.back().get(),BATCH)));
+  up.push_back(std::shared_ptr<INetLayer<type_t> >(new CNetLayerFunction<type_t>(NNeuron::NEURON_FUNCTION_SIGMOID,up.back().get(),BATCH)));
+
   if (strcmp(argv[1],"gen")==0)
   {
    for(size_t n=0;n<net.size();n++) net[n]->Reset();
+   for(size_t n=0;n<up.size();n++) up[n]->Reset();
    std::unique_ptr<IDataStream> stream(IDataStream::CreateNewDataStreamFile(argv[2],true));
    for(size_t n=0;n<net.size();n++) net[n]->Save(stream.get());
+   for(size_t n=0;n<up.size();n++) up[n]->Save(stream.get());
    return(0);
   }
   if (argc<4) return(3);
@@ -63,8 +75,10 @@ int main(int argc,char **argv)
    std::unique_ptr<IDataStream> stream(IDataStream::CreateNewDataStreamFile(argv[2],false));
    if (stream->IsFail()==true) throw("cannot open the weight file");
    for(size_t n=0;n<net.size();n++) net[n]->Load(stream.get(),true);
+   for(size_t n=0;n<up.size();n++) up[n]->Load(stream.get(),true);
   }
   for(size_t n=0;n<net.size();n++) net[n]->TrainingStart();
+  for(size_t n=0;n<up.size();n++) up[n]->TrainingStart();
 
   CTensor<type_t> input(BATCH,3,16,16);
   for(uint32_t w=0;w<BATCH;w++)
@@ -100,8 +114,30 @@ int main(int argc,char **argv)
   for(size_t n=0;n<net.size();n++) net[n]->TrainingUpdateWeight(0.01,iteration);
   for(size_t n=0;n<net.size();n++) net[n]->Forward();
   Dump(file,"output_2",net.back()->GetOutputTensor());
+
+  // the upsampling chain: forward, backward
+  CTensor<type_t> small(BATCH,3,8,8);
+  for(uint32_t w=0;w<BATCH;w++)
+   for(uint32_t z=0;z<3;z++)
+    for(uint32_t y=0;y<8;y++)
+     for(uint32_t x=0;x<8;x++) small.SetElement(w,z,y,x,static_cast<type_t>(cos(0.71*x+0.43*y+1.3*z+0.9*w)));
+  CTensor<type_t> error_up(BATCH,1,5,1);
+  for(uint32_t w=0;w<BATCH;w++)
+   for(uint32_t y=0;y<5;y++) error_up.SetElement(w,0,y,0,static_cast<type_t>(sin(0.77*y+0.6*w)));
+  up[0]->SetOutput(small);
+  for(size_t n=0;n<up.size();n++) up[n]->Forward();
+  Dump(file,"up_upsampled",up[1]->GetOutputTensor());
+  Dump(file,"up_conv_output",up[2]->GetOutputTensor());
+  Dump(file,"up_output",up.back()->GetOutputTensor());
+  for(size_t n=0;n<up.size();n++) up[n]->TrainingResetDeltaWeight();
+  up.back()->SetOutputError(error_up);
+  for(size_t m=0,n=up.size()-1;m<up.size();m++,n--) up[n]->TrainingBackward();
+  Dump(file,"up_conv_delta",up[2]->GetDeltaTensor());
+  Dump(file,"up_upsampling_delta",up[1]->GetDeltaTensor());
+  Dump(file,"up_input_delta",up[0]->GetDeltaTensor());
   fclose(file);
   for(size_t n=0;n<net.size();n++) net[n]->TrainingStop();
+  for(size_t n=0;n<up.size();n++) up[n]->TrainingStop();
   return(0);
  }
  catch(const char *text)

@@ -61,17 +61,24 @@ def test_reference_layers_match_the_cpu_backend(tmp_path, mode, tol):
     r = subprocess.run([exe, "run", _need("w0.net"), out, str(mode)], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
     got = _read_dump(out)
-    assert set(got) == set(want)
-    for name in ("output_1", "conv1_output", "conv2_output", "linear_delta", "conv2_delta", "conv1_delta", "output_2"):
+    assert set(got) == set(want) and len(want) == 13
+    # deltas that have passed the derivative of LeakyReLU (a step from 0.1 to 1 at zero): where the convolution output lies
+    # within the rounding error of zero, either side of the step is right.  The delta right below the step is compared
+    # away from those elements; deltas further down receive such an element through a convolution's backward pass, so for
+    # them a small fraction of elements may deviate (none do in FP32 mode).
+    at_step = {"conv1_delta": "conv1_output", "up_conv_delta": "up_conv_output"}
+    below_step = ("up_upsampling_delta", "up_input_delta")
+    for name in want:
         assert got[name].shape == want[name].shape, name
         scale = np.sqrt(np.mean(want[name] ** 2)) + 1e-30
-        diff = np.abs(got[name] - want[name])
-        if name == "conv1_delta":
-            # this delta has passed the derivative of LeakyReLU, a step from 0.1 to 1 at zero: where the
-            # layer's output lies within the rounding error of zero either side of the step is right
-            out = want["conv1_output"]
-            diff = diff[np.abs(out) > 16 * tol * np.sqrt(np.mean(out ** 2))]
-            assert diff.size > 0.9 * out.size
-        err = np.max(diff) / scale
-        # deltas pass through up to three contractions of TF32 operands: allow their errors to add up
-        assert err <= 4 * tol, (name, err)
+        diff = np.abs(got[name] - want[name]) / scale
+        if name in at_step:
+            out_ref = want[at_step[name]]
+            keep = np.abs(out_ref) > 16 * tol * np.sqrt(np.mean(out_ref ** 2))
+            assert keep.mean() > 0.9
+            diff = diff[keep]
+        if name in below_step and mode != 2:
+            assert np.mean(diff > 4 * tol) <= (0.15 if mode == 1 else 0.01), (name, np.mean(diff > 4 * tol))
+            assert np.median(diff) <= 4 * tol, (name, np.median(diff))
+            continue
+        assert np.max(diff) <= 4 * tol, (name, np.max(diff))

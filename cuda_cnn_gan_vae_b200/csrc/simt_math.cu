@@ -892,6 +892,44 @@ int b200_div(float *out, int out_w, const float *left, int left_w, const float *
     return launch_binary(out, out_w, left, left_w, right, right_w, n, OpDiv{ls, rs}, ST(stream));
 }
 
+// out[w][z] = a[w % aw][z] for z < za, b[w % bw][z - za] otherwise (split == 0), or the reverse copy: the first za planes
+// of in[w] go to a[w], the rest to b[w] (split != 0).  yx = Y*X elements per plane.
+__global__ void concat_split_z_kernel(float *cat, int cat_w, float *a, int aw, int za, float *b, int bw, int zb, size_t yx, int split)
+{
+    const int z_all = za + zb;
+    const size_t total = (size_t)cat_w * z_all * yx;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t e = idx % yx;
+        const size_t plane = idx / yx;
+        const int z = (int)(plane % z_all);
+        const int w = (int)(plane / z_all);
+        float *part = z < za ? a + ((size_t)(w % aw) * za + z) * yx + e : b + ((size_t)(w % bw) * zb + (z - za)) * yx + e;
+        if (split) *part = cat[idx]; else cat[idx] = *part;
+    }
+}
+
+int b200_concat_z(float *out, int out_w, const float *a, int a_w, int a_z, const float *b, int b_w, int b_z, size_t yx, void *stream)
+{
+    if (!out || !a || !b) return fail(B200_E_ARG, "null tensor pointer");
+    if (out_w <= 0 || a_w <= 0 || b_w <= 0 || a_z <= 0 || b_z <= 0) return fail(B200_E_SHAPE, "non-positive size");
+    const size_t total = (size_t)out_w * (a_z + b_z) * yx;
+    if (!total) return B200_OK;
+    concat_split_z_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(out, out_w, const_cast<float *>(a), a_w, a_z, const_cast<float *>(b), b_w, b_z, yx, 0);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+int b200_split_z(float *out_a, int a_z, float *out_b, int b_z, const float *in, int w, size_t yx, void *stream)
+{
+    if (!out_a || !out_b || !in) return fail(B200_E_ARG, "null tensor pointer");
+    if (w <= 0 || a_z <= 0 || b_z <= 0) return fail(B200_E_SHAPE, "non-positive size");
+    const size_t total = (size_t)w * (a_z + b_z) * yx;
+    if (!total) return B200_OK;
+    concat_split_z_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(const_cast<float *>(in), w, out_a, w, a_z, out_b, w, b_z, yx, 1);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
 int b200_transpose(float *out, const float *in, int planes, int rows, int cols, void *stream)
 {
     if (!out || !in) return fail(B200_E_ARG, "null tensor pointer");

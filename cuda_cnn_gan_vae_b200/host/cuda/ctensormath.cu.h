@@ -6,8 +6,8 @@
 // name, signature and shape checks (a mismatch throws a C string), makes its operands
 // device-resident, calls one ABI entry point on B200TensorStream() and marks the output as changed on
 // the device.  Compute entry points exist for float; other element types are storage only.
-// Not provided (outside the convolution hot path): ConcatecationZ, SplitZ, SetTimeStep,
-// CreateDropOutMatrix, SetNormalNoise, GetNoiseImageAndNoise.
+// Not provided (outside the convolution hot path): SetTimeStep, CreateDropOutMatrix, SetNormalNoise,
+// GetNoiseImageAndNoise.
 
 #include "ctensor.cu.h"
 
@@ -39,6 +39,8 @@ class CTensorMath
   static void Mul(CTensor<type_t> &cTensor_Output,const CTensor<type_t> &cTensor_Left,const type_t &value_right);
   static void Mul(CTensor<type_t> &cTensor_Output,const type_t &value_left,const CTensor<type_t> &cTensor_Right);
   static void Transponse(CTensor<type_t> &cTensor_Output,const CTensor<type_t> &cTensor_Input);
+  static void ConcatecationZ(CTensor<type_t> &cTensor_Output,const CTensor<type_t> &cTensor_InputA,const CTensor<type_t> &cTensor_InputB);
+  static void SplitZ(CTensor<type_t> &cTensor_OutputA,CTensor<type_t> &cTensor_OutputB,const CTensor<type_t> &cTensor_Input);
   static void TensorItemProduction(CTensor<type_t> &cTensor_Output,CTensor<type_t> &cTensor_Left,CTensor<type_t> &cTensor_Right);
   static CTensor<type_t> Transpose(const CTensor<type_t> &cTensor_Input);
   static void UpSampling(CTensor<type_t> &cTensor_Output,const CTensor<type_t> &cTensor_Input,uint32_t upsampling_x,uint32_t upsampling_y);
@@ -227,6 +229,41 @@ void CTensorMath<type_t>::TransponseMul(CTensor<type_t> &cTensor_Output,const CT
  B200Check(b200_mul(B200FloatPtr(cTensor_Output.DeviceWrite()),cTensor_Output.Size_W,l,cTensor_Left.Size_W,r,cTensor_Right.Size_W,
                     cTensor_Left.Size_Z,cTensor_Left.Size_Y,cTensor_Left.Size_X,cTensor_Right.Size_X,1,Stream()));
  cTensor_Output.SetDeviceOnChange();
+}
+
+// cuda/ctensormath.cu.h:502
+template<class type_t>
+void CTensorMath<type_t>::ConcatecationZ(CTensor<type_t> &cTensor_Output,const CTensor<type_t> &cTensor_InputA,const CTensor<type_t> &cTensor_InputB)
+{
+ if (cTensor_Output.Size_X!=cTensor_InputA.Size_X || cTensor_Output.Size_X!=cTensor_InputB.Size_X ||
+     cTensor_Output.Size_Y!=cTensor_InputA.Size_Y || cTensor_Output.Size_Y!=cTensor_InputB.Size_Y ||
+     cTensor_Output.Size_Z!=(cTensor_InputA.Size_Z+cTensor_InputB.Size_Z))
+ {
+  throw "CTensor::ConcatecationZ: tensor sizes do not match!";
+ }
+ const float *a=B200FloatPtr(cTensor_InputA.DeviceRead());
+ const float *b=B200FloatPtr(cTensor_InputB.DeviceRead());
+ B200Check(b200_concat_z(B200FloatPtr(cTensor_Output.DeviceWrite()),cTensor_Output.Size_W,a,cTensor_InputA.Size_W,cTensor_InputA.Size_Z,
+                         b,cTensor_InputB.Size_W,cTensor_InputB.Size_Z,static_cast<size_t>(cTensor_Output.Size_X)*cTensor_Output.Size_Y,Stream()));
+ cTensor_Output.SetDeviceOnChange();
+}
+
+// cuda/ctensormath.cu.h:569
+template<class type_t>
+void CTensorMath<type_t>::SplitZ(CTensor<type_t> &cTensor_OutputA,CTensor<type_t> &cTensor_OutputB,const CTensor<type_t> &cTensor_Input)
+{
+ if (cTensor_Input.Size_X!=cTensor_OutputA.Size_X || cTensor_Input.Size_X!=cTensor_OutputB.Size_X ||
+     cTensor_Input.Size_Y!=cTensor_OutputA.Size_Y || cTensor_Input.Size_Y!=cTensor_OutputB.Size_Y ||
+     cTensor_Input.Size_Z!=(cTensor_OutputA.Size_Z+cTensor_OutputB.Size_Z) ||
+     cTensor_Input.Size_W!=cTensor_OutputA.Size_W || cTensor_Input.Size_W!=cTensor_OutputB.Size_W)
+ {
+  throw "CTensor::SplitZ: tensor sizes do not match!";
+ }
+ const float *in=B200FloatPtr(cTensor_Input.DeviceRead());
+ B200Check(b200_split_z(B200FloatPtr(cTensor_OutputA.DeviceWrite()),cTensor_OutputA.Size_Z,B200FloatPtr(cTensor_OutputB.DeviceWrite()),cTensor_OutputB.Size_Z,
+                        in,cTensor_Input.Size_W,static_cast<size_t>(cTensor_Input.Size_X)*cTensor_Input.Size_Y,Stream()));
+ cTensor_OutputA.SetDeviceOnChange();
+ cTensor_OutputB.SetDeviceOnChange();
 }
 
 template<class type_t>

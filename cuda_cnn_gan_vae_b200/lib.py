@@ -55,6 +55,8 @@ SIGNATURES = {
     "b200_maxpool_backward": (_i, [_fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _vp]),
     "b200_upsample": (_i, [_fp, _fp, _i, _i, _i, _i, _i, _i, _vp]),
     "b200_downsample": (_i, [_fp, _fp, _i, _i, _i, _i, _i, _i, _vp]),
+    "b200_concat_z": (_i, [_fp, _i, _fp, _i, _i, _fp, _i, _i, _sz, _vp]),
+    "b200_split_z": (_i, [_fp, _i, _fp, _i, _fp, _i, _sz, _vp]),
     "b200_bn_forward": (_i, [_fp] * 10 + [_i, _sz, _f, _f, _vp]),
     "b200_bn_backward": (_i, [_fp] * 7 + [_i, _sz, _i, _vp]),
     "b200_bn_act_forward": (_i, [_fp] * 10 + [_i, _sz, _f, _f, _i, _d, _vp]),

@@ -177,3 +177,49 @@ class VAEStep:
             net.grads.all_reduce()
             net.TrainingUpdateWeight(speed, self.iteration, batch_scale=self.world)
         return x_hat
+
+
+class GANSeparableTrainer:
+    """One iteration of the reference's separable GAN training (cuda/netmodel/cmodel_basicgan.cu.h:TrainingSeparable, :700-823)
+    on a rank's shard: (1) the discriminator on generated images (TrainingDiscriminatorFake, :327-394), weights updated;
+    (2) the discriminator on real images (TrainingDiscriminatorReal, :396-464), weights updated; (3) the generator through
+    the discriminator, whose weight gradients are not formed (TrainingGenerator, :466-539), generator weights updated.
+    The errors at the discriminator's output are the reference's hinge rules -- 1 where D(fake) > -1, -1 where D(real) < 1,
+    -1 for the generator pass -- formed on the device instead of by a per-sample host loop over a read-back tensor."""
+
+    def __init__(self, generator, discriminator, world=1):
+        self.G, self.D, self.world = generator, discriminator, world
+        self.batch = generator.batch
+        self.error = torch.empty((self.batch, 1, 1, 1), device="cuda")
+        self.minus_one = torch.full((self.batch, 1, 1, 1), -1.0, device="cuda")
+        self.G.broadcast_weights()
+        self.D.broadcast_weights()
+
+    def _hinge(self, out, real):
+        """fake pass: 1 where out > -1 else 0; real pass: -1 where out < 1 else 0."""
+        out = out.view(self.batch, 1, 1, 1)
+        ops.CTensorMath.Set(self.error, out, -1.0 if real else 1.0, 1.0)      # 1 - out  /  out + 1
+        ops.CTensorMath.Signum(self.error)
+        ops.CTensorMath.Clip(self.error, 0.0, 1.0)
+        if real:
+            ops.CTensorMath.Set(self.error, self.error, -1.0, 0.0)
+        return self.error
+
+    def _update(self, net, speed, iteration):
+        net.grads.all_reduce()
+        net.TrainingUpdateWeight(speed, iteration, batch_scale=self.world)
+
+    def TrainingSeparable(self, noise_for_discriminator, real_images, noise_for_generator, disc_speed, gen_speed, iteration):
+        G, D = self.G, self.D
+        D.TrainingResetDeltaWeight()
+        D.TrainingBackward(self._hinge(D.Forward(G.Forward(noise_for_discriminator)), real=False), True)
+        self._update(D, disc_speed, iteration)
+        D.TrainingResetDeltaWeight()
+        D.TrainingBackward(self._hinge(D.Forward(real_images), real=True), True)
+        self._update(D, disc_speed, iteration)
+        G.TrainingResetDeltaWeight()
+        answers = D.Forward(G.Forward(noise_for_generator))
+        d_image = D.TrainingBackward(self.minus_one, False, need_input_error=True)
+        G.TrainingBackward(d_image, True)
+        self._update(G, gen_speed, iteration)
+        return answers

@@ -263,6 +263,24 @@ class CTensorMath:
         _check(load().b200_transpose(_ptr(output), _ptr(inp), inp.shape[0] * inp.shape[1], inp.shape[2], inp.shape[3], _stream()))
 
     @staticmethod
+    def ConcatecationZ(output, input_a, input_b):
+        _t(output), _t(input_a), _t(input_b)
+        if output.shape[2:] != input_a.shape[2:] or output.shape[2:] != input_b.shape[2:] or \
+                output.shape[1] != input_a.shape[1] + input_b.shape[1]:
+            raise B200Error(1, "CTensor::ConcatecationZ: tensor sizes do not match")
+        _check(load().b200_concat_z(_ptr(output), output.shape[0], _ptr(input_a), input_a.shape[0], input_a.shape[1], _ptr(input_b),
+                                    input_b.shape[0], input_b.shape[1], output.shape[2] * output.shape[3], _stream()))
+
+    @staticmethod
+    def SplitZ(output_a, output_b, inp):
+        _t(output_a), _t(output_b), _t(inp)
+        if inp.shape[2:] != output_a.shape[2:] or inp.shape[2:] != output_b.shape[2:] or inp.shape[0] != output_a.shape[0] or \
+                inp.shape[0] != output_b.shape[0] or inp.shape[1] != output_a.shape[1] + output_b.shape[1]:
+            raise B200Error(1, "CTensor::SplitZ: tensor sizes do not match")
+        _check(load().b200_split_z(_ptr(output_a), output_a.shape[1], _ptr(output_b), output_b.shape[1], _ptr(inp), inp.shape[0],
+                                   inp.shape[2] * inp.shape[3], _stream()))
+
+    @staticmethod
     def TensorItemProduction(output, left, right):
         _t(output), _t(left), _t(right)
         _same_zyx(output, left, right)

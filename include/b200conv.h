@@ -204,6 +204,10 @@ int b200_unary(float *out, int out_w, const float *in, int in_w, size_t n, int o
 /* CTensorMath::Div (cuda :738-800, cpu :197): out[w] = (ls*left[w%Lw]) / (rs*right[w%Rw]). */
 int b200_div(float *out, int out_w, const float *left, int left_w, const float *right, int right_w,
              size_t n, float ls, float rs, void *stream);
+/* CTensorMath::ConcatecationZ (cuda/ctensormath.cu.h:502): out[w] = the planes of a[w % a_w] followed by those of b[w % b_w];
+ * CTensorMath::SplitZ (:569): the first a_z planes of in[w] to out_a[w], the other b_z to out_b[w].  yx = Y*X. */
+int b200_concat_z(float *out, int out_w, const float *a, int a_w, int a_z, const float *b, int b_w, int b_z, size_t yx, void *stream);
+int b200_split_z(float *out_a, int a_z, float *out_b, int b_z, const float *in, int w, size_t yx, void *stream);
 /* CTensorMath::Transponse (cuda :2345-2390, cpu :787): every (w,z) plane rows x cols -> cols x rows. */
 int b200_transpose(float *out, const float *in, int planes, int rows, int cols, void *stream);
 /* CTensorMath::TensorItemProduction (cuda :2425, cpu :822). */

@@ -23,6 +23,23 @@ class OracleNet:
         self.outputs = [None] * len(net.layers)
         self.deltas = [None] * len(net.layers)      # error handed to the layer below (index = layer that produced it)
 
+    # ---- optimiser -----------------------------------------------------------------------------
+    def reset_gradients(self):
+        for g in self.grads:
+            for k in g:
+                g[k][...] = 0
+
+    def update(self, speed, iteration, batch_size, beta1=0.9, beta2=0.999, epsilon=1e-8):
+        """CTensorMath::Adam on every parameter tensor (cpu/ctensormath.h:1119-1165), moments kept per tensor."""
+        if not hasattr(self, "moments"):
+            self.moments = [{k: (np.zeros(v.shape, np.float32), np.zeros(v.shape, np.float32)) for k, v in p.items()} for p in self.params]
+        for i, p in enumerate(self.params):
+            for k in p:
+                m, v = self.moments[i][k]
+                w, m, v = self.port.adam(p[k], self.grads[i][k].astype(np.float32), m, v, batch_size, speed, beta1, beta2, epsilon, iteration)
+                p[k] = w.reshape(p[k].shape)
+                self.moments[i][k] = (m.reshape(p[k].shape), v.reshape(p[k].shape))
+
     # ---- forward -------------------------------------------------------------------------------
     def forward(self, x):
         B = x.shape[0]

@@ -296,6 +296,22 @@ def test_set_clip_signum_div_transpose_bit_exact(ops):
     ops.stream_status()
 
 
+def test_concatenation_and_split_along_z(ops):
+    rng = np.random.default_rng(12)
+    a = rng.standard_normal((3, 2, 5, 7)).astype(np.float32)
+    b = rng.standard_normal((1, 4, 5, 7)).astype(np.float32)          # broadcast over W
+    out = torch.empty(3, 6, 5, 7, device="cuda")
+    ops.CTensorMath.ConcatecationZ(out, dev(a), dev(b))
+    want = np.concatenate([a, np.broadcast_to(b, (3, 4, 5, 7))], axis=1)
+    assert np.array_equal(out.cpu().numpy(), want)
+    pa, pb = torch.empty(3, 2, 5, 7, device="cuda"), torch.empty(3, 4, 5, 7, device="cuda")
+    ops.CTensorMath.SplitZ(pa, pb, out)
+    assert np.array_equal(pa.cpu().numpy(), want[:, :2]) and np.array_equal(pb.cpu().numpy(), want[:, 2:])
+    with pytest.raises(ops.B200Error):
+        ops.CTensorMath.ConcatecationZ(out, dev(a), dev(a))
+    ops.stream_status()
+
+
 def test_shape_errors_raise(ops):
     a = torch.zeros(2, 3, 4, 4, device="cuda")
     with pytest.raises(ops.B200Error):

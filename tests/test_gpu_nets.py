@@ -246,3 +246,49 @@ def test_fused_normalisation_and_function_layers_are_bit_identical(ops, w_n):
         results.append((out, d_in, net.weights.buffer.clone(), net.grads.buffer.clone()))
     for a, b in zip(*results):
         assert torch.equal(a, b)
+
+
+def test_separable_gan_iteration_matches_twin(ops, port):
+    """One iteration of the reference's separable GAN training (discriminator on fakes, discriminator on real images,
+    generator through the discriminator; hinge errors, three Adam updates) against the same sequence on the oracle twin."""
+    from cuda_cnn_gan_vae_b200.nets import GANSeparableTrainer, dcgan_discriminator, dcgan_generator
+    ops.set_precision(ops.FP32)
+    B = 6
+    G = dcgan_generator(B, noise=12, base=16, widths=(8, 3), leaky_slope=0.1)
+    assert G.out_shape == (3, 16, 16)
+    D = dcgan_discriminator(B, image=(3, 16, 16), widths=(8, 16), leaky_slope=0.1)
+    D.layers.pop()                                            # the reference's hinge rules act on the Linear output, no sigmoid
+    D.out_shape = D.layers[-1].out_shape
+    tg, td = OracleNet(port, G), OracleNet(port, D)
+    trainer = GANSeparableTrainer(G, D)
+    rng = np.random.default_rng(31)
+    z1, z2 = (rng.uniform(-1, 1, (B, 1, 12, 1)).astype(np.float32) for _ in range(2))
+    real = rng.uniform(-1, 1, (B, 3, 16, 16)).astype(np.float32)
+    answers = trainer.TrainingSeparable(torch.from_numpy(z1).cuda(), torch.from_numpy(real).cuda(), torch.from_numpy(z2).cuda(), 1e-3, 2e-3, 1)
+    ops.stream_status()
+    # the twin
+    out = td.forward(tg.forward(z1)).reshape(B, 1, 1, 1)
+    td.backward(np.where(out > -1, 1.0, 0.0).astype(np.float32))
+    td.update(1e-3, 1, B)
+    td.reset_gradients()
+    out = td.forward(real).reshape(B, 1, 1, 1)
+    td.backward(np.where(out < 1, -1.0, 0.0).astype(np.float32))
+    td.update(1e-3, 1, B)
+    want_answers = td.forward(tg.forward(z2))
+    keep = {i: {k: v.copy() for k, v in g.items()} for i, g in enumerate(td.grads)}
+    d_image = td.backward(np.full((B, 1, 1, 1), -1.0, np.float32), need_input_error=True)
+    tg.backward(d_image)
+    tg.update(2e-3, 1, B)
+    check("discriminator answers in the generator pass", answers.cpu().numpy(), want_answers, 1e-4, True)
+    for net, twin, speed in ((D, td, 1e-3), (G, tg, 2e-3)):
+        for i, layer in enumerate(net.layers):
+            for name in layer.param_shapes():
+                got, want = layer.w[name].cpu().numpy(), twin.params[i][name]
+                # Adam's first step moves a weight by speed * g / (|g| + epsilon): about the learning rate whatever the size of
+                # the gradient.  A bias in front of a batch normalisation has a gradient that cancels to rounding noise (the
+                # error below the normalisation sums to zero over the batch), so its step is noise of up to the learning rate
+                # on both sides; every other weight must agree to a hundredth of a step.
+                noise_gradient = name in ("bias", "b") and i + 1 < len(net.layers) and type(layer).__name__ != "NetLayerBackConvolution"
+                tol = 2.1 * speed * 2 if noise_gradient else 0.01 * speed
+                assert np.max(np.abs(got - want)) <= tol, (type(layer).__name__, name, np.max(np.abs(got - want)))
+    assert keep is not None

@@ -50,6 +50,9 @@ struct PhaseInfo {
 
 struct TcParams {
     int stages, BN, acc_stride, tmem_cols;
+    int acc_stages;            // accumulator sets in tensor memory: 2 (epilogue of tile i overlaps the main loop of tile i+1) or 1
+    int acc_set_stride;        // columns from one accumulator set to the next
+    int small_off;             // 3xTF32: column offset, inside a set, of the accumulator of the two small product terms
     int a_boxes, b_boxes;
     uint32_t a_box_bytes, b_box_bytes, b_bytes, mini_bytes, stage_bytes;
     int ksub;                  // 32-wide K blocks per pipeline stage (each block = one set of operand boxes)
@@ -328,8 +331,8 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
             };
             for (int tile = work_begin; ok && tile < p.num_tiles; tile += work_step, tile_iter++) {
                 const TileCtx c = (CTAS == 2 && MODE == MODE_CONV) ? decode_pair(p, tile, 0) : decode_tile<MODE>(p, tile, 0);
-                const int acc = tile_iter & 1;
-                const uint32_t acc_phase = (uint32_t)(tile_iter >> 1) & 1u;
+                const int acc = p.acc_stages == 2 ? (tile_iter & 1) : 0;
+                const uint32_t acc_phase = (uint32_t)(p.acc_stages == 2 ? (tile_iter >> 1) : tile_iter) & 1u;
 #ifdef B200_TC_TIMING
                 const long long te0 = clock64();
 #endif
@@ -338,7 +341,12 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
                 dbg_mt += clock64() - te0;
 #endif
                 ptx::tc_fence_after();
-                const uint32_t d = tmem_base + (uint32_t)(acc * p.acc_stride);
+                const uint32_t d = tmem_base + (uint32_t)(acc * p.acc_set_stride);
+                // 3xTF32 with small_off != 0 (optional): the two small product terms go to an accumulator of their own.  The tensor
+                // core adds into its fp32 accumulator without rounding to nearest, an error proportional to the accumulator's
+                // magnitude per MMA; kept apart, the small terms (2^-11 of the product) add next to nothing to it, and the large
+                // accumulator sees one MMA per K step instead of three.  The epilogue adds the two.
+                const uint32_t d_small = d + (uint32_t)p.small_off;
                 for (int step = 0; step < c.nsteps; step += p.ksub) {
 #ifdef B200_TC_TIMING
                     const long long tf0 = clock64();
@@ -358,9 +366,9 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
                             const uint32_t acc_in = (step > 0 || m > 0 || k > 0) ? 1u : 0u;
                             if (X3) {
                                 const uint64_t a_lo = a_lo0 + so, b_lo = b_lo0 + so;
-                                issue(d, a_lo + k * ak16, b_hi + k * bk16, acc_in);   // small terms first
-                                issue(d, a_hi + k * ak16, b_lo + k * bk16, 1u);
-                                issue(d, a_hi + k * ak16, b_hi + k * bk16, 1u);
+                                issue(d_small, a_lo + k * ak16, b_hi + k * bk16, acc_in);      // small terms first
+                                issue(d_small, a_hi + k * ak16, b_lo + k * bk16, 1u);
+                                issue(d, a_hi + k * ak16, b_hi + k * bk16, p.small_off ? acc_in : 1u);
                             } else {
                                 issue(d, a_hi + k * ak16, b_hi + k * bk16, acc_in);
                             }
@@ -386,8 +394,8 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
 #endif
         for (int tile = work_begin; tile < p.num_tiles; tile += work_step, tile_iter++) {
             const TileCtx c = (CTAS == 2 && MODE == MODE_CONV) ? decode_pair(p, tile, (int)rank) : decode_tile<MODE>(p, tile, (int)rank);
-            const int acc = tile_iter & 1;
-            const uint32_t acc_phase = (uint32_t)(tile_iter >> 1) & 1u;
+            const int acc = p.acc_stages == 2 ? (tile_iter & 1) : 0;
+            const uint32_t acc_phase = (uint32_t)(p.acc_stages == 2 ? (tile_iter >> 1) : tile_iter) & 1u;
 #ifdef B200_TC_TIMING
             const long long tq0 = clock64();
 #endif
@@ -398,8 +406,18 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             ptx::tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * p.acc_stride);
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * p.acc_set_stride);
             float v[16];
+            // 16 columns of the tile: the accumulator, plus in 3xTF32 mode the accumulator of the small terms
+            auto load16 = [&](int c0) {
+                ptx::tmem_ld16(taddr + c0, v);
+                if (X3 && p.small_off) {
+                    float u[16];
+                    ptx::tmem_ld16(taddr + (uint32_t)p.small_off + c0, u);
+#pragma unroll
+                    for (int j = 0; j < 16; j++) v[j] = __fadd_rn(v[j], u[j]);
+                }
+            };
             if (MODE == MODE_CONV) {
                 const PhaseInfo &pi = p.phase[c.ph];
                 const int bx = row % p.BW, by = (row / p.BW) % p.BH, bi = row / (p.BW * p.BH);
@@ -409,7 +427,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
                 float *dst = p.out + (size_t)n * p.k_out * plane + (size_t)(yy * p.out_stride_y + pi.off_y) * p.OW +
                              (xx * p.out_stride_x + pi.off_x);
                 for (int c0 = 0; c0 < p.BN; c0 += 16) {
-                    ptx::tmem_ld16(taddr + c0, v);
+                    load16(c0);
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
                         const int k = c.nt * p.BN + c0 + j;
@@ -420,7 +438,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
                 const int f = c.ft * 128 + row;
                 float *dst = p.partial + (((size_t)c.split * p.taps_n + c.tap) * p.c_cols) * p.k_rows + f;
                 for (int c0 = 0; c0 < p.BN; c0 += 16) {
-                    ptx::tmem_ld16(taddr + c0, v);
+                    load16(c0);
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
                         const int ch = c.ct * p.BN + c0 + j;
@@ -431,7 +449,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
                 const int m = c.mt * 128 + row;
                 float *dst = p.out + (size_t)m * p.ldc + c.nt * p.BN;
                 for (int c0 = 0; c0 < p.BN; c0 += 16) {
-                    ptx::tmem_ld16(taddr + c0, v);
+                    load16(c0);
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
                         const int n = c.nt * p.BN + c0 + j;
@@ -830,7 +848,15 @@ static int launch_tc(const CUtensorMap maps[4], TcParams &p, bool x3, cudaStream
     if (stages > 8) stages = 8;
     if (stages < 2) return TC_UNSUPPORTED;
     p.stages = stages;
-    int cols = 2 * p.acc_stride;
+    // tensor memory: two accumulator sets so that the epilogue overlaps the next tile's main loop; a 3xTF32 set holds two
+    // accumulators (large term, small terms), so the widest tile (256 columns) leaves room for one set only
+    // (the separate accumulator costs the 256-column tile its epilogue overlap: +11 % kernel time on the benchmark layer for a
+    // third of the accumulation error, so it is an option: B200CONV_X3_SPLIT_ACC=1)
+    static const bool split_acc = getenv("B200CONV_X3_SPLIT_ACC") && getenv("B200CONV_X3_SPLIT_ACC")[0] == '1';
+    p.small_off = (x3 && split_acc) ? p.acc_stride : 0;
+    p.acc_set_stride = p.small_off ? 2 * p.acc_stride : p.acc_stride;
+    p.acc_stages = 2 * p.acc_set_stride <= 512 ? 2 : 1;
+    int cols = p.acc_stages * p.acc_set_stride;
     if (cols < 32) cols = 32;
     p.tmem_cols = cols;
     int r = status_word(&p.status);

@@ -9,6 +9,9 @@
 //               stage (twelve in 3xTF32 mode), accumulating in tensor memory; two accumulator
 //               stages let the epilogue of tile i overlap the main loop of tile i+1;
 //   warps 2-5   epilogue: tcgen05.ld of the accumulator (lane = output row), bias, coalesced stores.
+// A stage holds one or two K blocks of 32 (two when three such stages fit).  In CTA-pair mode (template CTAS = 2) a
+// cluster of two CTAs shares one 256-row MMA issued by the leader (tcgen05 cta_group::2): each CTA stages its own 128
+// rows of A and half of B's rows, which halves the B bytes per flop.
 // The problems differ only in how a (tile, step) pair maps to TMA coordinates and in the epilogue:
 //   CONV   rows = 128 output pixels (a BI x BH x BW box of the NHWC activation pack), columns =
 //          filters, K = (tap, 32-channel chunk).  Strided convolutions read a phase-split pack (one

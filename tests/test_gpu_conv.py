@@ -293,3 +293,33 @@ def test_few_channel_layers(ops, port, case, transposed):
     assert dot_rel_err(d_in.cpu().numpy(), want[1], mag[1]) <= TOL_X3
     assert dot_rel_err(dk.cpu().numpy().reshape(K, -1), dko.astype(np.float64).sum(0), mk.astype(np.float64).sum(0)) <= TOL_X3
     layer.close()
+
+
+@pytest.mark.parametrize("mode", ["x3", "tf32"])
+def test_single_layer_configuration_at_full_size(ops, port, mode):
+    """The CPU-runnable configuration at its stated size: batch 16 of 3x64x64 uniform[-1,1], 32 filters 3x3 stride 1 pad 1,
+    He-normal weights, zero bias, upstream delta N(0,1), seed 1 -- through the tensor-math calls and through the layer calls
+    (the few-channel path), forward + backward-data + batch-summed weight and bias gradients."""
+    B, C, H, W, K, k, s, p = 16, 3, 64, 64, 32, 3, 1, 1
+    ops.set_precision(ops.TF32X3 if mode == "x3" else ops.TF32)
+    tol = TOL_X3 if mode == "x3" else TOL_TF32
+    rng = np.random.default_rng(1)
+    x = rng.uniform(-1, 1, (B, C, H, W)).astype(np.float32)
+    wt = (rng.standard_normal((1, 1, K, C * k * k)) * np.sqrt(2.0 / (C * k * k))).astype(np.float32)
+    b = np.zeros((1, K, 1, 1), np.float32)
+    d = rng.standard_normal((B, K, H, W)).astype(np.float32)
+    want = oracle_trio(port, x, wt, b, d, k, s, p)
+    mag = oracle_trio(port, np.abs(x), np.abs(wt), np.abs(b), np.abs(d), k, s, p)
+    got, _ = run_trio(ops, x, wt, b, d, k, s, p)
+    layer = ops.ConvLayer(C, H, W, K, k, k, s, s, p, p, B)
+    y, dx = torch.empty(B, K, H, W, device="cuda"), torch.empty(B, C, H, W, device="cuda")
+    dk, db = torch.empty(1, 1, K, C * k * k, device="cuda"), torch.empty(1, K, 1, 1, device="cuda")
+    layer.forward(y, dev(x), dev(wt), dev(b))
+    layer.backward(dx, dk, db, dev(d), dev(x), dev(wt), accumulate=False)
+    ops.stream_status()
+    via_layer = (y.cpu().numpy(), dx.cpu().numpy(), dk.cpu().numpy().reshape(K, -1), db.cpu().numpy().reshape(K))
+    for which, result in (("tensor-math calls", got), ("layer calls", via_layer)):
+        for name, g, w, m in zip(("forward", "backward", "dkernel", "dbias"), result, want, mag):
+            err = dot_rel_err(g, w, m)
+            assert err <= (tol if name != "dbias" else 1e-5), (which, name, err)
+    layer.close()

@@ -63,8 +63,8 @@ def measured_peaks():
         with open(path) as f:
             p = json.load(f)
         return dict(bf16_sustained=p.get("bf16_tflops_sustained"), bf16_burst=p.get("bf16_tflops"), hbm=p.get("hbm_gbs"),
-                    source="MEASURED_PEAKS.json")
-    return dict(bf16_sustained=1400.0, bf16_burst=1590.0, hbm=6650.0, source="fallback")
+                    sm_mhz=(p.get("clocks_under_load") or {}).get("sm_mhz_median"), source="MEASURED_PEAKS.json")
+    return dict(bf16_sustained=1400.0, bf16_burst=1590.0, hbm=6650.0, sm_mhz=1300.0, source="fallback")
 
 
 class ClockSampler:
@@ -408,12 +408,17 @@ def main():
         # dram__bytes_read+write per tc_kernel launch from the ncu capture at batch 128 (profiles/), scaled by units
         traffic = 1.886e6 * B
         achieved = per_launch_flops / (kernel_ms * 1e-3) / 1e12 if kernel_ms else None
+        # the sustained peak was taken at a lower SM clock than this run holds under the same power cap: the fraction at
+        # equal clock says how much of the tensor pipe the kernel uses, the plain fraction how fast it is
+        run_mhz = (clocks or {}).get("sm_mhz")
+        equal_clock = (achieved / tf32_peak * peaks["sm_mhz"] / run_mhz) if (achieved and run_mhz and peaks.get("sm_mhz")) else None
         results[mode_name] = dict(
             value=step_flops / (ms * 1e-3) / 1e12, ms_per_step=ms, clocks=clocks, gpu_launches=int(launches),
             roofline=dict(bound="tensor", achieved=achieved, peak=tf32_peak, unit="TFLOP/s",
                           frac=(achieved / tf32_peak) if achieved else None, traffic=traffic if mode == ops.TF32 else None,
                           kernel="tc_kernel (tcgen05 implicit GEMM), mean of the forward, backward-data and weight-gradient launches",
                           kernel_ms=kernel_ms, mma_per_product=3 if mode == ops.TF32X3 else 1,
+                          peak_sm_mhz=peaks.get("sm_mhz"), frac_at_equal_clock=equal_clock,
                           tensor_pipe_frac=(achieved * (3 if mode == ops.TF32X3 else 1) / tf32_peak) if achieved else None,
                           peak_source=f"{peaks['source']}: bf16_tflops_sustained / 2 (kind::tf32 issues at half the bf16 rate), of measured"))
 

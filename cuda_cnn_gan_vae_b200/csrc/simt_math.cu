@@ -778,8 +778,12 @@ __global__ void vae_backward_kernel(float *__restrict__ d_mu, float *__restrict_
 }
 
 __global__ void adam_kernel(float *__restrict__ weight, const float *__restrict__ dweight, float *__restrict__ m, float *__restrict__ v,
-                            size_t n, float batch, double speed, double beta1, double beta2, double epsilon, double c1, double c2)
+                            size_t n, float batch, double speed, double beta1, double beta2, double epsilon, double c1, double c2,
+                            const double *__restrict__ corrections)
 {
+    // corrections != NULL: the two bias corrections 1 - beta^t are read from device memory (a launch with fixed arguments,
+    // replayable from a CUDA graph while the step number advances)
+    if (corrections) { c1 = corrections[0]; c2 = corrections[1]; }
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         float dw = __fdiv_rn(dweight[i], batch);
         float mm = (float)(beta1 * m[i] + (1.0 - beta1) * dw);
@@ -1259,7 +1263,19 @@ int b200_adam(float *weight, const float *dweight, float *m, float *v, size_t n,
     if (!batch_size) return fail(B200_E_ARG, "batch_size must be positive");
     if (!n) return B200_OK;
     double c1 = 1.0 - pow(beta1, iteration), c2 = 1.0 - pow(beta2, iteration);
-    adam_kernel<<<stream_grid(n, 256), 256, 0, ST(stream)>>>(weight, dweight, m, v, n, (float)batch_size, speed, beta1, beta2, epsilon, c1, c2);
+    adam_kernel<<<stream_grid(n, 256), 256, 0, ST(stream)>>>(weight, dweight, m, v, n, (float)batch_size, speed, beta1, beta2, epsilon, c1, c2, nullptr);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+int b200_adam_prepared(float *weight, const float *dweight, float *m, float *v, size_t n, uint32_t batch_size, double speed,
+                       double beta1, double beta2, double epsilon, const double *corrections, void *stream)
+{
+    if (!weight || !dweight || !m || !v || !corrections) return fail(B200_E_ARG, "null tensor pointer");
+    if (!batch_size) return fail(B200_E_ARG, "batch_size must be positive");
+    if (!n) return B200_OK;
+    adam_kernel<<<stream_grid(n, 256), 256, 0, ST(stream)>>>(weight, dweight, m, v, n, (float)batch_size, speed, beta1, beta2, epsilon, 0.0, 0.0,
+                                                             corrections);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }

@@ -240,6 +240,22 @@ class NetLayerUpSampling(_Layer):
         return self.prev_error
 
 
+class AdamCorrections:
+    """The two bias corrections of Adam for the current step in device memory, refreshed from the host before a step
+    (a 16-byte copy from pinned memory, stream-ordered)."""
+
+    def __init__(self, beta1=0.9, beta2=0.999):
+        self.beta1, self.beta2 = beta1, beta2
+        self.host = torch.zeros(2, dtype=torch.float64).pin_memory()
+        self.device = torch.zeros(2, dtype=torch.float64, device="cuda")
+
+    def set(self, iteration):
+        self.host[0] = 1.0 - self.beta1 ** iteration
+        self.host[1] = 1.0 - self.beta2 ** iteration
+        self.device.copy_(self.host, non_blocking=True)
+        return self.device
+
+
 class Net:
     """A chain of layers with the reference's training protocol (model/cmodelmain.cu.h drives every net the same way:
     TrainingResetDeltaWeight, Forward of all layers, SetOutputError on the last, TrainingBackward in reverse order,
@@ -286,11 +302,18 @@ class Net:
             error = layer.TrainingBackward(error.view((self.batch,) + layer.out_shape), create_delta_weight, need_prev=(i > 0 or need_input_error))
         return error
 
-    def TrainingUpdateWeight(self, speed, iteration, batch_scale=1, beta1=0.9, beta2=0.999, epsilon=1e-8):
+    def TrainingUpdateWeight(self, speed, iteration, batch_scale=1, beta1=0.9, beta2=0.999, epsilon=1e-8, corrections=None):
         """CTensorMath::Adam over every parameter of the net in one launch; batch_size = batch*batch_scale divides the
-        summed gradient (netlayer/cnetlayerconvolution.cu.h:533-552)."""
-        w, g, m, v = (a.buffer.view(1, 1, 1, -1) for a in (self.weights, self.grads, self.m, self.v))
-        ops.CTensorMath.Adam(w, g, m, v, int(self.batch * batch_scale), speed, beta1, beta2, epsilon, iteration)
+        summed gradient (netlayer/cnetlayerconvolution.cu.h:533-552).  corrections: a float64 CUDA tensor holding
+        {1 - beta1^iteration, 1 - beta2^iteration} (see adam_corrections); the launch then has fixed arguments and can be
+        part of a CUDA graph."""
+        w, g, m, v = (a.buffer for a in (self.weights, self.grads, self.m, self.v))
+        if corrections is None:
+            ops.CTensorMath.Adam(w.view(1, 1, 1, -1), g.view(1, 1, 1, -1), m.view(1, 1, 1, -1), v.view(1, 1, 1, -1),
+                                 int(self.batch * batch_scale), speed, beta1, beta2, epsilon, iteration)
+        else:
+            _check(load().b200_adam_prepared(_ptr(w), _ptr(g), _ptr(m), _ptr(v), w.numel(), int(self.batch * batch_scale), speed, beta1, beta2,
+                                             epsilon, _ptr(corrections), _stream()))
 
     def broadcast_weights(self):
         import torch.distributed as dist

@@ -64,6 +64,7 @@ SIGNATURES = {
     "b200_vae_forward": (_i, [_fp, _fp, _fp, _fp, _i, _sz, C.POINTER(C.c_float), _vp]),
     "b200_vae_backward": (_i, [_fp] * 6 + [_sz, _f, _vp]),
     "b200_adam": (_i, [_fp, _fp, _fp, _fp, _sz, C.c_uint32, _d, _d, _d, _d, _d, _vp]),
+    "b200_adam_prepared": (_i, [_fp, _fp, _fp, _fp, _sz, C.c_uint32, _d, _d, _d, _d, _vp, _vp]),
 }
 
 _lib = None

@@ -275,6 +275,11 @@ int b200_vae_backward(float *d_mu, float *d_logvar, const float *delta, const fl
 /* CTensorMath::Adam (cuda :2978-3022, cpu :1119-1165).  iteration is used as given (the CPU backend's rule). */
 int b200_adam(float *weight, const float *dweight, float *m, float *v, size_t n, uint32_t batch_size, double speed,
               double beta1, double beta2, double epsilon, double iteration, void *stream);
+/* The same update with the two bias corrections {1 - beta1^t, 1 - beta2^t} read from device memory (two doubles) instead of
+ * being formed from `iteration` on the host: every argument of the launch is then fixed, so a step that ends in Adam can be
+ * replayed from a CUDA graph while the caller refreshes the two numbers before each replay.  No reference counterpart. */
+int b200_adam_prepared(float *weight, const float *dweight, float *m, float *v, size_t n, uint32_t batch_size, double speed,
+                       double beta1, double beta2, double epsilon, const double *corrections, void *stream);
 
 #ifdef __cplusplus
 }

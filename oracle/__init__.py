@@ -81,6 +81,8 @@ class Oracle:
         wd, K, klen = dkernel.shape
         kz = klen // (kx * ky)
         dbias = dbias.reshape(-1, K)
+        # the back variant swaps the roles inside: its image argument is the transposed layer's input (K channels)
+        assert (image.shape[1], delta.shape[1]) == ((K, kz) if back_variant else (kz, K)), "operand channels do not match the kernel tensor"
         if self.kind == "port":
             fn = self.lib.orc_conv_back_wgrad if back_variant else self.lib.orc_conv_wgrad
             r = fn(_p(dkernel), wd, kx, ky, kz, K, _p(dbias), dbias.shape[0],

@@ -52,8 +52,9 @@ def test_back_wgrad_bit_exact(port, reference):
     big = r.normal(0, 1, (B, Cc, 8, 8)).astype(np.float32)
     dk = np.zeros((B, K, Cc * kx * kx), np.float32)
     db = np.ones((B, K), np.float32)
-    a = port.conv_wgrad(dk, db, big, small, kx, kx, s, s, p, p, back_variant=True)
-    c = reference.conv_wgrad(dk, db, big, small, kx, kx, s, s, p, p, back_variant=True)
+    # CreateBackDeltaWeightAndBias(dKernel, ..., image = layer input, delta = output error) swaps the two roles internally
+    a = port.conv_wgrad(dk, db, small, big, kx, kx, s, s, p, p, back_variant=True)
+    c = reference.conv_wgrad(dk, db, small, big, kx, kx, s, s, p, p, back_variant=True)
     assert a[0].tobytes() == c[0].tobytes() and a[1].tobytes() == c[1].tobytes()
     assert not a[1].any()
 

@@ -241,23 +241,29 @@ class NetLayerUpSampling(_Layer):
 
 
 class AdamCorrections:
-    """The two bias corrections of Adam for the current step in device memory, refreshed from the host before a step
-    (a 16-byte copy from pinned memory, stream-ordered)."""
+    """The two bias corrections of Adam for the current step in device memory, refreshed from the host before a step by a
+    16-byte stream-ordered copy.  The copy reads pinned host memory when it executes, and the host may run many steps ahead
+    of the device, so every step has its own slot in a ring of pinned pairs (far longer than a stream's queue of pending
+    work)."""
+    SLOTS = 4096
 
     def __init__(self, beta1=0.9, beta2=0.999):
         self.beta1, self.beta2 = beta1, beta2
-        self.host = torch.zeros(2, dtype=torch.float64).pin_memory()
+        self.host = torch.zeros(self.SLOTS, 2, dtype=torch.float64).pin_memory()
         self.device = torch.zeros(2, dtype=torch.float64, device="cuda")
+        self.calls = 0
 
     def set(self, iteration):
-        self.host[0] = 1.0 - self.beta1 ** iteration
-        self.host[1] = 1.0 - self.beta2 ** iteration
-        self.device.copy_(self.host, non_blocking=True)
+        slot = self.host[self.calls % self.SLOTS]
+        self.calls += 1
+        slot[0] = 1.0 - self.beta1 ** iteration
+        slot[1] = 1.0 - self.beta2 ** iteration
+        self.device.copy_(slot, non_blocking=True)
         return self.device
 
 
 class Net:
-    """A chain of layers with the reference's training protocol (model/cmodelmain.cu.h drives every net the same way:
+    """A chain of layers with the reference's training protocol (cuda/netmodel/cmodelmain.cu.h drives every net the same way:
     TrainingResetDeltaWeight, Forward of all layers, SetOutputError on the last, TrainingBackward in reverse order,
     TrainingUpdateWeight) on four arenas: weights, gradients, Adam m and v."""
 

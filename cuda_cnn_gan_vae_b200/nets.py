@@ -1,12 +1,12 @@
 """The networks of the benchmark configurations, assembled from the layer mirrors (layers.py) the way the reference's
-models assemble its layer classes (model/cmodel_basicgan.cu.h:CreateGenerator/CreateDiscriminator build the same
+models assemble its layer classes (cuda/netmodel/cmodel_basicgan.cu.h:CreateGenerator/CreateDiscriminator build the same
 chains from CNetLayerLinear, CNetLayerBackConvolution / CNetLayerConvolution, CNetLayerBatchNormalization and
 CNetLayerFunction)."""
 import torch
 
 from . import ops
 from .lib import load
-from .layers import (Net, NetLayerBackConvolution, NetLayerBatchNormalization, NetLayerBatchNormalizationFunction,
+from .layers import (AdamCorrections, Net, NetLayerBackConvolution, NetLayerBatchNormalization, NetLayerBatchNormalizationFunction,
                      NetLayerConvolution, NetLayerFunction, NetLayerLinear, NetLayerMaxPooling, NetLayerUpSampling)
 
 
@@ -50,7 +50,7 @@ class DCGANStep:
     forward on the generated images, the discriminator's backward pass with its weight gradients and the error at its
     input, the generator's backward pass with its weight gradients, one all-reduce per gradient arena and one Adam
     launch per net.  The error at the discriminator's output is output - label (the gradient of binary cross-entropy with
-    respect to the logit, formed as in model/cmodel_basicgan.cu.h:352-376 but on the device)."""
+    respect to the logit, formed as in cuda/netmodel/cmodel_basicgan.cu.h:352-376 but on the device)."""
 
     def __init__(self, batch, world=1, widths_g=(256, 128, 64, 3), widths_d=(64, 128, 256, 512), base=512, noise=100, leaky_slope=0.2,
                  use_graph=True, fused=False):
@@ -65,11 +65,14 @@ class DCGANStep:
         self.iteration = 0
         self.use_graph, self.graph, self.eager_steps = use_graph, None, 0
         self.out = None
-        self.side = torch.cuda.Stream() if world > 1 else None
+        self.side_d = torch.cuda.Stream() if world > 1 else None
+        self.side_g = torch.cuda.Stream() if world > 1 else None
+        self.corr = AdamCorrections()
 
-    def _gradients(self):
-        """Everything of the step up to the all-reduced gradients (all launches have fixed arguments: capturable).  The
-        discriminator's gradient arena is all-reduced on a side stream while the generator's backward pass runs."""
+    def _step(self, speed):
+        """The whole step with fixed launch arguments (capturable): gradients, all-reduces, Adam.  With several ranks the
+        discriminator's gradient arena is all-reduced on a side stream while the generator's backward pass runs, and the
+        generator's while the discriminator's Adam update runs."""
         main = torch.cuda.current_stream()
         self.G.TrainingResetDeltaWeight()
         self.D.TrainingResetDeltaWeight()
@@ -78,41 +81,48 @@ class DCGANStep:
         ops.CTensorMath.Sub(self.error, out, self.labels)
         d_image = self.D.TrainingBackward(self.error, True, need_input_error=True)
         if self.world > 1:
-            self.side.wait_stream(main)
-            with torch.cuda.stream(self.side):
+            self.side_d.wait_stream(main)
+            with torch.cuda.stream(self.side_d):
                 self.D.grads.all_reduce()
         self.G.TrainingBackward(d_image, True)
-        self.G.grads.all_reduce()
         if self.world > 1:
-            main.wait_stream(self.side)
+            self.side_g.wait_stream(main)
+            with torch.cuda.stream(self.side_g):
+                self.G.grads.all_reduce()
+            main.wait_stream(self.side_d)
+        self.D.TrainingUpdateWeight(speed, None, batch_scale=self.world, corrections=self.corr.device)
+        if self.world > 1:
+            main.wait_stream(self.side_g)
+        self.G.TrainingUpdateWeight(speed, None, batch_scale=self.world, corrections=self.corr.device)
         return out
 
     def __call__(self, z, labels, speed=2e-4):
-        """The step is launch-bound at 64 images (over a hundred launches of a few microseconds each), so after two eager
-        steps (which size every scratch buffer of the library) its launches up to the all-reduce are captured once in a
-        CUDA graph and replayed; the two Adam launches take the step number as a host argument and stay outside."""
+        """The step is a chain of over a hundred launches of a few microseconds each, so after two eager steps (which size
+        every scratch buffer of the library) it is captured once in a CUDA graph and replayed.  Adam's bias corrections for
+        the step are refreshed in device memory before each replay (layers.AdamCorrections), so the two Adam launches are
+        part of the graph."""
         self.iteration += 1
         if z.data_ptr() != self.z.data_ptr():
             self.z.copy_(z, non_blocking=True)
         if labels.data_ptr() != self.labels.data_ptr():
             self.labels.copy_(labels, non_blocking=True)
-        if self.graph is not None and load().b200_scratch_bytes() != self.scratch_bytes:
-            self.graph, self.eager_steps = None, 0      # the library's scratch arena was re-allocated: the graph holds stale addresses
+        self.corr.set(self.iteration)
+        if self.graph is not None and (load().b200_scratch_bytes() != self.scratch_bytes or speed != self.graph_speed):
+            self.graph, self.eager_steps = None, 0      # stale addresses (the library's scratch arena moved) or another learning rate
         if self.use_graph and self.graph is None and self.eager_steps >= 2:
             ops.stream_status()
-            self.scratch_bytes = load().b200_scratch_bytes()
+            self.scratch_bytes, self.graph_speed = load().b200_scratch_bytes(), speed
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, capture_error_mode="thread_local"):
-                self.out = self._gradients()
+                self.out = self._step(speed)
             self.graph = graph
         if self.graph is not None:
             self.graph.replay()
         else:
-            self.out = self._gradients()
+            self.out = self._step(speed)
             self.eager_steps += 1
-        self.D.TrainingUpdateWeight(speed, self.iteration, batch_scale=self.world)
-        self.G.TrainingUpdateWeight(speed, self.iteration, batch_scale=self.world)
         return self.out
+
 
 
 def vae_encoder(batch, image=(3, 128, 128), widths=(32, 64, 128, 256), leaky_slope=0.1, seed=4):

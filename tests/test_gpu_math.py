@@ -319,3 +319,21 @@ def test_shape_errors_raise(ops):
     with pytest.raises(ops.B200Error):
         ops.CTensorConv.ForwardConvolution(torch.zeros(2, 4, 3, 3, device="cuda"), a, torch.zeros(1, 1, 4, 27, device="cuda"),
                                            3, 3, 3, 4, torch.zeros(1, 4, 1, 1, device="cuda"), 1, 1, 1, 1)   # wrong output size
+
+
+def test_adam_with_device_resident_corrections(ops):
+    """b200_adam_prepared (bias corrections read from device memory) gives bit for bit what b200_adam gives."""
+    from cuda_cnn_gan_vae_b200.layers import AdamCorrections
+    from cuda_cnn_gan_vae_b200.lib import load
+    r = np.random.default_rng(19)
+    n = 10007
+    w, dw = r.normal(0, 1, n).astype(np.float32), r.normal(0, 1, n).astype(np.float32)
+    m, v = r.normal(0, .1, n).astype(np.float32), np.abs(r.normal(0, .1, n)).astype(np.float32)
+    W1, M1, V1 = dev(w).view(1, 1, 1, -1), dev(m).view(1, 1, 1, -1), dev(v).view(1, 1, 1, -1)
+    ops.CTensorMath.Adam(W1, dev(dw).view(1, 1, 1, -1), M1, V1, 16, 2e-4, 0.9, 0.999, 1e-8, 7)
+    W2, M2, V2, DW = dev(w), dev(m), dev(v), dev(dw)
+    corr = AdamCorrections()
+    c = corr.set(7)
+    ops._check(load().b200_adam_prepared(ops._ptr(W2), ops._ptr(DW), ops._ptr(M2), ops._ptr(V2), n, 16, 2e-4, 0.9, 0.999, 1e-8, ops._ptr(c), ops._stream()))
+    ops.stream_status()
+    assert torch.equal(W1.view(-1), W2) and torch.equal(M1.view(-1), M2) and torch.equal(V1.view(-1), V2)

@@ -52,8 +52,10 @@ int act_pack_fill_with_sums(const ActPack &pk, const float *src, float *rowsum, 
 int dbias_from_rowsums(float *dbias, int accumulate, const float *rowsum, int batch, int K, int runs, cudaStream_t s);
 size_t weight_pack_elems(const b200_conv_geom &g, bool backward);
 int weight_pack_fill(const b200_conv_geom &g, bool backward, const float *kernel, float *hi, float *lo, cudaStream_t s);
+// kpartial (optional): scratch of conv_gemm_partial_elems() floats that allows splitting the contraction of small layers
+size_t conv_gemm_partial_elems(bool backward, const b200_conv_geom &g, int batch);
 int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack &act, const float *w_hi, const float *w_lo,
-              const float *bias, bool x3, cudaStream_t s);
+              const float *bias, bool x3, cudaStream_t s, float *kpartial = nullptr, size_t kpartial_elems = 0);
 size_t wgrad_partial_elems(const b200_conv_geom &g, int batch);
 int wgrad_gemm(const b200_conv_geom &g, float *dkernel, int accumulate, const ActPack &x, const ActPack &d, float *partial,
                bool x3, cudaStream_t s);

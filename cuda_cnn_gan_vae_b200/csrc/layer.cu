@@ -15,7 +15,7 @@ struct b200_conv_layer {
     int batch;
     int transposed;
     int device;
-    enum { IN_HI, IN_LO, ER_HI, ER_LO, W_HI, W_LO, PARTIAL, DB_TMP, COL_HI, COL_LO, TMP, DK_TMP, NBUF };
+    enum { IN_HI, IN_LO, ER_HI, ER_LO, W_HI, W_LO, PARTIAL, DB_TMP, COL_HI, COL_LO, TMP, DK_TMP, KSPLIT, NBUF };
     float *buf[NBUF];
     size_t cap[NBUF];            // bytes
     int in_valid;                // the kept input pack matches the last forward call
@@ -87,6 +87,19 @@ static int pack_weights(b200_conv_layer *l, bool backward, const float *kernel, 
     return weight_pack_fill(l->g, backward, kernel, l->buf[b200_conv_layer::W_HI], x3 ? l->buf[b200_conv_layer::W_LO] : nullptr, s);
 }
 
+// conv_gemm with the layer's split-K scratch (sized on first use; none for layers whose output is large)
+static int layer_conv_gemm(b200_conv_layer *l, bool backward, const b200_conv_geom &g, float *out, const ActPack &act, const float *bias, bool x3,
+                           cudaStream_t s)
+{
+    const size_t elems = conv_gemm_partial_elems(backward, g, l->batch);
+    if (elems) {
+        int r = ensure(l, b200_conv_layer::KSPLIT, sizeof(float) * elems, s);
+        if (r) return r;
+    }
+    return conv_gemm(backward, g, out, act, l->buf[b200_conv_layer::W_HI], l->buf[b200_conv_layer::W_LO], bias, x3, s,
+                     elems ? l->buf[b200_conv_layer::KSPLIT] : nullptr, elems);
+}
+
 // ---- few-channel layers (smallc.cu): taps folded into the channel dimension, contractions as 1x1 convolutions ------------
 static bool use_smallc(const b200_conv_layer *l)
 {
@@ -129,7 +142,7 @@ static int smallc_conv(b200_conv_layer *l, float *out, const ActPack &col, const
 {
     int r;
     if ((r = smallc_weights_into(l, kernel, col.cp, false, x3, s))) return r;
-    return conv_gemm(false, smallc_geom(l->g), out, col, l->buf[b200_conv_layer::W_HI], l->buf[b200_conv_layer::W_LO], bias, x3, s);
+    return layer_conv_gemm(l, false, smallc_geom(l->g), out, col, bias, x3, s);
 }
 
 // dx = col2im(W''^T delta): the transposed convolution towards the few-channel tensor; `many` is the pack of the
@@ -144,8 +157,7 @@ static int smallc_tconv(b200_conv_layer *l, float *dx, const ActPack &many, cons
     b200_conv_geom q = smallc_geom(g);
     q.in_z = g.kernel_amount;
     q.kernel_amount = cc;
-    if ((r = conv_gemm(false, q, l->buf[b200_conv_layer::TMP], many, l->buf[b200_conv_layer::W_HI], l->buf[b200_conv_layer::W_LO], nullptr, x3, s)))
-        return r;
+    if ((r = layer_conv_gemm(l, false, q, l->buf[b200_conv_layer::TMP], many, nullptr, x3, s))) return r;
     return col2im_gather(g, dx, l->buf[b200_conv_layer::TMP], l->batch, s);
 }
 
@@ -226,8 +238,7 @@ int b200_conv_layer_forward(b200_conv_layer *l, float *out, const float *input, 
         ActPack in = in_shape(l);
         if ((r = pack_into(l, b200_conv_layer::IN_HI, in, input, x3, s)) == B200_OK &&
             (r = pack_weights(l, l->transposed, kernel, x3, s)) == B200_OK)
-            r = conv_gemm(l->transposed, l->g, out, in, l->buf[b200_conv_layer::W_HI], l->buf[b200_conv_layer::W_LO],
-                          l->transposed ? nullptr : bias, x3, s);
+            r = layer_conv_gemm(l, l->transposed, l->g, out, in, l->transposed ? nullptr : bias, x3, s);
         if (r == B200_OK) {
             l->in_valid = 1;
             l->in_precision = prec;
@@ -317,7 +328,7 @@ int b200_conv_layer_backward(b200_conv_layer *l, float *input_delta, float *dker
             // error of the layer input: BackwardConvolution for a convolution layer, ForwardConvolution
             // (zero bias) for a transposed-convolution layer
             if ((r = pack_weights(l, !l->transposed, kernel, x3, s)) == B200_OK)
-                r = conv_gemm(!l->transposed, g, input_delta, er, l->buf[b200_conv_layer::W_HI], l->buf[b200_conv_layer::W_LO], nullptr, x3, s);
+                r = layer_conv_gemm(l, !l->transposed, g, input_delta, er, nullptr, x3, s);
         }
         if (r == B200_OK && dkernel) {
             if (l->in_valid && l->in_precision == prec) {

@@ -68,6 +68,9 @@ struct TcParams {
     TapEntry taps[kMaxTaps];
     float *out;
     const float *bias;
+    int ksplit;                // CONV: the K steps of a tile are divided over ksplit work items (1 = no split)
+    float *kpartial;           // ksplit > 1: partial outputs [split][n][k][y][x], summed by conv_ksplit_reduce_kernel
+    long long out_elems;
     // WGRAD
     int ft_n, ct_n, taps_n, splits, chunks_x, chunks_y, chunks_i, k_rows, c_cols, wg_ctas;
     long long chunks_total;
@@ -83,7 +86,8 @@ struct TileCtx {
     int nsteps;
     int nt;                    // CONV/GEMM: n tile
     int ph, tx, ty, ig;        // CONV
-    int ft, tap, ct, split;    // WGRAD
+    int step_begin;            // CONV: first K step of this work item (split-K)
+    int ft, tap, ct, split;    // WGRAD (split also CONV)
     long long chunk_begin;     // WGRAD
     int mt;                    // GEMM
 };
@@ -94,6 +98,8 @@ struct TileCtx {
 __device__ __forceinline__ TileCtx decode_pair(const TcParams &p, int pair, int rank)
 {
     TileCtx c;
+    c.split = pair % p.ksplit;
+    pair /= p.ksplit;
     c.nt = pair % p.n_tiles_n;
     int mp = pair / p.n_tiles_n;
     int ph = 0;
@@ -101,7 +107,11 @@ __device__ __forceinline__ TileCtx decode_pair(const TcParams &p, int pair, int 
     const PhaseInfo &pi = p.phase[ph];
     int local = (mp - pi.pair_begin) * 2 + rank;
     c.ph = ph;
-    c.nsteps = pi.tap_count * p.c_chunks;
+    {
+        const int total = pi.tap_count * p.c_chunks;
+        c.step_begin = total * c.split / p.ksplit;
+        c.nsteps = total * (c.split + 1) / p.ksplit - c.step_begin;
+    }
     if (local < pi.tiles_x * pi.tiles_y * pi.tiles_i) {
         c.tx = local % pi.tiles_x;
         c.ty = (local / pi.tiles_x) % pi.tiles_y;
@@ -117,6 +127,8 @@ __device__ __forceinline__ TileCtx decode_tile(const TcParams &p, int tile, int 
 {
     TileCtx c;
     if (MODE == MODE_CONV) {
+        c.split = tile % p.ksplit;
+        tile /= p.ksplit;
         c.nt = tile % p.n_tiles_n;
         int mt = tile / p.n_tiles_n;
         int ph = 0;
@@ -127,7 +139,9 @@ __device__ __forceinline__ TileCtx decode_tile(const TcParams &p, int tile, int 
         c.tx = local % pi.tiles_x;
         c.ty = (local / pi.tiles_x) % pi.tiles_y;
         c.ig = local / (pi.tiles_x * pi.tiles_y);
-        c.nsteps = pi.tap_count * p.c_chunks;
+        const int total = pi.tap_count * p.c_chunks;
+        c.step_begin = total * c.split / p.ksplit;
+        c.nsteps = total * (c.split + 1) / p.ksplit - c.step_begin;
     } else if (MODE == MODE_WGRAD) {
         c.split = tile % p.splits;
         int rest = tile / p.splits;
@@ -248,7 +262,8 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
             int tap_begin = 0, base1 = 0, base2 = 0, base3 = 0, bcoord = 0;
             if (MODE == MODE_CONV) {
                 const PhaseInfo &pi = p.phase[c.ph];
-                ti = my_m / p.c_chunks; cc = my_m - ti * p.c_chunks;
+                const int g0 = c.step_begin + my_m;
+                ti = g0 / p.c_chunks; cc = g0 - ti * p.c_chunks;
                 tap_begin = pi.tap_begin;
                 base1 = c.tx * p.BW; base2 = c.ty * p.BH; base3 = c.ig * p.BI;
                 bcoord = c.nt * p.BN + (int)rank * (p.BN / 2) * (CTAS - 1);
@@ -427,14 +442,16 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
                 const int n = c.ig * p.BI + bi, yy = c.ty * p.BH + by, xx = c.tx * p.BW + bx;
                 const bool valid = n < p.n_img && yy < pi.ext_y && xx < pi.ext_x;
                 const size_t plane = (size_t)p.OH * p.OW;
-                float *dst = p.out + (size_t)n * p.k_out * plane + (size_t)(yy * p.out_stride_y + pi.off_y) * p.OW +
+                float *obase = p.ksplit > 1 ? p.kpartial + (size_t)c.split * (size_t)p.out_elems : p.out;
+                const float *bias = p.ksplit > 1 ? nullptr : p.bias;       // split-K: the bias is added by the reduction
+                float *dst = obase + (size_t)n * p.k_out * plane + (size_t)(yy * p.out_stride_y + pi.off_y) * p.OW +
                              (xx * p.out_stride_x + pi.off_x);
                 for (int c0 = 0; c0 < p.BN; c0 += 16) {
                     load16(c0);
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
                         const int k = c.nt * p.BN + c0 + j;
-                        if (valid && k < p.k_out) dst[(size_t)k * plane] = p.bias ? __fadd_rn(v[j], p.bias[k]) : v[j];
+                        if (valid && k < p.k_out) dst[(size_t)k * plane] = bias ? __fadd_rn(v[j], bias[k]) : v[j];
                     }
                 }
             } else if (MODE == MODE_WGRAD) {
@@ -618,6 +635,26 @@ __global__ void wgrad_reduce_kernel(float *__restrict__ dkernel, const float *__
         for (int sp = 0; sp < splits; sp++) s += partial[(((size_t)sp * taps + tap) * C + c) * K + f];
         size_t o = ((size_t)f * C + c) * taps + tap;
         dkernel[o] = accumulate ? dkernel[o] + s : s;
+    }
+}
+
+// out[i] = sum over the K splits (in increasing order) of partial[split][i] (+ bias of the element's channel)
+__global__ void conv_ksplit_reduce_kernel(float *__restrict__ out, const float *__restrict__ partial, int splits, size_t total,
+                                          const float *__restrict__ bias, int k_out, size_t plane)
+{
+    const size_t total4 = total / 4;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (size_t)gridDim.x * blockDim.x) {
+        float4 s = reinterpret_cast<const float4 *>(partial)[i];
+        for (int sp = 1; sp < splits; sp++) {
+            const float4 v = reinterpret_cast<const float4 *>(partial + (size_t)sp * total)[i];
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        if (bias) {
+            const size_t e = i * 4;
+            s.x += bias[(e / plane) % k_out]; s.y += bias[((e + 1) / plane) % k_out];
+            s.z += bias[((e + 2) / plane) % k_out]; s.w += bias[((e + 3) / plane) % k_out];
+        }
+        reinterpret_cast<float4 *>(out)[i] = s;
     }
 }
 
@@ -1054,8 +1091,16 @@ int weight_pack_fill(const b200_conv_geom &g, bool backward, const float *kernel
 // Forward convolution, or one backward-data convolution, on packed operands: `act` is the packed
 // tensor that is gathered (image, split by the stride, for the forward pass; delta, unsplit, for the
 // backward pass), w_hi/w_lo the matching weight pack, `out` the NCHW tensor produced.
+// Upper bound of the split-K scratch conv_gemm may use for this problem, in floats (0: the output is large enough that its
+// tiles fill the GPU and no split is considered).
+size_t conv_gemm_partial_elems(bool backward, const b200_conv_geom &g, int batch)
+{
+    const size_t out_elems = (size_t)batch * (backward ? (size_t)g.in_z * g.in_y * g.in_x : (size_t)g.kernel_amount * g.out_y * g.out_x);
+    return out_elems * sizeof(float) <= (16u << 20) ? 8 * out_elems : 0;
+}
+
 int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack &act, const float *w_hi, const float *w_lo,
-              const float *bias, bool x3, cudaStream_t s)
+              const float *bias, bool x3, cudaStream_t s, float *kpartial, size_t kpartial_elems)
 {
     if (!geom_supported(g)) return TC_UNSUPPORTED;
     const int batch = act.n;
@@ -1079,7 +1124,7 @@ int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack 
     const int pad_x = backward ? g.kernel_x - 1 - g.padding_x : g.padding_x;
     const int ext_y0 = ceil_div(OH, osy), ext_x0 = ceil_div(OW, osx);
     tile_shape(ext_y0, ext_x0, 128, &p.BW, &p.BH, &p.BI);
-    int ntaps = 0, mtiles = 0, mpairs = 0, nph = 0;
+    int ntaps = 0, mtiles = 0, mpairs = 0, nph = 0, min_taps = 1 << 30, max_taps = 0;
     bool any_empty = false;
     for (int ry = 0; ry < osy; ry++)
         for (int rx = 0; rx < osx; rx++) {
@@ -1110,6 +1155,8 @@ int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack 
             pi.tiles_x = ceil_div(pi.ext_x, p.BW); pi.tiles_y = ceil_div(pi.ext_y, p.BH); pi.tiles_i = ceil_div(batch, p.BI);
             pi.tile_begin = mtiles;
             pi.pair_begin = mpairs;
+            if (pi.tap_count < min_taps) min_taps = pi.tap_count;
+            if (pi.tap_count > max_taps) max_taps = pi.tap_count;
             mtiles += pi.tiles_x * pi.tiles_y * pi.tiles_i;
             mpairs += (pi.tiles_x * pi.tiles_y * pi.tiles_i + 1) / 2;
             p.phase[nph++] = pi;
@@ -1121,32 +1168,49 @@ int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack 
     // of the filter rows) moves the fewest operand bytes per flop, but a layer with few output pixels then yields only a
     // handful of work items for 148 SMs.  Model: time ~ waves x K-steps x (A bytes + B bytes per CTA and K-step), with A
     // = 128 rows and B = BN (or BN/2) rows; take the candidate with the least modelled time, the wider one on a tie.
-    int ctas = 1;
+    // Split-K (ks > 1) divides a tile's K steps over ks work items whose partial outputs a second kernel sums in a fixed
+    // order: for layers with few output pixels and a long contraction (the 4x4 / 8x8 layers of the DCGAN nets) it fills the
+    // SMs with wide tiles instead of many narrow ones that re-read the activations once per column tile.  Cost of the
+    // reduction: a launch plus (ks + 1) passes over the output.
+    int ctas = 1, ksplit = 1;
     {
         const int bn_max = (int)align_up(k_out < 256 ? k_out : 256, 16);
+        const long long out_elems = (long long)batch * k_out * OH * OW;
+        const int steps_max = max_taps * p.c_chunks, steps_min = min_taps * p.c_chunks;
+        static const bool split_enabled = !(getenv("B200CONV_KSPLIT") && getenv("B200CONV_KSPLIT")[0] == '0');      // debug switch
         long long best = -1;
         for (int bn = bn_max; bn >= 16; bn = (bn > 32 ? (int)align_up(bn / 2, 16) : bn - 16)) {
             for (int c = 2; c >= 1; c--) {
                 if (c == 2 && !(cta_pairs_enabled() && bn >= 32)) continue;
-                const long long items = (long long)(c == 2 ? mpairs : mtiles) * ceil_div(k_out, bn);
-                const long long waves = (items * c + sm_count() - 1) / sm_count();
-                const long long cost = waves * (128 + bn / c);
-                if (best < 0 || cost < best) { best = cost; p.BN = bn; ctas = c; }
+                for (int ks = 1; ks <= 8; ks *= 2) {
+                    if (ks > 1 && (!split_enabled || !kpartial || any_empty || out_elems % 4 || (size_t)ks * out_elems > kpartial_elems ||
+                                   steps_min < 4 * ks))
+                        break;
+                    const long long items = (long long)(c == 2 ? mpairs : mtiles) * ceil_div(k_out, bn) * ks;
+                    const long long waves = (items * c + sm_count() - 1) / sm_count();
+                    // cycles: bytes staged per CTA and K step at ~32 B/clk; reduction at ~2500 B/clk over the whole GPU
+                    const long long cost = waves * ceil_div(steps_max, ks) * (128 + bn / c) * 4 +
+                                           (ks > 1 ? 8000 + (long long)(ks + 1) * out_elems * 4 / 2500 : 0);
+                    if (best < 0 || cost < best) { best = cost; p.BN = bn; ctas = c; ksplit = ks; }
+                }
             }
             if (bn == 16) break;
         }
         // tuning aid: B200CONV_TILE="<BN>,<CTAs>" overrides the choice (read on every call)
         if (const char *e = getenv("B200CONV_TILE")) {
             int bn = 0, c = 0;
-            if (sscanf(e, "%d,%d", &bn, &c) == 2 && bn >= 16 && bn <= bn_max && bn % 16 == 0 && (c == 1 || (c == 2 && bn >= 32))) { p.BN = bn; ctas = c; }
+            if (sscanf(e, "%d,%d", &bn, &c) == 2 && bn >= 16 && bn <= bn_max && bn % 16 == 0 && (c == 1 || (c == 2 && bn >= 32))) { p.BN = bn; ctas = c; ksplit = 1; }
         }
+        p.ksplit = ksplit;
+        p.kpartial = kpartial;
+        p.out_elems = out_elems;
     }
     p.acc_stride = pow2_ceil(p.BN);
     set_kmajor(p, true, 128);
     set_kmajor(p, false, p.BN / ctas);
     p.idesc = make_idesc_tf32(p.BN, 0, 0, 128 * ctas);
     p.n_tiles_n = ceil_div(k_out, p.BN);
-    p.num_tiles = (ctas == 2 ? mpairs : mtiles) * p.n_tiles_n;
+    p.num_tiles = (ctas == 2 ? mpairs : mtiles) * p.n_tiles_n * p.ksplit;
 
     CUtensorMap maps[4];
     {
@@ -1163,7 +1227,15 @@ int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack 
         if ((r = make_map(&maps[2], w_hi, dims, pitch, box))) return r;
         if (x3 && (r = make_map(&maps[3], w_lo, dims, pitch, box))) return r;
     }
-    return launch_tc<MODE_CONV>(maps, p, x3, s, ctas);
+    if ((r = launch_tc<MODE_CONV>(maps, p, x3, s, ctas))) return r;
+    if (p.ksplit > 1) {
+        const size_t total = (size_t)p.out_elems;
+        size_t blocks = (total / 4 + 255) / 256;
+        if (blocks > (size_t)sm_count() * 16) blocks = (size_t)sm_count() * 16;
+        conv_ksplit_reduce_kernel<<<(unsigned)blocks, 256, 0, s>>>(out, kpartial, p.ksplit, total, bias, k_out, (size_t)OH * OW);
+        B200_LAUNCH_CHECK();
+    }
+    return B200_OK;
 }
 
 static int run_conv(bool backward, const b200_conv_geom &g, float *out, const float *act, const float *kernel, const float *bias,

@@ -20,7 +20,10 @@ def dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
-CASES = [(4, 64, 16, 16, 96, 3, 1, 1), (4, 3, 64, 64, 64, 4, 2, 1), (3, 40, 12, 12, 24, 3, 1, 1), (6, 128, 8, 8, 256, 4, 2, 1)]
+# the last two: few output pixels and a long contraction (the 8x8 / 4x4 layers of the DCGAN nets), where the library
+# splits the contraction of a tile over several work items and sums the partial outputs in a second kernel
+CASES = [(4, 64, 16, 16, 96, 3, 1, 1), (4, 3, 64, 64, 64, 4, 2, 1), (3, 40, 12, 12, 24, 3, 1, 1), (6, 128, 8, 8, 256, 4, 2, 1),
+         (8, 256, 8, 8, 512, 4, 2, 1), (5, 512, 4, 4, 100, 3, 1, 1)]
 
 
 @pytest.mark.parametrize("case", CASES)
@@ -68,7 +71,8 @@ def test_convolution_layer(ops, port, case, mode):
     layer2.close()
 
 
-@pytest.mark.parametrize("case", [(4, 64, 16, 16, 128, 4, 2, 1), (4, 3, 64, 64, 64, 4, 2, 1), (3, 24, 12, 12, 40, 3, 1, 1)])
+@pytest.mark.parametrize("case", [(4, 64, 16, 16, 128, 4, 2, 1), (4, 3, 64, 64, 64, 4, 2, 1), (3, 24, 12, 12, 40, 3, 1, 1),
+                                  (8, 256, 8, 8, 512, 4, 2, 1)])
 @pytest.mark.parametrize("mode", ["x3", "fp32"])
 def test_transposed_convolution_layer(ops, port, case, mode):
     """cnetlayerbackconvolution.cu.h: Forward = BackwardConvolution of the layer input; TrainingBackward =

@@ -1029,8 +1029,43 @@ int dbias_from_rowsums(float *dbias, int accumulate, const float *rowsum, int ba
     return B200_OK;
 }
 
+// The same re-layout through a shared-memory tile: a block owns one output row r and 32 inner indices i; it reads the
+// taps of each (r, i) pair as one contiguous run and writes, per tap, 32 consecutive inner elements (128 bytes).
+__global__ void __launch_bounds__(256) pack_weight_tiled_kernel(const float *__restrict__ src, float *__restrict__ hi, float *__restrict__ lo,
+                                                                int K, int C, int taps, int ip, int rot)
+{
+    __shared__ float tile[32][kMaxTaps + 1];
+    const int inner = rot ? K : C;
+    const int chunks = (ip + 31) / 32;
+    const int r = blockIdx.x / chunks, i0 = (blockIdx.x % chunks) * 32;
+    for (int e = threadIdx.x; e < 32 * taps; e += blockDim.x) {
+        const int il = e / taps, tp = e - il * taps;
+        const int i = i0 + il;
+        float v = 0.f;
+        if (i < inner) v = rot ? src[((size_t)i * C + r) * taps + tp] : src[((size_t)r * C + i) * taps + tp];
+        tile[il][tp] = v;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < 32 * taps; e += blockDim.x) {
+        const int tp = e >> 5, il = e & 31;
+        const int i = i0 + il;
+        if (i >= ip) continue;
+        const float v = tile[il][rot ? taps - 1 - tp : tp];
+        const float vh = ptx::to_tf32(v);
+        const size_t o = ((size_t)r * taps + tp) * ip + i;
+        hi[o] = vh;
+        if (lo) lo[o] = ptx::to_tf32(v - vh);
+    }
+}
+
 static int pack_weight(const float *src, float *hi, float *lo, int K, int C, int taps, int ip, int rot, cudaStream_t s)
 {
+    if (taps > 1 && taps <= kMaxTaps) {
+        const int rows = rot ? C : K;
+        pack_weight_tiled_kernel<<<rows * ((ip + 31) / 32), 256, 0, s>>>(src, hi, lo, K, C, taps, ip, rot);
+        B200_LAUNCH_CHECK();
+        return B200_OK;
+    }
     size_t total = (size_t)(rot ? C : K) * taps * ip;
     int grid = (int)((total + 255) / 256);
     if (grid > sm_count() * 16) grid = sm_count() * 16;

@@ -74,16 +74,19 @@ __global__ void col2im_gather_kernel(float *__restrict__ dx, const float *__rest
         const int nc = row / H;
         const int c = nc % C, n = nc / C;
         const float *tn = t + (size_t)n * cc * OH * OW;
+        // only the taps congruent to (y + py) mod sy (and likewise in x) divide exactly: start there and step by the stride
+        const int ky0 = (y + py) % sy;
         for (int x = threadIdx.x; x < W; x += blockDim.x) {
             float s = 0.f;
-            for (int ky = 0; ky < kh; ky++) {
+            const int kx0 = (x + px) % sx;
+            for (int ky = ky0; ky < kh; ky += sy) {
                 const int ny = y + py - ky;
-                if (ny < 0 || ny % sy) continue;
+                if (ny < 0) break;
                 const int oy = ny / sy;
                 if (oy >= OH) continue;
-                for (int kx = 0; kx < kw; kx++) {
+                for (int kx = kx0; kx < kw; kx += sx) {
                     const int nx = x + px - kx;
-                    if (nx < 0 || nx % sx) continue;
+                    if (nx < 0) break;
                     const int ox = nx / sx;
                     if (ox >= OW) continue;
                     s += tn[((size_t)((ky * kw + kx) * C + c) * OH + oy) * OW + ox];

@@ -972,6 +972,11 @@ static void set_mnmajor(TcParams &p, bool a_side, int extent)
 static int pack_act(const float *src, float *hi, float *lo, int N, int C, int H, int W, int Cp, int sy, int sx, int Hs, int Ws,
                     cudaStream_t s, float *rowsum = nullptr, int *rowsum_runs = nullptr)
 {
+    // An unsplit pack of a narrow image (a row shorter than the kernel's 32-pixel tile) is the same re-layout of a single row
+    // of H*W pixels: [n][y][x][c] and [n][c][y][x] are both linear in y*W + x.  Narrow rows would leave most of a tile idle.
+    if (sy == 1 && sx == 1 && W < 32 && H > 1 && W % 4 == 0) {
+        W = H * W; Ws = W; H = 1; Hs = 1;
+    }
     dim3 grid(ceil_div(Ws * sx, 32), Hs * sy, N), block(32, 8);
     if (grid.y > 65535 || grid.z > 65535) return TC_UNSUPPORTED;
     if (rowsum_runs) *rowsum_runs = 0;

@@ -232,10 +232,11 @@ class Oracle:
                                            self.FUNCS[func], int(derivative)) == 0
         return out.reshape(x.shape)
 
-    # ---- layer-level restatements (port only: the reference layers do not compile at HEAD or
-    #      draw unseedable noise; these follow the reference's sequence of tensor routines) ------
+    # ---- layer-level sequences ---------------------------------------------------------------------
+    # port: the plain-C restatement.  reference: the reference's own CTensorMath<float> routines called in
+    # the batch-normalisation layer's order (its class does not compile at the reference's head revision),
+    # and the reference's own CNetLayerVAECoderOutput<float> object.
     def bn_forward(self, x, gamma, beta, momentum=0.9, eps=1e-6, new_mean=None, new_var=None):
-        assert self.kind == "port"
         x, gamma, beta = _c(x), _c(gamma), _c(beta)
         W = x.shape[0]
         n = x[0].size
@@ -243,20 +244,31 @@ class Oracle:
         ivar, mean, var = (np.empty(x.shape[1:], np.float32) for _ in range(3))
         nm = _c(new_mean).copy() if new_mean is not None else None
         nv = _c(new_var).copy() if new_var is not None else None
-        self.lib.orc_bn_forward(_p(y), _p(xhat), _p(ivar), _p(mean), _p(var),
-                                _p(nm) if nm is not None else None, _p(nv) if nv is not None else None,
-                                _p(x), _p(gamma), _p(beta), W, C.c_size_t(n), C.c_float(momentum), C.c_float(eps))
+        if self.kind == "port":
+            self.lib.orc_bn_forward(_p(y), _p(xhat), _p(ivar), _p(mean), _p(var),
+                                    _p(nm) if nm is not None else None, _p(nv) if nv is not None else None,
+                                    _p(x), _p(gamma), _p(beta), W, C.c_size_t(n), C.c_float(momentum), C.c_float(eps))
+        else:
+            zyx = (tuple(x.shape[1:]) + (1, 1, 1))[:3] if x.ndim < 4 else x.shape[1:]
+            assert self.lib.ref_bn_forward(_p(y), _p(xhat), _p(ivar), _p(mean), _p(var),
+                                           _p(nm) if nm is not None else None, _p(nv) if nv is not None else None,
+                                           _p(x), _p(gamma), _p(beta), W, zyx[0], zyx[1], zyx[2], C.c_float(momentum),
+                                           C.c_double(eps)) == 0
         return dict(y=y, xhat=xhat, ivar=ivar, mean=mean, var=var, new_mean=nm, new_var=nv)
 
     def bn_backward(self, dy, xhat, ivar, gamma, dgamma=None, dbeta=None):
-        assert self.kind == "port"
         dy, xhat, ivar, gamma = _c(dy), _c(xhat), _c(ivar), _c(gamma)
         W = dy.shape[0]
         n = dy[0].size
         dx = np.empty_like(dy)
         dg = _c(dgamma).copy() if dgamma is not None else np.zeros(dy.shape[1:], np.float32)
         db = _c(dbeta).copy() if dbeta is not None else np.zeros(dy.shape[1:], np.float32)
-        self.lib.orc_bn_backward(_p(dx), _p(dg), _p(db), _p(dy), _p(xhat), _p(ivar), _p(gamma), W, C.c_size_t(n), 1)
+        if self.kind == "port":
+            self.lib.orc_bn_backward(_p(dx), _p(dg), _p(db), _p(dy), _p(xhat), _p(ivar), _p(gamma), W, C.c_size_t(n), 1)
+        else:
+            zyx = (tuple(dy.shape[1:]) + (1, 1, 1))[:3] if dy.ndim < 4 else dy.shape[1:]
+            assert self.lib.ref_bn_backward(_p(dx), _p(dg), _p(db), _p(dy), _p(xhat), _p(ivar), _p(gamma), W, zyx[0], zyx[1],
+                                            zyx[2], 1) == 0
         return dx, dg, db
 
     def vae_forward(self, mu, logvar, eps):
@@ -273,6 +285,27 @@ class Oracle:
         self.lib.orc_vae_backward(_p(dmu), _p(dlv), _p(delta), _p(mu), _p(logvar), _p(eps), C.c_size_t(mu.size),
                                   C.c_float(k))
         return dmu, dlv
+
+    def vae_layer(self, mu, logvar, delta, k):
+        """reference only: one Forward + SetOutputError of the reference's own VAE output layer object.  The layer draws
+        its noise from an unseedable generator, so the noise it used is returned with its results:
+        (z, eps, d_mu, d_logvar); feed eps to vae_forward / vae_backward of the port to compare."""
+        assert self.kind == "reference"
+        mu, logvar, delta = _c(mu), _c(logvar), _c(delta)
+        shape4 = (mu.shape + (1, 1, 1))[:4]
+        z, eps, dmu, dlv = (np.empty_like(mu) for _ in range(4))
+        devnull = os.open(os.devnull, os.O_WRONLY)       # the layer prints its KL loss to the console
+        keep = os.dup(1)
+        os.dup2(devnull, 1)
+        try:
+            r = self.lib.ref_vae_layer(_p(z), _p(eps), _p(dmu), _p(dlv), _p(mu), _p(logvar), _p(delta), shape4[0], shape4[1],
+                                       shape4[2], shape4[3], C.c_float(k))
+        finally:
+            os.dup2(keep, 1)
+            os.close(keep)
+            os.close(devnull)
+        assert r == 0, r
+        return z, eps, dmu, dlv
 
     def adam(self, weight, dweight, m, v, batch_size, speed, beta1, beta2, epsilon, iteration):
         weight, dweight, m, v = _c(weight).copy(), _c(dweight), _c(m).copy(), _c(v).copy()

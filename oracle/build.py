@@ -52,7 +52,8 @@ def build_ref(force=False):
     flags = ["-O3", "-std=c++14", "-fPIC", "-w", "-ffp-contract=off", "-I" + REF, "-I" + os.path.join(REF, "cpu")]
     shim = os.path.join(HERE, "ref_shim.cpp")
     if force or _stale(out, [shim]):
-        _run(["g++"] + flags + ["-shared", "-o", out, shim] + link)
+        # -DUSE_CPU: the reference's layer headers (the VAE output layer) then include its CPU tensor backend
+        _run(["g++"] + flags + ["-DUSE_CPU", "-shared", "-o", out, shim, os.path.join(REF, "common", "crandom.cpp")] + link)
     st = os.path.join(HERE, "ref_selftest.cpp")
     if force or _stale(selftest, [st]):
         _run(["g++"] + flags + ["-DUSE_CPU", "-I" + os.path.join(REF, "cuda"), "-o", selftest, st,

@@ -12,6 +12,14 @@
 
 #include "cpu/tensor.h"
 
+// The VAE output layer of the reference (netlayer/cnetlayervaecoderoutput.cu.h) compiles against its CPU
+// backend (-DUSE_CPU, set by oracle/build.py).  Its noise tensor, its two error tensors and the current
+// Kullback-Leibler weight are private members with no accessor; the checker reads them directly.
+#define private public
+#include "netlayer/cnetlayervaecoderoutput.cu.h"
+#undef private
+#include "netlayer/cnetlayerconvolutioninput.cu.h"
+
 typedef CTensor<float> T;
 
 static void put(T &t, const float *src)
@@ -226,6 +234,101 @@ int ref_adam(float *weight, const float *dweight, float *m, float *v, int n, uin
         put(w, weight); put(dw, dweight); put(mm, m); put(vv, v);
         CTensorMath<float>::Adam(w, dw, mm, vv, batch_size, speed, beta1, beta2, epsilon, iteration);
         get(w, weight); get(mm, m); get(vv, v);
+    })
+}
+
+// Batch-normalisation layer, training-mode forward pass.  The layer class itself does not compile at the
+// reference's head revision, so this drives the reference's own CTensorMath<float> routines in the order,
+// with the operands, scale arguments and temporaries of netlayer/cnetlayerbatchnormalization.cu.h:301-379
+// (momentum is a type_t member there, EPSILON a double constant passed to a type_t parameter).
+// n-element statistics are [1,Z,Y,X]; x, y, xhat are [W,Z,Y,X].
+int ref_bn_forward(float *y, float *xhat, float *ivar, float *mean, float *var, float *new_mean, float *new_var,
+                   const float *x, const float *gamma, const float *beta, int W, int Z, int Y, int X, float momentum, double eps)
+{
+    GUARD({
+        typedef CTensorMath<float> M;
+        T in(W, Z, Y, X), H(W, Z, Y, X), XHAT(W, Z, Y, X), TmpA_H(W, Z, Y, X);
+        T TmpA(1, Z, Y, X), VAR(1, Z, Y, X), SQRTVAR(1, Z, Y, X), IVAR(1, Z, Y, X), NewMean(1, Z, Y, X), NewVariable(1, Z, Y, X),
+            Gamma(1, Z, Y, X), Beta(1, Z, Y, X);
+        put(in, x); put(Gamma, gamma); put(Beta, beta);
+        if (new_mean) put(NewMean, new_mean); else M::Fill(NewMean, 0);
+        if (new_var) put(NewVariable, new_var); else M::Fill(NewVariable, 0);
+        float N = static_cast<float>(W);
+        float Momentum = momentum;
+        M::Fill(TmpA, 0);
+        M::AddSumW(TmpA, TmpA, in, 1, 1.0 / N);
+        M::Add(NewMean, NewMean, TmpA, Momentum, 1.0 - Momentum);
+        M::Sub(XHAT, in, TmpA, 1.0, 1.0);
+        M::Fill(VAR, 0);
+        M::Pow2(TmpA_H, XHAT, 1);
+        M::AddSumW(VAR, VAR, TmpA_H, 1, 1.0 / N);
+        M::Add(NewVariable, NewVariable, VAR, Momentum, 1.0 - Momentum);
+        M::SQRT(SQRTVAR, VAR, 1, eps);
+        M::Inv(IVAR, SQRTVAR);
+        M::TensorItemProduction(XHAT, XHAT, IVAR);
+        M::TensorItemProduction(TmpA_H, Gamma, XHAT);
+        M::Add(H, TmpA_H, Beta);
+        get(H, y); get(XHAT, xhat); get(IVAR, ivar); get(TmpA, mean); get(VAR, var);
+        if (new_mean) get(NewMean, new_mean);
+        if (new_var) get(NewVariable, new_var);
+    })
+}
+
+// Batch-normalisation layer, TrainingBackward: the reference's CTensorMath<float> calls of
+// netlayer/cnetlayerbatchnormalization.cu.h:578-604 in their order.  dgamma / dbeta are accumulated into.
+int ref_bn_backward(float *dx, float *dgamma, float *dbeta, const float *dy, const float *xhat, const float *ivar,
+                    const float *gamma, int W, int Z, int Y, int X, int create_delta_weight)
+{
+    GUARD({
+        typedef CTensorMath<float> M;
+        T Delta(W, Z, Y, X), XHAT(W, Z, Y, X), DXHAT(W, Z, Y, X), TmpA_H(W, Z, Y, X), Prev(W, Z, Y, X);
+        T TmpB(1, Z, Y, X), TmpC(1, Z, Y, X), IVAR(1, Z, Y, X), Gamma(1, Z, Y, X), dGamma(1, Z, Y, X), dBeta(1, Z, Y, X);
+        put(Delta, dy); put(XHAT, xhat); put(IVAR, ivar); put(Gamma, gamma); put(dGamma, dgamma); put(dBeta, dbeta);
+        float N = static_cast<float>(W);
+        M::Fill(TmpB, 0);
+        M::Fill(TmpC, 0);
+        M::TensorItemProduction(DXHAT, Delta, Gamma);
+        M::AddSumW(TmpB, TmpB, DXHAT);
+        M::TensorItemProduction(TmpA_H, DXHAT, XHAT);
+        M::AddSumW(TmpC, TmpC, TmpA_H);
+        if (create_delta_weight) {
+            M::TensorItemProduction(TmpA_H, Delta, XHAT);
+            M::AddSumW(dGamma, dGamma, TmpA_H);
+            M::AddSumW(dBeta, dBeta, Delta);
+        }
+        M::Mul(Prev, DXHAT, N);
+        M::TensorItemProduction(TmpA_H, XHAT, TmpC);
+        M::Sub(Prev, Prev, TmpA_H);
+        M::Sub(Prev, Prev, TmpB);
+        M::TensorItemProduction(Prev, Prev, IVAR);
+        M::Mul(Prev, Prev, 1.0 / N);
+        get(Prev, dx); get(dGamma, dgamma); get(dBeta, dbeta);
+    })
+}
+
+// The reference's own CNetLayerVAECoderOutput<float> (unmodified): Forward draws its noise from a
+// random_device-seeded generator, so the noise it used is handed back (eps_out) together with the layer
+// output; SetOutputError then runs on the same object with the Kullback-Leibler weight kl_speed and the
+// two errors it hands to the mean / log-variance layers are returned.  mu, logvar, delta: [W,Z,Y,X].
+int ref_vae_layer(float *z_out, float *eps_out, float *d_mu, float *d_logvar, const float *mu, const float *logvar,
+                  const float *delta, int W, int Z, int Y, int X, float kl_speed)
+{
+    GUARD({
+        CNetLayerConvolutionInput<float> mu_layer(Z, Y, X, W), lv_layer(Z, Y, X, W);
+        T m(W, Z, Y, X), l(W, Z, Y, X), d(W, Z, Y, X);
+        put(m, mu); put(l, logvar); put(d, delta);
+        mu_layer.SetOutput(m);
+        lv_layer.SetOutput(l);
+        CNetLayerVAECoderOutput<float> layer(kl_speed, &mu_layer, &lv_layer, W);
+        layer.TrainingStart();
+        layer.Forward();
+        get(layer.cTensor_H, z_out);
+        get(layer.cTensor_Epsilon, eps_out);
+        layer.KLSpeedCurrent = kl_speed;
+        layer.SetOutputError(d);
+        get(layer.cTensor_PrevLayerError_Mu, d_mu);
+        get(layer.cTensor_PrevLayerError_LogVar, d_logvar);
+        layer.TrainingStop();
     })
 }
 

@@ -101,6 +101,20 @@ def seeded_cases(ref):
     bb = r.normal(0, 1, (1, 1, 33, 17)).astype(np.float32)
     c = r.normal(0, 1, (6, 1, 40, 9)).astype(np.float32)
     out.update(gemm_a=a, gemm_b=bb, gemm_c=c, gemm_mul=ref.mul(a, bb), gemm_tmul=ref.tmul(a, c))
+    # batch normalisation (the reference's tensor routines in the layer's order) and the reference's VAE output layer object
+    bx = r.normal(1.5, 2.0, (16, 3, 4, 5)).astype(np.float32)
+    bg, bb_ = r.normal(1, 0.2, (3, 4, 5)).astype(np.float32), r.normal(0, 0.3, (3, 4, 5)).astype(np.float32)
+    f = ref.bn_forward(bx, bg, bb_, 0.9, 1e-6, np.zeros((3, 4, 5), np.float32), np.ones((3, 4, 5), np.float32))
+    bdy = r.normal(0, 1, bx.shape).astype(np.float32)
+    bdx, bdg, bdb = ref.bn_backward(bdy, f["xhat"], f["ivar"], bg)
+    out.update(bn_x=bx, bn_gamma=bg, bn_beta=bb_, bn_dy=bdy, bn_dx=bdx, bn_dgamma=bdg, bn_dbeta=bdb,
+               **{"bn_" + k: v for k, v in f.items()})
+    vmu = r.normal(0, 1, (6, 1, 40, 1)).astype(np.float32)
+    vlv = r.normal(0, 4, (6, 1, 40, 1)).astype(np.float32)
+    vlv[0, 0, :4, 0] = [11, -11, 10, -10]
+    vd = r.normal(0, 1, vmu.shape).astype(np.float32)
+    vz, veps, vdmu, vdlv = ref.vae_layer(vmu, vlv, vd, 0.25)
+    out.update(vae_mu=vmu, vae_logvar=vlv, vae_delta=vd, vae_eps=veps, vae_z=vz, vae_dmu=vdmu, vae_dlogvar=vdlv, vae_kl_speed=np.float32(0.25))
     xs = np.linspace(-35, 35, 141).astype(np.float32).reshape(1, 1, 1, -1)
     out["act_x"] = xs
     for f in Oracle.FUNCS:

@@ -80,9 +80,23 @@ def test_seeded_memory_bound(port, seeded):
         assert port.activation(seeded["act_x"], f, True).tobytes() == seeded[f"dact_{f}"].tobytes()
 
 
+def test_seeded_batchnorm_and_vae(port, seeded):
+    """Fixtures generated from the reference run in the build container (tests/golden/make_golden.py): the reference's
+    tensor routines in the batch-normalisation layer's order, and its VAE output layer object with the noise it drew."""
+    f = port.bn_forward(seeded["bn_x"], seeded["bn_gamma"], seeded["bn_beta"], 0.9, 1e-6, np.zeros((3, 4, 5), np.float32),
+                        np.ones((3, 4, 5), np.float32))
+    for key in ("y", "xhat", "ivar", "mean", "var", "new_mean", "new_var"):
+        assert f[key].tobytes() == seeded["bn_" + key].tobytes(), key
+    dx, dg, db = port.bn_backward(seeded["bn_dy"], f["xhat"], f["ivar"], seeded["bn_gamma"])
+    assert dx.tobytes() == seeded["bn_dx"].tobytes() and dg.tobytes() == seeded["bn_dgamma"].tobytes() and db.tobytes() == seeded["bn_dbeta"].tobytes()
+    z, _ = port.vae_forward(seeded["vae_mu"], seeded["vae_logvar"], seeded["vae_eps"])
+    assert z.tobytes() == seeded["vae_z"].tobytes()
+    dmu, dlv = port.vae_backward(seeded["vae_delta"], seeded["vae_mu"], seeded["vae_logvar"], seeded["vae_eps"], float(seeded["vae_kl_speed"]))
+    assert dmu.tobytes() == seeded["vae_dmu"].tobytes() and dlv.tobytes() == seeded["vae_dlogvar"].tobytes()
+
+
 def test_batchnorm_restatement_properties(port):
-    # no reference KAT exists for batch-norm (the reference layer does not compile at HEAD): check the
-    # restated sequence against closed forms in float64.
+    # closed forms in float64, next to the bit-exact comparison with the reference (test_oracle_vs_reference.py)
     r = np.random.default_rng(3)
     x = r.normal(1.5, 2.0, (16, 3, 4, 5)).astype(np.float32)
     gamma = r.normal(1, 0.1, (3, 4, 5)).astype(np.float32)

@@ -131,3 +131,44 @@ def test_adam_bit_exact(port, reference):
     b = reference.adam(w, dw, m, v, 16, 2e-4, 0.5, 0.999, 1e-8, 3)
     for p, q in zip(a, b):
         assert p.tobytes() == q.tobytes()
+
+
+@pytest.mark.parametrize("shape", [(16, 3, 4, 5), (64, 2, 3, 7), (5, 1, 1, 9)])
+def test_batch_normalisation_sequence_bit_exact(port, reference, shape):
+    """The batch-normalisation layer's forward and backward passes: the restatement against the reference's own tensor
+    routines driven in the layer's order (netlayer/cnetlayerbatchnormalization.cu.h:301-379, 578-604)."""
+    r = _rng(sum(shape))
+    x = r.normal(1.5, 2.0, shape).astype(np.float32)
+    gamma = r.normal(1, 0.2, shape[1:]).astype(np.float32)
+    beta = r.normal(0, 0.3, shape[1:]).astype(np.float32)
+    nm = r.normal(0, 1, shape[1:]).astype(np.float32)
+    nv = np.abs(r.normal(1, 0.2, shape[1:])).astype(np.float32)
+    a = port.bn_forward(x, gamma, beta, 0.9, 1e-6, nm, nv)
+    b = reference.bn_forward(x, gamma, beta, 0.9, 1e-6, nm, nv)
+    for key in ("y", "xhat", "ivar", "mean", "var", "new_mean", "new_var"):
+        assert a[key].tobytes() == b[key].tobytes(), key
+    dy = r.normal(0, 1, shape).astype(np.float32)
+    dg0 = r.normal(0, 1, shape[1:]).astype(np.float32)
+    db0 = r.normal(0, 1, shape[1:]).astype(np.float32)
+    pa = port.bn_backward(dy, a["xhat"], a["ivar"], gamma, dg0, db0)
+    pb = reference.bn_backward(dy, a["xhat"], a["ivar"], gamma, dg0, db0)
+    for p, q, key in zip(pa, pb, ("dx", "dgamma", "dbeta")):
+        assert p.tobytes() == q.tobytes(), key
+
+
+@pytest.mark.parametrize("kl_speed", [0.0, 0.25, 1.0])
+def test_vae_output_layer_bit_exact(port, reference, kl_speed):
+    """The reference's own CNetLayerVAECoderOutput<float> object (netlayer/cnetlayervaecoderoutput.cu.h:244-287, 424-460) runs
+    Forward and SetOutputError; the restatement, given the noise that object drew, must reproduce its output and the two
+    errors bit for bit, including log-variances beyond the clamp at +-10."""
+    r = _rng(23)
+    mu = r.normal(0, 1, (6, 1, 40, 1)).astype(np.float32)
+    lv = r.normal(0, 4, (6, 1, 40, 1)).astype(np.float32)
+    lv[0, 0, :4, 0] = [11, -11, 10, -10]
+    delta = r.normal(0, 1, mu.shape).astype(np.float32)
+    z, eps, dmu, dlv = reference.vae_layer(mu, lv, delta, kl_speed)
+    assert np.isfinite(eps).all() and eps.std() > 0.5
+    zp, _ = port.vae_forward(mu, lv, eps)
+    assert zp.tobytes() == z.tobytes()
+    pmu, plv = port.vae_backward(delta, mu, lv, eps, kl_speed)
+    assert pmu.tobytes() == dmu.tobytes() and plv.tobytes() == dlv.tobytes()

@@ -286,7 +286,7 @@ __global__ void summ_xy_kernel(float *__restrict__ out, int out_w, const float *
 // pooling / resampling
 // ---------------------------------------------------------------------------------------------
 __global__ void maxpool_kernel(float *__restrict__ out, uint2 *__restrict__ pos, const float *__restrict__ in,
-                               size_t planes, int in_y, int in_x, int pool_x, int pool_y)
+                               size_t planes, int in_y, int in_x, int pool_x, int pool_y, int vec2)
 {
     const int oy = in_y / pool_y, ox = in_x / pool_x;
     const size_t total = planes * oy * ox;
@@ -299,7 +299,7 @@ __global__ void maxpool_kernel(float *__restrict__ out, uint2 *__restrict__ pos,
         int ix = x * pool_x, iy = y * pool_y;
         float m = p[(size_t)iy * in_x + ix];
         uint32_t mx = ix, my = iy;
-        if (pool_x == 2 && pool_y == 2 && (in_x % 2 == 0)) {
+        if (vec2) {      // 2x2 windows, even rows, 8-byte aligned input: two 8-byte loads per window
             float2 r0 = *reinterpret_cast<const float2 *>(p + (size_t)iy * in_x + ix);
             float2 r1 = *reinterpret_cast<const float2 *>(p + (size_t)(iy + 1) * in_x + ix);
             if (r0.y > m) { m = r0.y; mx = ix + 1; my = iy; }
@@ -1048,7 +1048,10 @@ int b200_maxpool(float *out, uint32_t *pos, const float *in, int w, int z, int i
     size_t planes = (size_t)w * z;
     size_t total = planes * (in_y / pool_y) * (in_x / pool_x);
     if (!total) return B200_OK;
-    maxpool_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(out, reinterpret_cast<uint2 *>(pos), in, planes, in_y, in_x, pool_x, pool_y);
+    // positions are {X, Y} pairs stored with one 8-byte access each
+    if ((uintptr_t)pos & 7) return fail(B200_E_ARG, "max-pooling: the position tensor must be 8-byte aligned");
+    const int vec2 = pool_x == 2 && pool_y == 2 && in_x % 2 == 0 && ((uintptr_t)in & 7) == 0;
+    maxpool_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(out, reinterpret_cast<uint2 *>(pos), in, planes, in_y, in_x, pool_x, pool_y, vec2);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -1061,6 +1064,7 @@ int b200_maxpool_backward(float *out, const uint32_t *pos, const float *delta, i
     size_t planes = (size_t)w * z;
     size_t total = planes * out_y * out_x;
     if (!total) return B200_OK;
+    if ((uintptr_t)pos & 7) return fail(B200_E_ARG, "max-pooling: the position tensor must be 8-byte aligned");
     if (pool_x == 2 && pool_y == 2 && out_x % 2 == 0 && out_y % 2 == 0 && ((uintptr_t)out % 8) == 0 && planes * (size_t)(out_y / 2) < 0xFFFFFFFFull)
         maxpool_backward_2x2_kernel<<<stream_grid(total / 4, 256), 256, 0, ST(stream)>>>(out, reinterpret_cast<const uint2 *>(pos), delta,
                                                                                        (unsigned)(planes * (out_y / 2)), (unsigned)(out_x / 2));

@@ -1223,7 +1223,7 @@ int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack 
             for (int c = 2; c >= 1; c--) {
                 if (c == 2 && !(cta_pairs_enabled() && bn >= 32)) continue;
                 for (int ks = 1; ks <= 8; ks *= 2) {
-                    if (ks > 1 && (!split_enabled || !kpartial || any_empty || out_elems % 4 || (size_t)ks * out_elems > kpartial_elems ||
+                    if (ks > 1 && (!split_enabled || !kpartial || any_empty || out_elems % 4 || ((uintptr_t)out & 15) || (size_t)ks * out_elems > kpartial_elems ||
                                    steps_min < 4 * ks))
                         break;
                     const long long items = (long long)(c == 2 ? mpairs : mtiles) * ceil_div(k_out, bn) * ks;

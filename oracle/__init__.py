@@ -26,8 +26,12 @@ def _c(a):
 
 
 class Oracle:
-    def __init__(self, kind="port"):
+    def __init__(self, kind="port", threads=1):
+        """threads > 1: the batched routines (convolution trio, products) split their W range over that many host threads --
+        every W index is computed by the same single-threaded routine as before (the loops are independent per w,
+        cpu/ctensorconv.h:111), the threads only shorten the wait of a test on a full-size configuration."""
         self.kind = kind
+        self.threads = max(1, int(threads))
         if kind == "port":
             path = _build.build_oracle()
             self.pfx = "orc_"
@@ -45,9 +49,31 @@ class Oracle:
     def _fn(self, name):
         return getattr(self.lib, self.pfx + name)
 
+    def _over_w(self, W, fn):
+        """fn(begin, end) -> array or tuple of arrays for the W range [begin, end); results are concatenated along W."""
+        n = min(self.threads, W)
+        if n <= 1:
+            return fn(0, W)
+        from concurrent.futures import ThreadPoolExecutor
+        bounds = [(W * i // n, W * (i + 1) // n) for i in range(n)]
+        with ThreadPoolExecutor(n) as pool:
+            parts = list(pool.map(lambda b: fn(*b), bounds))
+        if isinstance(parts[0], tuple):
+            return tuple(np.concatenate([p[j] for p in parts], 0) for j in range(len(parts[0])))
+        return np.concatenate(parts, 0)
+
+    def _single(self):
+        one = Oracle.__new__(Oracle)
+        one.__dict__.update(self.__dict__)
+        one.threads = 1
+        return one
+
     # ---- convolution trio -------------------------------------------------------------------
     def conv_forward(self, image, kernel, bias, kx, ky, sx, sy, px, py, out_w=None):
         image, kernel, bias = _c(image), _c(kernel), _c(bias)
+        if self.threads > 1 and out_w is None and kernel.shape[0] == 1 and bias.size == kernel.shape[1] and image.shape[0] > 1:
+            one = self._single()
+            return self._over_w(image.shape[0], lambda b, e: one.conv_forward(image[b:e], kernel, bias, kx, ky, sx, sy, px, py))
         iw, cz, iy, ix = image.shape
         kw, K, klen = kernel.shape
         assert klen == cz * kx * ky
@@ -63,6 +89,9 @@ class Oracle:
 
     def conv_backward(self, delta, kernel, bias, out_zyx, kx, ky, sx, sy, px, py, out_w=None):
         delta, kernel, bias = _c(delta), _c(kernel), _c(bias)
+        if self.threads > 1 and out_w is None and kernel.shape[0] == 1 and bias.size == kernel.shape[1] and delta.shape[0] > 1:
+            one = self._single()
+            return self._over_w(delta.shape[0], lambda b, e: one.conv_backward(delta[b:e], kernel, bias, out_zyx, kx, ky, sx, sy, px, py))
         dw, K, dy, dx = delta.shape
         kw = kernel.shape[0]
         oz, oy, ox = out_zyx
@@ -78,6 +107,12 @@ class Oracle:
     def conv_wgrad(self, dkernel, dbias, image, delta, kx, ky, sx, sy, px, py, back_variant=False):
         """Accumulates into copies of dkernel (Wd,K,C*ky*kx) / dbias (Wb,K) and returns them."""
         dkernel, dbias, image, delta = _c(dkernel).copy(), _c(dbias).copy(), _c(image), _c(delta)
+        if self.threads > 1 and dkernel.shape[0] > 1 and dkernel.shape[0] == image.shape[0] == delta.shape[0] and \
+                dbias.size == dkernel.shape[0] * dkernel.shape[1]:
+            one = self._single()
+            db2 = dbias.reshape(dkernel.shape[0], dkernel.shape[1])
+            return self._over_w(dkernel.shape[0], lambda b, e: one.conv_wgrad(dkernel[b:e], db2[b:e], image[b:e], delta[b:e], kx, ky, sx, sy,
+                                                                             px, py, back_variant))
         wd, K, klen = dkernel.shape
         kz = klen // (kx * ky)
         dbias = dbias.reshape(-1, K)
@@ -99,6 +134,9 @@ class Oracle:
     # ---- dense products ---------------------------------------------------------------------
     def mul(self, left, right, out_w=None):
         left, right = _c(left), _c(right)
+        if self.threads > 1 and out_w is None and max(left.shape[0], right.shape[0]) > 1 and min(left.shape[0], right.shape[0]) in (1, max(left.shape[0], right.shape[0])):
+            one, W = self._single(), max(left.shape[0], right.shape[0])
+            return self._over_w(W, lambda b, e: one.mul(left if left.shape[0] == 1 else left[b:e], right if right.shape[0] == 1 else right[b:e]))
         lw, Z, LY, LX = left.shape
         rw, _, _, RX = right.shape
         ow = out_w or max(lw, rw)
@@ -111,6 +149,9 @@ class Oracle:
 
     def tmul(self, left, right, out_w=None):
         left, right = _c(left), _c(right)
+        if self.threads > 1 and out_w is None and max(left.shape[0], right.shape[0]) > 1 and min(left.shape[0], right.shape[0]) in (1, max(left.shape[0], right.shape[0])):
+            one, W = self._single(), max(left.shape[0], right.shape[0])
+            return self._over_w(W, lambda b, e: one.tmul(left if left.shape[0] == 1 else left[b:e], right if right.shape[0] == 1 else right[b:e]))
         lw, Z, KD, LX = left.shape
         rw, _, _, RX = right.shape
         ow = out_w or max(lw, rw)

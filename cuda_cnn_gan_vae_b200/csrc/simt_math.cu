@@ -5,6 +5,7 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "tc_ptx.cuh"
+#include "adam.cuh"
 #include <cmath>
 
 namespace b200 {
@@ -777,23 +778,49 @@ __global__ void vae_backward_kernel(float *__restrict__ d_mu, float *__restrict_
     }
 }
 
-__global__ void adam_kernel(float *__restrict__ weight, const float *__restrict__ dweight, float *__restrict__ m, float *__restrict__ v,
-                            size_t n, float batch, double speed, double beta1, double beta2, double epsilon, double c1, double c2,
-                            const double *__restrict__ corrections)
+// One pass over the parameter arena: 16-byte accesses on the four (five with the moving average) streams; the bias
+// corrections 1 - beta^t come from the launch arguments or, when `corrections` is given, from device memory (a launch
+// with fixed arguments, replayable from a CUDA graph while the step number advances).
+template <bool EMA>
+__global__ void __launch_bounds__(256) adam_kernel(float *__restrict__ weight, const float *__restrict__ dweight, float *__restrict__ m,
+                                                   float *__restrict__ v, float *__restrict__ ema, size_t n, AdamArgs a,
+                                                   const double *__restrict__ corrections, int vec)
 {
-    // corrections != NULL: the two bias corrections 1 - beta^t are read from device memory (a launch with fixed arguments,
-    // replayable from a CUDA graph while the step number advances)
-    if (corrections) { c1 = corrections[0]; c2 = corrections[1]; }
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-        float dw = __fdiv_rn(dweight[i], batch);
-        float mm = (float)(beta1 * m[i] + (1.0 - beta1) * dw);
-        float vv = (float)(beta2 * v[i] + (1.0 - beta2) * dw * dw);
-        float mc = (float)(mm / c1);
-        float vc = (float)(vv / c2);
-        float step = (float)(speed * mc / (sqrt((double)vc) + epsilon));
-        m[i] = mm; v[i] = vv;
-        weight[i] = __fsub_rn(weight[i], step);
+    if (corrections) { a.inv_c1 = 1.0 / corrections[0]; a.inv_c2 = 1.0 / corrections[1]; }
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (size_t)gridDim.x * blockDim.x;
+    const size_t n4 = vec ? n / 4 : 0;
+    for (size_t i = tid; i < n4; i += stride) {
+        float4 w = reinterpret_cast<float4 *>(weight)[i];
+        const float4 g = reinterpret_cast<const float4 *>(dweight)[i];
+        float4 mm = reinterpret_cast<float4 *>(m)[i], vv = reinterpret_cast<float4 *>(v)[i];
+        w.x = adam_element(w.x, g.x, mm.x, vv.x, a); w.y = adam_element(w.y, g.y, mm.y, vv.y, a);
+        w.z = adam_element(w.z, g.z, mm.z, vv.z, a); w.w = adam_element(w.w, g.w, mm.w, vv.w, a);
+        reinterpret_cast<float4 *>(weight)[i] = w;
+        reinterpret_cast<float4 *>(m)[i] = mm;
+        reinterpret_cast<float4 *>(v)[i] = vv;
+        if (EMA) {
+            float4 e = reinterpret_cast<float4 *>(ema)[i];
+            e.x = ema_element(e.x, w.x, a); e.y = ema_element(e.y, w.y, a); e.z = ema_element(e.z, w.z, a); e.w = ema_element(e.w, w.w, a);
+            reinterpret_cast<float4 *>(ema)[i] = e;
+        }
     }
+    for (size_t i = n4 * 4 + tid; i < n; i += stride) {
+        float mm = m[i], vv = v[i];
+        const float w = adam_element(weight[i], dweight[i], mm, vv, a);
+        weight[i] = w; m[i] = mm; v[i] = vv;
+        if (EMA) ema[i] = ema_element(ema[i], w, a);
+    }
+}
+
+static int launch_adam(float *weight, const float *dweight, float *m, float *v, float *ema, size_t n, const AdamArgs &a,
+                       const double *corrections, cudaStream_t s)
+{
+    const int vec = aligned16(weight) && aligned16(dweight) && aligned16(m) && aligned16(v) && (!ema || aligned16(ema));
+    const int grid = stream_grid(vec ? (n + 3) / 4 : n, 256);
+    if (ema) adam_kernel<true><<<grid, 256, 0, s>>>(weight, dweight, m, v, ema, n, a, corrections, vec);
+    else adam_kernel<false><<<grid, 256, 0, s>>>(weight, dweight, m, v, nullptr, n, a, corrections, vec);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1263,25 +1290,25 @@ int b200_vae_backward(float *d_mu, float *d_logvar, const float *delta, const fl
 int b200_adam(float *weight, const float *dweight, float *m, float *v, size_t n, uint32_t batch_size, double speed,
               double beta1, double beta2, double epsilon, double iteration, void *stream)
 {
-    if (!weight || !dweight || !m || !v) return fail(B200_E_ARG, "null tensor pointer");
-    if (!batch_size) return fail(B200_E_ARG, "batch_size must be positive");
-    if (!n) return B200_OK;
-    double c1 = 1.0 - pow(beta1, iteration), c2 = 1.0 - pow(beta2, iteration);
-    adam_kernel<<<stream_grid(n, 256), 256, 0, ST(stream)>>>(weight, dweight, m, v, n, (float)batch_size, speed, beta1, beta2, epsilon, c1, c2, nullptr);
-    B200_LAUNCH_CHECK();
-    return B200_OK;
+    return b200_adam_ema(weight, dweight, m, v, nullptr, n, batch_size, speed, beta1, beta2, epsilon, iteration, nullptr, 0.0, stream);
 }
 
 int b200_adam_prepared(float *weight, const float *dweight, float *m, float *v, size_t n, uint32_t batch_size, double speed,
                        double beta1, double beta2, double epsilon, const double *corrections, void *stream)
 {
-    if (!weight || !dweight || !m || !v || !corrections) return fail(B200_E_ARG, "null tensor pointer");
+    if (!corrections) return fail(B200_E_ARG, "null tensor pointer");
+    return b200_adam_ema(weight, dweight, m, v, nullptr, n, batch_size, speed, beta1, beta2, epsilon, 0.0, corrections, 0.0, stream);
+}
+
+int b200_adam_ema(float *weight, const float *dweight, float *m, float *v, float *ema, size_t n, uint32_t batch_size, double speed,
+                  double beta1, double beta2, double epsilon, double iteration, const double *corrections, double ema_k, void *stream)
+{
+    if (!weight || !dweight || !m || !v) return fail(B200_E_ARG, "null tensor pointer");
     if (!batch_size) return fail(B200_E_ARG, "batch_size must be positive");
     if (!n) return B200_OK;
-    adam_kernel<<<stream_grid(n, 256), 256, 0, ST(stream)>>>(weight, dweight, m, v, n, (float)batch_size, speed, beta1, beta2, epsilon, 0.0, 0.0,
-                                                             corrections);
-    B200_LAUNCH_CHECK();
-    return B200_OK;
+    const double c1 = corrections ? 1.0 : 1.0 - pow(beta1, iteration), c2 = corrections ? 1.0 : 1.0 - pow(beta2, iteration);
+    if (!corrections && (c1 == 0.0 || c2 == 0.0)) return fail(B200_E_ARG, "Adam: iteration must be positive");
+    return launch_adam(weight, dweight, m, v, ema, n, adam_args(batch_size, speed, beta1, beta2, epsilon, c1, c2, ema_k), corrections, ST(stream));
 }
 
 }  // extern "C"

@@ -63,6 +63,7 @@ template<class type_t> class CTensorConv;
 template<class type_t> class CTensorApplyFunc;
 template<class type_t> class CTensorTest;
 template<class type_t> struct STensorKernel;
+template<class type_t> class CB200LayerPort;
 
 template<class type_t> CTensor<type_t> operator+(const CTensor<type_t> &cTensor_Left,const CTensor<type_t> &cTensor_Right);
 template<class type_t> CTensor<type_t> operator-(const CTensor<type_t> &cTensor_Left,const CTensor<type_t> &cTensor_Right);
@@ -118,6 +119,7 @@ class CTensor
  template<class new_type_t> friend class CTensorConv;
  template<class new_type_t> friend class CTensorApplyFunc;
  template<class new_type_t> friend class CTensorTest;
+ template<class new_type_t> friend class CB200LayerPort;
  private:
   mutable uint32_t Size_X;
   mutable uint32_t Size_Y;

@@ -50,7 +50,13 @@ class CTensorMath
   static void Clip(CTensor<type_t> &cTensor,type_t min_value,type_t max_value);
   static void Signum(CTensor<type_t> &cTensor);
   static void Adam(CTensor<type_t> &cTensor_Weight,CTensor<type_t> &cTensor_dWeight,CTensor<type_t> &cTensor_M,CTensor<type_t> &cTensor_V,uint32_t batch_size,double speed,double beta1,double beta2,double epsilon,double iteration);
+  static void SetTimeStep(CTensor<type_t> &cTensor_Output,const CTensor<type_t> &cTensor_Input,const CTensor<uint32_t> &cTensor_TimeStep);
+  static void CreateDropOutMatrix(CTensor<type_t> &cTensor_Output,type_t drop_out);
+  static void SetNormalNoise(CTensor<type_t> &cTensor_Output);
+  static void GetNoiseImageAndNoise(CTensor<type_t> &cTensor_NoisyImage,CTensor<type_t> &cTensor_Noise,const CTensor<type_t> &cTensor_Image,const CTensor<type_t> &cTensor_SqrtAlphaBar,const CTensor<type_t> &cTensor_SqrtOneMinusAlphaBar);
  private:
+  // seed of the next random tensor: rand() as in the reference (cuda/ctensormath.cu.h:3205), widened by a call counter
+  static unsigned long long NextSeed(void) {static unsigned long long counter=0;counter++;return((static_cast<unsigned long long>(rand())<<32)^counter);}
   static bool SameZYX(const CTensor<type_t> &a,const CTensor<type_t> &b) {return(a.Size_X==b.Size_X && a.Size_Y==b.Size_Y && a.Size_Z==b.Size_Z);}
   static size_t PlaneCount(const CTensor<type_t> &a) {return(static_cast<size_t>(a.Size_X)*a.Size_Y*a.Size_Z);}
   static void* Stream(void) {return(static_cast<void*>(B200TensorStream()));}
@@ -264,6 +270,62 @@ void CTensorMath<type_t>::SplitZ(CTensor<type_t> &cTensor_OutputA,CTensor<type_t
                         in,cTensor_Input.Size_W,static_cast<size_t>(cTensor_Input.Size_X)*cTensor_Input.Size_Y,Stream()));
  cTensor_OutputA.SetDeviceOnChange();
  cTensor_OutputB.SetDeviceOnChange();
+}
+
+// cuda/ctensormath.cu.h:3061
+template<class type_t>
+void CTensorMath<type_t>::SetTimeStep(CTensor<type_t> &cTensor_Output,const CTensor<type_t> &cTensor_Input,const CTensor<uint32_t> &cTensor_TimeStep)
+{
+ if (!SameZYX(cTensor_Input,cTensor_Output) || cTensor_Input.Size_W!=cTensor_Output.Size_W || cTensor_TimeStep.Size_W!=cTensor_Input.Size_W ||
+     cTensor_TimeStep.Size_X!=1 || cTensor_TimeStep.Size_Y!=1 || cTensor_TimeStep.Size_Z!=1)
+ {
+  throw "CTensor::SetTimeStep: tensor sizes do not match!";
+ }
+ const float *in=B200FloatPtr(cTensor_Input.DeviceRead());
+ const uint32_t *time_step=cTensor_TimeStep.DeviceRead();
+ B200Check(b200_set_time_step(B200FloatPtr(cTensor_Output.DeviceWrite()),in,time_step,cTensor_Input.Size_W,PlaneCount(cTensor_Input),Stream()));
+ cTensor_Output.SetDeviceOnChange();
+}
+
+// cuda/ctensormath.cu.h:3131
+template<class type_t>
+void CTensorMath<type_t>::CreateDropOutMatrix(CTensor<type_t> &cTensor_Output,type_t drop_out)
+{
+ B200Check(b200_dropout_mask(B200FloatPtr(cTensor_Output.DeviceWrite()),PlaneCount(cTensor_Output)*cTensor_Output.Size_W,static_cast<float>(drop_out),NextSeed(),Stream()));
+ cTensor_Output.SetDeviceOnChange();
+}
+
+// cuda/ctensormath.cu.h:3187
+template<class type_t>
+void CTensorMath<type_t>::SetNormalNoise(CTensor<type_t> &cTensor_Output)
+{
+ B200Check(b200_normal_noise(B200FloatPtr(cTensor_Output.DeviceWrite()),PlaneCount(cTensor_Output)*cTensor_Output.Size_W,NextSeed(),Stream()));
+ cTensor_Output.SetDeviceOnChange();
+}
+
+// cuda/ctensormath.cu.h:3250
+template<class type_t>
+void CTensorMath<type_t>::GetNoiseImageAndNoise(CTensor<type_t> &cTensor_NoisyImage,CTensor<type_t> &cTensor_Noise,const CTensor<type_t> &cTensor_Image,const CTensor<type_t> &cTensor_SqrtAlphaBar,const CTensor<type_t> &cTensor_SqrtOneMinusAlphaBar)
+{
+ if (!SameZYX(cTensor_NoisyImage,cTensor_Noise) || cTensor_NoisyImage.Size_W!=cTensor_Noise.Size_W)
+ {
+  throw "CTensor::GetNoiseImageAndNoise: the sizes of NoisyImage and Noise do not match!";
+ }
+ if (!SameZYX(cTensor_NoisyImage,cTensor_Image) || cTensor_NoisyImage.Size_W!=cTensor_Image.Size_W)
+ {
+  throw "CTensor::GetNoiseImageAndNoise: the sizes of NoisyImage and Image do not match!";
+ }
+ if (cTensor_SqrtAlphaBar.Size_W!=cTensor_Image.Size_W || cTensor_SqrtOneMinusAlphaBar.Size_W!=cTensor_Image.Size_W)
+ {
+  throw "CTensor::GetNoiseImageAndNoise: the sizes of SqrtAlphaBar/SqrtOneMinusAlphaBar and Image do not match!";
+ }
+ const float *image=B200FloatPtr(cTensor_Image.DeviceRead());
+ const float *sa=B200FloatPtr(cTensor_SqrtAlphaBar.DeviceRead());
+ const float *so=B200FloatPtr(cTensor_SqrtOneMinusAlphaBar.DeviceRead());
+ B200Check(b200_noisy_image(B200FloatPtr(cTensor_NoisyImage.DeviceWrite()),B200FloatPtr(cTensor_Noise.DeviceWrite()),image,sa,so,cTensor_Image.Size_W,
+                            PlaneCount(cTensor_Image),1,NextSeed(),Stream()));
+ cTensor_Noise.SetDeviceOnChange();
+ cTensor_NoisyImage.SetDeviceOnChange();
 }
 
 template<class type_t>

@@ -240,6 +240,49 @@ class NetLayerUpSampling(_Layer):
         return self.prev_error
 
 
+class NetLayerTimeEmbedding(_Layer):
+    """netlayer/cnetlayertimeembedding.cu.h: Forward :224 adds the sinusoidal code of each sample's time step (SetTimeStep);
+    the error passes through unchanged (:318-322)."""
+
+    def __init__(self, in_shape, batch):
+        self.in_shape = self.out_shape = tuple(in_shape)
+        self.batch = batch
+        self.H = torch.empty((batch,) + self.in_shape, device="cuda")
+        self.time_line = torch.zeros((batch, 1, 1, 1), dtype=torch.int32, device="cuda")
+
+    def SetTimeStep(self, index, time_step):
+        self.time_line[index] = int(time_step)
+
+    def Forward(self, x):
+        ops.CTensorMath.SetTimeStep(self.H, x, self.time_line)
+        return self.H
+
+    def TrainingBackward(self, delta, create_delta_weight=True, need_prev=True):
+        return delta
+
+
+class NetLayerConcatenator(_Layer):
+    """netlayer/cnetlayerconcatenator.cu.h: Forward :235 joins the outputs of two layers along Z (ConcatecationZ);
+    SetOutputError :372 splits the error back (SplitZ).  Two inputs, so it sits outside Net's single chain."""
+
+    def __init__(self, in_shape_a, in_shape_b, batch):
+        if tuple(in_shape_a[1:]) != tuple(in_shape_b[1:]):
+            raise ops.B200Error(1, "concatenated layers must have the same Y and X size")
+        self.in_shape_a, self.in_shape_b, self.batch = tuple(in_shape_a), tuple(in_shape_b), batch
+        self.out_shape = (in_shape_a[0] + in_shape_b[0],) + tuple(in_shape_a[1:])
+        self.H = torch.empty((batch,) + self.out_shape, device="cuda")
+        self.prev_error_a = torch.empty((batch,) + self.in_shape_a, device="cuda")
+        self.prev_error_b = torch.empty((batch,) + self.in_shape_b, device="cuda")
+
+    def Forward(self, a, b):
+        ops.CTensorMath.ConcatecationZ(self.H, a, b)
+        return self.H
+
+    def TrainingBackward(self, delta, create_delta_weight=True, need_prev=True):
+        ops.CTensorMath.SplitZ(self.prev_error_a, self.prev_error_b, delta)
+        return self.prev_error_a, self.prev_error_b
+
+
 class AdamCorrections:
     """The two bias corrections of Adam for the current step in device memory, refreshed from the host before a step by a
     16-byte stream-ordered copy.  The copy reads pinned host memory when it executes, and the host may run many steps ahead
@@ -290,9 +333,33 @@ class Net:
             layer.bind({n: self.weights.views["%d.%s" % (i, n)] for n in names}, {n: self.grads.views["%d.%s" % (i, n)] for n in names})
             layer.init(rng)
 
+        self.ema, self.ema_k, self.use_ema = None, 0.999, False
+
     @property
     def parameter_count(self):
         return self.weights.buffer.numel()
+
+    def EnableEMA(self, state, ema_k=0.999):
+        """INetLayer::EnableEMA for every layer of the net (netlayer/cnetlayerconvolution.cu.h:622-634): the averaged weights
+        start as a copy of the weights; TrainingUpdateWeight then keeps ema = ema_k * ema + (1 - ema_k) * weight in the same
+        launch as Adam.  Disabling drops them."""
+        if state:
+            self.ema = GradArena({k: v[2] for k, v in self.weights.offsets.items()}, "cuda")
+            self.ema.buffer.copy_(self.weights.buffer)
+            self.ema_k = ema_k
+        else:
+            self.SetUseEMA(False)
+            self.ema = None
+
+    def SetUseEMA(self, state):
+        """INetLayer::SetUseEMA (netlayer/inetlayer.cu.h:97-101): Forward uses the averaged weights instead of the trained ones."""
+        if state and self.ema is None:
+            raise ops.B200Error(2, "SetUseEMA: the averaged weights were not enabled")
+        source = self.ema if state else self.weights
+        for i, layer in enumerate(self.layers):
+            names = list(layer.param_shapes())
+            layer.bind({n: source.views["%d.%s" % (i, n)] for n in names}, layer.g if names else {})
+        self.use_ema = bool(state)
 
     def TrainingResetDeltaWeight(self):
         ops.CTensorMath.Fill(self.grads.buffer.view(1, 1, 1, -1), 0.0)
@@ -314,12 +381,9 @@ class Net:
         {1 - beta1^iteration, 1 - beta2^iteration} (see adam_corrections); the launch then has fixed arguments and can be
         part of a CUDA graph."""
         w, g, m, v = (a.buffer for a in (self.weights, self.grads, self.m, self.v))
-        if corrections is None:
-            ops.CTensorMath.Adam(w.view(1, 1, 1, -1), g.view(1, 1, 1, -1), m.view(1, 1, 1, -1), v.view(1, 1, 1, -1),
-                                 int(self.batch * batch_scale), speed, beta1, beta2, epsilon, iteration)
-        else:
-            _check(load().b200_adam_prepared(_ptr(w), _ptr(g), _ptr(m), _ptr(v), w.numel(), int(self.batch * batch_scale), speed, beta1, beta2,
-                                             epsilon, _ptr(corrections), _stream()))
+        ema = self.ema.buffer if self.ema is not None else None
+        _check(load().b200_adam_ema(_ptr(w), _ptr(g), _ptr(m), _ptr(v), _ptr(ema), w.numel(), int(self.batch * batch_scale), speed, beta1,
+                                    beta2, epsilon, 0.0 if iteration is None else iteration, _ptr(corrections), self.ema_k, _stream()))
 
     def broadcast_weights(self):
         import torch.distributed as dist

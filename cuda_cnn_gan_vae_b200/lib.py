@@ -65,6 +65,11 @@ SIGNATURES = {
     "b200_vae_backward": (_i, [_fp] * 6 + [_sz, _f, _vp]),
     "b200_adam": (_i, [_fp, _fp, _fp, _fp, _sz, C.c_uint32, _d, _d, _d, _d, _d, _vp]),
     "b200_adam_prepared": (_i, [_fp, _fp, _fp, _fp, _sz, C.c_uint32, _d, _d, _d, _d, _vp, _vp]),
+    "b200_set_time_step": (_i, [_fp, _fp, _vp, _i, _sz, _vp]),
+    "b200_normal_noise": (_i, [_fp, _sz, C.c_ulonglong, _vp]),
+    "b200_dropout_mask": (_i, [_fp, _sz, _f, C.c_ulonglong, _vp]),
+    "b200_noisy_image": (_i, [_fp, _fp, _fp, _fp, _fp, _i, _sz, _i, C.c_ulonglong, _vp]),
+    "b200_adam_ema": (_i, [_fp, _fp, _fp, _fp, _fp, _sz, C.c_uint32, _d, _d, _d, _d, _d, _vp, _d, _vp]),
 }
 
 _lib = None

@@ -281,6 +281,36 @@ class CTensorMath:
                                    inp.shape[2] * inp.shape[3], _stream()))
 
     @staticmethod
+    def SetTimeStep(output, inp, time_step):
+        """time_step: uint32 (torch.int32 storage) tensor [W,1,1,1] (cuda/ctensormath.cu.h:3061)."""
+        _t(output), _t(inp)
+        if output.shape != inp.shape or time_step.numel() != inp.shape[0] or time_step.dtype != torch.int32:
+            raise B200Error(1, "CTensor::SetTimeStep: tensor sizes do not match")
+        _check(load().b200_set_time_step(_ptr(output), _ptr(inp), _ptr(time_step), inp.shape[0], _n(inp), _stream()))
+
+    @staticmethod
+    def SetNormalNoise(output, seed):
+        _t(output)
+        _check(load().b200_normal_noise(_ptr(output), output.numel(), seed, _stream()))
+
+    @staticmethod
+    def CreateDropOutMatrix(output, drop_out, seed):
+        _t(output)
+        _check(load().b200_dropout_mask(_ptr(output), output.numel(), drop_out, seed, _stream()))
+
+    @staticmethod
+    def GetNoiseImageAndNoise(noisy_image, noise, image, sqrt_alpha_bar, sqrt_one_minus_alpha_bar, seed=None):
+        """seed given: the noise is drawn and written to `noise` (the reference's behaviour, cuda/ctensormath.cu.h:3250);
+        seed None: `noise` is an input supplied by the caller."""
+        _t(noisy_image), _t(noise), _t(image), _t(sqrt_alpha_bar), _t(sqrt_one_minus_alpha_bar)
+        if noisy_image.shape != noise.shape or noisy_image.shape != image.shape:
+            raise B200Error(1, "CTensor::GetNoiseImageAndNoise: the sizes of NoisyImage, Noise and Image do not match")
+        if sqrt_alpha_bar.numel() != image.shape[0] or sqrt_one_minus_alpha_bar.numel() != image.shape[0]:
+            raise B200Error(1, "CTensor::GetNoiseImageAndNoise: the sizes of SqrtAlphaBar/SqrtOneMinusAlphaBar and Image do not match")
+        _check(load().b200_noisy_image(_ptr(noisy_image), _ptr(noise), _ptr(image), _ptr(sqrt_alpha_bar), _ptr(sqrt_one_minus_alpha_bar),
+                                       image.shape[0], _n(image), int(seed is not None), seed or 0, _stream()))
+
+    @staticmethod
     def TensorItemProduction(output, left, right):
         _t(output), _t(left), _t(right)
         _same_zyx(output, left, right)

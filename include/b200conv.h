@@ -272,7 +272,9 @@ int b200_vae_forward(float *z, const float *mu, const float *logvar, const float
 /* CNetLayerVAECoderOutput::SetOutputError (:424-455). */
 int b200_vae_backward(float *d_mu, float *d_logvar, const float *delta, const float *mu, const float *logvar,
                       const float *eps, size_t total, float kl_speed, void *stream);
-/* CTensorMath::Adam (cuda :2978-3022, cpu :1119-1165).  iteration is used as given (the CPU backend's rule). */
+/* CTensorMath::Adam (cuda :2978-3022, cpu :1119-1165).  iteration is used as given (the CPU backend's rule).  The moments m
+ * and v are bit-identical to the CPU backend's; the step is evaluated in fp32 instead of double, so an updated weight may
+ * differ from the CPU backend's in its last bit. */
 int b200_adam(float *weight, const float *dweight, float *m, float *v, size_t n, uint32_t batch_size, double speed,
               double beta1, double beta2, double epsilon, double iteration, void *stream);
 /* The same update with the two bias corrections {1 - beta1^t, 1 - beta2^t} read from device memory (two doubles) instead of
@@ -280,6 +282,29 @@ int b200_adam(float *weight, const float *dweight, float *m, float *v, size_t n,
  * replayed from a CUDA graph while the caller refreshes the two numbers before each replay.  No reference counterpart. */
 int b200_adam_prepared(float *weight, const float *dweight, float *m, float *v, size_t n, uint32_t batch_size, double speed,
                        double beta1, double beta2, double epsilon, const double *corrections, void *stream);
+/* ---- helpers of the diffusion model and the drop-out layer ------------------------------------- */
+
+/* CTensorMath::SetTimeStep (cuda/ctensormath.cu.h:3029-3096; the forward pass of CNetLayerTimeEmbedding,
+ * netlayer/cnetlayertimeembedding.cu.h:224-227): out[w,pos] = in[w,pos] + (pos even ? sin : cos)(t[w] / 10000^(pos/n)), pos the
+ * linear index inside one sample of n = Z*Y*X elements, t a DEVICE array of w uint32 time steps. */
+int b200_set_time_step(float *out, const float *in, const uint32_t *time_step, int w, size_t n, void *stream);
+/* CTensorMath::SetNormalNoise (cuda/ctensormath.cu.h:3161-3210): standard normal numbers.  The reference seeds cuRAND states
+ * with rand(); here the caller gives the seed of a counter-based Philox4x32-10 stream (same seed, same tensor). */
+int b200_normal_noise(float *out, size_t n, unsigned long long seed, void *stream);
+/* CTensorMath::CreateDropOutMatrix (cuda/ctensormath.cu.h:3101-3156): 0 with probability drop_out, else 1 / (1 - drop_out). */
+int b200_dropout_mask(float *out, size_t n, float drop_out, unsigned long long seed, void *stream);
+/* CTensorMath::GetNoiseImageAndNoise (cuda/ctensormath.cu.h:3216-3294): noisy[w] = sqrt_alpha_bar[w] * image[w] +
+ * sqrt_one_minus_alpha_bar[w] * noise[w] (the two coefficient arrays hold one float per sample).  generate != 0: the noise
+ * is drawn (seed) and written to `noise` in the same pass, as the reference does; generate == 0: `noise` is an input. */
+int b200_noisy_image(float *noisy, float *noise, const float *image, const float *sqrt_alpha_bar, const float *sqrt_one_minus_alpha_bar,
+                     int w, size_t n, int generate, unsigned long long seed, void *stream);
+
+/* Adam followed by the exponential moving average of the updated weights that the reference's layers keep when EMA is
+ * enabled (netlayer/cnetlayerconvolution.cu.h:547-551: Add(W_EMA, W_EMA, W, EMA_K, 1 - EMA_K) after the update), in the same
+ * pass over the parameters: ema = ema_k * ema + (1 - ema_k) * weight.  ema may be NULL (plain Adam).  corrections, when
+ * non-NULL, replaces `iteration` as in b200_adam_prepared. */
+int b200_adam_ema(float *weight, const float *dweight, float *m, float *v, float *ema, size_t n, uint32_t batch_size, double speed,
+                  double beta1, double beta2, double epsilon, double iteration, const double *corrections, double ema_k, void *stream);
 
 #ifdef __cplusplus
 }

@@ -348,6 +348,22 @@ class Oracle:
         assert r == 0, r
         return z, eps, dmu, dlv
 
+    def set_time_step(self, x, time_step):
+        """port only (the reference has SetTimeStep on its CUDA backend alone)."""
+        assert self.kind == "port"
+        x = _c(x)
+        t = np.ascontiguousarray(time_step, dtype=np.uint32).ravel()
+        out = np.empty_like(x)
+        self.lib.orc_set_time_step(_p(out), _p(x), t.ctypes.data_as(_u), x.shape[0], C.c_size_t(x[0].size))
+        return out
+
+    def noisy_image(self, image, noise, sa, so):
+        assert self.kind == "port"
+        image, noise, sa, so = _c(image), _c(noise), _c(sa).ravel(), _c(so).ravel()
+        out = np.empty_like(image)
+        self.lib.orc_noisy_image(_p(out), _p(image), _p(noise), _p(sa), _p(so), image.shape[0], C.c_size_t(image[0].size))
+        return out
+
     def adam(self, weight, dweight, m, v, batch_size, speed, beta1, beta2, epsilon, iteration):
         weight, dweight, m, v = _c(weight).copy(), _c(dweight), _c(m).copy(), _c(v).copy()
         n = weight.size

@@ -525,6 +525,33 @@ void orc_vae_backward(float *d_mu, float *d_logvar, const float *delta, const fl
     }
 }
 
+/* cuda/ctensormath.cu.h:3029-3058  SetTimeStep (the reference has this routine on its CUDA backend only, so this
+ * restatement follows the kernel's arithmetic and is NOT pinned to a reference run: parity unpinned for this routine):
+ * out[w,pos] = in[w,pos] + (pos even ? sin : cos)(t[w] / 10000^(pos/n)), float arithmetic. */
+void orc_set_time_step(float *out, const float *in, const uint32_t *time_step, int W, size_t n)
+{
+    for (int w = 0; w < W; w++)
+        for (size_t pos = 0; pos < n; pos++) {
+            float t = (float)time_step[w];
+            float angle = t / powf(10000.0f, (float)pos / (float)n);
+            float value = in[(size_t)w * n + pos];
+            if ((pos & 1) == 0) value += sinf(angle);
+            else value += cosf(angle);
+            out[(size_t)w * n + pos] = value;
+        }
+}
+
+/* cuda/ctensormath.cu.h:3216-3245  GetNoiseImageAndNoise with the noise supplied (CUDA backend only, parity unpinned):
+ * noisy = sqrt_alpha_bar[w]*image + sqrt_one_minus_alpha_bar[w]*noise. */
+void orc_noisy_image(float *noisy, const float *image, const float *noise, const float *sa, const float *so, int W, size_t n)
+{
+    for (int w = 0; w < W; w++)
+        for (size_t i = 0; i < n; i++) {
+            size_t k = (size_t)w * n + i;
+            noisy[k] = sa[w] * image[k] + so[w] * noise[k];
+        }
+}
+
 /* cpu/ctensormath.h:1119-1165  Adam step (the CPU variant: bias correction with `iteration` as given). */
 void orc_adam(float *weight, const float *dweight, float *m, float *v, size_t n, uint32_t batch_size,
               double speed, double beta1, double beta2, double epsilon, double iteration)

@@ -82,3 +82,69 @@ def test_reference_layers_match_the_cpu_backend(tmp_path, mode, tol):
             assert np.median(diff) <= 4 * tol, (name, np.median(diff))
             continue
         assert np.max(diff) <= 4 * tol, (name, np.max(diff))
+
+
+@pytest.mark.parametrize("mode,tol", [(2, 2e-5), (0, TOL_X3), (1, TOL_TF32)])
+def test_own_layer_classes_match_the_cpu_twin(tmp_path, port, mode, tol):
+    """host/netlayer/: this package's CNetLayerLinear, CNetLayerBackConvolution, CNetLayerBatchNormalization and
+    CNetLayerConvolution (fast path: layer contexts, batch-summed gradients) chained with the reference's unmodified input and
+    function layers.  The C++ program dumps its weights and every tensor of one training step; the same chain is rebuilt on
+    the CPU checker from the dumped weights (the reference's transposed-convolution and batch-normalisation layer classes do
+    not work at its head revision, so the expectation is the checker's sequence of the reference's tensor routines).  The
+    program itself asserts that both convolution layers' backward passes ran on the tensor cores and that a checkpoint in
+    the reference's format reloads into an identical network."""
+    import torch
+    from cuda_cnn_gan_vae_b200 import ops
+    from cuda_cnn_gan_vae_b200.layers import (Net, NetLayerBackConvolution, NetLayerBatchNormalization, NetLayerConvolution, NetLayerFunction,
+                                              NetLayerLinear)
+    from oracle.net_twin import OracleNet
+    from tests.test_gpu_nets import check
+    exe = _need("dropin_fastlayers")
+    dump = str(tmp_path / "dump_fast.txt")
+    r = subprocess.run([exe, dump, str(tmp_path / "net.bin"), str(mode)], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "PASS" in r.stdout, r.stdout[-3000:] + r.stderr[-2000:]
+    got = _read_dump(dump)
+    B = 16
+    ops.set_precision(ops.FP32)
+    net = Net((1, 20, 1), B, [(NetLayerLinear, dict(neurons=512)), ("reshape", (32, 4, 4)),
+                              (NetLayerBackConvolution, dict(kernel_amount=16, kernel_size=4, stride=2, padding=1)),
+                              (NetLayerBatchNormalization, dict(momentum=0.9)), (NetLayerFunction, dict(func="leaky_relu", leaky_slope=0.1)),
+                              (NetLayerConvolution, dict(kernel_amount=24, kernel_size=4, stride=2, padding=1)), (NetLayerFunction, dict(func="tanh"))])
+    names = {0: ("linear", ("w", "b")), 1: ("backconv", ("kernel", "bias")), 2: ("bn", ("gamma", "beta")), 4: ("conv", ("kernel", "bias"))}
+    for i, (prefix, params) in names.items():
+        for j, p in enumerate(params):
+            view = net.layers[i].w[p]
+            view.copy_(torch.from_numpy(got["%s_param%d" % (prefix, j)].astype(np.float32)).view(view.shape))
+    twin = OracleNet(port, net)
+    x = got["input"].astype(np.float32).reshape(B, 1, 20, 1)
+    error = got["error"].astype(np.float32).reshape(B, 24, 4, 4)
+    twin.forward(x)
+    exact = mode == 2
+    for n in range(1, 7):
+        check("output of layer %d" % n, got["output_%d" % n], twin.outputs[n - 1], tol if exact else 4 * tol, exact)
+    twin.backward(error)
+    # free-running comparison: in the tensor-core modes the rounding differences of the forward pass pass through the batch
+    # normalisation's backward pass (16 samples) and the step of LeakyReLU's derivative, so the bound on the way down is loose;
+    # the layer-by-layer comparisons on identical operands are in tests/test_gpu_nets.py and tests/test_gpu_full_size.py
+    down = 4 * tol if exact else 16 * tol
+    for n in (1, 2, 3, 5):          # own layers: the error that arrived at their output
+        check("delta at layer %d" % n, got["delta_%d" % n], twin.deltas[n], down, exact)
+    for n in (4, 6):                # the reference's function layers: f'(input) * error
+        check("delta of function layer %d" % n, got["delta_%d" % n], twin.deltas[n - 1], down, exact)
+    for i, (prefix, params) in names.items():
+        for j, p in enumerate(params):
+            want = twin.grads[i][p]
+            g = got["%s_gradient%d" % (prefix, j)]
+            if not want.any():
+                assert not g.any(), (prefix, p)
+                continue
+            check("gradient %s.%s" % (prefix, p), g, want, down, exact, twin.grad_mag[i].get(p))
+    # Adam with iteration + 1 = 1 (the reference CUDA backend's rule): every weight moves by about the learning rate
+    twin.update(0.01, 1, B)
+    for i, (prefix, params) in names.items():
+        for j, p in enumerate(params):
+            before, after, want = got["%s_param%d" % (prefix, j)], got["updated_%s_param%d" % (prefix, j)], twin.params[i][p].ravel()
+            if exact and not (prefix in ("linear", "backconv") and p in ("b", "bias")):      # biases before a normalisation: noise gradients
+                assert np.max(np.abs(after - want)) <= 1e-4 * 0.01 + 1e-6, (prefix, p, np.max(np.abs(after - want)))
+            assert np.max(np.abs(after - before)) <= 0.0101
+    assert np.isfinite(got["output_after_update"]).all()

@@ -258,16 +258,40 @@ def test_vae_output_layer(ops, port):
     assert np.allclose(dlv.cpu().numpy(), dlo, rtol=5e-6, atol=1e-5)
 
 
-def test_adam(ops, port):
+@pytest.mark.parametrize("batch", [16, 48])          # reciprocal of the batch exact or not
+@pytest.mark.parametrize("n", [32 * 27, 10007])       # 16-byte path with and without a scalar tail
+def test_adam(ops, port, batch, n):
+    """Moments bit-identical to the CPU backend; the weight, whose step is evaluated in fp32 instead of double, within one
+    unit in the last place and bit-identical for nearly every element."""
     r = np.random.default_rng(17)
-    shape = (1, 1, 32, 27)
+    shape = (1, 1, 1, n)
     w, dw = r.normal(0, 1, shape).astype(np.float32), r.normal(0, 1, shape).astype(np.float32)
     m, v = r.normal(0, .1, shape).astype(np.float32), np.abs(r.normal(0, .1, shape)).astype(np.float32)
-    wo, mo, vo = port.adam(w, dw, m, v, 16, 2e-4, 0.5, 0.999, 1e-8, 3)
+    wo, mo, vo = port.adam(w, dw, m, v, batch, 2e-4, 0.5, 0.999, 1e-8, 3)
     W, M, V = dev(w), dev(m), dev(v)
-    ops.CTensorMath.Adam(W, dev(dw), M, V, 16, 2e-4, 0.5, 0.999, 1e-8, 3)
-    assert np.allclose(W.cpu().numpy(), wo, rtol=1e-6, atol=1e-7)
-    assert np.allclose(M.cpu().numpy(), mo, rtol=1e-6, atol=1e-8) and np.allclose(V.cpu().numpy(), vo, rtol=1e-6, atol=1e-9)
+    ops.CTensorMath.Adam(W, dev(dw), M, V, batch, 2e-4, 0.5, 0.999, 1e-8, 3)
+    assert M.cpu().numpy().tobytes() == mo.reshape(shape).tobytes() and V.cpu().numpy().tobytes() == vo.reshape(shape).tobytes()
+    got, want = W.cpu().numpy().ravel(), wo.ravel()
+    assert np.all(np.abs(got - want) <= np.spacing(np.abs(want)))
+    assert np.mean(got == want) > 0.99
+
+
+def test_adam_with_moving_average(ops, port):
+    """b200_adam_ema: the update followed by ema = k * ema + (1 - k) * weight (the reference's Add with scales), one launch."""
+    from cuda_cnn_gan_vae_b200.lib import load
+    r = np.random.default_rng(23)
+    n, k = 5003, 0.999
+    w, dw, e = (r.normal(0, 1, n).astype(np.float32) for _ in range(3))
+    m, v = r.normal(0, .1, n).astype(np.float32), np.abs(r.normal(0, .1, n)).astype(np.float32)
+    W, DW, M, V, E = dev(w), dev(dw), dev(m), dev(v), dev(e)
+    ops._check(load().b200_adam_ema(ops._ptr(W), ops._ptr(DW), ops._ptr(M), ops._ptr(V), ops._ptr(E), n, 64, 1e-3, 0.9, 0.999, 1e-8, 2.0, None, k,
+                                    ops._stream()))
+    ops.stream_status()
+    got_w = W.cpu().numpy()
+    want_e = port.binary("add", e.reshape(1, 1, 1, n), got_w.reshape(1, 1, 1, n), k, 1.0 - k)
+    assert E.cpu().numpy().tobytes() == want_e.ravel().tobytes()
+    wo, _, _ = port.adam(w, dw, m, v, 64, 1e-3, 0.9, 0.999, 1e-8, 2.0)
+    assert np.all(np.abs(got_w - wo.ravel()) <= np.spacing(np.abs(wo.ravel())))
 
 
 def test_set_clip_signum_div_transpose_bit_exact(ops):

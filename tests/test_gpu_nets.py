@@ -142,6 +142,39 @@ def test_adam_over_the_parameter_arena(ops, port):
     assert np.abs(net.weights.buffer.cpu().numpy() - w0).max() > 1e-5
 
 
+def test_moving_average_of_the_weights(ops, port):
+    """EnableEMA / SetUseEMA of the layers (netlayer/cnetlayerconvolution.cu.h:547-551, 622-634; inetlayer.cu.h:97-101): the
+    averaged weights follow every update and Forward can be switched over to them."""
+    from cuda_cnn_gan_vae_b200.nets import dcgan_generator
+    ops.set_precision(ops.FP32)
+    B = 4
+    net = dcgan_generator(B, noise=20, base=64, widths=(32, 16, 3))
+    net.EnableEMA(True, 0.9)
+    rng = np.random.default_rng(6)
+    z = torch.from_numpy(rng.standard_normal((B, 1, 20, 1)).astype(np.float32)).cuda()
+    err = torch.from_numpy(rng.standard_normal((B, 3, 32, 32)).astype(np.float32)).cuda()
+    ema = net.weights.buffer.cpu().numpy().copy()
+    for it in (1, 2):
+        net.TrainingResetDeltaWeight()
+        net.Forward(z)
+        net.TrainingBackward(err, True)
+        net.TrainingUpdateWeight(1e-2, it)
+        w = net.weights.buffer.cpu().numpy()
+        ema = port.binary("add", ema.reshape(1, 1, 1, -1), w.reshape(1, 1, 1, -1), 0.9, 1.0 - 0.9).ravel()
+        assert net.ema.buffer.cpu().numpy().tobytes() == ema.tobytes()
+    out_w = net.Forward(z).clone()
+    net.SetUseEMA(True)
+    out_e = net.Forward(z).clone()
+    net.SetUseEMA(False)
+    assert torch.equal(net.Forward(z), out_w) and not torch.equal(out_e, out_w)
+    # the same forward pass with the averaged weights copied into the weight arena
+    net.weights.buffer.copy_(net.ema.buffer)
+    assert torch.equal(net.Forward(z), out_e)
+    net.EnableEMA(False)
+    assert net.ema is None
+    ops.stream_status()
+
+
 def test_dcgan_step_graph_replay_matches_eager(ops):
     """The combined step replayed from its CUDA graph gives the same weights and outputs as the eager launches."""
     from cuda_cnn_gan_vae_b200.nets import DCGANStep

@@ -298,6 +298,9 @@ def main():
     ap.add_argument("--hbm-only", action="store_true", help="run only the memory-bound kernel measurements (profiling aid)")
     ap.add_argument("--dcgan-batch", type=int, default=64, help="images per GPU in the DCGAN step")
     ap.add_argument("--dcgan-fused", action="store_true", help="batch normalisation and the function layer after it as one fused layer (comparison aid)")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="several ranks: sum the gradients with the library's own NVLink peer-memory kernels (default) or with NCCL")
+    ap.add_argument("--dcgan-no-overlap", action="store_true", help="run the discriminator's exchange on the main stream instead of beside the generator's backward pass")
     ap.add_argument("--dcgan-eager", action="store_true", help="launch the DCGAN step eagerly instead of replaying its CUDA graph (profiling aid)")
     args = ap.parse_args()
     keep_stdout_clean()
@@ -320,8 +323,6 @@ def main():
     torch.cuda.set_device(local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"           # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     if args.hbm_only:
         emit(json.dumps(dict(hbm_kernels=hbm_kernels(torch, ops, measured_peaks()["hbm"], iters=2))))
@@ -340,9 +341,19 @@ def main():
         dist.broadcast(wt, 0)                       # weights replicated from rank 0 at start-up
     y = torch.empty(B, K, H, W, device="cuda")
     dx = torch.empty(B, Cc, H, W, device="cuda")
-    from cuda_cnn_gan_vae_b200.dp import GradArena
-    grads = GradArena({"dW": (1, 1, K, Cc * k * k), "dB": (1, K, 1, 1)}, "cuda")   # contiguous dW | dB, all-reduced as one buffer
+    from cuda_cnn_gan_vae_b200.dp import GradArena, PeerBuffer, arena_layout
+    shapes = {"dW": (1, 1, K, Cc * k * k), "dB": (1, K, 1, 1)}
+    peer = None
+    if world > 1 and args.exchange == "peer":
+        peer = PeerBuffer(arena_layout(shapes)[1])      # the arena lives in memory every rank maps: the library's kernel sums it over NVLink
+    grads = GradArena(shapes, "cuda", peer.buffer[:arena_layout(shapes)[1]] if peer else None)   # contiguous dW | dB, summed as one buffer
     arena, dk, db = grads.buffer, grads.views["dW"], grads.views["dB"]
+
+    def sum_over_ranks():
+        if peer is not None:
+            ops._check(lib.b200_allreduce(peer.comm, 0, arena.numel(), 0, ops._stream()))
+        else:
+            grads.all_reduce()
     step_flops = flops_per_sample(c) * c["batch"]
 
     layer = ops.ConvLayer(Cc, H, W, K, k, k, 1, 1, 1, 1, B)
@@ -360,7 +371,7 @@ def main():
             main = torch.cuda.current_stream()
             side.wait_stream(main)
             with torch.cuda.stream(side):
-                grads.all_reduce()
+                sum_over_ranks()
             layer.backward(dx, None, None, delta, x, wt)
             main.wait_stream(side)
         else:
@@ -453,7 +464,7 @@ def main():
                 main.wait_event(arrived[i])
                 layer_mb.forward(y[sl], x[sl], wt, bias)
                 layer_mb.backward(dx[sl], dk, db, delta[sl], x[sl], wt, accumulate=(i > 0))
-            grads.all_reduce()
+            sum_over_ranks()
             hres.copy_(arena, non_blocking=True)
             main.synchronize()
 
@@ -479,7 +490,8 @@ def main():
                           "up to the all-reduce are replayed from a CUDA graph captured after two eager steps")
         for mode_name, mode in (("tf32x3", ops.TF32X3), ("tf32", ops.TF32)):
             ops.set_precision(mode)
-            trainer = DCGANStep(gb, world=world, use_graph=not args.dcgan_eager, fused=args.dcgan_fused)   # a graph is captured in the precision mode of its first steps
+            trainer = DCGANStep(gb, world=world, use_graph=not args.dcgan_eager, fused=args.dcgan_fused,
+                                update="fused" if args.exchange == "peer" else "nccl", overlap=not args.dcgan_no_overlap)   # a graph is captured in the precision mode of its first steps
             dcgan["parameters"] = dict(generator=trainer.G.parameter_count, discriminator=trainer.D.parameter_count)
             n0 = lib.b200_launch_count()
             trainer(z, labels)                            # eager: every launch of the step is counted once
@@ -517,8 +529,10 @@ def main():
                     ms_per_step=head["ms_per_step"], higher_is_better=True, scaling="strong", vs_baseline=None, dtype="tf32",
                     data="synthetic",
                     config=dict(workload="dp_conv_sweep: batch %d of 256x32x32 N(0,1), 256 filters 3x3 s1 p1, fwd+bwd-data+wgrad%s"
-                                % (c["batch"], " + NCCL all-reduce of dW|dB" if world > 1 else ""),
-                                global_batch=c["batch"], per_gpu_batch=B, parallelism=f"dp{world}", l2="inputs exceed L2 (1 GiB tensors)",
+                                % (c["batch"], " + sum of dW|dB over the ranks" if world > 1 else ""),
+                                global_batch=c["batch"], per_gpu_batch=B, parallelism=f"dp{world}",
+                                exchange=(("library kernels over NVLink peer memory (b200_allreduce, b200_allreduce_adam)" if args.exchange == "peer"
+                                           else "NCCL all-reduce") if world > 1 else None), l2="inputs exceed L2 (1 GiB tensors)",
                                 parity="tf32: 2e-3, tf32x3: 1e-4 vs the reference CPU backend (tests/test_gpu_conv.py)",
                                 flops_per_step=step_flops),
                     clocks=head["clocks"], gpu_launches=head["gpu_launches"], roofline=head["roofline"], e2e=e2e,

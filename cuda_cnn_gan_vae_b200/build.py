@@ -5,7 +5,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-SOURCES = ["abi.cu", "simt_conv.cu", "simt_math.cu", "tc_conv.cu", "smallc.cu", "noalloc.cu", "layer.cu", "diffusion.cu"]
+SOURCES = ["abi.cu", "simt_conv.cu", "simt_math.cu", "tc_conv.cu", "smallc.cu", "noalloc.cu", "layer.cu", "diffusion.cu", "comm.cu"]
 LIB = os.path.join(HERE, "libb200conv.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",

@@ -4,6 +4,7 @@
 // implicit-GEMM kernels and the general CUDA-core kernels.
 #include "common.cuh"
 #include "kernels.h"
+#include <atomic>
 #include <cstring>
 #include <mutex>
 
@@ -30,8 +31,8 @@ int fail(int code, const char *fmt, ...)
     return code;
 }
 
-static unsigned long long g_launches = 0;
-void count_launch() { g_launches++; }
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 void set_path(int p) { g_path = p; }
 int precision() { return g_precision; }
 
@@ -131,7 +132,7 @@ int b200_set_precision(int mode)
 
 size_t b200_scratch_bytes(void) { return g_arena[current_device()].cap; }
 
-unsigned long long b200_launch_count(void) { return g_launches; }
+unsigned long long b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int b200_profile_tensor_core(int enable)
 {
@@ -147,6 +148,15 @@ int b200_stream_status(void *stream)
     if (e != cudaSuccess) return fail(B200_E_CUDA, "stream failed: %s", cudaGetErrorString(e));
     unsigned code = tc_read_status(1);
     if (code) return fail(B200_E_TIMEOUT, "a device-side wait gave up (code 0x%x); results of the last calls are invalid", code);
+    return B200_OK;
+}
+
+int b200_debug_set_status(unsigned code)
+{
+    unsigned *dev = nullptr;
+    int r = status_word(&dev);
+    if (r) return r;
+    tc_write_status(code);
     return B200_OK;
 }
 
@@ -228,6 +238,7 @@ int b200_conv_wgrad_batch(const b200_conv_geom *g, float *dkernel, float *dbias,
 {
     int r = check_geom(g);
     if (r) return r;
+    if ((r = check_forward_dims(g))) return r;
     if (!dkernel || !image || !delta) return fail(B200_E_ARG, "null tensor pointer");
     if (batch <= 0) return fail(B200_E_SHAPE, "non-positive batch");
     if (g_precision != B200_FP32) {

@@ -72,6 +72,8 @@ int smallc_dkernel(const b200_conv_geom &g, float *dkernel, const float *dk, int
 
 // Status word written by device-side waits that gave up (0 = none); clear != 0 resets it.
 unsigned tc_read_status(int clear);
+// host-side write of the status word (what a device-side wait that gave up would have written); for tests of the decoding
+void tc_write_status(unsigned code);
 // device pointer of the per-device status word (pinned, mapped host memory) that bounded device-side waits report into
 int status_word(unsigned **dev);
 

@@ -55,6 +55,8 @@ int b200_conv_wgrad_batch_static(const b200_conv_geom *g, float *dkernel, float 
     if (batch <= 0 || g->kernel_amount <= 0 || g->in_z <= 0 || g->kernel_x <= 0 || g->kernel_y <= 0 || g->stride_x <= 0 ||
         g->stride_y <= 0 || g->in_y <= 0 || g->in_x <= 0 || g->out_y <= 0 || g->out_x <= 0 || g->padding_x < 0 || g->padding_y < 0)
         return fail(B200_E_SHAPE, "non-positive convolution geometry");
+    if (g->out_x != (g->in_x - g->kernel_x + 2 * g->padding_x) / g->stride_x + 1 || g->out_y != (g->in_y - g->kernel_y + 2 * g->padding_y) / g->stride_y + 1)
+        return fail(B200_E_SHAPE, "wrong output size for convolution: %dx%d does not follow from the image, kernel, stride and padding", g->out_y, g->out_x);
     const size_t klen = (size_t)g->kernel_amount * g->in_z * g->kernel_y * g->kernel_x;
     const size_t dk_floats = (size_t)batch * klen;
     const size_t db_floats = (size_t)batch * g->kernel_amount;

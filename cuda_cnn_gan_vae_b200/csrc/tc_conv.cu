@@ -795,7 +795,15 @@ unsigned tc_read_status(int clear)
     return v;
 }
 
-static size_t g_smem_optin = 0;
+void tc_write_status(unsigned code)
+{
+    int d = 0;
+    cudaGetDevice(&d);
+    if (d < 0 || d >= 64 || !g_status_host[d]) return;
+    *(volatile unsigned *)g_status_host[d] = code;
+}
+
+static size_t g_smem_optin_dev[64];
 
 // Optional timing of the tensor-core kernel alone: a pair of events around every launch, read back
 // by tc_profile_read().  Used by the benchmark to put a live duration under the roofline figure.
@@ -872,12 +880,15 @@ static int launch_one(const CUtensorMap maps[4], const TcParams &p, int grid, si
 template <int MODE>
 static int launch_tc(const CUtensorMap maps[4], TcParams &p, bool x3, cudaStream_t s, int ctas = 1)
 {
-    if (!g_smem_optin) {
-        int d = 0, v = 0;
-        cudaGetDevice(&d);
-        B200_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, d));
-        g_smem_optin = (size_t)v;
+    int cur = 0;
+    cudaGetDevice(&cur);
+    if (cur < 0 || cur >= 64) cur = 0;
+    if (!g_smem_optin_dev[cur]) {
+        int v = 0;
+        B200_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, cur));
+        g_smem_optin_dev[cur] = (size_t)v;
     }
+    const size_t g_smem_optin = g_smem_optin_dev[cur];
     p.b_bytes = (uint32_t)p.b_boxes * p.b_box_bytes;
     p.mini_bytes = (uint32_t)((kABytes + p.b_bytes) * (x3 ? 2 : 1));
     const size_t fixed = 1024 /*alignment slack*/ + 256 /*barriers*/;
@@ -1135,7 +1146,11 @@ int weight_pack_fill(const b200_conv_geom &g, bool backward, const float *kernel
 // tiles fill the GPU and no split is considered).
 size_t conv_gemm_partial_elems(bool backward, const b200_conv_geom &g, int batch)
 {
-    const size_t out_elems = (size_t)batch * (backward ? (size_t)g.in_z * g.in_y * g.in_x : (size_t)g.kernel_amount * g.out_y * g.out_x);
+    const int k_out = backward ? g.in_z : g.kernel_amount;
+    const size_t pixels = (size_t)batch * (backward ? (size_t)g.in_y * g.in_x : (size_t)g.out_y * g.out_x);
+    const size_t out_elems = pixels * k_out;
+    // a problem whose widest tiles already give every SM two work items gains nothing from a split: no scratch for it
+    if (((pixels + 127) / 128) * (size_t)ceil_div(k_out, 256) >= 2 * (size_t)sm_count()) return 0;
     return out_elems * sizeof(float) <= (16u << 20) ? 8 * out_elems : 0;
 }
 

@@ -6,8 +6,12 @@ per-sample gradients over W (AddSumW, netlayer/cnetlayerconvolution.cu.h:507-508
 argument of TrainingUpdateWeight (netlayer/inetlayer.cu.h:87).  Here every rank reduces its own shard
 inside the weight-gradient kernel and the shards are summed with one all-reduce.
 """
+import ctypes as C
+
 import torch
 import torch.distributed as dist
+
+from .lib import load
 
 
 def shard_bounds(batch, rank, world):
@@ -19,19 +23,80 @@ def shard_bounds(batch, rank, world):
     return begin, begin + base + (1 if rank < rem else 0)
 
 
+def slice_bounds(n, rank, world):
+    """[begin, end) in floats of the part of an n-float arena that `rank` reduces and updates in the library's fused
+    exchange (b200_comm_slice: 16-byte groups dealt out in equal runs, the last ranks may get less or nothing)."""
+    b, e = C.c_size_t(0), C.c_size_t(0)
+    r = load().b200_comm_slice(n, rank, world, C.byref(b), C.byref(e))
+    if r:
+        raise ValueError(load().b200_last_error().decode())
+    return b.value, e.value
+
+
+def arena_layout(shapes):
+    """name -> (offset, count, shape) with every tensor starting on a 16-byte boundary, and the total float count."""
+    offsets, total = {}, 0
+    for name, shape in shapes.items():
+        n = 1
+        for d in shape:
+            n *= d
+        offsets[name] = (total, n, tuple(shape))
+        total += (n + 3) // 4 * 4
+    return offsets, total
+
+
+class _DeviceSpan:
+    """Lets torch view device memory that the library allocated (CUDA array interface, version 2)."""
+
+    def __init__(self, ptr, floats):
+        self.__cuda_array_interface__ = dict(shape=(floats,), typestr="<f4", data=(ptr, False), version=2)
+
+
+class PeerBuffer:
+    """A communicator of the library (b200_comm_*): device memory that every rank of the process group maps, so that the
+    library's exchange kernels can read and write the peers' arenas over NVLink.  The handles travel through
+    torch.distributed (all_gather of a byte tensor); torch does nothing else here."""
+
+    def __init__(self, floats):
+        lib = load()
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        self.floats = (floats + 63) // 64 * 64
+        self.comm = C.c_void_p()
+        from .ops import _check
+        _check(lib.b200_comm_create(C.byref(self.comm), self.rank, self.world, self.floats * 4))
+        handle = (C.c_ubyte * 128)()
+        _check(lib.b200_comm_handle(self.comm, handle))
+        mine = torch.tensor(list(handle), dtype=torch.uint8, device="cuda")
+        everyone = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(everyone, mine)
+        blob = bytes(torch.stack(everyone).cpu().numpy().tobytes())
+        _check(lib.b200_comm_connect(self.comm, blob))
+        self._span = _DeviceSpan(lib.b200_comm_buffer(self.comm), self.floats)
+        self.buffer = torch.as_tensor(self._span, device="cuda")
+        dist.barrier()
+
+    def close(self):
+        if self.comm:
+            torch.cuda.synchronize()
+            dist.barrier()
+            self.buffer = None
+            load().b200_comm_destroy(self.comm)
+            self.comm = C.c_void_p()
+
+
 class GradArena:
     """One contiguous fp32 buffer holding every layer's dW and dB; `views[name]` are the tensors the
-    weight-gradient kernels write into directly (no staging copy before the collective)."""
+    weight-gradient kernels write into directly (no staging copy before the collective).  `storage`: a float tensor of the
+    arena's size to build the views on (a span of a PeerBuffer) instead of a fresh allocation."""
 
-    def __init__(self, shapes, device):
-        self.offsets, total = {}, 0
-        for name, shape in shapes.items():
-            n = 1
-            for d in shape:
-                n *= d
-            self.offsets[name] = (total, n, tuple(shape))
-            total += (n + 3) // 4 * 4            # keep every view 16-byte aligned
-        self.buffer = torch.zeros(total, dtype=torch.float32, device=device)
+    def __init__(self, shapes, device, storage=None):
+        self.offsets, total = arena_layout(shapes)
+        if storage is None:
+            self.buffer = torch.zeros(total, dtype=torch.float32, device=device)
+        else:
+            assert storage.numel() == total and storage.dtype == torch.float32
+            self.buffer = storage
+            self.buffer.zero_()
         self.views = {k: self.buffer[o:o + n].view(shape) for k, (o, n, shape) in self.offsets.items()}
 
     def all_reduce(self):

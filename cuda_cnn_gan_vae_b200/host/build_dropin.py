@@ -16,7 +16,9 @@ import tempfile
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("B200CONV_REFERENCE", "/root/reference")
+# where the reference tree (da-nie/CUDA-CNN-GAN-VAE) is checked out: B200CONV_REFERENCE, else a "reference" directory beside this
+# repository; absent on machines that only run the prebuilt checker
+REF = os.environ.get("B200CONV_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference")
 OUT = os.path.join(ROOT, "oracle", "_ref", "dropin")
 OURS = ("ctensor.cu.h", "ctensormath.cu.h", "ctensorconv.cu.h", "ctensorapplyfunc.cu.h", "tensor.cu.h")
 # this package's own layer classes (host/netlayer/): in the second shadow tree they stand in for the reference's headers of the

@@ -16,7 +16,7 @@ import numpy as np
 import torch
 
 from . import ops
-from .dp import GradArena
+from .dp import GradArena, PeerBuffer, arena_layout
 from .lib import load
 from .ops import ACT, _check, _ptr, _stream
 
@@ -310,8 +310,10 @@ class Net:
     TrainingResetDeltaWeight, Forward of all layers, SetOutputError on the last, TrainingBackward in reverse order,
     TrainingUpdateWeight) on four arenas: weights, gradients, Adam m and v."""
 
-    def __init__(self, in_shape, batch, spec, seed=0):
-        """spec: list of (class, kwargs).  The input of layer i is the output of layer i-1."""
+    def __init__(self, in_shape, batch, spec, seed=0, peer=False, channel=0):
+        """spec: list of (class, kwargs).  The input of layer i is the output of layer i-1.
+        peer: with several ranks, the weight and gradient arenas are placed in a PeerBuffer (memory every rank maps), and
+        TrainingUpdateWeight(fused=True) runs the library's reduce-scatter + Adam + all-gather kernel on `channel`."""
         self.batch, self.in_shape = batch, tuple(in_shape)
         self.layers, shape = [], tuple(in_shape)
         for cls, kw in spec:
@@ -326,7 +328,17 @@ class Net:
         for i, layer in enumerate(self.layers):
             for name, s in layer.param_shapes().items():
                 shapes["%d.%s" % (i, name)] = s
-        self.weights, self.grads, self.m, self.v = (GradArena(shapes, "cuda") for _ in range(4))
+        self.peer, self.channel = None, channel
+        import torch.distributed as dist
+        if peer and dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            _, total = arena_layout(shapes)
+            self.peer = PeerBuffer(2 * total)
+            self.weight_offset, self.grad_offset = 0, total
+            self.weights = GradArena(shapes, "cuda", self.peer.buffer[:total])
+            self.grads = GradArena(shapes, "cuda", self.peer.buffer[total:2 * total])
+            self.m, self.v = (GradArena(shapes, "cuda") for _ in range(2))
+        else:
+            self.weights, self.grads, self.m, self.v = (GradArena(shapes, "cuda") for _ in range(4))
         rng = np.random.default_rng(seed)
         for i, layer in enumerate(self.layers):
             names = list(layer.param_shapes())
@@ -374,6 +386,27 @@ class Net:
             layer = self.layers[i]
             error = layer.TrainingBackward(error.view((self.batch,) + layer.out_shape), create_delta_weight, need_prev=(i > 0 or need_input_error))
         return error
+
+    def TrainingUpdateWeightFused(self, speed, iteration, batch_scale=1, beta1=0.9, beta2=0.999, epsilon=1e-8, corrections=None):
+        """The data-parallel update in one kernel (b200_allreduce_adam): every rank sums its slice of the gradient arenas of
+        all ranks over NVLink, applies Adam to that slice and writes the new weights to all ranks.  Replaces grads.all_reduce()
+        followed by TrainingUpdateWeight; the moving average of the weights is not kept on this path."""
+        if self.peer is None:
+            self.grads.all_reduce()
+            return self.TrainingUpdateWeight(speed, iteration, batch_scale, beta1, beta2, epsilon, corrections)
+        if self.ema is not None:
+            raise ops.B200Error(2, "the fused update does not keep the moving average of the weights")
+        n = self.weights.buffer.numel()
+        _check(load().b200_allreduce_adam(self.peer.comm, self.grad_offset, self.weight_offset, _ptr(self.m.buffer), _ptr(self.v.buffer), n,
+                                          int(self.batch * batch_scale), speed, beta1, beta2, epsilon, 0.0 if iteration is None else iteration,
+                                          _ptr(corrections), self.channel, _stream()))
+
+    def peer_all_reduce(self):
+        """Sum of the gradient arenas over the ranks by the library's own exchange kernel (b200_allreduce), in place."""
+        if self.peer is None:
+            return self.grads.all_reduce()
+        _check(load().b200_allreduce(self.peer.comm, self.grad_offset, self.grads.buffer.numel(), self.channel, _stream()))
+        return self.grads.buffer
 
     def TrainingUpdateWeight(self, speed, iteration, batch_scale=1, beta1=0.9, beta2=0.999, epsilon=1e-8, corrections=None):
         """CTensorMath::Adam over every parameter of the net in one launch; batch_size = batch*batch_scale divides the

@@ -24,6 +24,7 @@ SIGNATURES = {
     "b200_shutdown": (_i, []),
     "b200_scratch_bytes": (_sz, []),
     "b200_stream_status": (_i, [_vp]),
+    "b200_debug_set_status": (_i, [C.c_uint]),
     "b200_launch_count": (C.c_ulonglong, []),
     "b200_profile_tensor_core": (_i, [_i]),
     "b200_profile_read": (_i, [C.POINTER(C.c_double), C.POINTER(C.c_int)]),
@@ -70,6 +71,15 @@ SIGNATURES = {
     "b200_dropout_mask": (_i, [_fp, _sz, _f, C.c_ulonglong, _vp]),
     "b200_noisy_image": (_i, [_fp, _fp, _fp, _fp, _fp, _i, _sz, _i, C.c_ulonglong, _vp]),
     "b200_adam_ema": (_i, [_fp, _fp, _fp, _fp, _fp, _sz, C.c_uint32, _d, _d, _d, _d, _d, _vp, _d, _vp]),
+    "b200_comm_create": (_i, [C.POINTER(C.c_void_p), _i, _i, _sz]),
+    "b200_comm_handle": (_i, [_vp, _vp]),
+    "b200_comm_connect": (_i, [_vp, _vp]),
+    "b200_comm_buffer": (C.c_void_p, [_vp]),
+    "b200_comm_buffer_bytes": (_sz, [_vp]),
+    "b200_comm_destroy": (_i, [_vp]),
+    "b200_comm_slice": (_i, [_sz, _i, _i, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
+    "b200_allreduce": (_i, [_vp, _sz, _sz, _i, _vp]),
+    "b200_allreduce_adam": (_i, [_vp, _sz, _sz, _fp, _fp, _sz, C.c_uint32, _d, _d, _d, _d, _d, _vp, _i, _vp]),
 }
 
 _lib = None

@@ -22,7 +22,7 @@ def _bn_function(spec, fused, leaky_slope):
         spec.append((NetLayerFunction, dict(func="leaky_relu", leaky_slope=leaky_slope)))
 
 
-def dcgan_generator(batch, noise=100, base=512, widths=(256, 128, 64, 3), leaky_slope=0.2, seed=2, fused=False):
+def dcgan_generator(batch, noise=100, base=512, widths=(256, 128, 64, 3), leaky_slope=0.2, seed=2, fused=False, peer=False, channel=0):
     """z[noise] -> Linear to base x 4 x 4 -> 4x4 stride-2 transposed convolutions to widths[-1] x 64 x 64; batch
     normalisation and LeakyReLU after every stage but the last, tanh at the output."""
     spec = [(NetLayerLinear, dict(neurons=base * 16)), ("reshape", (base, 4, 4))]
@@ -31,10 +31,10 @@ def dcgan_generator(batch, noise=100, base=512, widths=(256, 128, 64, 3), leaky_
         if i + 1 < len(widths):
             _bn_function(spec, fused, leaky_slope)
     spec.append((NetLayerFunction, dict(func="tanh")))
-    return Net((1, noise, 1), batch, spec, seed=seed)
+    return Net((1, noise, 1), batch, spec, seed=seed, peer=peer, channel=channel)
 
 
-def dcgan_discriminator(batch, image=(3, 64, 64), widths=(64, 128, 256, 512), leaky_slope=0.2, seed=3, fused=False):
+def dcgan_discriminator(batch, image=(3, 64, 64), widths=(64, 128, 256, 512), leaky_slope=0.2, seed=3, fused=False, peer=False, channel=0):
     """image -> 4x4 stride-2 convolutions with batch normalisation and LeakyReLU -> Linear to one logit -> sigmoid."""
     spec = []
     for width in widths:
@@ -42,7 +42,7 @@ def dcgan_discriminator(batch, image=(3, 64, 64), widths=(64, 128, 256, 512), le
         _bn_function(spec, fused, leaky_slope)
     spec.append((NetLayerLinear, dict(neurons=1)))
     spec.append((NetLayerFunction, dict(func="sigmoid")))
-    return Net(image, batch, spec, seed=seed)
+    return Net(image, batch, spec, seed=seed, peer=peer, channel=channel)
 
 
 class DCGANStep:
@@ -53,10 +53,15 @@ class DCGANStep:
     respect to the logit, formed as in cuda/netmodel/cmodel_basicgan.cu.h:352-376 but on the device)."""
 
     def __init__(self, batch, world=1, widths_g=(256, 128, 64, 3), widths_d=(64, 128, 256, 512), base=512, noise=100, leaky_slope=0.2,
-                 use_graph=True, fused=False):
-        self.batch, self.world = batch, world
-        self.G = dcgan_generator(batch, noise, base, widths_g, leaky_slope, fused=fused)
-        self.D = dcgan_discriminator(batch, self.G.out_shape, widths_d, leaky_slope, fused=fused)
+                 use_graph=True, fused=False, update="fused", overlap=True):
+        """update (several ranks): "fused" -- the library's reduce-scatter + Adam + all-gather kernel over NVLink peer memory,
+        one launch per net on the main stream; "nccl" -- an NCCL all-reduce of each gradient arena on a side stream followed
+        by the Adam launch."""
+        self.batch, self.world, self.overlap = batch, world, overlap
+        self.update = update if world > 1 else "local"
+        peer = self.update == "fused"
+        self.G = dcgan_generator(batch, noise, base, widths_g, leaky_slope, fused=fused, peer=peer, channel=1)
+        self.D = dcgan_discriminator(batch, self.G.out_shape, widths_d, leaky_slope, fused=fused, peer=peer, channel=0)
         self.G.broadcast_weights()
         self.D.broadcast_weights()
         self.error = torch.empty((batch, 1, 1, 1), device="cuda")
@@ -65,8 +70,8 @@ class DCGANStep:
         self.iteration = 0
         self.use_graph, self.graph, self.eager_steps = use_graph, None, 0
         self.out = None
-        self.side_d = torch.cuda.Stream() if world > 1 else None
-        self.side_g = torch.cuda.Stream() if world > 1 else None
+        self.side_d = torch.cuda.Stream() if (self.update == "nccl" or (self.update == "fused" and overlap)) else None
+        self.side_g = torch.cuda.Stream() if self.update == "nccl" else None
         self.corr = AdamCorrections()
 
     def _step(self, speed):
@@ -80,6 +85,20 @@ class DCGANStep:
         out = self.D.Forward(fake)
         ops.CTensorMath.Sub(self.error, out, self.labels)
         d_image = self.D.TrainingBackward(self.error, True, need_input_error=True)
+        if self.update == "fused":
+            # the generator's backward pass reads the error at the discriminator's input, not the discriminator's weights
+            # and the two nets use different channels of their communicators, so the discriminator's exchange may run beside it
+            if self.overlap:
+                self.side_d.wait_stream(main)
+                with torch.cuda.stream(self.side_d):
+                    self.D.TrainingUpdateWeightFused(speed, None, batch_scale=self.world, corrections=self.corr.device)
+            else:
+                self.D.TrainingUpdateWeightFused(speed, None, batch_scale=self.world, corrections=self.corr.device)
+            self.G.TrainingBackward(d_image, True)
+            self.G.TrainingUpdateWeightFused(speed, None, batch_scale=self.world, corrections=self.corr.device)
+            if self.overlap:
+                main.wait_stream(self.side_d)
+            return out
         if self.world > 1:
             self.side_d.wait_stream(main)
             with torch.cuda.stream(self.side_d):
@@ -100,18 +119,22 @@ class DCGANStep:
         """The step is a chain of over a hundred launches of a few microseconds each, so after two eager steps (which size
         every scratch buffer of the library) it is captured once in a CUDA graph and replayed.  Adam's bias corrections for
         the step are refreshed in device memory before each replay (layers.AdamCorrections), so the two Adam launches are
-        part of the graph."""
+        part of the graph.  While a replay is in flight no other call into the library may run on the same device: the
+        Linear layers' products inside the graph use the device's shared scratch arena."""
         self.iteration += 1
         if z.data_ptr() != self.z.data_ptr():
             self.z.copy_(z, non_blocking=True)
         if labels.data_ptr() != self.labels.data_ptr():
             self.labels.copy_(labels, non_blocking=True)
         self.corr.set(self.iteration)
-        if self.graph is not None and (load().b200_scratch_bytes() != self.scratch_bytes or speed != self.graph_speed):
-            self.graph, self.eager_steps = None, 0      # stale addresses (the library's scratch arena moved) or another learning rate
+        if self.graph is not None and (load().b200_scratch_bytes() != self.scratch_bytes or speed != self.graph_speed or
+                                       load().b200_get_precision() != self.graph_precision):
+            # stale addresses (the library's scratch arena moved), another learning rate, or another precision mode than the
+            # one the captured launches were chosen in
+            self.graph, self.eager_steps = None, 0
         if self.use_graph and self.graph is None and self.eager_steps >= 2:
             ops.stream_status()
-            self.scratch_bytes, self.graph_speed = load().b200_scratch_bytes(), speed
+            self.scratch_bytes, self.graph_speed, self.graph_precision = load().b200_scratch_bytes(), speed, load().b200_get_precision()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, capture_error_mode="thread_local"):
                 self.out = self._step(speed)

@@ -20,6 +20,12 @@
  *    b200_last_error() gives the text of the last failure on the calling thread.
  *  - Scratch memory (packed operands, split-K partial sums) comes from a per-device arena that the
  *    library grows with cudaMalloc on demand and releases in b200_shutdown().
+ *  - Threads: the reference is a single-threaded program and so is this library's state.  Use ONE host thread per device,
+ *    and one stream at a time per device for the stateless entry points (they share the device's scratch arena; a layer
+ *    context owns its buffers and serves one stream at a time).  The precision mode and the profiling switch are
+ *    process-wide.  Calls from several threads on the same device must be serialised by the caller.
+ *  - Alignment: tensors may start at any 4-byte boundary (the vector code paths are taken only when the pointers allow);
+ *    the position tensor of max-pooling must be 8-byte aligned.
  */
 #ifndef B200CONV_H
 #define B200CONV_H
@@ -38,7 +44,7 @@ enum {
     B200_E_CUDA = 3,       /* a CUDA runtime or driver call failed                                  */
     B200_E_TIMEOUT = 4,    /* a bounded device-side wait gave up; the context stays usable          */
     B200_E_NOMEM = 5,      /* a fixed-size scratch area is too small for this call                  */
-    B200_E_NCCL = 6
+    B200_E_NCCL = 6        /* reserved (the library's own exchange reports B200_E_CUDA / B200_E_TIMEOUT)          */
 };
 
 /* Arithmetic of the tensor-core contractions.  B200_TF32X3 (default) splits every operand into a
@@ -83,6 +89,10 @@ size_t b200_scratch_bytes(void);
  * counterpart is the cudaDeviceSynchronize + HANDLE_ERROR pair after every launch
  * (cuda/ctensormath.cu.h:1980-1981, cuda/handle_error.cu.h:7-18), minus the exit(). */
 int b200_stream_status(void *stream);
+/* Test aid with no reference counterpart: writes `code` into the current device's status word FROM THE HOST, exactly where a
+ * device-side wait that gave up would have recorded it, so that a caller's handling of B200_E_TIMEOUT can be exercised
+ * without making any kernel wait.  The next b200_stream_status() on the device reports and clears it. */
+int b200_debug_set_status(unsigned code);
 
 /* Number of kernels this library has launched in this process (all devices, all threads). */
 unsigned long long b200_launch_count(void);
@@ -305,6 +315,45 @@ int b200_noisy_image(float *noisy, float *noise, const float *image, const float
  * non-NULL, replaces `iteration` as in b200_adam_prepared. */
 int b200_adam_ema(float *weight, const float *dweight, float *m, float *v, float *ema, size_t n, uint32_t batch_size, double speed,
                   double beta1, double beta2, double epsilon, double iteration, const double *corrections, double ema_k, void *stream);
+
+/* ---- data-parallel exchange over NVLink peer memory -------------------------------------------- */
+
+/* The reference is a single-GPU program; what it has is the reduction of per-sample gradients over W (AddSumW,
+ * netlayer/cnetlayerconvolution.cu.h:507-508) and the batch_scale argument of TrainingUpdateWeight (netlayer/inetlayer.cu.h:87).
+ * Here each rank (one process, or one host thread, per GPU) reduces its shard inside the weight-gradient kernel and the
+ * shards are summed across GPUs by the calls below, which read and write the peers' memory directly over NVLink.
+ *
+ * A communicator owns one device allocation: a signal pad and a data region of `bytes` bytes (b200_comm_buffer) in which the
+ * caller places the arenas to be exchanged (gradients, weights), at the same offsets on every rank.  Set-up: every rank calls
+ * b200_comm_create, then b200_comm_handle, carries the B200_COMM_HANDLE_BYTES-byte handles of all ranks to all ranks by any
+ * means, and calls b200_comm_connect with them in rank order.  Ranks in different processes are mapped with CUDA IPC, ranks
+ * that share a process by enabling peer access.  Destroy only after every rank has finished its last exchange.
+ * Exchanges on one channel (0..3) of a communicator must be issued in the same order by every rank and are serialised by
+ * the stream order of each rank; exchanges that may overlap on a GPU (different streams) need different channels.
+ * Every device-side wait is bounded (about a second); a rank whose peers do not arrive reports B200_E_TIMEOUT through
+ * b200_stream_status and its results are invalid. */
+#define B200_COMM_HANDLE_BYTES 128
+typedef struct b200_comm b200_comm;
+int b200_comm_create(b200_comm **comm, int rank, int world, size_t bytes);
+int b200_comm_handle(b200_comm *comm, void *handle);
+int b200_comm_connect(b200_comm *comm, const void *handles);
+void *b200_comm_buffer(b200_comm *comm);
+size_t b200_comm_buffer_bytes(b200_comm *comm);
+int b200_comm_destroy(b200_comm *comm);
+/* The slice [begin, end) (in floats) of an arena of n floats that rank `rank` of `world` reduces and updates.  Host
+ * arithmetic only. */
+int b200_comm_slice(size_t n, int rank, int world, size_t *begin, size_t *end);
+/* In-place sum over the ranks of the n floats at float offset `offset` of the data region (n and offset multiples of 4):
+ * each rank adds its slice from all ranks in rank order and writes the sum to all ranks. */
+int b200_allreduce(b200_comm *comm, size_t offset, size_t n, int channel, void *stream);
+/* Reduce-scatter + Adam + all-gather in one kernel: rank r sums slice r of the gradient arenas (at grad_offset) of all ranks,
+ * applies CTensorMath::Adam (as b200_adam; batch_size is the global batch) to slice r of its weights (at weight_offset) and of
+ * its local moment arrays m, v (n floats each, only slice r is touched), and writes the new weights of slice r into the
+ * weight arenas of all ranks.  On return of the kernel every rank holds the same, fully updated weights; the gradient arenas
+ * keep their per-rank contents.  corrections: as in b200_adam_prepared (may be NULL). */
+int b200_allreduce_adam(b200_comm *comm, size_t grad_offset, size_t weight_offset, float *m, float *v, size_t n, uint32_t batch_size,
+                        double speed, double beta1, double beta2, double epsilon, double iteration, const double *corrections, int channel,
+                        void *stream);
 
 #ifdef __cplusplus
 }

@@ -13,7 +13,9 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("B200CONV_REFERENCE", "/root/reference")
+# where the reference tree (da-nie/CUDA-CNN-GAN-VAE) is checked out: B200CONV_REFERENCE, else a "reference" directory beside this
+# repository; absent on machines that only run the prebuilt checker
+REF = os.environ.get("B200CONV_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 REF_DIR = os.path.join(HERE, "_ref")
 
 

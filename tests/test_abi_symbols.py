@@ -55,3 +55,11 @@ def test_python_mirror_raises_reference_style_errors():
     from cuda_cnn_gan_vae_b200 import ops
     with pytest.raises(ops.B200Error):
         ops.CTensorMath.Mul(torch.zeros(1, 1, 2, 2), torch.zeros(1, 1, 2, 2), torch.zeros(1, 1, 2, 2))  # CPU tensors
+
+
+def test_wgrad_batch_rejects_an_inconsistent_output_size(lib):
+    from cuda_cnn_gan_vae_b200.lib import ConvGeom
+    wrong = ConvGeom(3, 8, 8, 4, 3, 3, 1, 1, 1, 1, 9, 8)
+    assert lib.b200_conv_wgrad_batch(C.byref(wrong), None, None, 0, None, None, 2, None) == 1          # B200_E_SHAPE before anything else
+    assert lib.b200_conv_wgrad_batch_static(C.byref(wrong), C.c_void_p(8), None, 0, C.c_void_p(8), C.c_void_p(8), 2, None) == 1
+    assert b"output size" in lib.b200_last_error()

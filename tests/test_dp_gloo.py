@@ -66,3 +66,22 @@ def test_two_rank_gradient_arena_matches_full_batch(tmp_path, port):
     got_b = np.load(tmp_path / "dB.npy").reshape(K)
     assert np.allclose(got_w, dk.astype(np.float64).sum(0), rtol=1e-5, atol=1e-5)
     assert np.allclose(got_b, db.astype(np.float64).sum(0), rtol=1e-5, atol=1e-5)
+
+
+def test_slice_arithmetic_of_the_fused_exchange():
+    """b200_comm_slice (host arithmetic of the library): the slices of all ranks tile the arena in 16-byte groups, in rank
+    order, for every world size; misuse is rejected."""
+    from cuda_cnn_gan_vae_b200.dp import slice_bounds
+    for n in (0, 4, 8, 1000, 4096 * 3 + 8, 3_600_000):
+        for world in (1, 2, 3, 4, 8, 16):
+            cursor = 0
+            for rank in range(world):
+                b, e = slice_bounds(n, rank, world)
+                assert b == cursor and e >= b and b % 4 == 0 and e % 4 == 0
+                cursor = e
+            assert cursor == n
+    import pytest
+    with pytest.raises(ValueError):
+        slice_bounds(10, 0, 2)          # not a multiple of 4 floats
+    with pytest.raises(ValueError):
+        slice_bounds(8, 2, 2)

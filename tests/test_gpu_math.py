@@ -361,3 +361,24 @@ def test_adam_with_device_resident_corrections(ops):
     ops._check(load().b200_adam_prepared(ops._ptr(W2), ops._ptr(DW), ops._ptr(M2), ops._ptr(V2), n, 16, 2e-4, 0.9, 0.999, 1e-8, ops._ptr(c), ops._stream()))
     ops.stream_status()
     assert torch.equal(W1.view(-1), W2) and torch.equal(M1.view(-1), M2) and torch.equal(V1.view(-1), V2)
+
+
+def test_timeout_status_is_reported_and_cleared(ops):
+    """The status word a device-side wait that gave up would write is set from the host (no kernel is made to wait):
+    b200_stream_status reports B200_E_TIMEOUT once, with the recorded code in the error text, and is clean again afterwards."""
+    from cuda_cnn_gan_vae_b200.lib import load
+    lib = load()
+    ops.stream_status()
+    x = torch.zeros(4, device="cuda")
+    ops.CTensorMath.Fill(x.view(1, 1, 1, 4), 1.0)               # any call: the status word exists once the library ran on the device
+    ops.set_precision(ops.TF32X3)
+    a = torch.randn(1, 1, 64, 64, device="cuda")
+    out = torch.empty(1, 1, 64, 64, device="cuda")
+    ops.CTensorMath.Mul(out, a, a)                              # a tensor-core launch creates the word
+    ops.stream_status()
+    assert lib.b200_debug_set_status(0x304) == 0                # issuer wait, B200_E_TIMEOUT
+    assert lib.b200_stream_status(None) == 4
+    assert b"0x304" in lib.b200_last_error()
+    assert lib.b200_stream_status(None) == 0
+    ops.CTensorMath.Mul(out, a, a)                              # the context is still usable
+    ops.stream_status()

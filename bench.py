@@ -57,6 +57,20 @@ def flops_per_sample(c):
     return 3 * 2.0 * c["K"] * c["C"] * c["k"] * c["k"] * oh * ow
 
 
+def profiled_traffic():
+    """dram bytes (read + written) per image and tensor-core launch, from the committed ncu summary of the kernel
+    (profiles/tc_kernel_dp_conv_sweep_batch128.md carries one machine-readable line for it); (bytes, source) or (None, why)."""
+    path = os.path.join(ROOT, "profiles", "tc_kernel_dp_conv_sweep_batch128.md")
+    try:
+        for line in open(path):
+            if line.startswith("traffic_bytes_per_image_and_launch:"):
+                fields = line.split()
+                return float(fields[1]), "profiles/tc_kernel_dp_conv_sweep_batch128.md (%s), scaled by the images of a launch" % " ".join(fields[2:])
+    except OSError:
+        pass
+    return None, "no ncu summary with a traffic line under profiles/"
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -166,7 +180,48 @@ def reference_arm(args, rank, world):
                 data="synthetic", config=dict(workload="dp_conv_sweep_256x32x32_k256_3x3 (CPU sample)", sample=sample),
                 cpu_baseline=dict(value=val, unit="TFLOP/s", cores=T, kind=kind, sample=sample, host_cores=os.cpu_count()),
                 e2e=dict(value=val, unit="TFLOP/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
+    # the one configuration the CPU backend runs WHOLE (BASELINE configs[0]): same step as the `cfg1` object of the GPU arm
+    line["cfg1"] = dict(single_thread=cfg1_cpu(steps=max(2, min(args.steps, 5)), threads=1),
+                        all_threads=cfg1_cpu(steps=max(2, min(args.steps, 5)), threads=T))
     emit(json.dumps(line))
+
+
+def _dot_rel_err(got, want, absdot):
+    """max |got - want| / sum |a||b| (the forward-error-bound form of relative error; tests/util.py)."""
+    import numpy as np
+    return float(np.max(np.abs(got.astype(np.float64) - want) / np.maximum(absdot.astype(np.float64), 1e-30)))
+
+
+def _survey_rel_err(got, want):
+    """max |got - want| / max(|want|, 1e-3 max |want|) (tests/util.py)."""
+    import numpy as np
+    want = want.astype(np.float64)
+    return float(np.max(np.abs(got.astype(np.float64) - want) / np.maximum(np.abs(want), 1e-3 * np.max(np.abs(want)))))
+
+
+def parity_leg(samples):
+    """The benchmark's own results on sampled images of the timed batch against the reference CPU backend (checker, all host
+    threads): both error figures per mode, for the bench line's config.parity.
+    samples: dict(x, d, w, idx, modes={mode: (y[idx], dx[idx])}) as numpy arrays."""
+    import numpy as np
+    from oracle import Oracle
+    try:
+        ref = Oracle("reference", threads=os.cpu_count() or 1)
+    except FileNotFoundError:
+        ref = Oracle("port", threads=os.cpu_count() or 1)
+    c = CFG
+    x, d, w = samples["x"], samples["d"], samples["w"]
+    zb = np.zeros((1, c["K"]), np.float32)
+    want_y, mag_y = ref.conv_forward(x, w, zb, 3, 3, 1, 1, 1, 1), ref.conv_forward(np.abs(x), np.abs(w), zb, 3, 3, 1, 1, 1, 1)
+    shape = (c["C"], c["H"], c["W"])
+    want_dx, mag_dx = ref.conv_backward(d, w, zb, shape, 3, 3, 1, 1, 1, 1), ref.conv_backward(np.abs(d), np.abs(w), zb, shape, 3, 3, 1, 1, 1, 1)
+    out = dict(checker="reference CPU backend (oracle/_ref)" if ref.kind == "reference" else "CPU restatement (oracle/)",
+               sample="forward and backward-data of images %s of the timed batch" % list(samples["idx"]),
+               tolerance="2e-3 (tf32) / 1e-4 (tf32x3) on dot_rel_err = |err| / sum|a||b|; survey_rel_err = |err| / max(|want|, 1e-3 max|want|) is reported beside it")
+    for mode, (y, dx) in samples["modes"].items():
+        out[mode] = dict(forward=dict(dot_rel_err=_dot_rel_err(y, want_y, mag_y), survey_rel_err=_survey_rel_err(y, want_y)),
+                         backward_data=dict(dot_rel_err=_dot_rel_err(dx, want_dx, mag_dx), survey_rel_err=_survey_rel_err(dx, want_dx)))
+    return out
 
 
 def cpu_baseline(seconds_budget=25.0):
@@ -207,7 +262,10 @@ def dcgan_cpu_baseline(images=2):
     from cuda_cnn_gan_vae_b200.nets import dcgan_discriminator, dcgan_generator
     from oracle import Oracle
     from oracle.net_twin import OracleNet
-    port = Oracle("port")
+    try:
+        port, kind = Oracle("reference"), "reference"
+    except FileNotFoundError:
+        port, kind = Oracle("port"), "port"
     G, D = dcgan_generator(images), dcgan_discriminator(images)
     tg, td = OracleNet(port, G), OracleNet(port, D)
     r = np.random.default_rng(7)
@@ -220,8 +278,225 @@ def dcgan_cpu_baseline(images=2):
     tg.backward(d_image)
     dt = time.perf_counter() - t0
     del torch
-    return dict(value=images / dt, unit="img/s", cores=1, kind="port", host_cores=os.cpu_count(),
+    return dict(value=images / dt, unit="img/s", cores=1, kind=kind, host_cores=os.cpu_count(),
                 sample=f"{images} images through generator + discriminator fwd+bwd+dW (no optimiser), single thread, {dt:.1f} s")
+
+
+class _L2Flush:
+    """Writes a buffer larger than L2 (126 MB) so that the next timed launch finds none of its operands cached."""
+
+    def __init__(self, torch):
+        self.buf = torch.empty(192 << 20, dtype=torch.uint8, device="cuda")
+
+    def __call__(self):
+        self.buf.zero_()
+
+
+def _timed_with_flush(torch, fn, flush, iters, warmup=3):
+    """Mean device time of fn in ms: one CUDA-event pair per call, an L2 flush before every call (outside the pair)."""
+    for _ in range(warmup):
+        fn()
+    total = 0.0
+    for _ in range(iters):
+        flush()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / iters
+
+
+CFG1 = dict(B=16, C=3, H=64, W=64, K=32, k=3)
+
+
+def cfg1_flops():
+    c = CFG1
+    return 3 * 2.0 * c["B"] * c["K"] * c["C"] * c["k"] * c["k"] * c["H"] * c["W"]
+
+
+def cfg1_inputs():
+    import numpy as np
+    c = CFG1
+    r = np.random.default_rng(1)
+    x = r.uniform(-1, 1, (c["B"], c["C"], c["H"], c["W"])).astype(np.float32)
+    wt = r.normal(0, (2.0 / (c["C"] * 9)) ** 0.5, (1, 1, c["K"], c["C"] * 9)).astype(np.float32)
+    d = r.normal(0, 1, (c["B"], c["K"], c["H"], c["W"])).astype(np.float32)
+    return x, wt, d
+
+
+def cfg1_gpu(torch, ops, iters=30):
+    """The CPU-runnable configuration (batch 16 of 3x64x64 U[-1,1], 32 filters 3x3 s1 p1, He-normal weights, zero bias,
+    N(0,1) error; seed 1): one step = the convolution layer's Forward and TrainingBackward.  Device-resident and through
+    host buffers, L2 flushed before every step (the operands are far smaller than L2)."""
+    c = CFG1
+    x, wt, d = cfg1_inputs()
+    hx, hd = torch.from_numpy(x).pin_memory(), torch.from_numpy(d).pin_memory()
+    X, D, WT = hx.cuda(), hd.cuda(), torch.from_numpy(wt).cuda()
+    bias = torch.zeros(1, c["K"], 1, 1, device="cuda")
+    y, dx = torch.empty_like(D), torch.empty_like(X)
+    dk, db = torch.empty_like(WT), torch.empty_like(bias)
+    hres = torch.empty(dk.numel() + db.numel()).pin_memory()
+    layer = ops.ConvLayer(c["C"], c["H"], c["W"], c["K"], 3, 3, 1, 1, 1, 1, c["B"])
+    flush = _L2Flush(torch)
+
+    def step():
+        layer.forward(y, X, WT, bias)
+        layer.backward(dx, dk, db, D, X, WT, accumulate=False)
+
+    def e2e_step():
+        X.copy_(hx, non_blocking=True)
+        D.copy_(hd, non_blocking=True)
+        step()
+        hres[:dk.numel()].copy_(dk.view(-1), non_blocking=True)
+        hres[dk.numel():].copy_(db.view(-1), non_blocking=True)
+
+    out = dict(workload="single convolution layer: batch 16 of 3x64x64 U[-1,1], 32 filters 3x3 s1 p1, fwd+bwd-data+wgrad (BASELINE configs[0])",
+               flops_per_step=cfg1_flops(), unit="TFLOP/s", l2="flushed before every step")
+    for name, mode in (("tf32x3", ops.TF32X3), ("tf32", ops.TF32), ("fp32", ops.FP32)):
+        ops.set_precision(mode)
+        ms = _timed_with_flush(torch, step, flush, iters)
+        out[name] = dict(value=cfg1_flops() / (ms * 1e-3) / 1e12, ms_per_step=ms, path="tcgen05" if ops.last_path() == ops.PATH_TCGEN05 else "cuda cores")
+    ops.set_precision(ops.TF32)
+    ms = _timed_with_flush(torch, e2e_step, flush, iters)
+    out["e2e"] = dict(value=cfg1_flops() / (ms * 1e-3) / 1e12, unit="TFLOP/s", ms_per_step=ms, h2d_bytes_per_step=int((hx.numel() + hd.numel()) * 4),
+                      d2h_bytes_per_step=int(hres.numel() * 4), note="image and error from pinned host memory, dW|dB read back; plain-TF32 mode")
+    ops.stream_status()
+    layer.close()
+    return out
+
+
+def cfg1_cpu(steps=3, threads=1):
+    """The same configuration, WHOLE, on the reference CPU backend: forward, backward-data with a zero bias, per-sample
+    weight gradients reduced over the batch (the layer's sequence, netlayer/cnetlayerconvolution.cu.h:310,484-508)."""
+    import numpy as np
+    from oracle import Oracle
+    try:
+        ref, kind = Oracle("reference", threads=threads), "reference"
+    except FileNotFoundError:
+        ref, kind = Oracle("port", threads=threads), "port"
+    c = CFG1
+    x, wt, d = cfg1_inputs()
+    zb = np.zeros((1, c["K"]), np.float32)
+
+    def step():
+        ref.conv_forward(x, wt[0], zb, 3, 3, 1, 1, 1, 1)
+        ref.conv_backward(d, wt[0], zb, (c["C"], c["H"], c["W"]), 3, 3, 1, 1, 1, 1)
+        dk, db = ref.conv_wgrad(np.zeros((c["B"], c["K"], c["C"] * 9), np.float32), np.zeros((c["B"], c["K"]), np.float32), x, d, 3, 3, 1, 1, 1, 1)
+        return dk.sum(0), db.sum(0)
+
+    step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    return dict(value=cfg1_flops() / dt / 1e12, unit="TFLOP/s", ms_per_step=dt * 1e3, cores=threads, kind=kind, host_cores=os.cpu_count(),
+                same_config=True, sample="the whole configuration (batch 16), %d steps" % steps)
+
+
+def vae_bench(torch, ops, lib, timed, steps, world=1):
+    """BASELINE configs[3]: the convolutional VAE training step at batch 128 of 3x128x128 per GPU (encoder 32-64-128-256 with
+    max-pooling, two Linear heads to 256, reparameterisation with supplied noise, mirror decoder, MSE + KL errors, Adam)."""
+    from cuda_cnn_gan_vae_b200.nets import VAEStep
+    B = 128
+    gen = torch.Generator(device="cuda").manual_seed(41)
+    hx = torch.rand(B, 3, 128, 128).pin_memory()
+    heps = torch.randn(B, 1, 256, 1).pin_memory()
+    x, eps = hx.cuda(), heps.cuda()
+    hres = torch.empty(1).pin_memory()
+    out = dict(unit="img/s", per_gpu_batch=B, workload="conv VAE train step: batch 128 of 3x128x128 U[0,1], encoder 3x3 convs 32-64-128-256 + 2x2 max-pool, "
+               "Linear heads to 256-d mean / log-variance, reparameterisation with N(0,1) noise, mirror decoder with upsampling, MSE + KL, Adam (BASELINE configs[3])")
+    del gen
+    for name, mode in (("tf32x3", ops.TF32X3), ("tf32", ops.TF32)):
+        ops.set_precision(mode)
+        step = VAEStep(B, world=world)
+        n0 = lib.b200_launch_count()
+        step(x, eps)
+        launches = lib.b200_launch_count() - n0
+        ms, clocks, _, _ = timed(lambda: step(x, eps), max(3, steps // 2), 3)
+        ops.stream_status()
+        out[name] = dict(value=B * world / (ms * 1e-3), ms_per_step=ms, gpu_launches=int(launches))
+        out["parameters"] = int(sum(net.parameter_count for net in step.nets))
+
+        if mode == ops.TF32:
+            def e2e_step():
+                x.copy_(hx, non_blocking=True)
+                eps.copy_(heps, non_blocking=True)
+                x_hat = step(x, eps)
+                hres.copy_(x_hat.view(-1)[:1], non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+            ms, _, _, _ = timed(e2e_step, max(3, steps // 2), 2)
+            out["e2e"] = dict(value=B * world / (ms * 1e-3), unit="img/s", ms_per_step=ms, h2d_bytes_per_step=int((hx.numel() + heps.numel()) * 4 * world),
+                              d2h_bytes_per_step=4 * world, note="images and noise from pinned host memory every step; plain-TF32 mode")
+        del step
+        torch.cuda.empty_cache()
+    out["value"] = out["tf32"]["value"]
+    return out
+
+
+def vae_cpu_baseline(images=1):
+    """The same step (no optimiser) on the CPU twin built from the reference CPU backend's routines, single thread."""
+    import numpy as np
+    from cuda_cnn_gan_vae_b200.nets import VAEStep
+    from oracle import Oracle
+    from oracle.net_twin import OracleNet
+    try:
+        ref, kind = Oracle("reference"), "reference"
+    except FileNotFoundError:
+        ref, kind = Oracle("port"), "port"
+    port = Oracle("port")
+    step = VAEStep(images)
+    enc, mu_t, lv_t, dec = (OracleNet(ref, net) for net in step.nets)
+    r = np.random.default_rng(9)
+    x = r.uniform(0, 1, (images, 3, 128, 128)).astype(np.float32)
+    eps = r.standard_normal((images, 256)).astype(np.float32)
+    t0 = time.perf_counter()
+    feat = enc.forward(x)
+    mu, lv = mu_t.forward(feat), lv_t.forward(feat)
+    z, _ = port.vae_forward(mu.reshape(images, -1), lv.reshape(images, -1), eps)
+    x_hat = dec.forward(z.reshape(images, 1, 256, 1))
+    n = float(x[0].size)
+    d_z = dec.backward(ref.binary("sub", x_hat, x, 2.0 / n, 2.0 / n), need_input_error=True)
+    d_mu, d_lv = port.vae_backward(d_z.reshape(images, -1), mu.reshape(images, -1), lv.reshape(images, -1), eps, 1.0)
+    e = ref.binary("add", mu_t.backward(d_mu.reshape(images, 1, 256, 1), need_input_error=True),
+                   lv_t.backward(d_lv.reshape(images, 1, 256, 1), need_input_error=True))
+    enc.backward(e)
+    dt = time.perf_counter() - t0
+    return dict(value=images / dt, unit="img/s", cores=1, kind=kind, host_cores=os.cpu_count(),
+                sample=f"{images} image(s) through encoder, heads, decoder fwd+bwd+dW (no optimiser), single thread, {dt:.1f} s")
+
+
+def gemm_bench(torch, ops, peak_gbs, iters=10):
+    """The Linear layers' three products (netlayer/cnetlayerlinear.cu.h:262-278, 415-445) at the shapes of the configurations:
+    out = W x (Mul), prev = W^T d (TransponseMul), dW = D^T X (TransponseMul over the batch).  These products are bound by the
+    bytes of their largest operand (a few FLOP per byte): algorithmic bytes = every operand and the result once / device
+    time with L2 flushed, against the measured HBM copy bandwidth."""
+    shapes = [("dcgan generator: 100 -> 8192, batch 64", 64, 8192, 100), ("dcgan discriminator: 8192 -> 1, batch 64", 64, 1, 8192),
+              ("vae heads: 16384 -> 256, batch 128", 128, 256, 16384), ("vae decoder input: 256 -> 16384, batch 128", 128, 16384, 256)]
+    flush = _L2Flush(torch)
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    out = dict(unit="GB/s", peak=peak_gbs, peak_source="hbm_gbs (copy bandwidth), of measured", l2="flushed before every call", shapes=[])
+    for mode_name, mode in (("tf32", ops.TF32), ("tf32x3", ops.TF32X3)):
+        ops.set_precision(mode)
+        for name, B, n_out, n_in in shapes:
+            Wm = torch.randn(1, 1, n_out, n_in, device="cuda", generator=gen) * (2.0 / n_in) ** 0.5
+            x = torch.randn(B, 1, n_in, 1, device="cuda", generator=gen)
+            d = torch.randn(B, 1, n_out, 1, device="cuda", generator=gen)
+            h, prev, dw = torch.empty(B, 1, n_out, 1, device="cuda"), torch.empty(B, 1, n_in, 1, device="cuda"), torch.empty(1, 1, n_out, n_in, device="cuda")
+            cases = (("forward", lambda: ops.CTensorMath.Mul(h, Wm, x)),
+                     ("backward", lambda: ops.CTensorMath.TransponseMul(prev, Wm, d)),
+                     ("weight_gradient", lambda: ops.CTensorMath.TransponseMul(dw, d.view(1, 1, B, n_out), x.view(1, 1, B, n_in))))
+            entry = dict(layer=name, mode=mode_name)
+            for cname, fn in cases:
+                ms = _timed_with_flush(torch, fn, flush, iters)
+                nbytes = 4.0 * (n_out * n_in + B * n_in + B * n_out)
+                gbs = nbytes / (ms * 1e-3) / 1e9
+                entry[cname] = dict(ms=ms, tflops=2.0 * B * n_out * n_in / (ms * 1e-3) / 1e12, algorithmic_mb=nbytes / 1e6, achieved_gbs=gbs,
+                                    frac=gbs / peak_gbs, path="tcgen05" if ops.last_path() == ops.PATH_TCGEN05 else "cuda cores")
+            out["shapes"].append(entry)
+    ops.stream_status()
+    return out
 
 
 def hbm_kernels(torch, ops, peak_gbs, iters=5):
@@ -295,12 +570,13 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-dcgan", action="store_true", help="leave out the DCGAN training-step measurement")
     ap.add_argument("--skip-hbm", action="store_true", help="leave out the memory-bound kernel measurements")
+    ap.add_argument("--skip-extra", action="store_true", help="leave out the cfg1, VAE and Linear-product measurements (single GPU only)")
     ap.add_argument("--hbm-only", action="store_true", help="run only the memory-bound kernel measurements (profiling aid)")
     ap.add_argument("--dcgan-batch", type=int, default=64, help="images per GPU in the DCGAN step")
     ap.add_argument("--dcgan-fused", action="store_true", help="batch normalisation and the function layer after it as one fused layer (comparison aid)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="several ranks: sum the gradients with the library's own NVLink peer-memory kernels (default) or with NCCL")
-    ap.add_argument("--dcgan-no-overlap", action="store_true", help="run the discriminator's exchange on the main stream instead of beside the generator's backward pass")
+    ap.add_argument("--dcgan-overlap", action="store_true", help="run the discriminator's exchange on a side stream beside the generator's backward pass (comparison aid)")
     ap.add_argument("--dcgan-eager", action="store_true", help="launch the DCGAN step eagerly instead of replaying its CUDA graph (profiling aid)")
     args = ap.parse_args()
     keep_stdout_clean()
@@ -409,15 +685,20 @@ def main():
     peaks = measured_peaks()
     tf32_peak = peaks["bf16_sustained"] / 2.0
     results = {}
+    sample_idx = [0, B // 3, B // 2, B - 1]
+    samples = dict(idx=sample_idx, modes={})
     for mode_name, mode in (("tf32x3", ops.TF32X3), ("tf32", ops.TF32)):
         ops.set_precision(mode)
         lib.b200_profile_tensor_core(1)
         ms, clocks, launches, kernel_ms = timed(step, args.steps, args.warmup, sample_clocks=True)
         lib.b200_profile_tensor_core(0)
         ops.stream_status()
+        if rank == 0 and world == 1 and not args.skip_cpu:
+            samples["modes"][mode_name] = (y[sample_idx].cpu().numpy(), dx[sample_idx].cpu().numpy())
         per_launch_flops = step_flops / world / 3.0
-        # dram__bytes_read+write per tc_kernel launch from the ncu capture at batch 128 (profiles/), scaled by units
-        traffic = 1.886e6 * B
+        # dram__bytes_read+write per tc_kernel launch from the committed ncu capture at batch 128, scaled by the units of a launch
+        per_image, traffic_source = profiled_traffic()
+        traffic = per_image * B if per_image else None
         achieved = per_launch_flops / (kernel_ms * 1e-3) / 1e12 if kernel_ms else None
         # the sustained peak was taken at a lower SM clock than this run holds under the same power cap: the fraction at
         # equal clock says how much of the tensor pipe the kernel uses, the plain fraction how fast it is
@@ -427,6 +708,8 @@ def main():
             value=step_flops / (ms * 1e-3) / 1e12, ms_per_step=ms, clocks=clocks, gpu_launches=int(launches),
             roofline=dict(bound="tensor", achieved=achieved, peak=tf32_peak, unit="TFLOP/s",
                           frac=(achieved / tf32_peak) if achieved else None, traffic=traffic if mode == ops.TF32 else None,
+                          traffic_source=traffic_source if mode == ops.TF32 else None,
+                          frac_of_burst=(achieved / (peaks["bf16_burst"] / 2.0)) if (achieved and peaks.get("bf16_burst")) else None,
                           kernel="tc_kernel (tcgen05 implicit GEMM), mean of the forward, backward-data and weight-gradient launches",
                           kernel_ms=kernel_ms, mma_per_product=3 if mode == ops.TF32X3 else 1,
                           peak_sm_mhz=peaks.get("sm_mhz"), frac_at_equal_clock=equal_clock,
@@ -491,7 +774,7 @@ def main():
         for mode_name, mode in (("tf32x3", ops.TF32X3), ("tf32", ops.TF32)):
             ops.set_precision(mode)
             trainer = DCGANStep(gb, world=world, use_graph=not args.dcgan_eager, fused=args.dcgan_fused,
-                                update="fused" if args.exchange == "peer" else "nccl", overlap=not args.dcgan_no_overlap)   # a graph is captured in the precision mode of its first steps
+                                update="fused" if args.exchange == "peer" else "nccl", overlap=args.dcgan_overlap)   # a graph is captured in the precision mode of its first steps
             dcgan["parameters"] = dict(generator=trainer.G.parameter_count, discriminator=trainer.D.parameter_count)
             n0 = lib.b200_launch_count()
             trainer(z, labels)                            # eager: every launch of the step is counted once
@@ -516,10 +799,31 @@ def main():
         dcgan["e2e"] = dict(value=gb * world / (ms * 1e-3), unit="img/s", ms_per_step=ms, h2d_bytes_per_step=int((hz.numel() + hl.numel()) * 4 * world),
                             d2h_bytes_per_step=int(hout.numel() * 4 * world), note="noise and labels from pinned host memory, discriminator outputs read back; plain-TF32 mode")
         dcgan["value"] = dcgan["tf32"]["value"]
+        if world > 1 and gb % world == 0:
+            # the same global batch of 64 images split over the ranks (strong scaling), for comparison with the weak-scaling figure
+            ops.set_precision(ops.TF32)
+            del trainer
+            small = DCGANStep(gb // world, world=world, use_graph=not args.dcgan_eager, fused=args.dcgan_fused,
+                              update="fused" if args.exchange == "peer" else "nccl", overlap=args.dcgan_overlap)
+            zs, ls = z[:gb // world].contiguous(), labels[:gb // world].contiguous()
+            ms, _, _, _ = timed(lambda: small(zs, ls), args.steps, max(args.warmup, 3))
+            ops.stream_status()
+            dcgan["strong_scaling"] = dict(global_batch=gb, per_gpu_batch=gb // world, value=gb / (ms * 1e-3), ms_per_step=ms, unit="img/s", mode="tf32")
+            del small
+
+    if samples["modes"]:
+        samples.update(x=x[sample_idx].cpu().numpy(), d=delta[sample_idx].cpu().numpy(), w=wt.cpu().numpy()[0])
+    cfg1 = vae = gemm = None
+    if world == 1 and not args.skip_extra:
+        x = delta = y = dx = None
+        torch.cuda.empty_cache()
+        cfg1 = cfg1_gpu(torch, ops)
+        vae = vae_bench(torch, ops, lib, timed, args.steps)
+        gemm = gemm_bench(torch, ops, peaks["hbm"])
 
     hbm = None
     if not args.skip_hbm and world == 1:
-        del x, delta, y, dx
+        x = delta = y = dx = None
         torch.cuda.empty_cache()
         hbm = hbm_kernels(torch, ops, peaks["hbm"])
 
@@ -533,14 +837,22 @@ def main():
                                 global_batch=c["batch"], per_gpu_batch=B, parallelism=f"dp{world}",
                                 exchange=(("library kernels over NVLink peer memory (b200_allreduce, b200_allreduce_adam)" if args.exchange == "peer"
                                            else "NCCL all-reduce") if world > 1 else None), l2="inputs exceed L2 (1 GiB tensors)",
-                                parity="tf32: 2e-3, tf32x3: 1e-4 vs the reference CPU backend (tests/test_gpu_conv.py)",
+                                parity="tf32: 2e-3, tf32x3: 1e-4 on dot_rel_err vs the reference CPU backend (tests/test_gpu_full_size.py); measured on this run's batch when the CPU leg runs",
                                 flops_per_step=step_flops),
                     clocks=head["clocks"], gpu_launches=head["gpu_launches"], roofline=head["roofline"], e2e=e2e,
-                    tf32x3=results["tf32x3"], dcgan=dcgan, hbm_kernels=hbm)
+                    tf32x3=results["tf32x3"], dcgan=dcgan, cfg1=cfg1, vae=vae, gemm=gemm, hbm_kernels=hbm)
         if not args.skip_cpu and world == 1:
             line["cpu_baseline"] = cpu_baseline()
+            if samples["modes"]:
+                line["config"]["parity"] = parity_leg(samples)
             if dcgan is not None:
                 dcgan["cpu_baseline"] = dcgan_cpu_baseline()
+            if cfg1 is not None:
+                cfg1["cpu_baseline"] = cfg1_cpu()
+                cfg1["vs_cpu_baseline_same_config"] = dict(device_ratio=cfg1["tf32"]["value"] / cfg1["cpu_baseline"]["value"],
+                                                           e2e_ratio=cfg1["e2e"]["value"] / cfg1["cpu_baseline"]["value"])
+            if vae is not None:
+                vae["cpu_baseline"] = vae_cpu_baseline()
         emit(json.dumps(line))
     if world > 1:
         # Leave without tearing the process group down: destroying NCCL communicators while CUDA graphs that hold

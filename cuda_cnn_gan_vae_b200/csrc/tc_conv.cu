@@ -153,9 +153,13 @@ __device__ __forceinline__ TileCtx decode_tile(const TcParams &p, int tile, int 
         c.chunk_begin = b;
         c.nsteps = (int)(e - b);
     } else {
+        c.split = tile % p.ksplit;
+        tile /= p.ksplit;
         c.nt = tile % p.n_tiles_n;
         c.mt = tile / p.n_tiles_n;
-        c.nsteps = (p.K + 31) / 32;
+        const int total = (p.K + 31) / 32;
+        c.step_begin = total * c.split / p.ksplit;
+        c.nsteps = total * (c.split + 1) / p.ksplit - c.step_begin;
     }
     return c;
 }
@@ -301,7 +305,8 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
                         if (is_a) { c0 = 0; c1 = cx * p.BW; c2 = cy * p.BH; c3 = pad ? (p.chunks_i + 1) * p.BI : ci * p.BI; c4 = c.ft * 4; }
                         else { c0 = 0; c1 = cx * p.BW + t.dx; c2 = cy * p.BH + t.dy; c3 = t.in_phase * p.n_img + ci * p.BI; c4 = c.ct * (p.BN / 32) + (int)rank * (p.BN / 64) * (CTAS - 1); }
                     } else {
-                        const int k0 = st * 32;           // beyond K for a filler block: zero-filled
+                        // a filler block (and everything past K) reads beyond the matrix: zero-filled
+                        const int k0 = pad ? ((p.K + 31) / 32 + 1) * 32 : (c.step_begin + st) * 32;
                         c2 = c3 = c4 = 0;
                         if (is_a) { if (p.a_mn) { c0 = 0; c1 = k0; c4 = c.mt * 4; } else { c0 = k0; c1 = c.mt * 128; } }
                         else { if (p.b_mn) { c0 = 0; c1 = k0; c4 = c.nt * (p.BN / 32); } else { c0 = k0; c1 = c.nt * p.BN; } }
@@ -467,7 +472,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
                 }
             } else {
                 const int m = c.mt * 128 + row;
-                float *dst = p.out + (size_t)m * p.ldc + c.nt * p.BN;
+                float *dst = (p.ksplit > 1 ? p.kpartial + (size_t)c.split * (size_t)p.out_elems : p.out) + (size_t)m * p.ldc + c.nt * p.BN;
                 for (int c0 = 0; c0 < p.BN; c0 += 16) {
                     load16(c0);
 #pragma unroll
@@ -1483,7 +1488,20 @@ int tc_gemm(float *out, const float *a, const float *b, int m, int n, int k, int
     if ((size_t)m * n < 4096 || k < 8) return TC_UNSUPPORTED;      // too small to be worth a tensor-core launch
     const bool x3 = precision == B200_TF32X3;
     const size_t a_elems = (size_t)m * k, b_elems = (size_t)n * k;
-    const size_t bytes = sizeof(float) * (a_elems + b_elems) * (x3 ? 2 : 1) + 16384;
+    // Split-K: a product with few output tiles and a long contraction (the VAE heads: 128 x 256 outputs over 16384 inputs
+    // are ONE tile) divides the K steps of a tile over several work items; conv_ksplit_reduce_kernel sums the partial
+    // outputs in a fixed order.  Taken when the tiles leave most SMs idle; every split keeps at least 8 K steps.
+    int ksplit = 1;
+    {
+        const int bn = (int)align_up(n < 256 ? n : 256, b_mn_major ? 32 : 16);
+        const long long tiles = (long long)ceil_div(m, 128) * ceil_div(n, bn);
+        const int steps = ceil_div(k, 32);
+        static const bool split_enabled = !(getenv("B200CONV_KSPLIT") && getenv("B200CONV_KSPLIT")[0] == '0');
+        if (split_enabled && ((size_t)m * n) % 4 == 0 && ((uintptr_t)out & 15) == 0)
+            while (tiles * ksplit * 2 <= sm_count() && steps / (ksplit * 2) >= 8 && ksplit < 64) ksplit *= 2;
+    }
+    const size_t part_elems = ksplit > 1 ? (size_t)ksplit * m * n : 0;
+    const size_t bytes = sizeof(float) * ((a_elems + b_elems) * (x3 ? 2 : 1) + part_elems) + 16384;
     int r = arena_reserve(bytes, s);
     if (r) return r;
     arena_reset();
@@ -1491,7 +1509,8 @@ int tc_gemm(float *out, const float *a, const float *b, int m, int n, int k, int
     float *a_lo = x3 ? (float *)arena_take(sizeof(float) * a_elems + 256) : nullptr;
     float *b_hi = (float *)arena_take(sizeof(float) * b_elems + 256);
     float *b_lo = x3 ? (float *)arena_take(sizeof(float) * b_elems + 256) : nullptr;
-    if (!a_hi || !b_hi || (x3 && (!a_lo || !b_lo))) return fail(B200_E_NOMEM, "scratch arena exhausted");
+    float *kpartial = part_elems ? (float *)arena_take(sizeof(float) * part_elems) : nullptr;
+    if (!a_hi || !b_hi || (x3 && (!a_lo || !b_lo)) || (part_elems && !kpartial)) return fail(B200_E_NOMEM, "scratch arena exhausted");
     int grid = sm_count() * 8;
     split_tf32_kernel<<<grid, 256, 0, s>>>(a, a_hi, a_lo, a_elems);
     B200_LAUNCH_CHECK();
@@ -1507,8 +1526,11 @@ int tc_gemm(float *out, const float *a, const float *b, int m, int n, int k, int
     p.idesc = make_idesc_tf32(p.BN, a_mn_major, b_mn_major);
     p.M = m; p.N = n; p.K = k; p.ldc = n; p.a_mn = a_mn_major; p.b_mn = b_mn_major;
     p.n_tiles_n = ceil_div(n, p.BN);
-    p.num_tiles = ceil_div(m, 128) * p.n_tiles_n;
     p.out = out;
+    p.ksplit = ksplit;
+    p.kpartial = kpartial;
+    p.out_elems = (long long)m * n;
+    p.num_tiles = ceil_div(m, 128) * p.n_tiles_n * ksplit;
 
     CUtensorMap maps[4];
     for (int side = 0; side < 2; side++) {
@@ -1530,7 +1552,15 @@ int tc_gemm(float *out, const float *a, const float *b, int m, int n, int k, int
             if (x3 && (r = make_map(&maps[2 * side + 1], lo, dims, pitch, box))) return r;
         }
     }
-    return launch_tc<MODE_GEMM>(maps, p, x3, s);
+    if ((r = launch_tc<MODE_GEMM>(maps, p, x3, s))) return r;
+    if (ksplit > 1) {
+        const size_t total = (size_t)m * n;
+        size_t blocks = (total / 4 + 255) / 256;
+        if (blocks > (size_t)sm_count() * 16) blocks = (size_t)sm_count() * 16;
+        conv_ksplit_reduce_kernel<<<(unsigned)blocks, 256, 0, s>>>(out, kpartial, ksplit, total, nullptr, 1, total);
+        B200_LAUNCH_CHECK();
+    }
+    return B200_OK;
 }
 
 }  // namespace b200

@@ -53,10 +53,12 @@ class DCGANStep:
     respect to the logit, formed as in cuda/netmodel/cmodel_basicgan.cu.h:352-376 but on the device)."""
 
     def __init__(self, batch, world=1, widths_g=(256, 128, 64, 3), widths_d=(64, 128, 256, 512), base=512, noise=100, leaky_slope=0.2,
-                 use_graph=True, fused=False, update="fused", overlap=True):
+                 use_graph=True, fused=False, update="fused", overlap=False):
         """update (several ranks): "fused" -- the library's reduce-scatter + Adam + all-gather kernel over NVLink peer memory,
         one launch per net on the main stream; "nccl" -- an NCCL all-reduce of each gradient arena on a side stream followed
-        by the Adam launch."""
+        by the Adam launch.  overlap: the discriminator's exchange on a side stream beside the generator's backward pass
+        (measured on 2 GPUs: no gain -- the exchange kernel's CTAs take whole SMs from the backward pass for as long as they
+        run -- so it is off by default)."""
         self.batch, self.world, self.overlap = batch, world, overlap
         self.update = update if world > 1 else "local"
         peer = self.update == "fused"

@@ -40,7 +40,8 @@ def test_kat_summ_xy_all_ones(ops):
 
 
 # Linear-layer products of the headline configurations (batch reduced): forward W*x, backward W^T*delta
-LINEAR = [(64, 8192, 100), (16, 1, 8192), (32, 256, 16384), (32, 16384, 256)]
+# the last two: the VAE heads and the decoder input at the batch of the configuration (one output tile, 512 K steps: split-K)
+LINEAR = [(64, 8192, 100), (16, 1, 8192), (32, 256, 16384), (32, 16384, 256), (128, 256, 16384), (128, 16384, 256)]
 
 
 @pytest.mark.parametrize("shape", LINEAR)

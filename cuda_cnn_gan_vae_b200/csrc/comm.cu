@@ -57,12 +57,19 @@ struct CommPeers {
     char *base[kCommMaxWorld];
 };
 
-struct ExchangeParams {
-    CommPeers peers;
-    int rank, world, channel;
+constexpr int kCommMaxSegments = 4;
+
+// One arena of an exchange: several (the arenas of several networks) share the launch and its two barriers.
+struct ExchangeSegment {
     size_t first, second;      // float offsets into the data region: (gradients, weights) or (buffer, unused)
     size_t n4;                 // 16-byte groups in the arena
     float *m, *v;              // local Adam moments (full-size arrays; only this rank's slice is touched)
+};
+
+struct ExchangeParams {
+    CommPeers peers;
+    int rank, world, channel, segments;
+    ExchangeSegment seg[kCommMaxSegments];
     AdamArgs adam;
     const double *corrections;
     unsigned *status;
@@ -140,10 +147,12 @@ __global__ void __launch_bounds__(512) exchange_kernel(const ExchangeParams p)
     if (!s_abort) {
         AdamArgs a = p.adam;
         if (ADAM && p.corrections) { a.inv_c1 = 1.0 / p.corrections[0]; a.inv_c2 = 1.0 / p.corrections[1]; }
-        const size_t per = (p.n4 + p.world - 1) / p.world;
-        const size_t begin = per * p.rank < p.n4 ? per * p.rank : p.n4;
-        const size_t end = begin + per < p.n4 ? begin + per : p.n4;
         const size_t data0 = kPadBytes / sizeof(float4);
+      for (int sg = 0; sg < p.segments; sg++) {
+        const ExchangeSegment &q = p.seg[sg];
+        const size_t per = (q.n4 + p.world - 1) / p.world;
+        const size_t begin = per * p.rank < q.n4 ? per * p.rank : q.n4;
+        const size_t end = begin + per < q.n4 ? begin + per : q.n4;
         // Two groups per thread and trip, and the loads from up to eight ranks issued together before the first addition: a
         // remote load takes a few microseconds, so a thread keeps 2 x world of them in flight instead of paying one round trip
         // per rank.  The additions stay in rank order (reproducible, and equal to a sequential sum over the ranks).
@@ -161,7 +170,7 @@ __global__ void __launch_bounds__(512) exchange_kernel(const ExchangeParams p)
 #pragma unroll
                     for (int rr = 0; rr < R; rr++)
                         if (r0 + rr < p.world && i < end)
-                            t[u][rr] = __ldcg(reinterpret_cast<const float4 *>(p.peers.base[r0 + rr]) + data0 + p.first / 4 + i);
+                            t[u][rr] = __ldcg(reinterpret_cast<const float4 *>(p.peers.base[r0 + rr]) + data0 + q.first / 4 + i);
                 }
 #pragma unroll
                 for (int u = 0; u < U; u++) {
@@ -178,21 +187,22 @@ __global__ void __launch_bounds__(512) exchange_kernel(const ExchangeParams p)
             for (int u = 0; u < U; u++) {
                 const size_t i = i0 + u * stride;
                 if (i >= end) break;
-                const size_t gi = data0 + p.first / 4 + i;
+                const size_t gi = data0 + q.first / 4 + i;
                 if (ADAM) {
-                    const size_t wi = data0 + p.second / 4 + i;
+                    const size_t wi = data0 + q.second / 4 + i;
                     float4 w = reinterpret_cast<const float4 *>(p.peers.base[p.rank])[wi];
-                    float4 mm = reinterpret_cast<float4 *>(p.m)[i], vv = reinterpret_cast<float4 *>(p.v)[i];
+                    float4 mm = reinterpret_cast<float4 *>(q.m)[i], vv = reinterpret_cast<float4 *>(q.v)[i];
                     w.x = adam_element(w.x, s[u].x, mm.x, vv.x, a); w.y = adam_element(w.y, s[u].y, mm.y, vv.y, a);
                     w.z = adam_element(w.z, s[u].z, mm.z, vv.z, a); w.w = adam_element(w.w, s[u].w, mm.w, vv.w, a);
-                    reinterpret_cast<float4 *>(p.m)[i] = mm;
-                    reinterpret_cast<float4 *>(p.v)[i] = vv;
+                    reinterpret_cast<float4 *>(q.m)[i] = mm;
+                    reinterpret_cast<float4 *>(q.v)[i] = vv;
                     for (int r = 0; r < p.world; r++) reinterpret_cast<float4 *>(p.peers.base[r])[wi] = w;
                 } else {
                     for (int r = 0; r < p.world; r++) reinterpret_cast<float4 *>(p.peers.base[r])[gi] = s[u];
                 }
             }
         }
+      }
     }
 
     // 3. done barrier: my stores into the peers' arenas are visible before the flag is, and nobody's gradients are
@@ -245,29 +255,38 @@ static int exchange_grid(size_t n4, int world)
     return (int)g;
 }
 
-static int launch_exchange(b200_comm *c, bool adam, size_t first, size_t second, size_t n, float *m, float *v, const AdamArgs &a,
-                           const double *corrections, int channel, cudaStream_t s)
+static int launch_exchange(b200_comm *c, bool adam, int count, const b200_exchange_segment *segs, const AdamArgs &a, const double *corrections,
+                           int channel, cudaStream_t s)
 {
     if (!c) return fail(B200_E_ARG, "null communicator");
     if (!c->connected) return fail(B200_E_ARG, "communicator is not connected");
     if (channel < 0 || channel >= kCommChannels) return fail(B200_E_ARG, "channel must lie in [0, %d)", kCommChannels);
-    if ((n % 4) || (first % 4) || (second % 4)) return fail(B200_E_ARG, "arena offsets and sizes must be multiples of 4 floats");
-    if ((first + n) * sizeof(float) > c->bytes || (adam && (second + n) * sizeof(float) > c->bytes))
-        return fail(B200_E_SHAPE, "arena reaches beyond the communicator's buffer");
-    if (adam && (((uintptr_t)m | (uintptr_t)v) & 15)) return fail(B200_E_ARG, "Adam moments must be 16-byte aligned");
-    if (!n) return B200_OK;
+    if (count < 1 || count > kCommMaxSegments || !segs) return fail(B200_E_ARG, "an exchange takes 1 to %d arenas", kCommMaxSegments);
+    ExchangeParams p;
+    memset(&p, 0, sizeof(p));
+    size_t largest = 0, total = 0;
+    for (int i = 0; i < count; i++) {
+        const b200_exchange_segment &g = segs[i];
+        if ((g.n % 4) || (g.grad_offset % 4) || (g.weight_offset % 4)) return fail(B200_E_ARG, "arena offsets and sizes must be multiples of 4 floats");
+        if ((g.grad_offset + g.n) * sizeof(float) > c->bytes || (adam && (g.weight_offset + g.n) * sizeof(float) > c->bytes))
+            return fail(B200_E_SHAPE, "arena reaches beyond the communicator's buffer");
+        if (adam && (!g.m || !g.v)) return fail(B200_E_ARG, "null Adam moments");
+        if (adam && (((uintptr_t)g.m | (uintptr_t)g.v) & 15)) return fail(B200_E_ARG, "Adam moments must be 16-byte aligned");
+        p.seg[i].first = g.grad_offset; p.seg[i].second = g.weight_offset; p.seg[i].n4 = g.n / 4;
+        p.seg[i].m = g.m; p.seg[i].v = g.v;
+        if (g.n / 4 > largest) largest = g.n / 4;
+        total += g.n;
+    }
+    if (!total) return B200_OK;
     int dev = 0;
     B200_CUDA(cudaGetDevice(&dev));
     if (dev != c->device) return fail(B200_E_ARG, "communicator belongs to device %d, current device is %d", c->device, dev);
-    ExchangeParams p;
-    memset(&p, 0, sizeof(p));
     for (int r = 0; r < c->world; r++) p.peers.base[r] = c->peer[r];
-    p.rank = c->rank; p.world = c->world; p.channel = channel;
-    p.first = first; p.second = second; p.n4 = n / 4;
-    p.m = m; p.v = v; p.adam = a; p.corrections = corrections;
+    p.rank = c->rank; p.world = c->world; p.channel = channel; p.segments = count;
+    p.adam = a; p.corrections = corrections;
     int r = status_word(&p.status);
     if (r) return r;
-    const int grid = exchange_grid(p.n4, c->world);
+    const int grid = exchange_grid(largest, c->world);
     if (adam) exchange_kernel<true><<<grid, 512, 0, s>>>(p);
     else exchange_kernel<false><<<grid, 512, 0, s>>>(p);
     B200_LAUNCH_CHECK();
@@ -383,19 +402,27 @@ int b200_allreduce(b200_comm *c, size_t offset, size_t n, int channel, void *str
     if (c && c->world == 1) return B200_OK;
     AdamArgs a;
     memset(&a, 0, sizeof(a));
-    return launch_exchange(c, false, offset, 0, n, nullptr, nullptr, a, nullptr, channel, (cudaStream_t)stream);
+    b200_exchange_segment g = {offset, 0, n, nullptr, nullptr};
+    return launch_exchange(c, false, 1, &g, a, nullptr, channel, (cudaStream_t)stream);
 }
 
 int b200_allreduce_adam(b200_comm *c, size_t grad_offset, size_t weight_offset, float *m, float *v, size_t n, uint32_t batch_size,
                         double speed, double beta1, double beta2, double epsilon, double iteration, const double *corrections, int channel,
                         void *stream)
 {
-    if (!c || !m || !v) return fail(B200_E_ARG, "null argument");
+    b200_exchange_segment g = {grad_offset, weight_offset, n, m, v};
+    return b200_allreduce_adam_multi(c, 1, &g, batch_size, speed, beta1, beta2, epsilon, iteration, corrections, channel, stream);
+}
+
+int b200_allreduce_adam_multi(b200_comm *c, int count, const b200_exchange_segment *segments, uint32_t batch_size, double speed, double beta1,
+                              double beta2, double epsilon, double iteration, const double *corrections, int channel, void *stream)
+{
+    if (!c || !segments) return fail(B200_E_ARG, "null argument");
     if (!batch_size) return fail(B200_E_ARG, "batch_size must be positive");
     const double c1 = corrections ? 1.0 : 1.0 - pow(beta1, iteration), c2 = corrections ? 1.0 : 1.0 - pow(beta2, iteration);
     if (!corrections && (c1 == 0.0 || c2 == 0.0)) return fail(B200_E_ARG, "Adam: iteration must be positive");
-    return launch_exchange(c, true, grad_offset, weight_offset, n, m, v, adam_args(batch_size, speed, beta1, beta2, epsilon, c1, c2, 0.0), corrections,
-                           channel, (cudaStream_t)stream);
+    return launch_exchange(c, true, count, segments, adam_args(batch_size, speed, beta1, beta2, epsilon, c1, c2, 0.0), corrections, channel,
+                           (cudaStream_t)stream);
 }
 
 }  // extern "C"

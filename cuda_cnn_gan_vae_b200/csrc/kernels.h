@@ -44,7 +44,13 @@ struct ActPack {
 };
 constexpr size_t kPackPad = 256;
 ActPack act_pack_shape(int n, int c, int h, int w, int sy, int sx);
-int act_pack_fill(const ActPack &pk, const float *src, cudaStream_t s);
+// A neuron function applied while an operand is packed (the function layer in front of a convolution layer): func is a
+// B200_ACT_* code; act_out, if not NULL, also receives f(src) in the source layout.
+struct PackFunction { int func; double slope; float *act_out; };
+// A neuron function applied to out + bias in the epilogue of the convolution (the function layer behind it): pre_out, if not
+// NULL, receives the value before the function (what the function layer keeps for its derivative).
+struct EpilogueFunction { int func; double slope; float *pre_out; };
+int act_pack_fill(const ActPack &pk, const float *src, cudaStream_t s, const PackFunction *pf = nullptr);
 // The same pack with the first stage of a bias gradient fused in: rowsum (act_pack_rowsum_elems floats) receives partial
 // plane sums [n][c][runs]; *runs == 0 on return means the shape took the scalar pack kernel and no sums were produced.
 size_t act_pack_rowsum_elems(const ActPack &pk);
@@ -55,7 +61,7 @@ int weight_pack_fill(const b200_conv_geom &g, bool backward, const float *kernel
 // kpartial (optional): scratch of conv_gemm_partial_elems() floats that allows splitting the contraction of small layers
 size_t conv_gemm_partial_elems(bool backward, const b200_conv_geom &g, int batch);
 int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack &act, const float *w_hi, const float *w_lo,
-              const float *bias, bool x3, cudaStream_t s, float *kpartial = nullptr, size_t kpartial_elems = 0);
+              const float *bias, bool x3, cudaStream_t s, float *kpartial = nullptr, size_t kpartial_elems = 0, const EpilogueFunction *ef = nullptr);
 size_t wgrad_partial_elems(const b200_conv_geom &g, int batch);
 int wgrad_gemm(const b200_conv_geom &g, float *dkernel, int accumulate, const ActPack &x, const ActPack &d, float *partial,
                bool x3, cudaStream_t s);

@@ -15,7 +15,7 @@ struct b200_conv_layer {
     int batch;
     int transposed;
     int device;
-    enum { IN_HI, IN_LO, ER_HI, ER_LO, W_HI, W_LO, PARTIAL, DB_TMP, COL_HI, COL_LO, TMP, DK_TMP, KSPLIT, NBUF };
+    enum { IN_HI, IN_LO, ER_HI, ER_LO, W_HI, W_LO, PARTIAL, DB_TMP, COL_HI, COL_LO, TMP, DK_TMP, KSPLIT, ACT_TMP, NBUF };
     float *buf[NBUF];
     size_t cap[NBUF];            // bytes
     int in_valid;                // the kept input pack matches the last forward call
@@ -25,6 +25,10 @@ struct b200_conv_layer {
     int er_valid;                // the packed output error of a weights-only backward call may serve the input-only call that follows
     int er_precision;
     const float *er_ptr;
+    // how the last forward call got its input when a neuron function was fused in front of the layer: 0 the caller's tensor
+    // is the layer input; 1 only the packed copy holds f(input); 2 f(input) also lies in the ACT_TMP buffer; 3 in the caller's
+    // input_act_out.  The backward call reads its `input` argument only when it must re-pack, and then needs f(input).
+    int fused_input;
 };
 
 namespace b200 {
@@ -65,7 +69,8 @@ static ActPack er_shape(const b200_conv_layer *l)
 }
 
 // rowsum_runs != NULL: the pack also leaves partial plane sums of src in the DB_TMP buffer (first stage of the bias gradient)
-static int pack_into(b200_conv_layer *l, int hi_slot, ActPack &pk, const float *src, bool x3, cudaStream_t s, int *rowsum_runs = nullptr)
+static int pack_into(b200_conv_layer *l, int hi_slot, ActPack &pk, const float *src, bool x3, cudaStream_t s, int *rowsum_runs = nullptr,
+                     const PackFunction *pf = nullptr)
 {
     int r;
     const size_t bytes = sizeof(float) * pk.elems() + kPackPad;
@@ -73,7 +78,7 @@ static int pack_into(b200_conv_layer *l, int hi_slot, ActPack &pk, const float *
     if (x3 && (r = ensure(l, hi_slot + 1, bytes, s))) return r;
     pk.hi = l->buf[hi_slot];
     pk.lo = x3 ? l->buf[hi_slot + 1] : nullptr;
-    if (!rowsum_runs) return act_pack_fill(pk, src, s);
+    if (!rowsum_runs) return act_pack_fill(pk, src, s, pf);
     if ((r = ensure(l, b200_conv_layer::DB_TMP, sizeof(float) * act_pack_rowsum_elems(pk), s))) return r;
     return act_pack_fill_with_sums(pk, src, l->buf[b200_conv_layer::DB_TMP], rowsum_runs, s);
 }
@@ -89,7 +94,7 @@ static int pack_weights(b200_conv_layer *l, bool backward, const float *kernel, 
 
 // conv_gemm with the layer's split-K scratch (sized on first use; none for layers whose output is large)
 static int layer_conv_gemm(b200_conv_layer *l, bool backward, const b200_conv_geom &g, float *out, const ActPack &act, const float *bias, bool x3,
-                           cudaStream_t s)
+                           cudaStream_t s, const EpilogueFunction *ef = nullptr)
 {
     const size_t elems = conv_gemm_partial_elems(backward, g, l->batch);
     if (elems) {
@@ -97,7 +102,7 @@ static int layer_conv_gemm(b200_conv_layer *l, bool backward, const b200_conv_ge
         if (r) return r;
     }
     return conv_gemm(backward, g, out, act, l->buf[b200_conv_layer::W_HI], l->buf[b200_conv_layer::W_LO], bias, x3, s,
-                     elems ? l->buf[b200_conv_layer::KSPLIT] : nullptr, elems);
+                     elems ? l->buf[b200_conv_layer::KSPLIT] : nullptr, elems, ef);
 }
 
 // ---- few-channel layers (smallc.cu): taps folded into the channel dimension, contractions as 1x1 convolutions ------------
@@ -138,11 +143,12 @@ static int smallc_weights_into(b200_conv_layer *l, const float *kernel, int pitc
 }
 
 // out[n, k, oy, ox] = sum_c' W'[k][c'] col[n, oy, ox, c'] (+ bias): the convolution of the few-channel tensor
-static int smallc_conv(b200_conv_layer *l, float *out, const ActPack &col, const float *kernel, const float *bias, bool x3, cudaStream_t s)
+static int smallc_conv(b200_conv_layer *l, float *out, const ActPack &col, const float *kernel, const float *bias, bool x3, cudaStream_t s,
+                       const EpilogueFunction *ef = nullptr)
 {
     int r;
     if ((r = smallc_weights_into(l, kernel, col.cp, false, x3, s))) return r;
-    return layer_conv_gemm(l, false, smallc_geom(l->g), out, col, bias, x3, s);
+    return layer_conv_gemm(l, false, smallc_geom(l->g), out, col, bias, x3, s, ef);
 }
 
 // dx = col2im(W''^T delta): the transposed convolution towards the few-channel tensor; `many` is the pack of the
@@ -209,24 +215,61 @@ int b200_conv_layer_destroy(b200_conv_layer *l)
     return B200_OK;
 }
 
-int b200_conv_layer_forward(b200_conv_layer *l, float *out, const float *input, const float *kernel, const float *bias, void *stream)
+// Forward pass with the optional fusions.  The tensor-core paths apply f->input_func while they pack the layer input and
+// f->output_func in the epilogue; where a path cannot (few-channel layers pack through im2col, the transposed few-channel
+// layer finishes in a gather kernel, the CUDA-core path), the same results are produced with separate activation launches.
+static int layer_forward(b200_conv_layer *l, float *out, const float *input, const float *kernel, const float *bias, const b200_conv_fusion *f,
+                         void *stream)
 {
     cudaStream_t s = (cudaStream_t)stream;
-    if (!l || !out || !input || !kernel) return fail(B200_E_ARG, "null argument");
     const int prec = precision();
+    const b200_conv_geom &g = l->g;
     l->in_valid = 0;
     int r = TC_UNSUPPORTED;
     l->col_valid = 0;
     l->er_valid = 0;
+    const bool in_act = f && f->input_func >= 0, out_act = f && f->output_func >= 0;
+    l->fused_input = in_act ? (f->input_act_out ? 3 : 1) : 0;
+    const size_t in_count = (size_t)l->batch * (l->transposed ? (size_t)g.kernel_amount * g.out_y * g.out_x : (size_t)g.in_z * g.in_y * g.in_x);
+    const size_t out_count = (size_t)l->batch * (l->transposed ? (size_t)g.in_z * g.in_y * g.in_x : (size_t)g.kernel_amount * g.out_y * g.out_x);
+    // the activated input as a tensor of its own (paths that cannot apply the function while packing)
+    const float *plain_input = input;
+    bool input_materialised = false;
+    auto materialise_input = [&]() -> int {
+        if (!in_act || input_materialised) return B200_OK;
+        float *dst = f->input_act_out;
+        if (!dst) {
+            int e = ensure(l, b200_conv_layer::ACT_TMP, sizeof(float) * in_count, s);
+            if (e) return e;
+            dst = l->buf[b200_conv_layer::ACT_TMP];
+            l->fused_input = 2;
+        }
+        int e = b200_activation(dst, input, in_count, f->input_func, 0, f->input_slope, stream);
+        if (e) return e;
+        plain_input = dst;
+        input_materialised = true;
+        return B200_OK;
+    };
+    // the neuron function behind the layer as a launch of its own: the convolution goes to output_pre (or in place)
+    auto finish_output = [&](float *conv_out) -> int {
+        if (!out_act) return B200_OK;
+        return b200_activation(out, conv_out, out_count, f->output_func, 0, f->output_slope, stream);
+    };
+    float *unfused_out = (out_act && f->output_pre) ? f->output_pre : out;
+    EpilogueFunction ef = {out_act ? f->output_func : -1, out_act ? f->output_slope : 0.0, out_act ? f->output_pre : nullptr};
+    const EpilogueFunction *efp = out_act ? &ef : nullptr;
+
     if (prec != B200_FP32 && use_smallc(l)) {
         const bool x3 = prec == B200_TF32X3;
+        if ((r = materialise_input())) return r;
         if (!l->transposed) {
             ActPack col;
-            if ((r = col_into(l, col, input, x3, s)) == B200_OK) r = smallc_conv(l, out, col, kernel, bias, x3, s);
+            if ((r = col_into(l, col, plain_input, x3, s)) == B200_OK) r = smallc_conv(l, out, col, kernel, bias, x3, s, efp);
             if (r == B200_OK) { l->col_valid = 1; l->col_precision = prec; }
         } else {
             ActPack in = in_shape(l);
-            if ((r = pack_into(l, b200_conv_layer::IN_HI, in, input, x3, s)) == B200_OK) r = smallc_tconv(l, out, in, kernel, x3, s);
+            if ((r = pack_into(l, b200_conv_layer::IN_HI, in, plain_input, x3, s)) == B200_OK) r = smallc_tconv(l, unfused_out, in, kernel, x3, s);
+            if (r == B200_OK) r = finish_output(unfused_out);
             if (r == B200_OK) { l->in_valid = 1; l->in_precision = prec; }
         }
         if (r == B200_OK) { set_path(B200_PATH_TCGEN05); return r; }
@@ -236,9 +279,11 @@ int b200_conv_layer_forward(b200_conv_layer *l, float *out, const float *input, 
     if (prec != B200_FP32) {
         const bool x3 = prec == B200_TF32X3;
         ActPack in = in_shape(l);
-        if ((r = pack_into(l, b200_conv_layer::IN_HI, in, input, x3, s)) == B200_OK &&
+        PackFunction pf = {in_act ? f->input_func : -1, in_act ? f->input_slope : 0.0, in_act ? f->input_act_out : nullptr};
+        const bool fuse_pack = in_act && !input_materialised;
+        if ((r = pack_into(l, b200_conv_layer::IN_HI, in, plain_input, x3, s, nullptr, fuse_pack ? &pf : nullptr)) == B200_OK &&
             (r = pack_weights(l, l->transposed, kernel, x3, s)) == B200_OK)
-            r = layer_conv_gemm(l, l->transposed, l->g, out, in, l->transposed ? nullptr : bias, x3, s);
+            r = layer_conv_gemm(l, l->transposed, g, out, in, l->transposed ? nullptr : bias, x3, s, efp);
         if (r == B200_OK) {
             l->in_valid = 1;
             l->in_precision = prec;
@@ -248,8 +293,28 @@ int b200_conv_layer_forward(b200_conv_layer *l, float *out, const float *input, 
         if (r != TC_UNSUPPORTED) return r;
     }
     // general path: the stateless tensor-math entry points
-    if (!l->transposed) return b200_conv_forward(&l->g, out, l->batch, input, l->batch, kernel, 1, bias, 1, stream);
-    return b200_conv_backward(&l->g, out, l->batch, input, l->batch, kernel, 1, nullptr, 0, stream);
+    if ((r = materialise_input())) return r;
+    if (!l->transposed) r = b200_conv_forward(&g, unfused_out, l->batch, plain_input, l->batch, kernel, 1, bias, 1, stream);
+    else r = b200_conv_backward(&g, unfused_out, l->batch, plain_input, l->batch, kernel, 1, nullptr, 0, stream);
+    if (r) return r;
+    return finish_output(unfused_out);
+}
+
+int b200_conv_layer_forward(b200_conv_layer *l, float *out, const float *input, const float *kernel, const float *bias, void *stream)
+{
+    if (!l || !out || !input || !kernel) return fail(B200_E_ARG, "null argument");
+    return layer_forward(l, out, input, kernel, bias, nullptr, stream);
+}
+
+int b200_conv_layer_forward_fused(b200_conv_layer *l, float *out, const float *input, const float *kernel, const float *bias,
+                                  const b200_conv_fusion *fusion, void *stream)
+{
+    if (!l || !out || !input || !kernel) return fail(B200_E_ARG, "null argument");
+    if (fusion) {
+        if (fusion->input_func > B200_ACT_GELU || fusion->output_func > B200_ACT_GELU) return fail(B200_E_ARG, "unknown neuron function");
+        if (fusion->output_pre == out && fusion->output_func >= 0) return fail(B200_E_ARG, "output_pre must not alias the output");
+    }
+    return layer_forward(l, out, input, kernel, bias, fusion, stream);
 }
 
 int b200_conv_layer_backward(b200_conv_layer *l, float *input_delta, float *dkernel, float *dbias, int accumulate,
@@ -261,6 +326,14 @@ int b200_conv_layer_backward(b200_conv_layer *l, float *input_delta, float *dker
     const b200_conv_geom &g = l->g;
     const int prec = precision();
     int r = TC_UNSUPPORTED;
+    // after a forward call with a neuron function fused in front, the layer input f(x) may exist only inside the library
+    if (l->fused_input == 2) input = l->buf[b200_conv_layer::ACT_TMP];
+    if (l->fused_input == 1 && dkernel) {
+        const bool kept = prec != B200_FP32 && ((use_smallc(l) && !l->transposed) ? (l->col_valid && l->col_precision == prec) : (l->in_valid && l->in_precision == prec));
+        if (!kept)
+            return fail(B200_E_ARG, "the layer input of the fused forward call was kept only in packed form for another precision mode: "
+                                    "pass input_act_out to b200_conv_layer_forward_fused and hand that tensor to the backward call");
+    }
     // A weights-only call followed by an input-only call on the same output error (the order that lets a caller start the
     // all-reduce of the gradients while the input error is still being computed) packs the error once.
     const bool reuse_er = l->er_valid && l->er_ptr == output_delta && l->er_precision == prec && !dkernel && input_delta;

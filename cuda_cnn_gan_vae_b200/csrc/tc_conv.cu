@@ -26,6 +26,7 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "tc_ptx.cuh"
+#include "act.cuh"
 #include <cstdlib>
 #include <cstring>
 #include <vector>
@@ -68,6 +69,9 @@ struct TcParams {
     TapEntry taps[kMaxTaps];
     float *out;
     const float *bias;
+    int act_func;              // CONV: neuron function applied to out + bias in the epilogue (B200_ACT_*), -1 = none
+    double act_slope;
+    float *pre_out;            // CONV: optional second output, the value before the neuron function
     int ksplit;                // CONV: the K steps of a tile are divided over ksplit work items (1 = no split)
     float *kpartial;           // ksplit > 1: partial outputs [split][n][k][y][x], summed by conv_ksplit_reduce_kernel
     long long out_elems;
@@ -143,11 +147,15 @@ __device__ __forceinline__ TileCtx decode_tile(const TcParams &p, int tile, int 
         c.step_begin = total * c.split / p.ksplit;
         c.nsteps = total * (c.split + 1) / p.ksplit - c.step_begin;
     } else if (MODE == MODE_WGRAD) {
-        c.split = tile % p.splits;
-        int rest = tile / p.splits;
-        c.ct = rest % p.ct_n; rest /= p.ct_n;
-        c.tap = rest % p.taps_n;
-        c.ft = (rest / p.taps_n) * p.wg_ctas + rank;     // CTA pair: the pair owns two neighbouring filter tiles
+        // The tap varies fastest: the CTAs that run side by side work on the taps of ONE range of output pixels, so the error
+        // chunk they all read and the (shifted) image chunks come from HBM once and from L2 for the other taps.  With the
+        // split fastest instead, every tap streamed both tensors from HBM again (9 or 16 times the traffic, which is what
+        // bounds this kernel on layers with few channels).
+        c.tap = tile % p.taps_n;
+        int rest = tile / p.taps_n;
+        c.split = rest % p.splits; rest /= p.splits;
+        c.ct = rest % p.ct_n;
+        c.ft = (rest / p.ct_n) * p.wg_ctas + rank;       // CTA pair: the pair owns two neighbouring filter tiles
         long long b = p.chunks_total * c.split / p.splits;
         long long e = p.chunks_total * (c.split + 1) / p.splits;
         c.chunk_begin = b;
@@ -182,7 +190,9 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
     }
 }
 
-template <int MODE, bool X3, int CTAS>
+// ACT: the CONV epilogue also applies a neuron function and / or writes the value before it (instantiated separately so that
+// the plain epilogue keeps its short store loop).
+template <int MODE, bool X3, int CTAS, bool ACT>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ CUtensorMap mapA_lo,
           const __grid_constant__ CUtensorMap mapB_hi, const __grid_constant__ CUtensorMap mapB_lo,
@@ -448,15 +458,55 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
                 const bool valid = n < p.n_img && yy < pi.ext_y && xx < pi.ext_x;
                 const size_t plane = (size_t)p.OH * p.OW;
                 float *obase = p.ksplit > 1 ? p.kpartial + (size_t)c.split * (size_t)p.out_elems : p.out;
-                const float *bias = p.ksplit > 1 ? nullptr : p.bias;       // split-K: the bias is added by the reduction
-                float *dst = obase + (size_t)n * p.k_out * plane + (size_t)(yy * p.out_stride_y + pi.off_y) * p.OW +
-                             (xx * p.out_stride_x + pi.off_x);
-                for (int c0 = 0; c0 < p.BN; c0 += 16) {
+                const float *bias = p.ksplit > 1 ? nullptr : p.bias;       // split-K: bias and neuron function are applied by the reduction
+                const size_t off = (size_t)n * p.k_out * plane + (size_t)(yy * p.out_stride_y + pi.off_y) * p.OW + (xx * p.out_stride_x + pi.off_x);
+                float *dst = obase + off;
+                float *pre = (!ACT || p.ksplit > 1 || !p.pre_out) ? nullptr : p.pre_out + off;
+                const int func = (!ACT || p.ksplit > 1) ? -1 : p.act_func;
+                for (int c0 = 0; ACT && c0 < p.BN; c0 += 16) {
                     load16(c0);
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
                         const int k = c.nt * p.BN + c0 + j;
-                        if (valid && k < p.k_out) dst[(size_t)k * plane] = bias ? __fadd_rn(v[j], bias[k]) : v[j];
+                        if (valid && k < p.k_out) {
+                            float val = bias ? __fadd_rn(v[j], bias[k]) : v[j];
+                            if (pre) pre[(size_t)k * plane] = val;
+                            if (func >= 0) val = act_apply(val, func, p.act_slope);      // the function layer fused into the epilogue
+                            dst[(size_t)k * plane] = val;
+                        }
+                    }
+                }
+                if (!ACT && !(X3 && p.small_off)) {
+                    // plain epilogue, software-pipelined: the tensor-memory load of the next 16 columns is in flight while
+                    // the current 16 are stored (a load-wait-store sequence per 16 columns left the stores idle half the time)
+                    uint32_t ra[16], rb[16];
+                    auto store16 = [&](const uint32_t *r, int c0) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            const int k = c.nt * p.BN + c0 + j;
+                            const float val = __uint_as_float(r[j]);
+                            if (valid && k < p.k_out) dst[(size_t)k * plane] = bias ? __fadd_rn(val, bias[k]) : val;
+                        }
+                    };
+                    ptx::tmem_ld16_issue(taddr, ra);
+                    for (int c0 = 0; c0 < p.BN; c0 += 32) {
+                        ptx::tmem_ld_wait(ra);
+                        if (c0 + 16 < p.BN) ptx::tmem_ld16_issue(taddr + c0 + 16, rb);
+                        store16(ra, c0);
+                        if (c0 + 16 < p.BN) {
+                            ptx::tmem_ld_wait(rb);
+                            if (c0 + 32 < p.BN) ptx::tmem_ld16_issue(taddr + c0 + 32, ra);
+                            store16(rb, c0 + 16);
+                        }
+                    }
+                } else if (!ACT) {
+                    for (int c0 = 0; c0 < p.BN; c0 += 16) {
+                        load16(c0);
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            const int k = c.nt * p.BN + c0 + j;
+                            if (valid && k < p.k_out) dst[(size_t)k * plane] = bias ? __fadd_rn(v[j], bias[k]) : v[j];
+                        }
                     }
                 }
             } else if (MODE == MODE_WGRAD) {
@@ -511,8 +561,10 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
 
 // NCHW fp32 -> phase-split NHWC, TF32-rounded high part and (optionally) TF32-rounded remainder:
 //   dst[ph][n][h/sy][w/sx][c],  ph = (h % sy) * sx + (w % sx),  channel pitch Cp (multiple of 4).
+// func >= 0: the neuron function is applied to every element on the way (the function layer in front of a convolution
+// layer fused into the layer's pack); act_out, if given, also receives the activated tensor in the source layout.
 __global__ void pack_act_kernel(const float *__restrict__ src, float *__restrict__ hi, float *__restrict__ lo,
-                                int N, int C, int H, int W, int Cp, int sy, int sx, int Hs, int Ws)
+                                int N, int C, int H, int W, int Cp, int sy, int sx, int Hs, int Ws, int func, double slope, float *__restrict__ act_out)
 {
     __shared__ float tile[32][33];
     const int n = blockIdx.z, h = blockIdx.y, w0 = blockIdx.x * 32;
@@ -523,7 +575,13 @@ __global__ void pack_act_kernel(const float *__restrict__ src, float *__restrict
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             int c = c0 + ty + 8 * i, w = w0 + tx;
-            tile[ty + 8 * i][tx] = (row_ok && c < C && w < W) ? src[(((size_t)n * C + c) * H + h) * W + w] : 0.f;
+            float v = 0.f;
+            if (row_ok && c < C && w < W) {
+                const size_t at = (((size_t)n * C + c) * H + h) * W + w;
+                v = src[at];
+                if (func >= 0) { v = act_apply(v, func, slope); if (act_out) act_out[at] = v; }
+            }
+            tile[ty + 8 * i][tx] = v;
         }
         __syncthreads();
         const int c = c0 + tx;
@@ -550,7 +608,8 @@ __global__ void pack_act_kernel(const float *__restrict__ src, float *__restrict
 // thread.  Needs W % 4 == 0 and a 16-byte aligned source.
 __global__ void __launch_bounds__(256)
 pack_act_vec_kernel(const float *__restrict__ src, float *__restrict__ hi, float *__restrict__ lo,
-                    int N, int C, int H, int W, int Cp, int sy, int sx, int Hs, int Ws, int rows_per_block, float *__restrict__ rowsum)
+                    int N, int C, int H, int W, int Cp, int sy, int sx, int Hs, int Ws, int rows_per_block, float *__restrict__ rowsum,
+                    int func, double slope, float *__restrict__ act_out)
 {
     __shared__ float tile[32][33];
     const int n = blockIdx.z, h0 = blockIdx.y * rows_per_block, w0 = blockIdx.x * 32;
@@ -566,7 +625,14 @@ pack_act_vec_kernel(const float *__restrict__ src, float *__restrict__ hi, float
         float acc = 0.f;                            // this thread's share of the plane sum of channel c (bias gradient)
         for (int h = h0; h < h1; h++) {
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (h < H && c < C && wl < W) v = *reinterpret_cast<const float4 *>(src + (((size_t)n * C + c) * H + h) * W + wl);
+            if (h < H && c < C && wl < W) {
+                const size_t at = (((size_t)n * C + c) * H + h) * W + wl;
+                v = *reinterpret_cast<const float4 *>(src + at);
+                if (func >= 0) {
+                    v.x = act_apply(v.x, func, slope); v.y = act_apply(v.y, func, slope); v.z = act_apply(v.z, func, slope); v.w = act_apply(v.w, func, slope);
+                    if (act_out) *reinterpret_cast<float4 *>(act_out + at) = v;
+                }
+            }
             acc += (v.x + v.y) + (v.z + v.w);
             tile[lc][4 * lq + 0] = v.x; tile[lc][4 * lq + 1] = v.y; tile[lc][4 * lq + 2] = v.z; tile[lc][4 * lq + 3] = v.w;
             __syncthreads();
@@ -645,7 +711,8 @@ __global__ void wgrad_reduce_kernel(float *__restrict__ dkernel, const float *__
 
 // out[i] = sum over the K splits (in increasing order) of partial[split][i] (+ bias of the element's channel)
 __global__ void conv_ksplit_reduce_kernel(float *__restrict__ out, const float *__restrict__ partial, int splits, size_t total,
-                                          const float *__restrict__ bias, int k_out, size_t plane)
+                                          const float *__restrict__ bias, int k_out, size_t plane, int func = -1, double slope = 0.0,
+                                          float *__restrict__ pre = nullptr)
 {
     const size_t total4 = total / 4;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (size_t)gridDim.x * blockDim.x) {
@@ -659,6 +726,8 @@ __global__ void conv_ksplit_reduce_kernel(float *__restrict__ out, const float *
             s.x += bias[(e / plane) % k_out]; s.y += bias[((e + 1) / plane) % k_out];
             s.z += bias[((e + 2) / plane) % k_out]; s.w += bias[((e + 3) / plane) % k_out];
         }
+        if (pre) reinterpret_cast<float4 *>(pre)[i] = s;
+        if (func >= 0) { s.x = act_apply(s.x, func, slope); s.y = act_apply(s.y, func, slope); s.z = act_apply(s.z, func, slope); s.w = act_apply(s.w, func, slope); }
         reinterpret_cast<float4 *>(out)[i] = s;
     }
 }
@@ -860,10 +929,11 @@ static bool deep_stages_enabled()
     return v == 1;
 }
 
-template <int MODE, bool X3, int CTAS>
+template <int MODE, bool X3, int CTAS, bool ACT = false>
 static int launch_one(const CUtensorMap maps[4], const TcParams &p, int grid, size_t smem, cudaStream_t s)
 {
-    B200_CUDA(cudaFuncSetAttribute(tc_kernel<MODE, X3, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (MODE == MODE_CONV && !ACT && p.ksplit <= 1 && (p.act_func >= 0 || p.pre_out)) return launch_one<MODE, X3, CTAS, MODE == MODE_CONV>(maps, p, grid, smem, s);
+    B200_CUDA(cudaFuncSetAttribute(tc_kernel<MODE, X3, CTAS, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(grid);
@@ -877,7 +947,7 @@ static int launch_one(const CUtensorMap maps[4], const TcParams &p, int grid, si
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = CTAS > 1 ? 1 : 0;
-    B200_CUDA(cudaLaunchKernelEx(&cfg, tc_kernel<MODE, X3, CTAS>, maps[0], maps[X3 ? 1 : 0], maps[2], maps[X3 ? 3 : 2], p));
+    B200_CUDA(cudaLaunchKernelEx(&cfg, tc_kernel<MODE, X3, CTAS, ACT>, maps[0], maps[X3 ? 1 : 0], maps[2], maps[X3 ? 3 : 2], p));
     return B200_OK;
 }
 
@@ -986,8 +1056,11 @@ static void set_mnmajor(TcParams &p, bool a_side, int extent)
 // rowsum (optional, act_pack_rowsum_elems floats): receives per-block partial plane sums when the vector kernel runs;
 // *rowsum_runs tells the caller how many partial sums each (image, channel) got (0: not produced).
 static int pack_act(const float *src, float *hi, float *lo, int N, int C, int H, int W, int Cp, int sy, int sx, int Hs, int Ws,
-                    cudaStream_t s, float *rowsum = nullptr, int *rowsum_runs = nullptr)
+                    cudaStream_t s, float *rowsum = nullptr, int *rowsum_runs = nullptr, const PackFunction *pf = nullptr)
 {
+    const int func = pf ? pf->func : -1;
+    const double slope = pf ? pf->slope : 0.0;
+    float *act_out = pf ? pf->act_out : nullptr;
     // An unsplit pack of a narrow image (a row shorter than the kernel's 32-pixel tile) is the same re-layout of a single row
     // of H*W pixels: [n][y][x][c] and [n][c][y][x] are both linear in y*W + x.  Narrow rows would leave most of a tile idle.
     if (sy == 1 && sx == 1 && W < 32 && H > 1 && W % 4 == 0) {
@@ -996,15 +1069,15 @@ static int pack_act(const float *src, float *hi, float *lo, int N, int C, int H,
     dim3 grid(ceil_div(Ws * sx, 32), Hs * sy, N), block(32, 8);
     if (grid.y > 65535 || grid.z > 65535) return TC_UNSUPPORTED;
     if (rowsum_runs) *rowsum_runs = 0;
-    if (W % 4 == 0 && ((uintptr_t)src & 15) == 0) {
+    if (W % 4 == 0 && ((uintptr_t)src & 15) == 0 && ((uintptr_t)act_out & 15) == 0) {
         // with the bias-gradient sums fused in, a block walks 8 rows so that it leaves one partial sum per 8 rows and channel
         int rows_per_block = rowsum ? 8 : 1;
         while (rows_per_block > 1 && (long long)grid.x * ceil_div((int)grid.y, rows_per_block) * N < 8LL * sm_count()) rows_per_block /= 2;
         dim3 vgrid(grid.x, ceil_div((int)grid.y, rows_per_block), N);
-        pack_act_vec_kernel<<<vgrid, 256, 0, s>>>(src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws, rows_per_block, rowsum);
+        pack_act_vec_kernel<<<vgrid, 256, 0, s>>>(src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws, rows_per_block, rowsum, func, slope, act_out);
         if (rowsum && rowsum_runs) *rowsum_runs = (int)(vgrid.x * vgrid.y);
     } else
-        pack_act_kernel<<<grid, block, 0, s>>>(src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws);
+        pack_act_kernel<<<grid, block, 0, s>>>(src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws, func, slope, act_out);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -1126,9 +1199,9 @@ ActPack act_pack_shape(int n, int c, int h, int w, int sy, int sx)
     return pk;
 }
 
-int act_pack_fill(const ActPack &pk, const float *src, cudaStream_t s)
+int act_pack_fill(const ActPack &pk, const float *src, cudaStream_t s, const PackFunction *pf)
 {
-    return pack_act(src, pk.hi, pk.lo, pk.n, pk.c, pk.h, pk.w, pk.cp, pk.sy, pk.sx, pk.hs, pk.ws, s);
+    return pack_act(src, pk.hi, pk.lo, pk.n, pk.c, pk.h, pk.w, pk.cp, pk.sy, pk.sx, pk.hs, pk.ws, s, nullptr, nullptr, pf);
 }
 
 size_t weight_pack_elems(const b200_conv_geom &g, bool backward)
@@ -1160,7 +1233,7 @@ size_t conv_gemm_partial_elems(bool backward, const b200_conv_geom &g, int batch
 }
 
 int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack &act, const float *w_hi, const float *w_lo,
-              const float *bias, bool x3, cudaStream_t s, float *kpartial, size_t kpartial_elems)
+              const float *bias, bool x3, cudaStream_t s, float *kpartial, size_t kpartial_elems, const EpilogueFunction *ef)
 {
     if (!geom_supported(g)) return TC_UNSUPPORTED;
     const int batch = act.n;
@@ -1178,6 +1251,9 @@ int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack 
     p.c_chunks = ceil_div(act_c, 32);
     p.n_img = batch; p.k_out = k_out; p.OH = OH; p.OW = OW; p.out_stride_y = osy; p.out_stride_x = osx;
     p.out = out; p.bias = bias;
+    p.act_func = ef ? ef->func : -1;
+    p.act_slope = ef ? ef->slope : 0.0;
+    p.pre_out = ef ? ef->pre_out : nullptr;
 
     // output phases and their tap lists
     const int pad_y = backward ? g.kernel_y - 1 - g.padding_y : g.padding_y;
@@ -1221,6 +1297,7 @@ int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack 
             mpairs += (pi.tiles_x * pi.tiles_y * pi.tiles_i + 1) / 2;
             p.phase[nph++] = pi;
         }
+    if (any_empty && p.act_func >= 0) return TC_UNSUPPORTED;      // outputs that no tap reaches would miss f(0): the caller applies the function separately
     if (any_empty) B200_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * (size_t)batch * k_out * OH * OW, s));
     if (nph == 0) return B200_OK;
     p.phases = nph;
@@ -1243,7 +1320,7 @@ int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack 
             for (int c = 2; c >= 1; c--) {
                 if (c == 2 && !(cta_pairs_enabled() && bn >= 32)) continue;
                 for (int ks = 1; ks <= 8; ks *= 2) {
-                    if (ks > 1 && (!split_enabled || !kpartial || any_empty || out_elems % 4 || ((uintptr_t)out & 15) || (size_t)ks * out_elems > kpartial_elems ||
+                    if (ks > 1 && (!split_enabled || !kpartial || any_empty || out_elems % 4 || ((uintptr_t)out & 15) || ((uintptr_t)p.pre_out & 15) || (size_t)ks * out_elems > kpartial_elems ||
                                    steps_min < 4 * ks))
                         break;
                     const long long items = (long long)(c == 2 ? mpairs : mtiles) * ceil_div(k_out, bn) * ks;
@@ -1292,7 +1369,8 @@ int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack 
         const size_t total = (size_t)p.out_elems;
         size_t blocks = (total / 4 + 255) / 256;
         if (blocks > (size_t)sm_count() * 16) blocks = (size_t)sm_count() * 16;
-        conv_ksplit_reduce_kernel<<<(unsigned)blocks, 256, 0, s>>>(out, kpartial, p.ksplit, total, bias, k_out, (size_t)OH * OW);
+        conv_ksplit_reduce_kernel<<<(unsigned)blocks, 256, 0, s>>>(out, kpartial, p.ksplit, total, bias, k_out, (size_t)OH * OW, p.act_func, p.act_slope,
+                                                                   p.pre_out);
         B200_LAUNCH_CHECK();
     }
     return B200_OK;
@@ -1317,7 +1395,7 @@ static int run_conv(bool backward, const b200_conv_geom &g, float *out, const fl
     if (!pk.hi || !w_hi || (x3 && (!pk.lo || !w_lo))) return fail(B200_E_NOMEM, "scratch arena exhausted");
     if ((r = act_pack_fill(pk, act, s))) return r;
     if ((r = weight_pack_fill(g, backward, kernel, w_hi, w_lo, s))) return r;
-    return conv_gemm(backward, g, out, pk, w_hi, w_lo, bias, x3, s);
+    return conv_gemm(backward, g, out, pk, w_hi, w_lo, bias, x3, s, nullptr, 0, nullptr);
 }
 
 int tc_conv_forward(const b200_conv_geom &g, float *out, const float *image, const float *kernel, const float *bias,

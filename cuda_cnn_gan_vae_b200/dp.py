@@ -73,7 +73,17 @@ class PeerBuffer:
         _check(lib.b200_comm_connect(self.comm, blob))
         self._span = _DeviceSpan(lib.b200_comm_buffer(self.comm), self.floats)
         self.buffer = torch.as_tensor(self._span, device="cuda")
+        self.taken = 0
         dist.barrier()
+
+    def take(self, floats):
+        """The next `floats` floats of the buffer (a multiple of 4, so every span starts on a 16-byte boundary) as
+        (offset, tensor): several networks place their arenas in one buffer and share one exchange launch."""
+        floats = (floats + 3) // 4 * 4
+        if self.taken + floats > self.floats:
+            raise ValueError("peer buffer exhausted: %d + %d > %d floats" % (self.taken, floats, self.floats))
+        offset, self.taken = self.taken, self.taken + floats
+        return offset, self.buffer[offset:offset + floats]
 
     def close(self):
         if self.comm:

@@ -11,6 +11,7 @@ net live in four contiguous arenas (weights / gradients / m / v) with identical 
 a data-parallel step all-reduces, and one b200_adam call updates every parameter of the net.
 """
 import ctypes as C
+import os
 
 import numpy as np
 import torch
@@ -70,10 +71,29 @@ class NetLayerConvolution(_Layer):
         self.w["kernel"].copy_(torch.from_numpy((rng.standard_normal(self.kernel_shape) * np.sqrt(2.0 / fan_in)).astype(np.float32)))
         self.w["bias"].zero_()
 
+    # Function layers folded into this layer's Forward (set by Net when it finds the pairs; netlayer/cnetlayerfunction.cu.h:202):
+    # `before` is the function layer in front (its function is applied while this layer packs its input), `after` the one
+    # behind (applied in the epilogue of the convolution kernel; this layer's H still receives the value before the function).
+    before = after = None
+
     def Forward(self, x):
-        self.x = x
-        self.ctx.forward(self.H, x, self.w["kernel"], None if self.transposed else self.w["bias"])
-        return self.H
+        """x: the layer input, or the INPUT of the function layer in front when that layer is folded in."""
+        bias = None if self.transposed else self.w["bias"]
+        if self.before is None and self.after is None:
+            self.x = x
+            self.ctx.forward(self.H, x, self.w["kernel"], bias)
+            return self.H
+        b, a = self.before, self.after
+        # what TrainingBackward hands to the library as the layer input: f(x) where it exists as a tensor
+        self.x = (b.H if b.materialise else x) if b is not None else x
+        self.ctx.forward_fused(a.H if a is not None else self.H, x, self.w["kernel"], bias,
+                               input_func=b.func if b is not None else None, input_slope=b.slope if b is not None else 0.1,
+                               input_act_out=b.H if (b is not None and b.materialise) else None,
+                               output_func=a.func if a is not None else None, output_slope=a.slope if a is not None else 0.1,
+                               output_pre=self.H if a is not None else None)
+        if a is not None:
+            a.x = self.H                    # the function layer's input, for its derivative on the way back
+        return self.H                       # the function layer behind, if folded, hands its H on from its own Forward
 
     def TrainingBackward(self, delta, create_delta_weight=True, need_prev=True):
         self.ctx.backward(self.prev_error if need_prev else None,
@@ -131,6 +151,12 @@ class NetLayerFunction(_Layer):
     """netlayer/cnetlayerfunction.cu.h: Forward applies the neuron function; SetOutputError :347-358 forms
     delta = f'(layer input) * error, which TrainingBackward hands to the previous layer."""
 
+    # folded = "into_next": the convolution layer behind applies the function while it packs its input (Forward here only
+    # remembers its input; H is written by that layer when `materialise` is set); folded = "into_prev": the convolution layer
+    # in front applies it in its epilogue and writes H.  Net sets these; a stand-alone layer has neither.
+    folded = None
+    materialise = True
+
     def __init__(self, in_shape, batch, func, leaky_slope=0.1):
         self.in_shape = self.out_shape = tuple(in_shape)
         self.batch, self.func, self.slope = batch, func, leaky_slope
@@ -138,7 +164,11 @@ class NetLayerFunction(_Layer):
         self.delta = torch.empty((batch,) + self.in_shape, device="cuda")
 
     def Forward(self, x):
+        if self.folded == "into_prev":
+            return self.H                   # written by the convolution layer in front; self.x was set by Net
         self.x = x
+        if self.folded == "into_next":
+            return x                        # the convolution layer behind applies the function to x
         ops.CTensorApplyFunc.Apply(self.H, x, self.func, self.slope)
         return self.H
 
@@ -310,10 +340,12 @@ class Net:
     TrainingResetDeltaWeight, Forward of all layers, SetOutputError on the last, TrainingBackward in reverse order,
     TrainingUpdateWeight) on four arenas: weights, gradients, Adam m and v."""
 
-    def __init__(self, in_shape, batch, spec, seed=0, peer=False, channel=0):
+    def __init__(self, in_shape, batch, spec, seed=0, peer=False, channel=0, fold=True):
         """spec: list of (class, kwargs).  The input of layer i is the output of layer i-1.
-        peer: with several ranks, the weight and gradient arenas are placed in a PeerBuffer (memory every rank maps), and
-        TrainingUpdateWeight(fused=True) runs the library's reduce-scatter + Adam + all-gather kernel on `channel`."""
+        peer: True, or a PeerBuffer shared with other nets.  With several ranks, the weight and gradient arenas are placed in
+        the PeerBuffer (memory every rank maps), and
+        TrainingUpdateWeight(fused=True) runs the library's reduce-scatter + Adam + all-gather kernel on `channel`.
+        fold: function layers next to a convolution layer are folded into that layer's Forward (see fold_functions)."""
         self.batch, self.in_shape = batch, tuple(in_shape)
         self.layers, shape = [], tuple(in_shape)
         for cls, kw in spec:
@@ -324,6 +356,7 @@ class Net:
             self.layers.append(layer)
             shape = layer.out_shape
         self.out_shape = shape
+        self.fold_functions(fold)
         shapes = {}
         for i, layer in enumerate(self.layers):
             for name, s in layer.param_shapes().items():
@@ -332,10 +365,11 @@ class Net:
         import torch.distributed as dist
         if peer and dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
             _, total = arena_layout(shapes)
-            self.peer = PeerBuffer(2 * total)
-            self.weight_offset, self.grad_offset = 0, total
-            self.weights = GradArena(shapes, "cuda", self.peer.buffer[:total])
-            self.grads = GradArena(shapes, "cuda", self.peer.buffer[total:2 * total])
+            self.peer = peer if isinstance(peer, PeerBuffer) else PeerBuffer(2 * total)
+            self.weight_offset, w_span = self.peer.take(total)
+            self.grad_offset, g_span = self.peer.take(total)
+            self.weights = GradArena(shapes, "cuda", w_span[:total])
+            self.grads = GradArena(shapes, "cuda", g_span[:total])
             self.m, self.v = (GradArena(shapes, "cuda") for _ in range(2))
         else:
             self.weights, self.grads, self.m, self.v = (GradArena(shapes, "cuda") for _ in range(4))
@@ -346,6 +380,33 @@ class Net:
             layer.init(rng)
 
         self.ema, self.ema_k, self.use_ema = None, 0.999, False
+
+    def fold_functions(self, enable=True, materialise=True):
+        """Folds every function layer that directly follows a convolution layer into that layer's epilogue, and every other
+        function layer that directly precedes one into that layer's input pack (b200_conv_layer_forward_fused): same values, one
+        launch and one pass over the tensor less per pair (in B200_FP32 mode the library runs the same sequence as separate
+        launches).  materialise=False: a function layer folded into the layer BEHIND it no
+        longer writes its own output tensor (nothing else reads it in a chain)."""
+        conv = (NetLayerConvolution, NetLayerBackConvolution)
+        for layer in self.layers:
+            if isinstance(layer, conv):
+                layer.before = layer.after = None
+            if isinstance(layer, NetLayerFunction):
+                layer.folded, layer.materialise = None, True
+        if not enable or os.environ.get("B200CONV_FOLD") == "0":          # tuning aid: B200CONV_FOLD=0 keeps every layer separate
+            return
+        for i, layer in enumerate(self.layers):
+            if not isinstance(layer, NetLayerFunction):
+                continue
+            prev_l = self.layers[i - 1] if i > 0 else None
+            next_l = self.layers[i + 1] if i + 1 < len(self.layers) else None
+            # into the epilogue only where the contraction is long enough to hide the second output stream behind the tensor-core
+            # work of the next tile (measured on the VAE encoder: with 27..576-term sums the kernel is bound by its epilogue's
+            # stores and the folded layer was slower than the two launches)
+            if isinstance(prev_l, conv) and prev_l.out_shape == layer.in_shape and prev_l.kernel_shape[3] >= 1024:
+                layer.folded, prev_l.after = "into_prev", layer
+            elif isinstance(next_l, conv) and next_l.in_shape == layer.out_shape:
+                layer.folded, layer.materialise, next_l.before = "into_next", materialise, layer
 
     @property
     def parameter_count(self):
@@ -400,6 +461,23 @@ class Net:
         _check(load().b200_allreduce_adam(self.peer.comm, self.grad_offset, self.weight_offset, _ptr(self.m.buffer), _ptr(self.v.buffer), n,
                                           int(self.batch * batch_scale), speed, beta1, beta2, epsilon, 0.0 if iteration is None else iteration,
                                           _ptr(corrections), self.channel, _stream()))
+
+    @staticmethod
+    def TrainingUpdateWeightFusedTogether(nets, speed, iteration, batch_scale=1, beta1=0.9, beta2=0.999, epsilon=1e-8, corrections=None):
+        """The fused data-parallel update of several nets that share one PeerBuffer in ONE launch (b200_allreduce_adam_multi):
+        one pair of device-side barriers for all of them."""
+        from .lib import ExchangeSegment
+        peer = nets[0].peer
+        if peer is None or any(net.peer is not peer for net in nets) or len({net.batch for net in nets}) != 1:
+            for net in nets:
+                net.TrainingUpdateWeightFused(speed, iteration, batch_scale, beta1, beta2, epsilon, corrections)
+            return
+        segs = (ExchangeSegment * len(nets))()
+        for seg, net in zip(segs, nets):
+            seg.grad_offset, seg.weight_offset, seg.n = net.grad_offset, net.weight_offset, net.weights.buffer.numel()
+            seg.m, seg.v = net.m.buffer.data_ptr(), net.v.buffer.data_ptr()
+        _check(load().b200_allreduce_adam_multi(peer.comm, len(nets), segs, int(nets[0].batch * batch_scale), speed, beta1, beta2, epsilon,
+                                                0.0 if iteration is None else iteration, _ptr(corrections), nets[0].channel, _stream()))
 
     def peer_all_reduce(self):
         """Sum of the gradient arenas over the ranks by the library's own exchange kernel (b200_allreduce), in place."""

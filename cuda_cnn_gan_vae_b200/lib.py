@@ -13,6 +13,17 @@ class ConvGeom(C.Structure):
 
 
 _fp, _vp, _i, _sz, _f, _d = C.c_void_p, C.c_void_p, C.c_int, C.c_size_t, C.c_float, C.c_double
+
+
+class ExchangeSegment(C.Structure):
+    """struct b200_exchange_segment."""
+    _fields_ = [("grad_offset", C.c_size_t), ("weight_offset", C.c_size_t), ("n", C.c_size_t), ("m", C.c_void_p), ("v", C.c_void_p)]
+
+
+class ConvFusion(C.Structure):
+    """struct b200_conv_fusion."""
+    _fields_ = [("input_func", C.c_int), ("input_slope", C.c_double), ("input_act_out", C.c_void_p), ("output_func", C.c_int),
+                ("output_slope", C.c_double), ("output_pre", C.c_void_p)]
 _G = C.POINTER(ConvGeom)
 
 # name -> (restype, argtypes); must list every function declared in include/b200conv.h
@@ -36,6 +47,7 @@ SIGNATURES = {
     "b200_conv_layer_create": (_i, [C.POINTER(C.c_void_p), _G, _i, _i]),
     "b200_conv_layer_destroy": (_i, [_vp]),
     "b200_conv_layer_forward": (_i, [_vp, _fp, _fp, _fp, _fp, _vp]),
+    "b200_conv_layer_forward_fused": (_i, [_vp, _fp, _fp, _fp, _fp, _vp, _vp]),
     "b200_conv_layer_backward": (_i, [_vp, _fp, _fp, _fp, _i, _fp, _fp, _fp, _vp]),
     "b200_conv_wgrad_batch_static": (_i, [_G, _fp, _fp, _i, _fp, _fp, _i, _vp]),
     "b200_static_scratch_bytes": (_sz, []),
@@ -80,6 +92,7 @@ SIGNATURES = {
     "b200_comm_slice": (_i, [_sz, _i, _i, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     "b200_allreduce": (_i, [_vp, _sz, _sz, _i, _vp]),
     "b200_allreduce_adam": (_i, [_vp, _sz, _sz, _fp, _fp, _sz, C.c_uint32, _d, _d, _d, _d, _d, _vp, _i, _vp]),
+    "b200_allreduce_adam_multi": (_i, [_vp, _i, _vp, C.c_uint32, _d, _d, _d, _d, _d, _vp, _i, _vp]),
 }
 
 _lib = None

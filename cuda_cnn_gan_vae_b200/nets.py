@@ -53,7 +53,7 @@ class DCGANStep:
     respect to the logit, formed as in cuda/netmodel/cmodel_basicgan.cu.h:352-376 but on the device)."""
 
     def __init__(self, batch, world=1, widths_g=(256, 128, 64, 3), widths_d=(64, 128, 256, 512), base=512, noise=100, leaky_slope=0.2,
-                 use_graph=True, fused=False, update="fused", overlap=False):
+                 use_graph=True, fused=False, update="fused", overlap=False, lean=True):
         """update (several ranks): "fused" -- the library's reduce-scatter + Adam + all-gather kernel over NVLink peer memory,
         one launch per net on the main stream; "nccl" -- an NCCL all-reduce of each gradient arena on a side stream followed
         by the Adam launch.  overlap: the discriminator's exchange on a side stream beside the generator's backward pass
@@ -62,8 +62,14 @@ class DCGANStep:
         self.batch, self.world, self.overlap = batch, world, overlap
         self.update = update if world > 1 else "local"
         peer = self.update == "fused"
+        if peer:
+            from .dp import PeerBuffer
+            peer = PeerBuffer(32 << 20)         # one buffer for both nets (weights + gradients of ~6.4 M parameters, with room to spare)
         self.G = dcgan_generator(batch, noise, base, widths_g, leaky_slope, fused=fused, peer=peer, channel=1)
         self.D = dcgan_discriminator(batch, self.G.out_shape, widths_d, leaky_slope, fused=fused, peer=peer, channel=0)
+        if lean:    # function layers folded into the convolution behind them do not write an output tensor nobody reads
+            self.G.fold_functions(True, materialise=False)
+            self.D.fold_functions(True, materialise=False)
         self.G.broadcast_weights()
         self.D.broadcast_weights()
         self.error = torch.empty((batch, 1, 1, 1), device="cuda")
@@ -94,12 +100,14 @@ class DCGANStep:
                 self.side_d.wait_stream(main)
                 with torch.cuda.stream(self.side_d):
                     self.D.TrainingUpdateWeightFused(speed, None, batch_scale=self.world, corrections=self.corr.device)
-            else:
-                self.D.TrainingUpdateWeightFused(speed, None, batch_scale=self.world, corrections=self.corr.device)
-            self.G.TrainingBackward(d_image, True)
-            self.G.TrainingUpdateWeightFused(speed, None, batch_scale=self.world, corrections=self.corr.device)
-            if self.overlap:
+                self.G.TrainingBackward(d_image, True)
+                self.G.TrainingUpdateWeightFused(speed, None, batch_scale=self.world, corrections=self.corr.device)
                 main.wait_stream(self.side_d)
+                return out
+            # default: both nets in one exchange launch after the generator's backward pass (one pair of device-side barriers
+            # per step instead of two)
+            self.G.TrainingBackward(d_image, True)
+            Net.TrainingUpdateWeightFusedTogether([self.D, self.G], speed, None, batch_scale=self.world, corrections=self.corr.device)
             return out
         if self.world > 1:
             self.side_d.wait_stream(main)

@@ -447,6 +447,18 @@ class ConvLayer:
         _check(load().b200_conv_layer_forward(self._h, _ptr(output), _ptr(inp), _ptr(kernel),
                                               _ptr(bias) if bias is not None else None, _stream()))
 
+    def forward_fused(self, output, inp, kernel, bias=None, input_func=None, input_slope=0.1, input_act_out=None, output_func=None,
+                      output_slope=0.1, output_pre=None):
+        """b200_conv_layer_forward_fused: input_func is the function layer in front of this layer (applied while the input is
+        packed; input_act_out optionally receives f(inp)), output_func the one behind it (applied in the epilogue; output_pre
+        optionally receives the value before the function)."""
+        from .lib import ConvFusion
+        _t(output), _t(inp), _t(kernel)
+        f = ConvFusion(ACT[input_func] if input_func else -1, input_slope, input_act_out.data_ptr() if input_act_out is not None else None,
+                       ACT[output_func] if output_func else -1, output_slope, output_pre.data_ptr() if output_pre is not None else None)
+        _check(load().b200_conv_layer_forward_fused(self._h, _ptr(output), _ptr(inp), _ptr(kernel), _ptr(bias) if bias is not None else None,
+                                                    C.byref(f), _stream()))
+
     def backward(self, input_delta, dkernel, dbias, output_delta, inp, kernel, accumulate=True):
         _t(output_delta), _t(inp), _t(kernel)
         _check(load().b200_conv_layer_backward(self._h, _ptr(input_delta) if input_delta is not None else None,

@@ -157,6 +157,28 @@ int b200_conv_layer_destroy(b200_conv_layer *layer);
  * its bias is ignored, as in the reference's CUDA backend). */
 int b200_conv_layer_forward(b200_conv_layer *layer, float *out, const float *input, const float *kernel, const float *bias,
                             void *stream);
+/* Forward with the function layers around the convolution layer folded in (CNetLayerFunction::Forward,
+ * netlayer/cnetlayerfunction.cu.h:202: H = f(input of the function layer)):
+ *   input_func  >= 0: the layer's input is f_in(input) -- the function layer IN FRONT of this layer; f_in is applied while
+ *                     the input is re-laid out for the tensor cores, so the activated tensor need not exist.  input_act_out,
+ *                     if not NULL, also receives f_in(input) (same shape as input).
+ *   output_func >= 0: out = f_out(conv + bias) -- the function layer BEHIND this layer, applied in the epilogue of the
+ *                     convolution kernel.  output_pre, if not NULL, receives conv + bias (what that function layer keeps
+ *                     for its derivative in SetOutputError, :347-358).
+ * -1 switches a side off; both off (or fusion == NULL) is b200_conv_layer_forward.  The results are bit-identical to the
+ * separate calls b200_activation -> b200_conv_layer_forward -> b200_activation in the same precision mode.  A later
+ * b200_conv_layer_backward must be given, as `input`, f_in(input) if it has to re-pack (it does not when it follows this
+ * call in the same precision mode on a tensor-core path; pass input_act_out to be safe in B200_FP32 mode). */
+typedef struct b200_conv_fusion {
+    int input_func;
+    double input_slope;
+    float *input_act_out;
+    int output_func;
+    double output_slope;
+    float *output_pre;
+} b200_conv_fusion;
+int b200_conv_layer_forward_fused(b200_conv_layer *layer, float *out, const float *input, const float *kernel, const float *bias,
+                                  const b200_conv_fusion *fusion, void *stream);
 /* input_delta (may be NULL) = error of the layer input; dkernel / dbias (may be NULL) (+)= batch-summed
  * gradients (dbias of a transposed layer is cleared, as the reference does).  `input` must hold what the
  * forward call saw: it is only read when the kept pack cannot be used (no forward call yet, precision
@@ -354,6 +376,16 @@ int b200_allreduce(b200_comm *comm, size_t offset, size_t n, int channel, void *
 int b200_allreduce_adam(b200_comm *comm, size_t grad_offset, size_t weight_offset, float *m, float *v, size_t n, uint32_t batch_size,
                         double speed, double beta1, double beta2, double epsilon, double iteration, const double *corrections, int channel,
                         void *stream);
+
+/* The same for up to four arenas (the networks of one training step) in ONE launch: one pair of barriers and one launch
+ * instead of one per network.  All arenas lie in the communicator's buffer; Adam's arguments are shared. */
+typedef struct b200_exchange_segment {
+    size_t grad_offset, weight_offset, n;      /* floats, multiples of 4 */
+    float *m, *v;                               /* local Adam moments of the arena (n floats each) */
+} b200_exchange_segment;
+int b200_allreduce_adam_multi(b200_comm *comm, int count, const b200_exchange_segment *segments, uint32_t batch_size, double speed,
+                              double beta1, double beta2, double epsilon, double iteration, const double *corrections, int channel,
+                              void *stream);
 
 #ifdef __cplusplus
 }

@@ -67,6 +67,33 @@ def main():
             b, e = slice_bounds(n, rank, world)
             assert torch.equal(m[b:e], rm[b:e]) and torch.equal(v[b:e], rv[b:e]), ("moments of the own slice", n, it)
             assert torch.equal(grads, mine), "the gradient arena keeps this rank's contents"
+    # ---- two arenas in one launch (b200_allreduce_adam_multi) against two single launches ------------------------------
+    from cuda_cnn_gan_vae_b200.lib import ExchangeSegment
+    na, nb = sizes[2], sizes[3]
+    offs = [0, na, 2 * na, 2 * na + nb]                 # gradients a, weights a, gradients b, weights b (reusing the front of the buffer)
+    init = torch.randn(2 * na + 2 * nb, device="cuda", generator=torch.Generator(device="cuda").manual_seed(11))
+    init[0:na] = torch.randn(na, device="cuda", generator=gen)
+    init[2 * na:2 * na + nb] = torch.randn(nb, device="cuda", generator=gen)
+    results = []
+    for together in (False, True):
+        peer.buffer[:init.numel()].copy_(init)
+        ma, va, mb, vb = (torch.zeros(k, device="cuda") for k in (na, na, nb, nb))
+        dist.barrier()
+        if together:
+            segs = (ExchangeSegment * 2)()
+            segs[0].grad_offset, segs[0].weight_offset, segs[0].n, segs[0].m, segs[0].v = offs[0], offs[1], na, ma.data_ptr(), va.data_ptr()
+            segs[1].grad_offset, segs[1].weight_offset, segs[1].n, segs[1].m, segs[1].v = offs[2], offs[3], nb, mb.data_ptr(), vb.data_ptr()
+            ops._check(lib.b200_allreduce_adam_multi(peer.comm, 2, segs, 16 * world, 1e-3, 0.9, 0.999, 1e-8, 1.0, None, 2, ops._stream()))
+        else:
+            ops._check(lib.b200_allreduce_adam(peer.comm, offs[0], offs[1], ops._ptr(ma), ops._ptr(va), na, 16 * world, 1e-3, 0.9, 0.999, 1e-8, 1.0,
+                                               None, 2, ops._stream()))
+            ops._check(lib.b200_allreduce_adam(peer.comm, offs[2], offs[3], ops._ptr(mb), ops._ptr(vb), nb, 16 * world, 1e-3, 0.9, 0.999, 1e-8, 1.0,
+                                               None, 2, ops._stream()))
+        ops.stream_status()
+        dist.barrier()
+        results.append((peer.buffer[:init.numel()].clone(), ma, va, mb, vb))
+    for a_t, b_t in zip(*results):
+        assert torch.equal(a_t, b_t), "one launch for two arenas differs from two launches"
     # ---- device time of the two exchanges at the sizes of the benchmark (reported, not asserted) ----------------------
     n = sizes[-1]
     g_off, w_off = offset - 2 * n, offset - n

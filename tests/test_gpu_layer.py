@@ -129,3 +129,53 @@ def test_split_backward_call_reuses_the_packed_error(ops):
     ops.stream_status()
     assert torch.allclose(dx2, 2 * dx1, rtol=1e-4, atol=1e-5)
     layer.close()
+
+
+FUSED_CASES = [(4, 64, 16, 16, 96, 3, 1, 1, False), (6, 128, 8, 8, 256, 4, 2, 1, False), (5, 512, 4, 4, 100, 3, 1, 1, False),      # plain, strided, split-K
+               (4, 3, 64, 64, 64, 4, 2, 1, False), (3, 40, 12, 12, 24, 3, 1, 1, False),                                           # few-channel input, ragged
+               (4, 64, 16, 16, 128, 4, 2, 1, True), (4, 3, 64, 64, 64, 4, 2, 1, True)]                                            # transposed layers
+
+
+@pytest.mark.parametrize("case", FUSED_CASES)
+@pytest.mark.parametrize("mode", ["x3", "tf32", "fp32"])
+def test_fused_forward_equals_separate_calls(ops, case, mode):
+    """b200_conv_layer_forward_fused (function layer in front applied while packing, function layer behind applied in the
+    epilogue) gives bit for bit what activation -> forward -> activation give, on every path; the backward call that follows
+    gives the same gradients although the activated input was never handed to it as a tensor."""
+    B, C, H, W, K, k, s, p, transposed = case
+    ops.set_precision({"x3": ops.TF32X3, "tf32": ops.TF32, "fp32": ops.FP32}[mode])
+    x, wt, b, d = conv_inputs(sum(case[:8]) + 5, B, C, H, W, K, k, s, p)
+    if transposed:
+        x, d = d, x                                     # layer input: K channels (small), output error: C channels (large)
+    X, WT, BI, D = dev(x), dev(wt), dev(b), dev(d)
+    bias = None if transposed else BI
+    # separate launches
+    ref = ops.ConvLayer(C, H, W, K, k, k, s, s, p, p, B, transposed=transposed)
+    fx = torch.empty_like(X)
+    ops.CTensorApplyFunc.Apply(fx, X, "leaky_relu", 0.2)
+    pre_ref = torch.empty_like(D)
+    ref.forward(pre_ref, fx, WT, bias)
+    out_ref = torch.empty_like(D)
+    ops.CTensorApplyFunc.Apply(out_ref, pre_ref, "tanh")
+    dk_ref, dx_ref = torch.zeros_like(WT), torch.empty_like(X)
+    ref.backward(dx_ref, dk_ref, None, D, fx, WT, accumulate=False)
+    # fused
+    lay = ops.ConvLayer(C, H, W, K, k, k, s, s, p, p, B, transposed=transposed)
+    for act_out in (torch.full_like(X, float("nan")), None):
+        pre, out = torch.full_like(D, float("nan")), torch.full_like(D, float("nan"))
+        lay.forward_fused(out, X, WT, bias, input_func="leaky_relu", input_slope=0.2, input_act_out=act_out, output_func="tanh", output_pre=pre)
+        assert torch.equal(out, out_ref) and torch.equal(pre, pre_ref)
+        if act_out is not None:
+            assert torch.equal(act_out, fx)
+        dk, dx = torch.zeros_like(WT), torch.empty_like(X)
+        lay.backward(dx, dk, None, D, act_out if act_out is not None else X, WT, accumulate=False)     # X: NOT the layer input; must not be read
+        assert torch.equal(dk, dk_ref) and torch.equal(dx, dx_ref)
+    # one side only
+    out = torch.full_like(D, float("nan"))
+    lay.forward_fused(out, fx, WT, bias, output_func="tanh")
+    assert torch.equal(out, out_ref)
+    lay.forward_fused(out, X, WT, bias, input_func="leaky_relu", input_slope=0.2)
+    assert torch.equal(out, pre_ref)
+    ops.stream_status()
+    ref.close()
+    lay.close()

@@ -52,12 +52,13 @@ def run_and_compare(ops, port, net, x, error, tol, strict, need_input_error=Fals
     twin = OracleNet(port, net)
     B = x.shape[0]
     net.TrainingResetDeltaWeight()
-    inputs, cur = [], torch.from_numpy(x).cuda()
+    cur = torch.from_numpy(x).cuda()
     for layer in net.layers:
-        cur = cur.view((B,) + layer.in_shape)
-        inputs.append(cur.cpu().numpy())
-        cur = layer.Forward(cur)
+        cur = layer.Forward(cur.view((B,) + layer.in_shape))
     out = cur.cpu().numpy()
+    # the input of layer i is the output tensor of layer i-1 (a function layer folded into the convolution layer behind it
+    # passes its own input on and lets that layer write its output tensor)
+    inputs = [x] + [layer.H.cpu().numpy().reshape((B,) + nxt.in_shape) for layer, nxt in zip(net.layers[:-1], net.layers[1:])]
     errors_in, errors_out, cur = [None] * len(net.layers), [None] * len(net.layers), torch.from_numpy(error).cuda()
     for i in range(len(net.layers) - 1, -1, -1):
         layer = net.layers[i]
@@ -173,6 +174,36 @@ def test_moving_average_of_the_weights(ops, port):
     net.EnableEMA(False)
     assert net.ema is None
     ops.stream_status()
+
+
+@pytest.mark.parametrize("mode", ["fp32", "x3", "tf32"])
+def test_folded_function_layers_change_nothing(ops, mode):
+    """Nets with their function layers folded into the neighbouring convolution layers (default), folded without writing the
+    function layers' own outputs, and not folded at all give bit-identical outputs, input errors and gradients."""
+    from cuda_cnn_gan_vae_b200.nets import dcgan_discriminator, dcgan_generator, vae_encoder
+    ops.set_precision({"fp32": ops.FP32, "x3": ops.TF32X3, "tf32": ops.TF32}[mode])
+    B = 8
+    rng = np.random.default_rng(12)
+    builders = [(lambda: dcgan_discriminator(B, image=(3, 32, 32), widths=(16, 32, 64)), (B, 3, 32, 32)),
+                (lambda: dcgan_generator(B, noise=20, base=64, widths=(32, 16, 3)), (B, 1, 20, 1)),
+                (lambda: vae_encoder(B, image=(3, 32, 32), widths=(8, 16, 32)), (B, 3, 32, 32))]
+    for build, in_shape in builders:
+        x = torch.from_numpy(rng.uniform(-1, 1, in_shape).astype(np.float32)).cuda()
+        results = []
+        for variant in ("folded", "lean", "separate"):
+            net = build()
+            net.fold_functions(variant != "separate", materialise=(variant != "lean"))
+            folded = sum(1 for l in net.layers if getattr(l, "folded", None))
+            assert (folded > 0) == (variant != "separate")
+            err = torch.from_numpy(np.random.default_rng(13).standard_normal((B,) + net.out_shape).astype(np.float32)).cuda()
+            net.TrainingResetDeltaWeight()
+            out = net.Forward(x).clone()
+            d_in = net.TrainingBackward(err, True, need_input_error=True).clone()
+            ops.stream_status()
+            results.append((out, d_in, net.grads.buffer.clone()))
+        for other in results[1:]:
+            for a, b in zip(results[0], other):
+                assert torch.equal(a, b)
 
 
 def test_dcgan_step_graph_replay_matches_eager(ops):

@@ -5,6 +5,7 @@
 #include "common.cuh"
 #include "kernels.h"
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 

@@ -58,6 +58,8 @@ int act_pack_fill_with_sums(const ActPack &pk, const float *src, float *rowsum, 
 int dbias_from_rowsums(float *dbias, int accumulate, const float *rowsum, int batch, int K, int runs, cudaStream_t s);
 size_t weight_pack_elems(const b200_conv_geom &g, bool backward);
 int weight_pack_fill(const b200_conv_geom &g, bool backward, const float *kernel, float *hi, float *lo, cudaStream_t s);
+// the forward pack (f_*) and the rotated pack of the backward pass (b_*) in one launch
+int weight_pack_fill_both(const b200_conv_geom &g, const float *kernel, float *f_hi, float *f_lo, float *b_hi, float *b_lo, cudaStream_t s);
 // kpartial (optional): scratch of conv_gemm_partial_elems() floats that allows splitting the contraction of small layers
 size_t conv_gemm_partial_elems(bool backward, const b200_conv_geom &g, int batch);
 int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack &act, const float *w_hi, const float *w_lo,

@@ -15,7 +15,7 @@ struct b200_conv_layer {
     int batch;
     int transposed;
     int device;
-    enum { IN_HI, IN_LO, ER_HI, ER_LO, W_HI, W_LO, PARTIAL, DB_TMP, COL_HI, COL_LO, TMP, DK_TMP, KSPLIT, ACT_TMP, NBUF };
+    enum { IN_HI, IN_LO, ER_HI, ER_LO, W_HI, W_LO, W2_HI, W2_LO, PARTIAL, DB_TMP, COL_HI, COL_LO, TMP, DK_TMP, KSPLIT, ACT_TMP, NBUF };
     float *buf[NBUF];
     size_t cap[NBUF];            // bytes
     int in_valid;                // the kept input pack matches the last forward call
@@ -29,6 +29,11 @@ struct b200_conv_layer {
     // is the layer input; 1 only the packed copy holds f(input); 2 f(input) also lies in the ACT_TMP buffer; 3 in the caller's
     // input_act_out.  The backward call reads its `input` argument only when it must re-pack, and then needs f(input).
     int fused_input;
+    // The forward call packs the weights for both passes in one launch: W_HI/W_LO hold the orientation of the pass that
+    // packed, W2_HI/W2_LO the other one, valid for the backward call that follows (same kernel pointer, same precision mode).
+    int w_slot;                  // W_HI or W2_HI: the pack the next contraction reads
+    int w2_valid, w2_precision;
+    const float *w2_kernel;
 };
 
 namespace b200 {
@@ -83,13 +88,35 @@ static int pack_into(b200_conv_layer *l, int hi_slot, ActPack &pk, const float *
     return act_pack_fill_with_sums(pk, src, l->buf[b200_conv_layer::DB_TMP], rowsum_runs, s);
 }
 
-static int pack_weights(b200_conv_layer *l, bool backward, const float *kernel, bool x3, cudaStream_t s)
+// first_of_step: the forward call; it also leaves the pack of the other orientation for the backward call that follows.
+// The weights must not change between a layer's forward call and the backward call after it (no training loop of the
+// reference changes them there: TrainingUpdateWeight runs after all backward passes).
+static int pack_weights(b200_conv_layer *l, bool backward, const float *kernel, bool x3, cudaStream_t s, bool first_of_step = false)
 {
     int r;
+    static const bool both = !(getenv("B200CONV_PACK_BOTH") && getenv("B200CONV_PACK_BOTH")[0] == '0');      // debug switch
+    const int prec = x3 ? B200_TF32X3 : B200_TF32;
+    if (!first_of_step && l->w2_valid && l->w2_kernel == kernel && l->w2_precision == prec) {
+        l->w_slot = b200_conv_layer::W2_HI;          // packed by the forward call
+        return B200_OK;
+    }
+    l->w2_valid = 0;
+    l->w_slot = b200_conv_layer::W_HI;
     const size_t bytes = sizeof(float) * weight_pack_elems(l->g, backward);
     if ((r = ensure(l, b200_conv_layer::W_HI, bytes, s))) return r;
     if (x3 && (r = ensure(l, b200_conv_layer::W_LO, bytes, s))) return r;
-    return weight_pack_fill(l->g, backward, kernel, l->buf[b200_conv_layer::W_HI], x3 ? l->buf[b200_conv_layer::W_LO] : nullptr, s);
+    if (!first_of_step || !both)
+        return weight_pack_fill(l->g, backward, kernel, l->buf[b200_conv_layer::W_HI], x3 ? l->buf[b200_conv_layer::W_LO] : nullptr, s);
+    const size_t other = sizeof(float) * weight_pack_elems(l->g, !backward);
+    if ((r = ensure(l, b200_conv_layer::W2_HI, other, s))) return r;
+    if (x3 && (r = ensure(l, b200_conv_layer::W2_LO, other, s))) return r;
+    float *mine_hi = l->buf[b200_conv_layer::W_HI], *mine_lo = x3 ? l->buf[b200_conv_layer::W_LO] : nullptr;
+    float *other_hi = l->buf[b200_conv_layer::W2_HI], *other_lo = x3 ? l->buf[b200_conv_layer::W2_LO] : nullptr;
+    r = backward ? weight_pack_fill_both(l->g, kernel, other_hi, other_lo, mine_hi, mine_lo, s)
+                 : weight_pack_fill_both(l->g, kernel, mine_hi, mine_lo, other_hi, other_lo, s);
+    if (r) return r;
+    l->w2_valid = 1; l->w2_precision = prec; l->w2_kernel = kernel;
+    return B200_OK;
 }
 
 // conv_gemm with the layer's split-K scratch (sized on first use; none for layers whose output is large)
@@ -101,7 +128,7 @@ static int layer_conv_gemm(b200_conv_layer *l, bool backward, const b200_conv_ge
         int r = ensure(l, b200_conv_layer::KSPLIT, sizeof(float) * elems, s);
         if (r) return r;
     }
-    return conv_gemm(backward, g, out, act, l->buf[b200_conv_layer::W_HI], l->buf[b200_conv_layer::W_LO], bias, x3, s,
+    return conv_gemm(backward, g, out, act, l->buf[l->w_slot], l->buf[l->w_slot + 1], bias, x3, s,
                      elems ? l->buf[b200_conv_layer::KSPLIT] : nullptr, elems, ef);
 }
 
@@ -139,6 +166,8 @@ static int smallc_weights_into(b200_conv_layer *l, const float *kernel, int pitc
     const size_t bytes = sizeof(float) * rows * pitch + kPackPad;
     if ((r = ensure(l, b200_conv_layer::W_HI, bytes, s))) return r;
     if (x3 && (r = ensure(l, b200_conv_layer::W_LO, bytes, s))) return r;
+    l->w_slot = b200_conv_layer::W_HI;
+    l->w2_valid = 0;
     return smallc_weights(g, kernel, l->buf[b200_conv_layer::W_HI], x3 ? l->buf[b200_conv_layer::W_LO] : nullptr, pitch, transposed, s);
 }
 
@@ -201,6 +230,7 @@ int b200_conv_layer_create(b200_conv_layer **layer, const b200_conv_geom *g, int
     l->g = *g;
     l->batch = batch;
     l->transposed = transposed != 0;
+    l->w_slot = b200_conv_layer::W_HI;
     cudaGetDevice(&l->device);
     *layer = l;
     return B200_OK;
@@ -282,7 +312,7 @@ static int layer_forward(b200_conv_layer *l, float *out, const float *input, con
         PackFunction pf = {in_act ? f->input_func : -1, in_act ? f->input_slope : 0.0, in_act ? f->input_act_out : nullptr};
         const bool fuse_pack = in_act && !input_materialised;
         if ((r = pack_into(l, b200_conv_layer::IN_HI, in, plain_input, x3, s, nullptr, fuse_pack ? &pf : nullptr)) == B200_OK &&
-            (r = pack_weights(l, l->transposed, kernel, x3, s)) == B200_OK)
+            (r = pack_weights(l, l->transposed, kernel, x3, s, true)) == B200_OK)
             r = layer_conv_gemm(l, l->transposed, g, out, in, l->transposed ? nullptr : bias, x3, s, efp);
         if (r == B200_OK) {
             l->in_valid = 1;

@@ -1125,13 +1125,12 @@ int dbias_from_rowsums(float *dbias, int accumulate, const float *rowsum, int ba
 
 // The same re-layout through a shared-memory tile: a block owns one output row r and 32 inner indices i; it reads the
 // taps of each (r, i) pair as one contiguous run and writes, per tap, 32 consecutive inner elements (128 bytes).
-__global__ void __launch_bounds__(256) pack_weight_tiled_kernel(const float *__restrict__ src, float *__restrict__ hi, float *__restrict__ lo,
-                                                                int K, int C, int taps, int ip, int rot)
+__device__ __forceinline__ void pack_weight_tile(int block, const float *__restrict__ src, float *__restrict__ hi, float *__restrict__ lo,
+                                                                int K, int C, int taps, int ip, int rot, float (*tile)[kMaxTaps + 1])
 {
-    __shared__ float tile[32][kMaxTaps + 1];
     const int inner = rot ? K : C;
     const int chunks = (ip + 31) / 32;
-    const int r = blockIdx.x / chunks, i0 = (blockIdx.x % chunks) * 32;
+    const int r = block / chunks, i0 = (block % chunks) * 32;
     for (int e = threadIdx.x; e < 32 * taps; e += blockDim.x) {
         const int il = e / taps, tp = e - il * taps;
         const int i = i0 + il;
@@ -1150,6 +1149,23 @@ __global__ void __launch_bounds__(256) pack_weight_tiled_kernel(const float *__r
         hi[o] = vh;
         if (lo) lo[o] = ptx::to_tf32(v - vh);
     }
+}
+
+__global__ void __launch_bounds__(256) pack_weight_tiled_kernel(const float *__restrict__ src, float *__restrict__ hi, float *__restrict__ lo,
+                                                                int K, int C, int taps, int ip, int rot)
+{
+    __shared__ float tile[32][kMaxTaps + 1];
+    pack_weight_tile(blockIdx.x, src, hi, lo, K, C, taps, ip, rot, tile);
+}
+
+// Both orientations in one launch: the first n_forward blocks write the forward pack, the others the rotated one.
+__global__ void __launch_bounds__(256) pack_weight_both_kernel(const float *__restrict__ src, float *__restrict__ f_hi, float *__restrict__ f_lo,
+                                                               float *__restrict__ b_hi, float *__restrict__ b_lo, int K, int C, int taps, int ip_f,
+                                                               int ip_b, int n_forward)
+{
+    __shared__ float tile[32][kMaxTaps + 1];
+    if ((int)blockIdx.x < n_forward) pack_weight_tile(blockIdx.x, src, f_hi, f_lo, K, C, taps, ip_f, 0, tile);
+    else pack_weight_tile(blockIdx.x - n_forward, src, b_hi, b_lo, K, C, taps, ip_b, 1, tile);
 }
 
 static int pack_weight(const float *src, float *hi, float *lo, int K, int C, int taps, int ip, int rot, cudaStream_t s)
@@ -1208,6 +1224,20 @@ size_t weight_pack_elems(const b200_conv_geom &g, bool backward)
 {
     const int taps = g.kernel_x * g.kernel_y;
     return backward ? (size_t)g.in_z * taps * align_up(g.kernel_amount, 4) : (size_t)g.kernel_amount * taps * align_up(g.in_z, 4);
+}
+
+int weight_pack_fill_both(const b200_conv_geom &g, const float *kernel, float *f_hi, float *f_lo, float *b_hi, float *b_lo, cudaStream_t s)
+{
+    const int taps = g.kernel_x * g.kernel_y;
+    const int ip_f = (int)align_up(g.in_z, 4), ip_b = (int)align_up(g.kernel_amount, 4);
+    if (taps < 2 || taps > kMaxTaps) {
+        int r = pack_weight(kernel, f_hi, f_lo, g.kernel_amount, g.in_z, taps, ip_f, 0, s);
+        return r ? r : pack_weight(kernel, b_hi, b_lo, g.kernel_amount, g.in_z, taps, ip_b, 1, s);
+    }
+    const int n_f = g.kernel_amount * ((ip_f + 31) / 32), n_b = g.in_z * ((ip_b + 31) / 32);
+    pack_weight_both_kernel<<<n_f + n_b, 256, 0, s>>>(kernel, f_hi, f_lo, b_hi, b_lo, g.kernel_amount, g.in_z, taps, ip_f, ip_b, n_f);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
 }
 
 int weight_pack_fill(const b200_conv_geom &g, bool backward, const float *kernel, float *hi, float *lo, cudaStream_t s)

@@ -149,7 +149,9 @@ int b200_conv_wgrad_batch(const b200_conv_geom *g, float *dkernel, float *dbias,
  * weight-gradient kernels.  `g` always describes the underlying convolution; for a transposed layer the
  * layer input has kernel_amount channels of out_y x out_x and the layer output in_z channels of
  * in_y x in_x.  One context serves one layer and one stream at a time; create/destroy allocate and free
- * device memory (buffers grow on first use). */
+ * device memory (buffers grow on first use).  The forward call also prepares the re-laid-out weights of the backward pass:
+ * `kernel` must not change between a layer's forward call and the backward call that follows it (TrainingUpdateWeight runs
+ * after all backward passes in every training loop of the reference). */
 typedef struct b200_conv_layer b200_conv_layer;
 int b200_conv_layer_create(b200_conv_layer **layer, const b200_conv_geom *g, int batch, int transposed);
 int b200_conv_layer_destroy(b200_conv_layer *layer);

@@ -184,17 +184,23 @@ def test_folded_function_layers_change_nothing(ops, mode):
     ops.set_precision({"fp32": ops.FP32, "x3": ops.TF32X3, "tf32": ops.TF32}[mode])
     B = 8
     rng = np.random.default_rng(12)
-    builders = [(lambda: dcgan_discriminator(B, image=(3, 32, 32), widths=(16, 32, 64)), (B, 3, 32, 32)),
-                (lambda: dcgan_generator(B, noise=20, base=64, widths=(32, 16, 3)), (B, 1, 20, 1)),
-                (lambda: vae_encoder(B, image=(3, 32, 32), widths=(8, 16, 32)), (B, 3, 32, 32))]
-    for build, in_shape in builders:
+    from cuda_cnn_gan_vae_b200.layers import Net, NetLayerConvolution, NetLayerFunction, NetLayerMaxPooling
+    # the last: a contraction long enough (128 channels x 3 x 3 taps) for the function layer behind it to go into the epilogue
+    long_conv = [(NetLayerConvolution, dict(kernel_amount=16, kernel_size=3, stride=1, padding=1)), (NetLayerFunction, dict(func="leaky_relu", leaky_slope=0.2)),
+                 (NetLayerMaxPooling, dict(pooling=2)), (NetLayerConvolution, dict(kernel_amount=24, kernel_size=3, stride=1, padding=1)),
+                 (NetLayerFunction, dict(func="tanh"))]
+    builders = [(lambda: dcgan_discriminator(B, image=(3, 32, 32), widths=(16, 32, 64)), (B, 3, 32, 32), True),
+                (lambda: dcgan_generator(B, noise=20, base=64, widths=(32, 16, 3)), (B, 1, 20, 1), True),
+                (lambda: vae_encoder(B, image=(3, 32, 32), widths=(8, 16, 32)), (B, 3, 32, 32), False),       # short contractions: nothing to fold
+                (lambda: Net((128, 8, 8), B, long_conv, seed=9), (B, 128, 8, 8), True)]
+    for build, in_shape, expect_folds in builders:
         x = torch.from_numpy(rng.uniform(-1, 1, in_shape).astype(np.float32)).cuda()
         results = []
         for variant in ("folded", "lean", "separate"):
             net = build()
             net.fold_functions(variant != "separate", materialise=(variant != "lean"))
             folded = sum(1 for l in net.layers if getattr(l, "folded", None))
-            assert (folded > 0) == (variant != "separate")
+            assert (folded > 0) == (variant != "separate" and expect_folds)
             err = torch.from_numpy(np.random.default_rng(13).standard_normal((B,) + net.out_shape).astype(np.float32)).cuda()
             net.TrainingResetDeltaWeight()
             out = net.Forward(x).clone()

@@ -571,6 +571,9 @@ def main():
     ap.add_argument("--skip-dcgan", action="store_true", help="leave out the DCGAN training-step measurement")
     ap.add_argument("--skip-hbm", action="store_true", help="leave out the memory-bound kernel measurements")
     ap.add_argument("--skip-extra", action="store_true", help="leave out the cfg1, VAE and Linear-product measurements (single GPU only)")
+    ap.add_argument("--vae-only", action="store_true", help="run only the VAE training-step measurement (profiling aid)")
+    ap.add_argument("--conv-layer", default=None, metavar="C,H,W,K,k,s,p,B",
+                    help="run only Forward + TrainingBackward of one convolution layer of this geometry in plain TF32 (profiling aid)")
     ap.add_argument("--hbm-only", action="store_true", help="run only the memory-bound kernel measurements (profiling aid)")
     ap.add_argument("--dcgan-batch", type=int, default=64, help="images per GPU in the DCGAN step")
     ap.add_argument("--dcgan-fused", action="store_true", help="batch normalisation and the function layer after it as one fused layer (comparison aid)")
@@ -602,6 +605,27 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     if args.hbm_only:
         emit(json.dumps(dict(hbm_kernels=hbm_kernels(torch, ops, measured_peaks()["hbm"], iters=2))))
+        return
+    if args.conv_layer:
+        Cc, H, W, K, k, s_, p_, B = (int(v) for v in args.conv_layer.split(","))
+        ops.set_precision(ops.TF32)
+        oy, ox = (H - k + 2 * p_) // s_ + 1, (W - k + 2 * p_) // s_ + 1
+        x, d = torch.randn(B, Cc, H, W, device="cuda"), torch.randn(B, K, oy, ox, device="cuda")
+        wt, bias = torch.randn(1, 1, K, Cc * k * k, device="cuda") * (2.0 / (Cc * k * k)) ** 0.5, torch.zeros(1, K, 1, 1, device="cuda")
+        y, dx, dk, db = torch.empty_like(d), torch.empty_like(x), torch.empty_like(wt), torch.empty_like(bias)
+        layer = ops.ConvLayer(Cc, H, W, K, k, k, s_, s_, p_, p_, B)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for i in range(args.warmup + args.steps):
+            if i == args.warmup:
+                e0.record()
+            layer.forward(y, x, wt, bias)
+            layer.backward(dx, dk, db, d, x, wt, accumulate=False)
+        e1.record()
+        torch.cuda.synchronize()
+        ops.stream_status()
+        ms = e0.elapsed_time(e1) / max(1, args.steps)
+        flops = 3 * 2.0 * B * K * Cc * k * k * oy * ox
+        emit(json.dumps(dict(conv_layer=args.conv_layer, mode="tf32", ms_per_step=ms, value=flops / (ms * 1e-3) / 1e12, unit="TFLOP/s")))
         return
     c = dict(CFG, batch=args.batch)
     assert c["batch"] % world == 0, "global batch must divide over the ranks"
@@ -682,6 +706,11 @@ def main():
         lib.b200_profile_read(C.byref(kms), C.byref(kn))
         return ms.item() / steps, clocks, launches, (kms.value / kn.value if kn.value else None)
 
+    if args.vae_only:
+        del x, delta, y, dx
+        torch.cuda.empty_cache()
+        emit(json.dumps(dict(vae=vae_bench(torch, ops, lib, timed, args.steps))))
+        return
     peaks = measured_peaks()
     tf32_peak = peaks["bf16_sustained"] / 2.0
     results = {}

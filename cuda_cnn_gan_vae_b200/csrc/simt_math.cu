@@ -838,11 +838,49 @@ __global__ void warp_dot_kernel(float *__restrict__ out, int out_w, const float 
     }
 }
 
+// The same product with one BLOCK per output element: for a handful of long dot products (the discriminator's last layer:
+// 64 outputs of 8192 terms) one warp per output leaves the GPU idle and walks each row in 64 dependent steps.
+__global__ void __launch_bounds__(256) block_dot_kernel(float *__restrict__ out, int out_w, const float *__restrict__ left, int left_w,
+                                                        const float *__restrict__ right, int right_w, int Z, int LY, int LX)
+{
+    __shared__ float part[8];
+    const size_t idx = blockIdx.x;
+    const int y = idx % LY;
+    const size_t t = idx / LY;
+    const int z = t % Z;
+    const int w = t / Z;
+    const float *a = left + (((size_t)(w % left_w) * Z + z) * LY + y) * LX;
+    const float *b = right + ((size_t)(w % right_w) * Z + z) * LX;
+    float acc = 0.f;
+    if ((LX % 4 == 0) && ((((uintptr_t)a) | ((uintptr_t)b)) % 16 == 0)) {
+        const float4 *a4 = reinterpret_cast<const float4 *>(a), *b4 = reinterpret_cast<const float4 *>(b);
+        for (int k = threadIdx.x; k < LX / 4; k += 256) {
+            const float4 u = a4[k], v = b4[k];
+            acc += u.x * v.x + u.y * v.y + u.z * v.z + u.w * v.w;
+        }
+    } else {
+        for (int k = threadIdx.x; k < LX; k += 256) acc += a[k] * b[k];
+    }
+    acc = warp_sum(acc);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float s = part[0];
+        for (int i = 1; i < 8; i++) s += part[i];
+        out[idx] = s;
+    }
+}
+
 int warp_dot_mul(float *out, int out_w, const float *left, int left_w, const float *right, int right_w, int z, int ly, int lx,
                  cudaStream_t s)
 {
     const size_t total = (size_t)out_w * z * ly;
     if (!total) return B200_OK;
+    if (total <= (size_t)sm_count() * 8 && lx >= 1024) {
+        block_dot_kernel<<<(unsigned)total, 256, 0, s>>>(out, out_w, left, left_w, right, right_w, z, ly, lx);
+        B200_LAUNCH_CHECK();
+        return B200_OK;
+    }
     warp_dot_kernel<<<stream_grid(total * 32, 256), 256, 0, s>>>(out, out_w, left, left_w, right, right_w, z, ly, lx);
     B200_LAUNCH_CHECK();
     return B200_OK;

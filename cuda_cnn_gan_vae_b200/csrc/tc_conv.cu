@@ -691,6 +691,23 @@ __global__ void split_tf32_kernel(const float *__restrict__ src, float *__restri
     }
 }
 
+// two tensors in one launch: the first `blocks_a` blocks split a, the others b
+__global__ void split_tf32_pair_kernel(const float *__restrict__ a, float *__restrict__ a_hi, float *__restrict__ a_lo, size_t na,
+                                       const float *__restrict__ b, float *__restrict__ b_hi, float *__restrict__ b_lo, size_t nb, int blocks_a)
+{
+    const bool first = (int)blockIdx.x < blocks_a;
+    const float *src = first ? a : b;
+    float *hi = first ? a_hi : b_hi, *lo = first ? a_lo : b_lo;
+    const size_t n = first ? na : nb;
+    const size_t block = first ? blockIdx.x : blockIdx.x - blocks_a, blocks = first ? blocks_a : gridDim.x - blocks_a;
+    for (size_t i = block * blockDim.x + threadIdx.x; i < n; i += blocks * blockDim.x) {
+        const float v = src[i];
+        const float vh = ptx::to_tf32(v);
+        hi[i] = vh;
+        if (lo) lo[i] = ptx::to_tf32(v - vh);
+    }
+}
+
 // dkernel[f][c*taps + tap] (+)= sum over splits (in increasing order) of partial[split][tap][c][f]
 __global__ void wgrad_reduce_kernel(float *__restrict__ dkernel, const float *__restrict__ partial, int splits, int taps,
                                     int C, int K, int accumulate)
@@ -1619,11 +1636,13 @@ int tc_gemm(float *out, const float *a, const float *b, int m, int n, int k, int
     float *b_lo = x3 ? (float *)arena_take(sizeof(float) * b_elems + 256) : nullptr;
     float *kpartial = part_elems ? (float *)arena_take(sizeof(float) * part_elems) : nullptr;
     if (!a_hi || !b_hi || (x3 && (!a_lo || !b_lo)) || (part_elems && !kpartial)) return fail(B200_E_NOMEM, "scratch arena exhausted");
-    int grid = sm_count() * 8;
-    split_tf32_kernel<<<grid, 256, 0, s>>>(a, a_hi, a_lo, a_elems);
-    B200_LAUNCH_CHECK();
-    split_tf32_kernel<<<grid, 256, 0, s>>>(b, b_hi, b_lo, b_elems);
-    B200_LAUNCH_CHECK();
+    {
+        // both operands in one launch: blocks [0, ga) split A, the rest B
+        const int ga = (int)((a_elems + 256 * 8 - 1) / (256 * 8)) < sm_count() * 8 ? (int)((a_elems + 256 * 8 - 1) / (256 * 8)) : sm_count() * 8;
+        const int gb = (int)((b_elems + 256 * 8 - 1) / (256 * 8)) < sm_count() * 8 ? (int)((b_elems + 256 * 8 - 1) / (256 * 8)) : sm_count() * 8;
+        split_tf32_pair_kernel<<<ga + gb, 256, 0, s>>>(a, a_hi, a_lo, a_elems, b, b_hi, b_lo, b_elems, ga);
+        B200_LAUNCH_CHECK();
+    }
 
     TcParams p;
     memset(&p, 0, sizeof(p));

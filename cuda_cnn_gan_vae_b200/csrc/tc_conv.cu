@@ -42,6 +42,7 @@ constexpr int kMaxPhases = 16;
 constexpr long long kWaitCycles = 2000000000LL;
 
 struct TapEntry { int8_t dy, dx; uint8_t in_phase, wtap; };
+struct TapGroup { uint8_t count, tap[4], unused[3]; };      // WGRAD with packed taps: the taps (of one stride phase) of a work item
 
 struct PhaseInfo {
     int tile_begin;            // first M-tile of this output phase
@@ -79,6 +80,11 @@ struct TcParams {
     int ft_n, ct_n, taps_n, splits, chunks_x, chunks_y, chunks_i, k_rows, c_cols, wg_ctas;
     long long chunks_total;
     float *partial;
+    // WGRAD with few filters: the 128 rows of the MMA hold `members` taps x `tapm` filters (tapm = filters padded to 32 or 64;
+    // 0 = one tap per work item), a work item covers a group of taps of one stride phase
+    int tapm, members, items_n;
+    uint32_t member_bytes;
+    TapGroup groups[kMaxTaps];
     // GEMM
     int M, N, K, ldc, a_mn, b_mn;
 #ifdef B200_TC_TIMING
@@ -151,8 +157,8 @@ __device__ __forceinline__ TileCtx decode_tile(const TcParams &p, int tile, int 
         // chunk they all read and the (shifted) image chunks come from HBM once and from L2 for the other taps.  With the
         // split fastest instead, every tap streamed both tensors from HBM again (9 or 16 times the traffic, which is what
         // bounds this kernel on layers with few channels).
-        c.tap = tile % p.taps_n;
-        int rest = tile / p.taps_n;
+        c.tap = tile % p.items_n;                        // a tap, or a group of taps
+        int rest = tile / p.items_n;
         c.split = rest % p.splits; rest /= p.splits;
         c.ct = rest % p.ct_n;
         c.ft = (rest / p.ct_n) * p.wg_ctas + rank;       // CTA pair: the pair owns two neighbouring filter tiles
@@ -256,12 +262,14 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
         // Fixed role of this lane: which K block of a stage (my_m), which operand and plane, where in the
         // stage it lands.  One warp-wide TMA instruction then fills a whole stage.
         const int planes = X3 ? 2 : 1;
-        const int n_boxes = 2 * planes;                          // A and B, high (and low) plane
+        const int a_parts = (MODE == MODE_WGRAD && p.tapm) ? p.members : 1;      // packed taps: one box per member tap
+        const int n_boxes = (a_parts + 1) * planes;              // A (parts) and B, high (and low) plane
         const bool active = lane < n_boxes * p.ksub;
         const int my_m = lane / n_boxes, my_box = lane - my_m * n_boxes;
-        const bool is_a = my_box < planes;
+        const bool is_a = my_box < a_parts * planes;
         const bool is_lo = (my_box & 1) && X3;
-        const uint32_t my_off = (uint32_t)my_m * p.mini_bytes + (is_a ? (is_lo ? off_a_lo : 0u) : (is_lo ? off_b_lo : off_b_hi));
+        const int my_part = is_a ? my_box / planes : 0;
+        const uint32_t my_off = (uint32_t)my_m * p.mini_bytes + (is_a ? (is_lo ? off_a_lo : 0u) + (uint32_t)my_part * p.member_bytes : (is_lo ? off_b_lo : off_b_hi));
         const CUtensorMap *my_map = is_a ? (is_lo ? &mapA_lo : &mapA_hi) : (is_lo ? &mapB_lo : &mapB_hi);
         const uint32_t smem0 = ptx::smem_u32(smem);
         const uint32_t my_turn = warp == 0 ? 0u : 1u;
@@ -309,6 +317,15 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
                         const TapEntry t = p.taps[tap_begin + (pad ? 0 : ti)];
                         if (is_a) { c0 = cc * 32; c1 = base1 + t.dx; c2 = base2 + t.dy; c3 = pad ? p.n_img + p.BI : base3; c4 = t.in_phase; }
                         else { c0 = cc * 32; c1 = t.wtap; c2 = bcoord; c3 = 0; c4 = 0; }
+                    } else if (MODE == MODE_WGRAD && p.tapm) {
+                        // The image chunk is taken unshifted from its phase plane and every member tap brings the error chunk
+                        // that meets it: pixel X of the plane pairs with output pixel X - d of the tap.  Members a short group
+                        // lacks, and filler blocks, read past the batch (zeros, same byte count).
+                        const TapGroup &grp = p.groups[c.tap];
+                        const bool absent = my_part >= grp.count;
+                        const TapEntry t = p.taps[grp.tap[absent ? 0 : my_part]];
+                        if (is_a) { c0 = 0; c1 = cx * p.BW - t.dx; c2 = cy * p.BH - t.dy; c3 = (pad || absent) ? (p.chunks_i + 1) * p.BI : ci * p.BI; c4 = 0; }
+                        else { c0 = 0; c1 = cx * p.BW; c2 = cy * p.BH; c3 = t.in_phase * p.n_img + ci * p.BI; c4 = c.ct * (p.BN / 32); }
                     } else if (MODE == MODE_WGRAD) {
                         const TapEntry t = p.taps[c.tap];
                         // coordinate 4 walks the 32-channel blocks, so one box brings all blocks of the operand
@@ -510,14 +527,23 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
                     }
                 }
             } else if (MODE == MODE_WGRAD) {
-                const int f = c.ft * 128 + row;
-                float *dst = p.partial + (((size_t)c.split * p.taps_n + c.tap) * p.c_cols) * p.k_rows + f;
+                int f = c.ft * 128 + row, tap = c.tap;
+                bool row_ok = f < p.k_rows;
+                if (p.tapm) {
+                    // packed taps: row = member * tapm + filter
+                    const TapGroup &grp = p.groups[c.tap];
+                    const int member = row / p.tapm;
+                    f = row - member * p.tapm;
+                    row_ok = member < grp.count && f < p.k_rows;
+                    tap = grp.tap[member < grp.count ? member : 0];
+                }
+                float *dst = p.partial + (((size_t)c.split * p.taps_n + tap) * p.c_cols) * p.k_rows + f;
                 for (int c0 = 0; c0 < p.BN; c0 += 16) {
                     load16(c0);
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
                         const int ch = c.ct * p.BN + c0 + j;
-                        if (f < p.k_rows && ch < p.c_cols) dst[(size_t)ch * p.k_rows] = v[j];
+                        if (row_ok && ch < p.c_cols) dst[(size_t)ch * p.k_rows] = v[j];
                     }
                 }
             } else {
@@ -1457,24 +1483,70 @@ int tc_conv_backward(const b200_conv_geom &g, float *out_delta, const float *del
     return run_conv(true, g, out_delta, delta, kernel, nullptr, batch, precision, s);
 }
 
-// Split-K plan of the weight gradient: number of CTAs along the pixel dimension.
-static int wgrad_splits(const b200_conv_geom &g, int batch)
+// Debug switch: B200CONV_WGRAD_PACK_TAPS=0 in the environment keeps one tap per work item of the weight gradient.
+static bool wgrad_pack_taps_enabled()
 {
-    int BW, BH, BI;
-    tile_shape(g.out_y, g.out_x, 32, &BW, &BH, &BI);
-    const long long chunks = (long long)ceil_div(g.out_x, BW) * ceil_div(g.out_y, BH) * ceil_div(batch, BI);
-    const int BN = (int)align_up(g.in_z < 256 ? g.in_z : 256, 32);
-    const int base = ceil_div(g.kernel_amount, 128) * ceil_div(g.in_z, BN) * g.kernel_x * g.kernel_y;
+    static const bool on = !(getenv("B200CONV_WGRAD_PACK_TAPS") && getenv("B200CONV_WGRAD_PACK_TAPS")[0] == '0');
+    return on;
+}
+
+// Plan of the weight gradient: the pixel chunks that form the K dimension, how many taps share a work item, and the split-K
+// factor (number of CTAs along the pixel dimension).
+struct WgradPlan {
+    int tapm;                  // 0, or filters per member tap (32 or 64) when several taps share the 128 rows of the MMA
+    int members;               // taps per work item
+    int items;                 // work items per (channel tile, split): taps, or tap groups
+    int BW, BH, BI, chunks_x, chunks_y, chunks_i;
+    int BN, splits;
+    TapGroup groups[kMaxTaps];
+};
+
+static WgradPlan wgrad_plan(const b200_conv_geom &g, int batch)
+{
+    WgradPlan w;
+    memset(&w, 0, sizeof(w));
+    const int taps = g.kernel_x * g.kernel_y, K = g.kernel_amount;
+    const int sy = g.stride_y, sx = g.stride_x;
+    w.BN = (int)align_up(g.in_z < 256 ? g.in_z : 256, 32);
+    // With at most 64 filters a tap fills a quarter or half of the MMA's 128 rows, and every tap would stage the image chunk
+    // again: 4 (2) taps of one stride phase share the rows and one staged image chunk instead.
+    if (wgrad_pack_taps_enabled() && K <= 64 && taps >= 2 && taps <= kMaxTaps) {
+        w.tapm = K <= 32 ? 32 : 64;
+        w.members = 128 / w.tapm;
+        const int phases = sy * sx;
+        for (int ph = 0; ph < phases; ph++) {
+            int open = -1;                                   // group of this phase that still has room
+            for (int ky = 0; ky < g.kernel_y; ky++)
+                for (int kx = 0; kx < g.kernel_x; kx++) {
+                    if (pos_mod(ky - g.padding_y, sy) * sx + pos_mod(kx - g.padding_x, sx) != ph) continue;
+                    if (open < 0 || w.groups[open].count == w.members) open = w.items++;
+                    TapGroup &grp = w.groups[open];
+                    grp.tap[grp.count++] = (uint8_t)(ky * g.kernel_x + kx);
+                }
+        }
+        // the pixel chunks walk a phase plane of the image
+        const int hs = ceil_div(g.in_y, sy), ws = ceil_div(g.in_x, sx);
+        tile_shape(hs, ws, 32, &w.BW, &w.BH, &w.BI);
+        w.chunks_x = ceil_div(ws, w.BW); w.chunks_y = ceil_div(hs, w.BH);
+    } else {
+        w.items = taps;
+        tile_shape(g.out_y, g.out_x, 32, &w.BW, &w.BH, &w.BI);
+        w.chunks_x = ceil_div(g.out_x, w.BW); w.chunks_y = ceil_div(g.out_y, w.BH);
+    }
+    w.chunks_i = ceil_div(batch, w.BI);
+    const long long chunks = (long long)w.chunks_x * w.chunks_y * w.chunks_i;
+    const int base = (w.tapm ? 1 : ceil_div(K, 128)) * ceil_div(g.in_z, w.BN) * w.items;
     long long splits = sm_count() / base;
     if (splits < 1) splits = 1;
     if (splits > chunks) splits = chunks;
     if (splits > 64) splits = 64;
-    return (int)splits;
+    w.splits = (int)splits;
+    return w;
 }
 
 size_t wgrad_partial_elems(const b200_conv_geom &g, int batch)
 {
-    return (size_t)wgrad_splits(g, batch) * g.kernel_x * g.kernel_y * g.in_z * g.kernel_amount;
+    return (size_t)wgrad_plan(g, batch).splits * g.kernel_x * g.kernel_y * g.in_z * g.kernel_amount;
 }
 
 // Batch-summed weight gradient on packed operands: x = image pack (split by the stride), d = delta
@@ -1491,20 +1563,24 @@ int wgrad_gemm(const b200_conv_geom &g, float *dkernel, int accumulate, const Ac
 
     TcParams p;
     memset(&p, 0, sizeof(p));
-    p.BN = (int)align_up(C < 256 ? C : 256, 32);
+    const WgradPlan plan = wgrad_plan(g, batch);
+    p.BN = plan.BN;
     p.acc_stride = pow2_ceil(p.BN);
     // CTA pairs: two neighbouring filter tiles share one 256-row MMA, each CTA stages half of the channels
     const int ctas = (cta_pairs_enabled() && K > 128 && p.BN % 64 == 0) ? 2 : 1;
     set_mnmajor(p, true, 128);
     set_mnmajor(p, false, p.BN / ctas);
     p.idesc = make_idesc_tf32(p.BN, 1, 1, 128 * ctas);
-    p.ft_n = ceil_div(K, 128); p.ct_n = ceil_div(C, p.BN); p.taps_n = taps; p.wg_ctas = ctas;
+    p.ft_n = plan.tapm ? 1 : ceil_div(K, 128); p.ct_n = ceil_div(C, p.BN); p.taps_n = taps; p.wg_ctas = ctas;
     p.k_rows = K; p.c_cols = C; p.n_img = batch;
-    tile_shape(g.out_y, g.out_x, 32, &p.BW, &p.BH, &p.BI);
-    p.chunks_x = ceil_div(g.out_x, p.BW); p.chunks_y = ceil_div(g.out_y, p.BH); p.chunks_i = ceil_div(batch, p.BI);
+    p.BW = plan.BW; p.BH = plan.BH; p.BI = plan.BI;
+    p.chunks_x = plan.chunks_x; p.chunks_y = plan.chunks_y; p.chunks_i = plan.chunks_i;
     p.chunks_total = (long long)p.chunks_x * p.chunks_y * p.chunks_i;
-    p.splits = wgrad_splits(g, batch);
-    p.num_tiles = ceil_div(p.ft_n, ctas) * p.ct_n * taps * p.splits;        // work items: tiles, or pairs of filter tiles
+    p.splits = plan.splits;
+    p.tapm = plan.tapm; p.members = plan.members; p.items_n = plan.items;
+    p.member_bytes = (uint32_t)(plan.tapm / 32) * 4096u;
+    memcpy(p.groups, plan.groups, sizeof(p.groups));
+    p.num_tiles = ceil_div(p.ft_n, ctas) * p.ct_n * p.items_n * p.splits;   // work items: tiles, or pairs of filter tiles
     p.partial = partial;
     for (int ky = 0; ky < g.kernel_y; ky++)
         for (int kx = 0; kx < g.kernel_x; kx++) {
@@ -1520,8 +1596,9 @@ int wgrad_gemm(const b200_conv_geom &g, float *dkernel, int accumulate, const Ac
         const long long dims[3] = {g.out_x, g.out_y, batch};
         const long long pitch[3] = {d.cp, (long long)g.out_x * d.cp, (long long)g.out_y * g.out_x * d.cp};
         const int box[3] = {p.BW, p.BH, p.BI};
-        if ((r = make_blocked_map(&maps[0], d.hi, K, dims, pitch, box, 4))) return r;
-        if (x3 && (r = make_blocked_map(&maps[1], d.lo, K, dims, pitch, box, 4))) return r;
+        const int a_blocks = plan.tapm ? plan.tapm / 32 : 4;      // packed taps: a box is one member tap's filters
+        if ((r = make_blocked_map(&maps[0], d.hi, K, dims, pitch, box, a_blocks))) return r;
+        if (x3 && (r = make_blocked_map(&maps[1], d.lo, K, dims, pitch, box, a_blocks))) return r;
     }
     {
         // phase and image index share one dimension ([phase][n] is contiguous in the pack)

@@ -642,6 +642,17 @@ def main():
     y = torch.empty(B, K, H, W, device="cuda")
     dx = torch.empty(B, Cc, H, W, device="cuda")
     from cuda_cnn_gan_vae_b200.dp import GradArena, PeerBuffer, arena_layout
+    exchange_note = None
+    if world > 1 and args.exchange == "peer":
+        # the peer-memory exchange proves itself on this box before anything is timed with it: all ranks map one another's
+        # memory and sum small integers; a rank that cannot sends every rank to NCCL, and the line says so
+        probe = PeerBuffer(1 << 16, strict=False)
+        why = probe.failed or probe.self_test()
+        if not probe.failed:
+            probe.close()
+        if why:
+            args.exchange = "nccl"
+            exchange_note = "peer-memory exchange not usable on this box (%s): NCCL used instead" % why
     shapes = {"dW": (1, 1, K, Cc * k * k), "dB": (1, K, 1, 1)}
     peer = None
     if world > 1 and args.exchange == "peer":
@@ -865,7 +876,7 @@ def main():
                                 % (c["batch"], " + sum of dW|dB over the ranks" if world > 1 else ""),
                                 global_batch=c["batch"], per_gpu_batch=B, parallelism=f"dp{world}",
                                 exchange=(("library kernels over NVLink peer memory (b200_allreduce, b200_allreduce_adam)" if args.exchange == "peer"
-                                           else "NCCL all-reduce") if world > 1 else None), l2="inputs exceed L2 (1 GiB tensors)",
+                                           else "NCCL all-reduce") if world > 1 else None), exchange_note=exchange_note, l2="inputs exceed L2 (1 GiB tensors)",
                                 parity="tf32: 2e-3, tf32x3: 1e-4 on dot_rel_err vs the reference CPU backend (tests/test_gpu_full_size.py); measured on this run's batch when the CPU leg runs",
                                 flops_per_step=step_flops),
                     clocks=head["clocks"], gpu_launches=head["gpu_launches"], roofline=head["roofline"], e2e=e2e,

@@ -57,24 +57,74 @@ class PeerBuffer:
     library's exchange kernels can read and write the peers' arenas over NVLink.  The handles travel through
     torch.distributed (all_gather of a byte tensor); torch does nothing else here."""
 
-    def __init__(self, floats):
+    def __init__(self, floats, strict=True):
+        """Collective over the process group.  strict=False: a rank that cannot create or map the memory (no peer access
+        between two devices, say) does not raise; every rank then ends with `failed` set to the reason and no buffer, so
+        that the caller can fall back to NCCL on all ranks together."""
         lib = load()
         self.rank, self.world = dist.get_rank(), dist.get_world_size()
         self.floats = (floats + 63) // 64 * 64
         self.comm = C.c_void_p()
+        self.failed = None
+        self.buffer = None
+        self.taken = 0
         from .ops import _check
-        _check(lib.b200_comm_create(C.byref(self.comm), self.rank, self.world, self.floats * 4))
         handle = (C.c_ubyte * 128)()
-        _check(lib.b200_comm_handle(self.comm, handle))
+        error = None
+        try:
+            _check(lib.b200_comm_create(C.byref(self.comm), self.rank, self.world, self.floats * 4))
+            _check(lib.b200_comm_handle(self.comm, handle))
+        except Exception as e:      # every rank still takes part in the collectives below
+            error = e
         mine = torch.tensor(list(handle), dtype=torch.uint8, device="cuda")
         everyone = [torch.empty_like(mine) for _ in range(self.world)]
         dist.all_gather(everyone, mine)
-        blob = bytes(torch.stack(everyone).cpu().numpy().tobytes())
-        _check(lib.b200_comm_connect(self.comm, blob))
+        bad = torch.tensor([1 if error else 0], device="cuda")
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if not int(bad.item()):
+            try:
+                blob = bytes(torch.stack(everyone).cpu().numpy().tobytes())
+                _check(lib.b200_comm_connect(self.comm, blob))
+            except Exception as e:
+                error = e
+            bad = torch.tensor([1 if error else 0], device="cuda")
+            dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if int(bad.item()):
+            self.failed = str(error) if error else "another rank could not create or map the peer memory"
+            if self.comm:
+                lib.b200_comm_destroy(self.comm)
+                self.comm = C.c_void_p()
+            if strict:
+                raise RuntimeError("peer buffer: " + self.failed)
+            return
         self._span = _DeviceSpan(lib.b200_comm_buffer(self.comm), self.floats)
         self.buffer = torch.as_tensor(self._span, device="cuda")
-        self.taken = 0
         dist.barrier()
+
+    def self_test(self, floats=1 << 16):
+        """Collective: sums small integers (exact in fp32 in any order) over the ranks with the library's exchange kernel and
+        checks the result on every rank.  Returns None, or the reason it failed (the same verdict on every rank)."""
+        lib = load()
+        from .ops import _check, _stream, stream_status
+        n = min(self.floats, floats) // 4 * 4
+        error = None
+        try:
+            base = torch.arange(n, device="cuda", dtype=torch.float32) % 251
+            self.buffer[:n] = base + self.rank
+            dist.barrier()
+            _check(lib.b200_allreduce(self.comm, 0, n, 0, _stream()))
+            torch.cuda.synchronize()
+            stream_status()
+            want = base * self.world + self.world * (self.world - 1) // 2
+            if not torch.equal(self.buffer[:n], want):
+                error = "the sum over the ranks is wrong"
+        except Exception as e:
+            error = str(e)
+        bad = torch.tensor([1 if error else 0], device="cuda")
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if int(bad.item()):
+            return error or "the self-test failed on another rank"
+        return None
 
     def take(self, floats):
         """The next `floats` floats of the buffer (a multiple of 4, so every span starts on a 16-byte boundary) as

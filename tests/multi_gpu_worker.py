@@ -23,6 +23,9 @@ def main():
     sizes = [4, 64, 1000, 4096 * 3 + 8, 1 << 20, 3_600_000]
     total = sum(sizes) * 3 + 64
     peer = PeerBuffer(total)
+    assert peer.failed is None
+    why = peer.self_test()
+    assert why is None, why
     gen = torch.Generator(device="cuda").manual_seed(100 + rank)
 
     def gathered_sum(t):

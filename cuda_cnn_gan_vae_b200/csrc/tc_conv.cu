@@ -629,15 +629,21 @@ __global__ void pack_act_kernel(const float *__restrict__ src, float *__restrict
     }
 }
 
-// Same re-layout with 128-bit accesses: a block moves 32 pixels x 32 channels per iteration, one
-// float4 load (4 pixels of one channel) and one float4 store per plane (4 channels of one pixel) per
-// thread.  Needs W % 4 == 0 and a 16-byte aligned source.
+// Same re-layout with 128-bit accesses: a block moves 4 rows x 32 pixels x 32 channels per iteration, per row one
+// float4 load (4 pixels of one channel) and one float4 store per plane (4 channels of one pixel) per thread.  Needs
+// W % 4 == 0 and a 16-byte aligned source.
+// The four loads of an iteration are issued together: with one load in flight per thread the resident threads of an SM
+// could not cover the latency of the memory, and the four rows of a channel are neighbours in the source (512 contiguous
+// bytes for a 32-pixel row) instead of lone 128-byte pieces.
+// (ROWS = 1 or 2 for tensors too small to give every block four rows: fewer registers, more resident blocks.)
+constexpr int kPackRows = 4;
+template <int ROWS>
 __global__ void __launch_bounds__(256)
 pack_act_vec_kernel(const float *__restrict__ src, float *__restrict__ hi, float *__restrict__ lo,
                     int N, int C, int H, int W, int Cp, int sy, int sx, int Hs, int Ws, int rows_per_block, float *__restrict__ rowsum,
                     int func, double slope, float *__restrict__ act_out)
 {
-    __shared__ float tile[32][33];
+    __shared__ float tile[ROWS][32][33];
     const int n = blockIdx.z, h0 = blockIdx.y * rows_per_block, w0 = blockIdx.x * 32;
     const int h1 = min(h0 + rows_per_block, Hs * sy);
     const int tid = threadIdx.x;
@@ -649,29 +655,42 @@ pack_act_vec_kernel(const float *__restrict__ src, float *__restrict__ hi, float
         const int c = c0 + lc;
         const int cq = c0 + 4 * sq;
         float acc = 0.f;                            // this thread's share of the plane sum of channel c (bias gradient)
-        for (int h = h0; h < h1; h++) {
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (h < H && c < C && wl < W) {
-                const size_t at = (((size_t)n * C + c) * H + h) * W + wl;
-                v = *reinterpret_cast<const float4 *>(src + at);
-                if (func >= 0) {
-                    v.x = act_apply(v.x, func, slope); v.y = act_apply(v.y, func, slope); v.z = act_apply(v.z, func, slope); v.w = act_apply(v.w, func, slope);
-                    if (act_out) *reinterpret_cast<float4 *>(act_out + at) = v;
-                }
+        for (int hb = h0; hb < h1; hb += ROWS) {
+            float4 v[ROWS];
+#pragma unroll
+            for (int j = 0; j < ROWS; j++) {
+                const int h = hb + j;
+                v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (h < h1 && h < H && c < C && wl < W) v[j] = *reinterpret_cast<const float4 *>(src + (((size_t)n * C + c) * H + h) * W + wl);
             }
-            acc += (v.x + v.y) + (v.z + v.w);
-            tile[lc][4 * lq + 0] = v.x; tile[lc][4 * lq + 1] = v.y; tile[lc][4 * lq + 2] = v.z; tile[lc][4 * lq + 3] = v.w;
+#pragma unroll
+            for (int j = 0; j < ROWS; j++) {
+                const int h = hb + j;
+                if (func >= 0 && h < h1 && h < H && c < C && wl < W) {
+                    v[j].x = act_apply(v[j].x, func, slope); v[j].y = act_apply(v[j].y, func, slope);
+                    v[j].z = act_apply(v[j].z, func, slope); v[j].w = act_apply(v[j].w, func, slope);
+                    if (act_out) *reinterpret_cast<float4 *>(act_out + (((size_t)n * C + c) * H + h) * W + wl) = v[j];
+                }
+                if (h >= h1) break;                     // the same for every thread of the block
+                acc += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+                tile[j][lc][4 * lq + 0] = v[j].x; tile[j][lc][4 * lq + 1] = v[j].y; tile[j][lc][4 * lq + 2] = v[j].z; tile[j][lc][4 * lq + 3] = v[j].w;
+            }
             __syncthreads();
             if (ws < Ws * sx && cq < Cp) {
-                const int hq = h / sy, hr = h % sy;
-                const int ph = hr * sx + (ws % sx);
-                const size_t obase = ((((size_t)ph * N + n) * Hs + hq) * Ws + (ws / sx)) * Cp;
-                float4 a = make_float4(tile[4 * sq + 0][sp], tile[4 * sq + 1][sp], tile[4 * sq + 2][sp], tile[4 * sq + 3][sp]);
-                float4 b = make_float4(ptx::to_tf32(a.x), ptx::to_tf32(a.y), ptx::to_tf32(a.z), ptx::to_tf32(a.w));
-                *reinterpret_cast<float4 *>(hi + obase + cq) = b;
-                if (lo)
-                    *reinterpret_cast<float4 *>(lo + obase + cq) =
-                        make_float4(ptx::to_tf32(a.x - b.x), ptx::to_tf32(a.y - b.y), ptx::to_tf32(a.z - b.z), ptx::to_tf32(a.w - b.w));
+#pragma unroll
+                for (int j = 0; j < ROWS; j++) {
+                    const int h = hb + j;
+                    if (h >= h1) break;
+                    const int hq = h / sy, hr = h % sy;
+                    const int ph = hr * sx + (ws % sx);
+                    const size_t obase = ((((size_t)ph * N + n) * Hs + hq) * Ws + (ws / sx)) * Cp;
+                    float4 a = make_float4(tile[j][4 * sq + 0][sp], tile[j][4 * sq + 1][sp], tile[j][4 * sq + 2][sp], tile[j][4 * sq + 3][sp]);
+                    float4 b = make_float4(ptx::to_tf32(a.x), ptx::to_tf32(a.y), ptx::to_tf32(a.z), ptx::to_tf32(a.w));
+                    *reinterpret_cast<float4 *>(hi + obase + cq) = b;
+                    if (lo)
+                        *reinterpret_cast<float4 *>(lo + obase + cq) =
+                            make_float4(ptx::to_tf32(a.x - b.x), ptx::to_tf32(a.y - b.y), ptx::to_tf32(a.z - b.z), ptx::to_tf32(a.w - b.w));
+                }
             }
             __syncthreads();
         }
@@ -1104,20 +1123,27 @@ static int pack_act(const float *src, float *hi, float *lo, int N, int C, int H,
     const int func = pf ? pf->func : -1;
     const double slope = pf ? pf->slope : 0.0;
     float *act_out = pf ? pf->act_out : nullptr;
-    // An unsplit pack of a narrow image (a row shorter than the kernel's 32-pixel tile) is the same re-layout of a single row
-    // of H*W pixels: [n][y][x][c] and [n][c][y][x] are both linear in y*W + x.  Narrow rows would leave most of a tile idle.
-    if (sy == 1 && sx == 1 && W < 32 && H > 1 && W % 4 == 0) {
-        W = H * W; Ws = W; H = 1; Hs = 1;
+    // An unsplit pack is the same re-layout for any way of cutting the H*W pixels of a plane into rows: [n][y][x][c] and
+    // [n][c][y][x] are both linear in y*W + x.  Rows of exactly 32 pixels fill the kernel's tile, and the rows a block moves
+    // together are then neighbours in memory; failing that, a narrow image becomes a single row (narrow rows would leave most
+    // of a tile idle).
+    if (sy == 1 && sx == 1 && H > 1) {
+        const long long px = (long long)H * W;
+        if (px % 32 == 0 && px / 32 <= 65535) { H = (int)(px / 32); W = 32; Hs = H; Ws = W; }
+        else if (W < 32 && W % 4 == 0) { W = (int)px; Ws = W; H = 1; Hs = 1; }
     }
     dim3 grid(ceil_div(Ws * sx, 32), Hs * sy, N), block(32, 8);
     if (grid.y > 65535 || grid.z > 65535) return TC_UNSUPPORTED;
     if (rowsum_runs) *rowsum_runs = 0;
     if (W % 4 == 0 && ((uintptr_t)src & 15) == 0 && ((uintptr_t)act_out & 15) == 0) {
-        // with the bias-gradient sums fused in, a block walks 8 rows so that it leaves one partial sum per 8 rows and channel
-        int rows_per_block = rowsum ? 8 : 1;
-        while (rows_per_block > 1 && (long long)grid.x * ceil_div((int)grid.y, rows_per_block) * N < 8LL * sm_count()) rows_per_block /= 2;
+        // a block walks 4 rows, one iteration per channel chunk (8 with the bias-gradient sums fused in: one partial sum per 8
+        // rows and channel); fewer when that would leave the grid short of a few waves of blocks
+        int rows_per_block = rowsum ? 8 : kPackRows;
+        while (rows_per_block > 1 && (long long)grid.x * ceil_div((int)grid.y, rows_per_block) * N < 16LL * sm_count()) rows_per_block /= 2;
         dim3 vgrid(grid.x, ceil_div((int)grid.y, rows_per_block), N);
-        pack_act_vec_kernel<<<vgrid, 256, 0, s>>>(src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws, rows_per_block, rowsum, func, slope, act_out);
+        if (rows_per_block >= 4) pack_act_vec_kernel<4><<<vgrid, 256, 0, s>>>(src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws, rows_per_block, rowsum, func, slope, act_out);
+        else if (rows_per_block == 2) pack_act_vec_kernel<2><<<vgrid, 256, 0, s>>>(src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws, rows_per_block, rowsum, func, slope, act_out);
+        else pack_act_vec_kernel<1><<<vgrid, 256, 0, s>>>(src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws, rows_per_block, rowsum, func, slope, act_out);
         if (rowsum && rowsum_runs) *rowsum_runs = (int)(vgrid.x * vgrid.y);
     } else
         pack_act_kernel<<<grid, block, 0, s>>>(src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws, func, slope, act_out);

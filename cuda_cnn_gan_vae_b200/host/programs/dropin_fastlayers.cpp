@@ -16,6 +16,7 @@
 #include <cmath>
 #include <memory>
 #include <vector>
+#include <random>
 
 #include "netlayer/cnetlayerconvolutioninput.cu.h"
 #include "netlayer/cnetlayerlinear.cu.h"
@@ -74,6 +75,28 @@ static void DumpAllParams(FILE *file,net_t &net,const char *tag,bool gradients)
  DumpParams<CNetLayerConvolution<type_t> >(file,(t+"conv").c_str(),net[5].get(),gradients);
 }
 
+// Reset() of the Linear and of the convolution layer draws its weights from std::random_device (common/crandom.h:94): another
+// network on every run.  The comparison wants ONE network, so the weights are drawn again over the same range from a
+// generator with a fixed seed.
+template<class layer_t>
+static void RedrawWeights(INetLayer<type_t> *layer,uint32_t seed)
+{
+ layer_t *own=dynamic_cast<layer_t*>(layer);
+ if (own==NULL) throw("unexpected layer class");
+ CTensor<type_t> &weight=own->GetParamTensor(0);
+ type_t limit=0;
+ for(uint32_t w=0;w<weight.GetSizeW();w++)
+  for(uint32_t z=0;z<weight.GetSizeZ();z++)
+   for(uint32_t y=0;y<weight.GetSizeY();y++)
+    for(uint32_t x=0;x<weight.GetSizeX();x++) limit=std::max(limit,static_cast<type_t>(fabs(weight.GetElement(w,z,y,x))));
+ std::mt19937 generator(seed);
+ std::uniform_real_distribution<type_t> distribution(-limit,limit);
+ for(uint32_t w=0;w<weight.GetSizeW();w++)
+  for(uint32_t z=0;z<weight.GetSizeZ();z++)
+   for(uint32_t y=0;y<weight.GetSizeY();y++)
+    for(uint32_t x=0;x<weight.GetSizeX();x++) weight.SetElement(w,z,y,x,distribution(generator));
+}
+
 int main(int argc,char **argv)
 {
  if (argc<3) return(3);
@@ -85,6 +108,10 @@ int main(int argc,char **argv)
   net_t net;
   Build(net);
   for(size_t n=0;n<net.size();n++) net[n]->Reset();
+  const uint32_t seed=(argc>4)?static_cast<uint32_t>(atoi(argv[4])):777u;
+  RedrawWeights<CNetLayerLinear<type_t> >(net[1].get(),seed);
+  RedrawWeights<CNetLayerBackConvolution<type_t> >(net[2].get(),seed+1);
+  RedrawWeights<CNetLayerConvolution<type_t> >(net[5].get(),seed+2);
   for(size_t n=0;n<net.size();n++) net[n]->TrainingModeAdam();
   for(size_t n=0;n<net.size();n++) net[n]->TrainingStart();
 

@@ -135,10 +135,14 @@ def test_own_layer_classes_match_the_cpu_twin(tmp_path, port, mode, tol):
     for n in range(1, 7):
         check("output of layer %d" % n, got["output_%d" % n], twin.outputs[n - 1], tol if exact else 4 * tol, exact)
     twin.backward(error)
-    # free-running comparison: in the tensor-core modes the rounding differences of the forward pass pass through the batch
-    # normalisation's backward pass (16 samples) and the step of LeakyReLU's derivative, so the bound on the way down is loose;
-    # the layer-by-layer comparisons on identical operands are in tests/test_gpu_nets.py and tests/test_gpu_full_size.py
-    down = 4 * tol if exact else 16 * tol
+    # Free-running comparison.  In plain TF32 the forward outputs agree to ~7e-4 (RMS), which puts a few of the 16384 inputs of
+    # LeakyReLU on the other side of zero; each of them changes the derivative from 0.1 to 1, and those elements pass down
+    # through the batch normalisation's backward pass (16 samples) and the transposed convolution.  Over twelve weight seeds
+    # of this program the RMS error of the tensors below the step lay between 1.4e-3 and 5.4e-2 in plain TF32 (2.5e-6 at most in
+    # 3xTF32, where no input changes side); the program draws its weights with a fixed seed, and the bound for plain TF32 is
+    # set above that range.  The layer-by-layer comparisons on identical operands, with the tight bounds, are in
+    # tests/test_gpu_nets.py and tests/test_gpu_full_size.py.
+    down = 4 * tol if exact else (0.1 if mode == 1 else 16 * tol)
     for n in (1, 2, 3, 5):          # own layers: the error that arrived at their output
         check("delta at layer %d" % n, got["delta_%d" % n], twin.deltas[n], down, exact)
     for n in (4, 6):                # the reference's function layers: f'(input) * error

@@ -34,6 +34,20 @@ int fail(int code, const char *fmt, ...)
 
 static std::atomic<unsigned long long> g_launches{0};
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+bool dependent_launch_enabled()
+{
+    static const bool on = !(getenv("B200CONV_PDL") && getenv("B200CONV_PDL")[0] == '0');
+    return on;
+}
+static thread_local cudaError_t g_launch_error = cudaSuccess;
+void note_launch_error(cudaError_t e) { if (g_launch_error == cudaSuccess) g_launch_error = e; }
+cudaError_t take_launch_error()
+{
+    const cudaError_t e = g_launch_error;
+    g_launch_error = cudaSuccess;
+    return e;
+}
 void set_path(int p) { g_path = p; }
 int precision() { return g_precision; }
 

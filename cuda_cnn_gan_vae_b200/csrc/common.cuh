@@ -24,11 +24,61 @@ int precision();
 
 // Every kernel launch of the library goes through this check, which also counts it.
 void count_launch();
-#define B200_LAUNCH_CHECK()          \
-    do {                             \
-        ::b200::count_launch();      \
-        B200_CUDA(cudaGetLastError()); \
+#define B200_LAUNCH_CHECK()                    \
+    do {                                       \
+        ::b200::count_launch();                \
+        B200_CUDA(::b200::take_launch_error()); \
+        B200_CUDA(cudaGetLastError());         \
     } while (0)
+
+// Programmatic dependent launch.  Every kernel of the library begins with grid_dependency_wait() (before its first access
+// to global memory: it returns once the kernels before it in the stream have completed and their writes are visible) and is
+// launched with the programmatic-stream-serialisation attribute, so its blocks are set up while the previous kernel drains
+// instead of after it has retired.  The training steps are chains of a hundred short launches; the hand-over between two of
+// them is a sizeable part of each.  No kernel signals early, so the order of all memory accesses is that of plain stream
+// order.  B200CONV_PDL=0 in the environment launches without the attribute (the wait is then a no-op).
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+bool dependent_launch_enabled();
+void note_launch_error(cudaError_t e);
+cudaError_t take_launch_error();
+
+struct Launch {
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[2];
+    Launch(dim3 grid, dim3 block, size_t smem = 0, cudaStream_t stream = 0)
+    {
+        cfg = cudaLaunchConfig_t{};
+        cfg.gridDim = grid;
+        cfg.blockDim = block;
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cfg.attrs = attr;
+        cfg.numAttrs = 0;
+        if (dependent_launch_enabled()) {
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.numAttrs = 1;
+        }
+    }
+    // thread-block cluster of `x` CTAs (the CTA-pair kernels)
+    Launch &cluster(unsigned x)
+    {
+        if (x > 1) {
+            cudaLaunchAttribute &a = attr[cfg.numAttrs++];
+            a.id = cudaLaunchAttributeClusterDimension;
+            a.val.clusterDim.x = x;
+            a.val.clusterDim.y = 1;
+            a.val.clusterDim.z = 1;
+        }
+        return *this;
+    }
+    template <typename... KArgs, typename... Args>
+    void operator()(void (*kernel)(KArgs...), Args &&...args) const
+    {
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+        if (e != cudaSuccess) note_launch_error(e);
+    }
+};
 
 // Scratch arena: one growing cudaMalloc block per device, carved by bump allocation for the
 // duration of one library call.  The stream order of the call protects reuse between calls on the

@@ -19,6 +19,7 @@ static inline int grid_for(size_t items)
 // out[w, pos] = in[w, pos] + (pos even ? sin : cos)(t[w] / 10000^(pos / n)),  pos = linear index inside one sample
 __global__ void time_step_kernel(float *__restrict__ out, const float *__restrict__ in, const uint32_t *__restrict__ time_step, int W, size_t n)
 {
+    grid_dependency_wait();
     const size_t total = (size_t)W * n;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t w = idx / n;
@@ -56,6 +57,7 @@ __global__ void __launch_bounds__(256) random_kernel(float *__restrict__ out, fl
                                                      const float *__restrict__ sa, const float *__restrict__ so, size_t n_per_w, size_t total,
                                                      unsigned long long seed, float p, float keep_scale)
 {
+    grid_dependency_wait();
     const size_t groups = (total + 3) / 4;
     for (size_t g = (size_t)blockIdx.x * blockDim.x + threadIdx.x; g < groups; g += (size_t)gridDim.x * blockDim.x) {
         const Philox r = philox4x32_10((uint32_t)g, (uint32_t)(g >> 32), 0u, 0u, (uint32_t)seed, (uint32_t)(seed >> 32));
@@ -90,6 +92,7 @@ __global__ void __launch_bounds__(256) random_kernel(float *__restrict__ out, fl
 __global__ void noisy_image_kernel(float *__restrict__ noisy, const float *__restrict__ image, const float *__restrict__ noise,
                                    const float *__restrict__ sa, const float *__restrict__ so, size_t n_per_w, size_t total)
 {
+    grid_dependency_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t w = i / n_per_w;
         noisy[i] = __fadd_rn(__fmul_rn(sa[w], image[i]), __fmul_rn(so[w], noise[i]));
@@ -108,7 +111,7 @@ int b200_set_time_step(float *out, const float *in, const uint32_t *time_step, i
     if (!out || !in || !time_step) return fail(B200_E_ARG, "null tensor pointer");
     if (w <= 0 || n > 0xFFFFFFFFull) return fail(B200_E_SHAPE, "CTensor::SetTimeStep: bad sizes");
     if (!n) return B200_OK;
-    time_step_kernel<<<grid_for((size_t)w * n), 256, 0, ST(stream)>>>(out, in, time_step, w, n);
+    Launch(grid_for((size_t)w * n), 256, 0, ST(stream))(time_step_kernel, out, in, time_step, w, n);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -117,7 +120,7 @@ int b200_normal_noise(float *out, size_t n, unsigned long long seed, void *strea
 {
     if (!out) return fail(B200_E_ARG, "null tensor pointer");
     if (!n) return B200_OK;
-    random_kernel<0><<<grid_for((n + 3) / 4), 256, 0, ST(stream)>>>(out, nullptr, nullptr, nullptr, nullptr, n, n, seed, 0.f, 0.f);
+    Launch(grid_for((n + 3) / 4), 256, 0, ST(stream))(random_kernel<0>, out, nullptr, nullptr, nullptr, nullptr, n, n, seed, 0.f, 0.f);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -127,7 +130,7 @@ int b200_dropout_mask(float *out, size_t n, float drop_out, unsigned long long s
     if (!out) return fail(B200_E_ARG, "null tensor pointer");
     if (!(drop_out >= 0.f && drop_out < 1.f)) return fail(B200_E_ARG, "drop-out probability must lie in [0, 1)");
     if (!n) return B200_OK;
-    random_kernel<2><<<grid_for((n + 3) / 4), 256, 0, ST(stream)>>>(out, nullptr, nullptr, nullptr, nullptr, n, n, seed, drop_out,
+    Launch(grid_for((n + 3) / 4), 256, 0, ST(stream))(random_kernel<2>, out, nullptr, nullptr, nullptr, nullptr, n, n, seed, drop_out,
                                                                    (float)(1.0 / (1.0 - drop_out)));
     B200_LAUNCH_CHECK();
     return B200_OK;
@@ -141,10 +144,10 @@ int b200_noisy_image(float *noisy, float *noise, const float *image, const float
     const size_t total = (size_t)w * n;
     if (!total) return B200_OK;
     if (generate)
-        random_kernel<1><<<grid_for((total + 3) / 4), 256, 0, ST(stream)>>>(noise, noisy, image, sqrt_alpha_bar, sqrt_one_minus_alpha_bar, n, total,
+        Launch(grid_for((total + 3) / 4), 256, 0, ST(stream))(random_kernel<1>, noise, noisy, image, sqrt_alpha_bar, sqrt_one_minus_alpha_bar, n, total,
                                                                            seed, 0.f, 0.f);
     else
-        noisy_image_kernel<<<grid_for(total), 256, 0, ST(stream)>>>(noisy, image, noise, sqrt_alpha_bar, sqrt_one_minus_alpha_bar, n, total);
+        Launch(grid_for(total), 256, 0, ST(stream))(noisy_image_kernel, noisy, image, noise, sqrt_alpha_bar, sqrt_one_minus_alpha_bar, n, total);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }

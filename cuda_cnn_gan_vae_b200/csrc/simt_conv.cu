@@ -13,6 +13,7 @@ __global__ void simt_conv_forward_kernel(b200_conv_geom g, float *__restrict__ o
                                          const float *__restrict__ kernel, int kernel_w,
                                          const float *__restrict__ bias, int bias_w)
 {
+    grid_dependency_wait();
     const size_t total = (size_t)out_w * g.kernel_amount * g.out_y * g.out_x;
     const int klen = g.in_z * g.kernel_y * g.kernel_x;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -45,6 +46,7 @@ __global__ void simt_conv_backward_kernel(b200_conv_geom g, float *__restrict__ 
                                           const float *__restrict__ kernel, int kernel_w,
                                           const float *__restrict__ bias, int bias_w)
 {
+    grid_dependency_wait();
     const size_t total = (size_t)out_w * g.in_z * g.in_y * g.in_x;
     const int klen = g.in_z * g.kernel_y * g.kernel_x;
     const int pad_y = g.kernel_y - 1 - g.padding_y, pad_x = g.kernel_x - 1 - g.padding_x;
@@ -86,6 +88,7 @@ __global__ void simt_conv_wgrad_kernel(b200_conv_geom g, float *__restrict__ dke
                                        const float *__restrict__ image, int image_w,
                                        const float *__restrict__ delta, int delta_w)
 {
+    grid_dependency_wait();
     const int klen = g.in_z * g.kernel_y * g.kernel_x;
     const size_t total = (size_t)dkernel_w * g.kernel_amount * klen;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -117,6 +120,7 @@ __global__ void simt_conv_wgrad_kernel(b200_conv_geom g, float *__restrict__ dke
 __global__ void simt_conv_dbias_kernel(int kernel_amount, int plane, float *__restrict__ dbias, int dbias_w,
                                        int dkernel_w, const float *__restrict__ delta, int delta_w)
 {
+    grid_dependency_wait();
     int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= dbias_w * kernel_amount) return;
     int f = idx % kernel_amount, wb = idx / kernel_amount;
@@ -140,7 +144,7 @@ int simt_conv_forward(const b200_conv_geom &g, float *out, int out_w, const floa
 {
     size_t total = (size_t)out_w * g.kernel_amount * g.out_y * g.out_x;
     if (!total) return B200_OK;
-    simt_conv_forward_kernel<<<grid_for(total, 256), 256, 0, s>>>(g, out, out_w, image, image_w, kernel, kernel_w, bias, bias_w);
+    Launch(grid_for(total, 256), 256, 0, s)(simt_conv_forward_kernel, g, out, out_w, image, image_w, kernel, kernel_w, bias, bias_w);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -150,7 +154,7 @@ int simt_conv_backward(const b200_conv_geom &g, float *out, int out_w, const flo
 {
     size_t total = (size_t)out_w * g.in_z * g.in_y * g.in_x;
     if (!total) return B200_OK;
-    simt_conv_backward_kernel<<<grid_for(total, 256), 256, 0, s>>>(g, out, out_w, delta, delta_w, kernel, kernel_w, bias, bias_w);
+    Launch(grid_for(total, 256), 256, 0, s)(simt_conv_backward_kernel, g, out, out_w, delta, delta_w, kernel, kernel_w, bias, bias_w);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -160,11 +164,11 @@ int simt_conv_wgrad(const b200_conv_geom &g, float *dkernel, int dkernel_w, floa
 {
     size_t total = (size_t)dkernel_w * g.kernel_amount * g.in_z * g.kernel_y * g.kernel_x;
     if (!total) return B200_OK;
-    simt_conv_wgrad_kernel<<<grid_for(total, 128), 128, 0, s>>>(g, dkernel, dkernel_w, image, image_w, delta, delta_w);
+    Launch(grid_for(total, 128), 128, 0, s)(simt_conv_wgrad_kernel, g, dkernel, dkernel_w, image, image_w, delta, delta_w);
     B200_LAUNCH_CHECK();
     if (dbias) {
         int n = dbias_w * g.kernel_amount;
-        simt_conv_dbias_kernel<<<ceil_div(n, 128), 128, 0, s>>>(g.kernel_amount, g.out_y * g.out_x, dbias, dbias_w,
+        Launch(ceil_div(n, 128), 128, 0, s)(simt_conv_dbias_kernel, g.kernel_amount, g.out_y * g.out_x, dbias, dbias_w,
                                                                dkernel_w, delta, delta_w);
         B200_LAUNCH_CHECK();
     }

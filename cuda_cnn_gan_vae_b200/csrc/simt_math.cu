@@ -32,6 +32,7 @@ struct OpDiv { float ls, rs; __device__ float operator()(float l, float r) const
 // out[p] (cols x rows) = in[p]^T (rows x cols) for every (w,z) plane p; 32x32 shared-memory tiles
 __global__ void transpose_kernel(float *__restrict__ out, const float *__restrict__ in, int rows, int cols)
 {
+    grid_dependency_wait();
     __shared__ float tile[32][33];
     const size_t plane = (size_t)blockIdx.z * rows * cols;
     const int x0 = blockIdx.x * 32, y0 = blockIdx.y * 32;
@@ -50,6 +51,7 @@ template <class F, bool VEC>
 __global__ void binary_kernel(float *__restrict__ out, int out_w, const float *left, int left_w,
                               const float *right, int right_w, size_t n, F f)
 {
+    grid_dependency_wait();
     const size_t per_w = VEC ? n / 4 : n;
     const size_t total = per_w * out_w;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -74,8 +76,8 @@ static int launch_binary(float *out, int out_w, const float *left, int left_w, c
     if (!n) return B200_OK;
     bool vec = (n % 4 == 0) && aligned16(out) && aligned16(left) && aligned16(right);
     size_t total = (vec ? n / 4 : n) * out_w;
-    if (vec) binary_kernel<F, true><<<stream_grid(total, 256), 256, 0, s>>>(out, out_w, left, left_w, right, right_w, n, f);
-    else binary_kernel<F, false><<<stream_grid(total, 256), 256, 0, s>>>(out, out_w, left, left_w, right, right_w, n, f);
+    if (vec) Launch(stream_grid(total, 256), 256, 0, s)(binary_kernel<F, true>, out, out_w, left, left_w, right, right_w, n, f);
+    else Launch(stream_grid(total, 256), 256, 0, s)(binary_kernel<F, false>, out, out_w, left, left_w, right, right_w, n, f);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -98,6 +100,7 @@ __device__ __forceinline__ float unary_apply(float v, int op, float a, float b)
 
 __global__ void unary_kernel(float *__restrict__ out, int out_w, const float *in, int in_w, size_t n, int op, float a, float b)
 {
+    grid_dependency_wait();
     const size_t total = n * out_w;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         size_t w = idx / n, i = idx - w * n;
@@ -107,6 +110,7 @@ __global__ void unary_kernel(float *__restrict__ out, int out_w, const float *in
 
 __global__ void fill_kernel(float *__restrict__ out, size_t n, float v)
 {
+    grid_dependency_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) out[i] = v;
 }
 
@@ -118,6 +122,7 @@ __global__ void fill_kernel(float *__restrict__ out, size_t n, float v)
 __global__ void add_sum_w_kernel(float *out, int out_w, const float *left, int left_w, const float *right, int right_w,
                                  size_t n, float ls, float rs)
 {
+    grid_dependency_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         float sl = 0.f, sr = 0.f;
         for (int w = 0; w < left_w; w++) sl = __fadd_rn(sl, left[(size_t)w * n + i]);
@@ -136,6 +141,7 @@ template <bool VEC>
 __global__ void bias_act_kernel(float *t, float *pre, int t_w, int z, size_t yx, const float *__restrict__ bias, int bias_w,
                                 int func, double slope)
 {
+    grid_dependency_wait();
     const size_t per_plane = VEC ? yx / 4 : yx;
     const size_t total = per_plane * z * t_w;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -163,6 +169,7 @@ __global__ void bias_act_kernel(float *t, float *pre, int t_w, int z, size_t yx,
 __global__ void activation_kernel(float *__restrict__ out, const float *__restrict__ in, const float *__restrict__ err,
                                   size_t n, int func, int derivative, double slope)
 {
+    grid_dependency_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         float v = in[i];
         float r = derivative ? act_derivative(v, func, slope) : act_apply(v, func, slope);
@@ -174,6 +181,7 @@ __global__ void activation_kernel(float *__restrict__ out, const float *__restri
 __global__ void activation_vec_kernel(float4 *__restrict__ out, const float4 *__restrict__ in, const float4 *__restrict__ err,
                                       size_t n4, int func, int derivative, double slope)
 {
+    grid_dependency_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
         const float4 v = in[i];
         float4 r;
@@ -196,10 +204,10 @@ static void launch_activation(float *out, const float *in, const float *err, siz
                               cudaStream_t s)
 {
     if (n % 4 == 0 && aligned16(out) && aligned16(in) && (!err || aligned16(err)))
-        activation_vec_kernel<<<stream_grid(n / 4, 256), 256, 0, s>>>(reinterpret_cast<float4 *>(out), reinterpret_cast<const float4 *>(in),
+        Launch(stream_grid(n / 4, 256), 256, 0, s)(activation_vec_kernel, reinterpret_cast<float4 *>(out), reinterpret_cast<const float4 *>(in),
                                                                      reinterpret_cast<const float4 *>(err), n / 4, func, derivative, slope);
     else
-        activation_kernel<<<stream_grid(n, 256), 256, 0, s>>>(out, in, err, n, func, derivative, slope);
+        Launch(stream_grid(n, 256), 256, 0, s)(activation_kernel, out, in, err, n, func, derivative, slope);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -215,6 +223,7 @@ __device__ __forceinline__ float warp_sum(float v)
 
 __global__ void summ_xy_kernel(float *__restrict__ out, int out_w, const float *__restrict__ in, int in_w, int z, size_t yx)
 {
+    grid_dependency_wait();
     __shared__ float part[32];
     const int planes = out_w * z;
     for (int p = blockIdx.x; p < planes; p += gridDim.x) {
@@ -245,6 +254,7 @@ __global__ void summ_xy_kernel(float *__restrict__ out, int out_w, const float *
 __global__ void maxpool_kernel(float *__restrict__ out, uint2 *__restrict__ pos, const float *__restrict__ in,
                                size_t planes, int in_y, int in_x, int pool_x, int pool_y, int vec2)
 {
+    grid_dependency_wait();
     const int oy = in_y / pool_y, ox = in_x / pool_x;
     const size_t total = planes * oy * ox;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -279,6 +289,7 @@ __global__ void maxpool_kernel(float *__restrict__ out, uint2 *__restrict__ pos,
 __global__ void maxpool_backward_kernel(float *__restrict__ out, const uint2 *__restrict__ pos, const float *__restrict__ delta,
                                         size_t planes, int out_y, int out_x, int pool_x, int pool_y)
 {
+    grid_dependency_wait();
     const int dy = out_y / pool_y, dx = out_x / pool_x;
     const size_t total = planes * out_y * out_x;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -302,6 +313,7 @@ __global__ void maxpool_backward_kernel(float *__restrict__ out, const uint2 *__
 __global__ void maxpool_backward_2x2_kernel(float *__restrict__ out, const uint2 *__restrict__ pos, const float *__restrict__ delta,
                                             unsigned rows, unsigned dx)
 {
+    grid_dependency_wait();
     // rows = planes * dy window rows; each owns two output rows of 2*dx floats
     const size_t total = (size_t)rows * dx;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -322,6 +334,7 @@ __global__ void maxpool_backward_2x2_kernel(float *__restrict__ out, const uint2
 // factor 2 in both directions: one thread per input element, two 8-byte stores
 __global__ void upsample_2x2_kernel(float *__restrict__ out, const float *__restrict__ in, unsigned rows, unsigned in_x)
 {
+    grid_dependency_wait();
     const size_t total = (size_t)rows * in_x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const unsigned x = (unsigned)(i % in_x);
@@ -337,6 +350,7 @@ __global__ void upsample_2x2_kernel(float *__restrict__ out, const float *__rest
 // the reference's order (column by column, rows inside)
 __global__ void downsample_2x2_kernel(float *__restrict__ out, const float *__restrict__ in, unsigned rows, unsigned out_x)
 {
+    grid_dependency_wait();
     const size_t total = (size_t)rows * out_x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const unsigned x = (unsigned)(i % out_x);
@@ -354,6 +368,7 @@ __global__ void downsample_2x2_kernel(float *__restrict__ out, const float *__re
 __global__ void upsample_kernel(float *__restrict__ out, const float *__restrict__ in, size_t planes, int in_y, int in_x,
                                 int out_y, int out_x, int ux, int uy)
 {
+    grid_dependency_wait();
     const size_t total = planes * out_y * out_x;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         int x = idx % out_x;
@@ -368,6 +383,7 @@ __global__ void upsample_kernel(float *__restrict__ out, const float *__restrict
 __global__ void downsample_kernel(float *__restrict__ out, const float *__restrict__ in, size_t planes, int in_y, int in_x,
                                   int out_y, int out_x, int dsx, int dsy)
 {
+    grid_dependency_wait();
     const size_t total = planes * out_y * out_x;
     const float div = (float)(dsx * dsy);
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -399,6 +415,7 @@ __global__ void bn_forward_kernel(float *__restrict__ y, float *__restrict__ xha
                                   const float *__restrict__ x, const float *__restrict__ gamma, const float *__restrict__ beta,
                                   int W, size_t n, float momentum, float eps)
 {
+    grid_dependency_wait();
     const float invN = (float)(1.0 / (double)(float)W);
     const float om = (float)(1.0 - (double)momentum);
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
@@ -432,6 +449,7 @@ __global__ void __launch_bounds__(128) bn_forward_reg_kernel(float *__restrict__
                                       const float *__restrict__ x, const float *__restrict__ gamma, const float *__restrict__ beta,
                                       int W, size_t n, float momentum, float eps)
 {
+    grid_dependency_wait();
     const float invN = (float)(1.0 / (double)(float)W);
     const float om = (float)(1.0 - (double)momentum);
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
@@ -468,6 +486,7 @@ __global__ void __launch_bounds__(128) bn_backward_reg_kernel(float *dx, float *
                                        const float *__restrict__ xhat, const float *__restrict__ ivar, const float *__restrict__ gamma,
                                        int W, size_t n, int create_delta_weight)
 {
+    grid_dependency_wait();
     const float N = (float)W;
     const float invN = (float)(1.0 / (double)N);
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
@@ -547,6 +566,7 @@ __global__ void __launch_bounds__(TW) bn_forward_smem_kernel(float *__restrict__
                                       const float *__restrict__ x, const float *__restrict__ gamma, const float *__restrict__ beta,
                                       int W, size_t n, float momentum, float eps, unsigned *status, int func, double slope)
 {
+    grid_dependency_wait();
     // func >= 0: the activation of the function layer that follows is applied to the output (y = f(gamma*xhat + beta))
     extern __shared__ __align__(128) float xs[];          // [W][TW]
     __shared__ __align__(8) unsigned long long bar_storage;
@@ -600,6 +620,7 @@ __global__ void __launch_bounds__(2 * TW) bn_backward_smem_kernel(float *__restr
                                        int W, size_t n, int create_delta_weight, unsigned *status, const float *__restrict__ beta, int func,
                                        double slope)
 {
+    grid_dependency_wait();
     // func >= 0: dy is the error above the function layer that follows this one; it is first multiplied by f'(gamma*xhat + beta)
     // (the layer's output, recomputed from xhat), which is what that function layer would have handed down
     extern __shared__ __align__(128) float xs[];          // dy rows [W][TW], xhat rows [W][TW]
@@ -671,6 +692,7 @@ __global__ void bn_backward_kernel(float *dx, float *dgamma, float *dbeta, const
                                    const float *__restrict__ xhat, const float *__restrict__ ivar, const float *__restrict__ gamma,
                                    int W, size_t n, int create_delta_weight)
 {
+    grid_dependency_wait();
     const float N = (float)W;
     const float invN = (float)(1.0 / (double)N);
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
@@ -705,6 +727,7 @@ __global__ void bn_backward_kernel(float *dx, float *dgamma, float *dbeta, const
 __global__ void vae_forward_kernel(float *__restrict__ z, const float *__restrict__ mu, const float *__restrict__ logvar,
                                    const float *__restrict__ eps, size_t total, float *kl_partial)
 {
+    grid_dependency_wait();
     __shared__ float part[32];
     float kl = 0.f;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -727,6 +750,7 @@ __global__ void vae_backward_kernel(float *__restrict__ d_mu, float *__restrict_
                                     const float *__restrict__ mu, const float *__restrict__ logvar, const float *__restrict__ eps,
                                     size_t total, float k)
 {
+    grid_dependency_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         float lv = logvar[i], d = delta[i];
         d_logvar[i] = d * (0.5f * eps[i] * expf(lv * 0.5f)) - 0.5f * (1.f - expf(lv)) * k;
@@ -742,6 +766,7 @@ __global__ void __launch_bounds__(256) adam_kernel(float *__restrict__ weight, c
                                                    float *__restrict__ v, float *__restrict__ ema, size_t n, AdamArgs a,
                                                    const double *__restrict__ corrections, int vec)
 {
+    grid_dependency_wait();
     if (corrections) { a.inv_c1 = 1.0 / corrections[0]; a.inv_c2 = 1.0 / corrections[1]; }
     const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (size_t)gridDim.x * blockDim.x;
     const size_t n4 = vec ? n / 4 : 0;
@@ -773,8 +798,8 @@ static int launch_adam(float *weight, const float *dweight, float *m, float *v, 
 {
     const int vec = aligned16(weight) && aligned16(dweight) && aligned16(m) && aligned16(v) && (!ema || aligned16(ema));
     const int grid = stream_grid(vec ? (n + 3) / 4 : n, 256);
-    if (ema) adam_kernel<true><<<grid, 256, 0, s>>>(weight, dweight, m, v, ema, n, a, corrections, vec);
-    else adam_kernel<false><<<grid, 256, 0, s>>>(weight, dweight, m, v, nullptr, n, a, corrections, vec);
+    if (ema) Launch(grid, 256, 0, s)(adam_kernel<true>, weight, dweight, m, v, ema, n, a, corrections, vec);
+    else Launch(grid, 256, 0, s)(adam_kernel<false>, weight, dweight, m, v, nullptr, n, a, corrections, vec);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -785,6 +810,7 @@ static int launch_adam(float *weight, const float *dweight, float *m, float *v, 
 __global__ void simt_mul_kernel(float *__restrict__ out, int out_w, const float *__restrict__ left, int left_w,
                                 const float *__restrict__ right, int right_w, int Z, int LY, int LX, int RX, int tl)
 {
+    grid_dependency_wait();
     // tl == 0: out (LY x RX) = left (LY x LX) * right (LX x RX)
     // tl == 1: out (LX x RX) = left^T, left is (LY x LX), right (LY x RX)
     const int OR = tl ? LX : LY, KD = tl ? LY : LX;
@@ -812,6 +838,7 @@ __global__ void simt_mul_kernel(float *__restrict__ out, int out_w, const float 
 __global__ void warp_dot_kernel(float *__restrict__ out, int out_w, const float *__restrict__ left, int left_w,
                                 const float *__restrict__ right, int right_w, int Z, int LY, int LX)
 {
+    grid_dependency_wait();
     const int lane = threadIdx.x & 31;
     const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
     const size_t total = (size_t)out_w * Z * LY;
@@ -843,6 +870,7 @@ __global__ void warp_dot_kernel(float *__restrict__ out, int out_w, const float 
 __global__ void __launch_bounds__(256) block_dot_kernel(float *__restrict__ out, int out_w, const float *__restrict__ left, int left_w,
                                                         const float *__restrict__ right, int right_w, int Z, int LY, int LX)
 {
+    grid_dependency_wait();
     __shared__ float part[8];
     const size_t idx = blockIdx.x;
     const int y = idx % LY;
@@ -877,11 +905,11 @@ int warp_dot_mul(float *out, int out_w, const float *left, int left_w, const flo
     const size_t total = (size_t)out_w * z * ly;
     if (!total) return B200_OK;
     if (total <= (size_t)sm_count() * 8 && lx >= 1024) {
-        block_dot_kernel<<<(unsigned)total, 256, 0, s>>>(out, out_w, left, left_w, right, right_w, z, ly, lx);
+        Launch((unsigned)total, 256, 0, s)(block_dot_kernel, out, out_w, left, left_w, right, right_w, z, ly, lx);
         B200_LAUNCH_CHECK();
         return B200_OK;
     }
-    warp_dot_kernel<<<stream_grid(total * 32, 256), 256, 0, s>>>(out, out_w, left, left_w, right, right_w, z, ly, lx);
+    Launch(stream_grid(total * 32, 256), 256, 0, s)(warp_dot_kernel, out, out_w, left, left_w, right, right_w, z, ly, lx);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -891,7 +919,7 @@ int simt_mul(float *out, int out_w, const float *left, int left_w, const float *
 {
     size_t total = (size_t)out_w * z * (transpose_left ? lx : ly) * rx;
     if (!total) return B200_OK;
-    simt_mul_kernel<<<stream_grid(total, 256), 256, 0, s>>>(out, out_w, left, left_w, right, right_w, z, ly, lx, rx, transpose_left);
+    Launch(stream_grid(total, 256), 256, 0, s)(simt_mul_kernel, out, out_w, left, left_w, right, right_w, z, ly, lx, rx, transpose_left);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -921,6 +949,7 @@ int b200_div(float *out, int out_w, const float *left, int left_w, const float *
 // of in[w] go to a[w], the rest to b[w] (split != 0).  yx = Y*X elements per plane.
 __global__ void concat_split_z_kernel(float *cat, int cat_w, float *a, int aw, int za, float *b, int bw, int zb, size_t yx, int split)
 {
+    grid_dependency_wait();
     const int z_all = za + zb;
     const size_t total = (size_t)cat_w * z_all * yx;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -939,7 +968,7 @@ int b200_concat_z(float *out, int out_w, const float *a, int a_w, int a_z, const
     if (out_w <= 0 || a_w <= 0 || b_w <= 0 || a_z <= 0 || b_z <= 0) return fail(B200_E_SHAPE, "non-positive size");
     const size_t total = (size_t)out_w * (a_z + b_z) * yx;
     if (!total) return B200_OK;
-    concat_split_z_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(out, out_w, const_cast<float *>(a), a_w, a_z, const_cast<float *>(b), b_w, b_z, yx, 0);
+    Launch(stream_grid(total, 256), 256, 0, ST(stream))(concat_split_z_kernel, out, out_w, const_cast<float *>(a), a_w, a_z, const_cast<float *>(b), b_w, b_z, yx, 0);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -950,7 +979,7 @@ int b200_split_z(float *out_a, int a_z, float *out_b, int b_z, const float *in, 
     if (w <= 0 || a_z <= 0 || b_z <= 0) return fail(B200_E_SHAPE, "non-positive size");
     const size_t total = (size_t)w * (a_z + b_z) * yx;
     if (!total) return B200_OK;
-    concat_split_z_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(const_cast<float *>(in), w, out_a, w, a_z, out_b, w, b_z, yx, 1);
+    Launch(stream_grid(total, 256), 256, 0, ST(stream))(concat_split_z_kernel, const_cast<float *>(in), w, out_a, w, a_z, out_b, w, b_z, yx, 1);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -961,7 +990,7 @@ int b200_transpose(float *out, const float *in, int planes, int rows, int cols, 
     if (planes <= 0 || rows <= 0 || cols <= 0) return fail(B200_E_SHAPE, "non-positive matrix size");
     if (planes > 65535) return fail(B200_E_SHAPE, "too many planes for one transpose call");
     dim3 grid((cols + 31) / 32, (rows + 31) / 32, planes), block(32, 8);
-    transpose_kernel<<<grid, block, 0, ST(stream)>>>(out, in, rows, cols);
+    Launch(grid, block, 0, ST(stream))(transpose_kernel, out, in, rows, cols);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -978,7 +1007,7 @@ int b200_add_sum_w(float *out, int out_w, const float *left, int left_w, const f
     if (!out || !left || !right) return fail(B200_E_ARG, "null tensor pointer");
     if (out_w <= 0 || left_w <= 0 || right_w <= 0) return fail(B200_E_SHAPE, "non-positive W count");
     if (!n) return B200_OK;
-    add_sum_w_kernel<<<stream_grid(n, 128), 128, 0, ST(stream)>>>(out, out_w, left, left_w, right, right_w, n, ls, rs);
+    Launch(stream_grid(n, 128), 128, 0, ST(stream))(add_sum_w_kernel, out, out_w, left, left_w, right, right_w, n, ls, rs);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -992,8 +1021,8 @@ static int bias_act_launch(float *t, float *pre, int t_w, int z, size_t yx, cons
     if (!yx) return B200_OK;
     bool vec = (yx % 4 == 0) && aligned16(t) && (!pre || aligned16(pre));
     size_t total = (vec ? yx / 4 : yx) * z * t_w;
-    if (vec) bias_act_kernel<true><<<stream_grid(total, 256), 256, 0, s>>>(t, pre, t_w, z, yx, bias, bias_w, func, leaky_slope);
-    else bias_act_kernel<false><<<stream_grid(total, 256), 256, 0, s>>>(t, pre, t_w, z, yx, bias, bias_w, func, leaky_slope);
+    if (vec) Launch(stream_grid(total, 256), 256, 0, s)(bias_act_kernel<true>, t, pre, t_w, z, yx, bias, bias_w, func, leaky_slope);
+    else Launch(stream_grid(total, 256), 256, 0, s)(bias_act_kernel<false>, t, pre, t_w, z, yx, bias, bias_w, func, leaky_slope);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -1016,7 +1045,7 @@ int b200_summ_xy(float *out, int out_w, const float *in, int in_w, int z, size_t
     int planes = out_w * z;
     int block = yx >= 4096 ? 256 : (yx >= 512 ? 128 : 32);
     int grid = planes < sm_count() * 16 ? planes : sm_count() * 16;
-    summ_xy_kernel<<<grid, block, 0, ST(stream)>>>(out, out_w, in, in_w, z, yx);
+    Launch(grid, block, 0, ST(stream))(summ_xy_kernel, out, out_w, in, in_w, z, yx);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -1026,7 +1055,7 @@ int b200_unary(float *out, int out_w, const float *in, int in_w, size_t n, int o
     if (!out || !in) return fail(B200_E_ARG, "null tensor pointer");
     if (out_w <= 0 || in_w <= 0 || op < 0 || op > 6) return fail(B200_E_ARG, "bad unary arguments");
     if (!n) return B200_OK;
-    unary_kernel<<<stream_grid(n * out_w, 256), 256, 0, ST(stream)>>>(out, out_w, in, in_w, n, op, a, b);
+    Launch(stream_grid(n * out_w, 256), 256, 0, ST(stream))(unary_kernel, out, out_w, in, in_w, n, op, a, b);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -1035,7 +1064,7 @@ int b200_fill(float *out, size_t n, float value, void *stream)
 {
     if (!out) return fail(B200_E_ARG, "null tensor pointer");
     if (!n) return B200_OK;
-    fill_kernel<<<stream_grid(n, 256), 256, 0, ST(stream)>>>(out, n, value);
+    Launch(stream_grid(n, 256), 256, 0, ST(stream))(fill_kernel, out, n, value);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -1072,7 +1101,7 @@ int b200_maxpool(float *out, uint32_t *pos, const float *in, int w, int z, int i
     // positions are {X, Y} pairs stored with one 8-byte access each
     if ((uintptr_t)pos & 7) return fail(B200_E_ARG, "max-pooling: the position tensor must be 8-byte aligned");
     const int vec2 = pool_x == 2 && pool_y == 2 && in_x % 2 == 0 && ((uintptr_t)in & 7) == 0;
-    maxpool_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(out, reinterpret_cast<uint2 *>(pos), in, planes, in_y, in_x, pool_x, pool_y, vec2);
+    Launch(stream_grid(total, 256), 256, 0, ST(stream))(maxpool_kernel, out, reinterpret_cast<uint2 *>(pos), in, planes, in_y, in_x, pool_x, pool_y, vec2);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -1087,10 +1116,10 @@ int b200_maxpool_backward(float *out, const uint32_t *pos, const float *delta, i
     if (!total) return B200_OK;
     if ((uintptr_t)pos & 7) return fail(B200_E_ARG, "max-pooling: the position tensor must be 8-byte aligned");
     if (pool_x == 2 && pool_y == 2 && out_x % 2 == 0 && out_y % 2 == 0 && ((uintptr_t)out % 8) == 0 && planes * (size_t)(out_y / 2) < 0xFFFFFFFFull)
-        maxpool_backward_2x2_kernel<<<stream_grid(total / 4, 256), 256, 0, ST(stream)>>>(out, reinterpret_cast<const uint2 *>(pos), delta,
+        Launch(stream_grid(total / 4, 256), 256, 0, ST(stream))(maxpool_backward_2x2_kernel, out, reinterpret_cast<const uint2 *>(pos), delta,
                                                                                        (unsigned)(planes * (out_y / 2)), (unsigned)(out_x / 2));
     else
-        maxpool_backward_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(out, reinterpret_cast<const uint2 *>(pos), delta, planes,
+        Launch(stream_grid(total, 256), 256, 0, ST(stream))(maxpool_backward_kernel, out, reinterpret_cast<const uint2 *>(pos), delta, planes,
                                                                                out_y, out_x, pool_x, pool_y);
     B200_LAUNCH_CHECK();
     return B200_OK;
@@ -1104,9 +1133,9 @@ int b200_upsample(float *out, const float *in, int w, int z, int in_y, int in_x,
     size_t total = planes * in_y * uy * in_x * ux;
     if (!total) return B200_OK;
     if (ux == 2 && uy == 2 && ((uintptr_t)out % 8) == 0 && planes * (size_t)in_y < 0xFFFFFFFFull)
-        upsample_2x2_kernel<<<stream_grid(total / 4, 256), 256, 0, ST(stream)>>>(out, in, (unsigned)(planes * in_y), (unsigned)in_x);
+        Launch(stream_grid(total / 4, 256), 256, 0, ST(stream))(upsample_2x2_kernel, out, in, (unsigned)(planes * in_y), (unsigned)in_x);
     else
-        upsample_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(out, in, planes, in_y, in_x, in_y * uy, in_x * ux, ux, uy);
+        Launch(stream_grid(total, 256), 256, 0, ST(stream))(upsample_kernel, out, in, planes, in_y, in_x, in_y * uy, in_x * ux, ux, uy);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -1119,9 +1148,9 @@ int b200_downsample(float *out, const float *in, int w, int z, int in_y, int in_
     size_t total = planes * (in_y / dy) * (in_x / dx);
     if (!total) return B200_OK;
     if (dx == 2 && dy == 2 && in_x % 2 == 0 && in_y % 2 == 0 && ((uintptr_t)in % 8) == 0 && planes * (size_t)(in_y / 2) < 0xFFFFFFFFull)
-        downsample_2x2_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(out, in, (unsigned)(planes * (in_y / 2)), (unsigned)(in_x / 2));
+        Launch(stream_grid(total, 256), 256, 0, ST(stream))(downsample_2x2_kernel, out, in, (unsigned)(planes * (in_y / 2)), (unsigned)(in_x / 2));
     else
-        downsample_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(out, in, planes, in_y, in_x, in_y / dy, in_x / dx, dx, dy);
+        Launch(stream_grid(total, 256), 256, 0, ST(stream))(downsample_kernel, out, in, planes, in_y, in_x, in_y / dy, in_x / dx, dx, dy);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -1141,18 +1170,18 @@ static int bn_forward_impl(float *y, float *xhat, float *ivar, float *mean, floa
             int r = status_word(&status);
             if (r) return r;
             B200_CUDA(cudaFuncSetAttribute(bn_forward_smem_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            bn_forward_smem_kernel<128><<<(unsigned)((n + 127) / 128), 128, smem, ST(stream)>>>(
+            Launch((unsigned)((n + 127) / 128), 128, smem, ST(stream))(bn_forward_smem_kernel<128>, 
                 y, xhat, ivar, mean, var, new_mean, new_var, x, gamma, beta, w, n, momentum, eps, status, func, leaky_slope);
             B200_LAUNCH_CHECK();
             return B200_OK;
         }
     }
-#define B200_BN_FWD(WMAX) bn_forward_reg_kernel<WMAX><<<stream_grid(n, 128), 128, 0, ST(stream)>>>(y, xhat, ivar, mean, var, new_mean, new_var, x, gamma, beta, w, n, momentum, eps)
+#define B200_BN_FWD(WMAX) Launch(stream_grid(n, 128), 128, 0, ST(stream))(bn_forward_reg_kernel<WMAX>, y, xhat, ivar, mean, var, new_mean, new_var, x, gamma, beta, w, n, momentum, eps)
     if (w <= 16) B200_BN_FWD(16);
     else if (w <= 32) B200_BN_FWD(32);
     else if (w <= 64) B200_BN_FWD(64);
     else if (w <= 128) B200_BN_FWD(128);
-    else bn_forward_kernel<<<stream_grid(n, 128), 128, 0, ST(stream)>>>(y, xhat, ivar, mean, var, new_mean, new_var, x, gamma, beta,
+    else Launch(stream_grid(n, 128), 128, 0, ST(stream))(bn_forward_kernel, y, xhat, ivar, mean, var, new_mean, new_var, x, gamma, beta,
                                                                        w, n, momentum, eps);
 #undef B200_BN_FWD
     B200_LAUNCH_CHECK();
@@ -1180,6 +1209,7 @@ int b200_bn_act_forward(float *out, float *xhat, float *ivar, float *mean, float
 __global__ void bn_act_delta_kernel(float *dx, const float *error, const float *__restrict__ xhat, const float *__restrict__ gamma,
                                     const float *__restrict__ beta, size_t total, size_t n, int func, double slope)
 {
+    grid_dependency_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t i = idx % n;
         const float o = __fadd_rn(__fmul_rn(gamma[i], xhat[idx]), beta[i]);
@@ -1203,7 +1233,7 @@ static int bn_backward_impl(float *dx, float *dgamma, float *dbeta, const float 
             int r = status_word(&status);
             if (r) return r;
             B200_CUDA(cudaFuncSetAttribute(bn_backward_smem_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            bn_backward_smem_kernel<64><<<(unsigned)((n + 63) / 64), 128, smem, ST(stream)>>>(
+            Launch((unsigned)((n + 63) / 64), 128, smem, ST(stream))(bn_backward_smem_kernel<64>, 
                 dx, dgamma, dbeta, dy, xhat, ivar, gamma, w, n, create_delta_weight, status, beta, func, leaky_slope);
             B200_LAUNCH_CHECK();
             return B200_OK;
@@ -1211,15 +1241,15 @@ static int bn_backward_impl(float *dx, float *dgamma, float *dbeta, const float 
     }
     if (func >= 0) {
         // general kernels: the error is first turned into the function layer's delta, in place in dx
-        bn_act_delta_kernel<<<stream_grid((size_t)w * n, 256), 256, 0, ST(stream)>>>(dx, dy, xhat, gamma, beta, (size_t)w * n, n, func, leaky_slope);
+        Launch(stream_grid((size_t)w * n, 256), 256, 0, ST(stream))(bn_act_delta_kernel, dx, dy, xhat, gamma, beta, (size_t)w * n, n, func, leaky_slope);
         B200_LAUNCH_CHECK();
         dy = dx;
     }
-#define B200_BN_BWD(WMAX) bn_backward_reg_kernel<WMAX><<<stream_grid(n, 128), 128, 0, ST(stream)>>>(dx, dgamma, dbeta, dy, xhat, ivar, gamma, w, n, create_delta_weight)
+#define B200_BN_BWD(WMAX) Launch(stream_grid(n, 128), 128, 0, ST(stream))(bn_backward_reg_kernel<WMAX>, dx, dgamma, dbeta, dy, xhat, ivar, gamma, w, n, create_delta_weight)
     if (w <= 16) B200_BN_BWD(16);
     else if (w <= 32) B200_BN_BWD(32);
     else if (w <= 64) B200_BN_BWD(64);
-    else bn_backward_kernel<<<stream_grid(n, 128), 128, 0, ST(stream)>>>(dx, dgamma, dbeta, dy, xhat, ivar, gamma, w, n, create_delta_weight);
+    else Launch(stream_grid(n, 128), 128, 0, ST(stream))(bn_backward_kernel, dx, dgamma, dbeta, dy, xhat, ivar, gamma, w, n, create_delta_weight);
 #undef B200_BN_BWD
     B200_LAUNCH_CHECK();
     return B200_OK;
@@ -1255,7 +1285,7 @@ int b200_vae_forward(float *z, const float *mu, const float *logvar, const float
         arena_reset();
         partial = (float *)arena_take(sizeof(float) * grid);
     }
-    vae_forward_kernel<<<grid, 256, 0, ST(stream)>>>(z, mu, logvar, eps, total, partial);
+    Launch(grid, 256, 0, ST(stream))(vae_forward_kernel, z, mu, logvar, eps, total, partial);
     B200_LAUNCH_CHECK();
     if (kl_host) {
         float *h = (float *)malloc(sizeof(float) * grid);
@@ -1276,7 +1306,7 @@ int b200_vae_backward(float *d_mu, float *d_logvar, const float *delta, const fl
 {
     if (!d_mu || !d_logvar || !delta || !mu || !logvar || !eps) return fail(B200_E_ARG, "null tensor pointer");
     if (!total) return B200_OK;
-    vae_backward_kernel<<<stream_grid(total, 256), 256, 0, ST(stream)>>>(d_mu, d_logvar, delta, mu, logvar, eps, total, kl_speed);
+    Launch(stream_grid(total, 256), 256, 0, ST(stream))(vae_backward_kernel, d_mu, d_logvar, delta, mu, logvar, eps, total, kl_speed);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }

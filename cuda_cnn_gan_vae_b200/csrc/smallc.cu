@@ -19,6 +19,7 @@ namespace b200 {
 __global__ void im2col_pack_kernel(float *__restrict__ hi, float *__restrict__ lo, const float *__restrict__ x, int N, int C, int H, int W,
                                    int OH, int OW, int kh, int kw, int sy, int sx, int py, int px, int cp)
 {
+    grid_dependency_wait();
     const int cc = C * kh * kw;
     const int row_elems = OW * cp;
     for (int row = blockIdx.x; row < N * OH; row += gridDim.x) {
@@ -46,6 +47,7 @@ __global__ void im2col_pack_kernel(float *__restrict__ hi, float *__restrict__ l
 __global__ void smallc_weight_kernel(float *__restrict__ hi, float *__restrict__ lo, const float *__restrict__ w, int K, int C, int taps,
                                      int pitch, int transposed)
 {
+    grid_dependency_wait();
     const int cc = C * taps;
     const int rows = transposed ? cc : K, inner = transposed ? K : cc;
     const size_t total = (size_t)rows * pitch;
@@ -68,6 +70,7 @@ __global__ void smallc_weight_kernel(float *__restrict__ hi, float *__restrict__
 __global__ void col2im_gather_kernel(float *__restrict__ dx, const float *__restrict__ t, int N, int C, int H, int W, int OH, int OW,
                                      int kh, int kw, int sy, int sx, int py, int px)
 {
+    grid_dependency_wait();
     const int cc = C * kh * kw;
     for (int row = blockIdx.x; row < N * C * H; row += gridDim.x) {
         const int y = row % H;
@@ -100,6 +103,7 @@ __global__ void col2im_gather_kernel(float *__restrict__ dx, const float *__rest
 // dkernel[k][c*taps + tap] (+)= dk[k][tap*C + c]
 __global__ void smallc_dkernel_kernel(float *__restrict__ dkernel, const float *__restrict__ dk, int K, int C, int taps, int accumulate)
 {
+    grid_dependency_wait();
     const int cc = C * taps;
     const int total = K * cc;
     for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
@@ -136,7 +140,7 @@ b200_conv_geom smallc_geom(const b200_conv_geom &g)
 int im2col_pack(const b200_conv_geom &g, const ActPack &col, const float *x, int batch, cudaStream_t s)
 {
     const int rows = batch * g.out_y;
-    im2col_pack_kernel<<<rows < sm_count() * 32 ? rows : sm_count() * 32, 256, 0, s>>>(col.hi, col.lo, x, batch, g.in_z, g.in_y, g.in_x, g.out_y, g.out_x, g.kernel_y,
+    Launch(rows < sm_count() * 32 ? rows : sm_count() * 32, 256, 0, s)(im2col_pack_kernel, col.hi, col.lo, x, batch, g.in_z, g.in_y, g.in_x, g.out_y, g.out_x, g.kernel_y,
                                                       g.kernel_x, g.stride_y, g.stride_x, g.padding_y, g.padding_x, col.cp);
     B200_LAUNCH_CHECK();
     return B200_OK;
@@ -146,7 +150,7 @@ int smallc_weights(const b200_conv_geom &g, const float *kernel, float *hi, floa
 {
     const int taps = g.kernel_x * g.kernel_y;
     const size_t total = (size_t)(transposed ? g.in_z * taps : g.kernel_amount) * pitch;
-    smallc_weight_kernel<<<grid_for(total), 256, 0, s>>>(hi, lo, kernel, g.kernel_amount, g.in_z, taps, pitch, transposed ? 1 : 0);
+    Launch(grid_for(total), 256, 0, s)(smallc_weight_kernel, hi, lo, kernel, g.kernel_amount, g.in_z, taps, pitch, transposed ? 1 : 0);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -155,7 +159,7 @@ int col2im_gather(const b200_conv_geom &g, float *dx, const float *t, int batch,
 {
     const int rows = batch * g.in_z * g.in_y;
     const int threads = g.in_x >= 128 ? 128 : (g.in_x >= 64 ? 64 : 32);
-    col2im_gather_kernel<<<rows < sm_count() * 64 ? rows : sm_count() * 64, threads, 0, s>>>(dx, t, batch, g.in_z, g.in_y, g.in_x, g.out_y, g.out_x, g.kernel_y, g.kernel_x,
+    Launch(rows < sm_count() * 64 ? rows : sm_count() * 64, threads, 0, s)(col2im_gather_kernel, dx, t, batch, g.in_z, g.in_y, g.in_x, g.out_y, g.out_x, g.kernel_y, g.kernel_x,
                                                         g.stride_y, g.stride_x, g.padding_y, g.padding_x);
     B200_LAUNCH_CHECK();
     return B200_OK;
@@ -164,7 +168,7 @@ int col2im_gather(const b200_conv_geom &g, float *dx, const float *t, int batch,
 int smallc_dkernel(const b200_conv_geom &g, float *dkernel, const float *dk, int accumulate, cudaStream_t s)
 {
     const int taps = g.kernel_x * g.kernel_y;
-    smallc_dkernel_kernel<<<grid_for((size_t)g.kernel_amount * g.in_z * taps), 256, 0, s>>>(dkernel, dk, g.kernel_amount, g.in_z, taps, accumulate);
+    Launch(grid_for((size_t)g.kernel_amount * g.in_z * taps), 256, 0, s)(smallc_dkernel_kernel, dkernel, dk, g.kernel_amount, g.in_z, taps, accumulate);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }

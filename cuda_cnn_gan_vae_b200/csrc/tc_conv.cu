@@ -242,6 +242,9 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
     if (CTAS == 2) ptx::cluster_sync();      // the peer's barriers are initialised before anything signals them
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // barriers, tensor memory and descriptors are set up while the previous kernel of the stream drains; nothing above
+    // touches global memory
+    grid_dependency_wait();
 
     const uint32_t a_bytes = kABytes;
     const uint32_t off_a_lo = a_bytes;
@@ -592,6 +595,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
 __global__ void pack_act_kernel(const float *__restrict__ src, float *__restrict__ hi, float *__restrict__ lo,
                                 int N, int C, int H, int W, int Cp, int sy, int sx, int Hs, int Ws, int func, double slope, float *__restrict__ act_out)
 {
+    grid_dependency_wait();
     __shared__ float tile[32][33];
     const int n = blockIdx.z, h = blockIdx.y, w0 = blockIdx.x * 32;
     const int tx = threadIdx.x, ty = threadIdx.y;
@@ -643,6 +647,7 @@ pack_act_vec_kernel(const float *__restrict__ src, float *__restrict__ hi, float
                     int N, int C, int H, int W, int Cp, int sy, int sx, int Hs, int Ws, int rows_per_block, float *__restrict__ rowsum,
                     int func, double slope, float *__restrict__ act_out)
 {
+    grid_dependency_wait();
     __shared__ float tile[ROWS][32][33];
     const int n = blockIdx.z, h0 = blockIdx.y * rows_per_block, w0 = blockIdx.x * 32;
     const int h1 = min(h0 + rows_per_block, Hs * sy);
@@ -711,6 +716,7 @@ pack_act_vec_kernel(const float *__restrict__ src, float *__restrict__ hi, float
 __global__ void pack_weight_kernel(const float *__restrict__ src, float *__restrict__ hi, float *__restrict__ lo,
                                    int K, int C, int taps, int ip, int rot)
 {
+    grid_dependency_wait();
     const int rows = rot ? C : K, inner = rot ? K : C;
     const size_t total = (size_t)rows * taps * ip;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -728,6 +734,7 @@ __global__ void pack_weight_kernel(const float *__restrict__ src, float *__restr
 
 __global__ void split_tf32_kernel(const float *__restrict__ src, float *__restrict__ hi, float *__restrict__ lo, size_t n)
 {
+    grid_dependency_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         float v = src[i];
         float vh = ptx::to_tf32(v);
@@ -740,6 +747,7 @@ __global__ void split_tf32_kernel(const float *__restrict__ src, float *__restri
 __global__ void split_tf32_pair_kernel(const float *__restrict__ a, float *__restrict__ a_hi, float *__restrict__ a_lo, size_t na,
                                        const float *__restrict__ b, float *__restrict__ b_hi, float *__restrict__ b_lo, size_t nb, int blocks_a)
 {
+    grid_dependency_wait();
     const bool first = (int)blockIdx.x < blocks_a;
     const float *src = first ? a : b;
     float *hi = first ? a_hi : b_hi, *lo = first ? a_lo : b_lo;
@@ -757,6 +765,7 @@ __global__ void split_tf32_pair_kernel(const float *__restrict__ a, float *__res
 __global__ void wgrad_reduce_kernel(float *__restrict__ dkernel, const float *__restrict__ partial, int splits, int taps,
                                     int C, int K, int accumulate)
 {
+    grid_dependency_wait();
     const size_t total = (size_t)K * C * taps;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         // idx enumerates (tap, c, f) with f fastest so that the reads are coalesced
@@ -776,6 +785,7 @@ __global__ void conv_ksplit_reduce_kernel(float *__restrict__ out, const float *
                                           const float *__restrict__ bias, int k_out, size_t plane, int func = -1, double slope = 0.0,
                                           float *__restrict__ pre = nullptr)
 {
+    grid_dependency_wait();
     const size_t total4 = total / 4;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (size_t)gridDim.x * blockDim.x) {
         float4 s = reinterpret_cast<const float4 *>(partial)[i];
@@ -800,6 +810,7 @@ __global__ void conv_ksplit_reduce_kernel(float *__restrict__ out, const float *
 __global__ void wgrad_reduce_tiled_kernel(float *__restrict__ dkernel, const float *__restrict__ partial, int splits, int taps,
                                           int C, int K, int c_run, int accumulate)
 {
+    grid_dependency_wait();
     extern __shared__ float tile[];                       // [tap][c_run][33]
     const int c_tiles = (C + c_run - 1) / c_run;
     const int f0 = (blockIdx.x / c_tiles) * 32, c0 = (blockIdx.x % c_tiles) * c_run;
@@ -996,20 +1007,8 @@ static int launch_one(const CUtensorMap maps[4], const TcParams &p, int grid, si
 {
     if (MODE == MODE_CONV && !ACT && p.ksplit <= 1 && (p.act_func >= 0 || p.pre_out)) return launch_one<MODE, X3, CTAS, MODE == MODE_CONV>(maps, p, grid, smem, s);
     B200_CUDA(cudaFuncSetAttribute(tc_kernel<MODE, X3, CTAS, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = CTAS;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = CTAS > 1 ? 1 : 0;
-    B200_CUDA(cudaLaunchKernelEx(&cfg, tc_kernel<MODE, X3, CTAS, ACT>, maps[0], maps[X3 ? 1 : 0], maps[2], maps[X3 ? 3 : 2], p));
+    Launch(dim3(grid), dim3(kThreads), smem, s).cluster(CTAS)(tc_kernel<MODE, X3, CTAS, ACT>, maps[0], maps[X3 ? 1 : 0], maps[2], maps[X3 ? 3 : 2], p);
+    B200_CUDA(take_launch_error());
     return B200_OK;
 }
 
@@ -1141,12 +1140,12 @@ static int pack_act(const float *src, float *hi, float *lo, int N, int C, int H,
         int rows_per_block = rowsum ? 8 : kPackRows;
         while (rows_per_block > 1 && (long long)grid.x * ceil_div((int)grid.y, rows_per_block) * N < 16LL * sm_count()) rows_per_block /= 2;
         dim3 vgrid(grid.x, ceil_div((int)grid.y, rows_per_block), N);
-        if (rows_per_block >= 4) pack_act_vec_kernel<4><<<vgrid, 256, 0, s>>>(src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws, rows_per_block, rowsum, func, slope, act_out);
-        else if (rows_per_block == 2) pack_act_vec_kernel<2><<<vgrid, 256, 0, s>>>(src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws, rows_per_block, rowsum, func, slope, act_out);
-        else pack_act_vec_kernel<1><<<vgrid, 256, 0, s>>>(src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws, rows_per_block, rowsum, func, slope, act_out);
+        if (rows_per_block >= 4) Launch(vgrid, 256, 0, s)(pack_act_vec_kernel<4>, src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws, rows_per_block, rowsum, func, slope, act_out);
+        else if (rows_per_block == 2) Launch(vgrid, 256, 0, s)(pack_act_vec_kernel<2>, src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws, rows_per_block, rowsum, func, slope, act_out);
+        else Launch(vgrid, 256, 0, s)(pack_act_vec_kernel<1>, src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws, rows_per_block, rowsum, func, slope, act_out);
         if (rowsum && rowsum_runs) *rowsum_runs = (int)(vgrid.x * vgrid.y);
     } else
-        pack_act_kernel<<<grid, block, 0, s>>>(src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws, func, slope, act_out);
+        Launch(grid, block, 0, s)(pack_act_kernel, src, hi, lo, N, C, H, W, Cp, sy, sx, Hs, Ws, func, slope, act_out);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -1156,6 +1155,7 @@ static int pack_act(const float *src, float *hi, float *lo, int N, int C, int H,
 __global__ void __launch_bounds__(256) dbias_from_rowsums_kernel(float *__restrict__ dbias, const float *__restrict__ rowsum, int N, int C, int runs,
                                                                  int accumulate)
 {
+    grid_dependency_wait();
     __shared__ float part[8];
     const int c = blockIdx.x;
     const int total = N * runs;
@@ -1187,7 +1187,7 @@ int act_pack_fill_with_sums(const ActPack &pk, const float *src, float *rowsum, 
 
 int dbias_from_rowsums(float *dbias, int accumulate, const float *rowsum, int batch, int K, int runs, cudaStream_t s)
 {
-    dbias_from_rowsums_kernel<<<K, 256, 0, s>>>(dbias, rowsum, batch, K, runs, accumulate);
+    Launch(K, 256, 0, s)(dbias_from_rowsums_kernel, dbias, rowsum, batch, K, runs, accumulate);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -1223,6 +1223,7 @@ __device__ __forceinline__ void pack_weight_tile(int block, const float *__restr
 __global__ void __launch_bounds__(256) pack_weight_tiled_kernel(const float *__restrict__ src, float *__restrict__ hi, float *__restrict__ lo,
                                                                 int K, int C, int taps, int ip, int rot)
 {
+    grid_dependency_wait();
     __shared__ float tile[32][kMaxTaps + 1];
     pack_weight_tile(blockIdx.x, src, hi, lo, K, C, taps, ip, rot, tile);
 }
@@ -1232,6 +1233,7 @@ __global__ void __launch_bounds__(256) pack_weight_both_kernel(const float *__re
                                                                float *__restrict__ b_hi, float *__restrict__ b_lo, int K, int C, int taps, int ip_f,
                                                                int ip_b, int n_forward)
 {
+    grid_dependency_wait();
     __shared__ float tile[32][kMaxTaps + 1];
     if ((int)blockIdx.x < n_forward) pack_weight_tile(blockIdx.x, src, f_hi, f_lo, K, C, taps, ip_f, 0, tile);
     else pack_weight_tile(blockIdx.x - n_forward, src, b_hi, b_lo, K, C, taps, ip_b, 1, tile);
@@ -1241,14 +1243,14 @@ static int pack_weight(const float *src, float *hi, float *lo, int K, int C, int
 {
     if (taps > 1 && taps <= kMaxTaps) {
         const int rows = rot ? C : K;
-        pack_weight_tiled_kernel<<<rows * ((ip + 31) / 32), 256, 0, s>>>(src, hi, lo, K, C, taps, ip, rot);
+        Launch(rows * ((ip + 31) / 32), 256, 0, s)(pack_weight_tiled_kernel, src, hi, lo, K, C, taps, ip, rot);
         B200_LAUNCH_CHECK();
         return B200_OK;
     }
     size_t total = (size_t)(rot ? C : K) * taps * ip;
     int grid = (int)((total + 255) / 256);
     if (grid > sm_count() * 16) grid = sm_count() * 16;
-    pack_weight_kernel<<<grid, 256, 0, s>>>(src, hi, lo, K, C, taps, ip, rot);
+    Launch(grid, 256, 0, s)(pack_weight_kernel, src, hi, lo, K, C, taps, ip, rot);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -1304,7 +1306,7 @@ int weight_pack_fill_both(const b200_conv_geom &g, const float *kernel, float *f
         return r ? r : pack_weight(kernel, b_hi, b_lo, g.kernel_amount, g.in_z, taps, ip_b, 1, s);
     }
     const int n_f = g.kernel_amount * ((ip_f + 31) / 32), n_b = g.in_z * ((ip_b + 31) / 32);
-    pack_weight_both_kernel<<<n_f + n_b, 256, 0, s>>>(kernel, f_hi, f_lo, b_hi, b_lo, g.kernel_amount, g.in_z, taps, ip_f, ip_b, n_f);
+    Launch(n_f + n_b, 256, 0, s)(pack_weight_both_kernel, kernel, f_hi, f_lo, b_hi, b_lo, g.kernel_amount, g.in_z, taps, ip_f, ip_b, n_f);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -1468,7 +1470,7 @@ int conv_gemm(bool backward, const b200_conv_geom &g, float *out, const ActPack 
         const size_t total = (size_t)p.out_elems;
         size_t blocks = (total / 4 + 255) / 256;
         if (blocks > (size_t)sm_count() * 16) blocks = (size_t)sm_count() * 16;
-        conv_ksplit_reduce_kernel<<<(unsigned)blocks, 256, 0, s>>>(out, kpartial, p.ksplit, total, bias, k_out, (size_t)OH * OW, p.act_func, p.act_slope,
+        Launch((unsigned)blocks, 256, 0, s)(conv_ksplit_reduce_kernel, out, kpartial, p.ksplit, total, bias, k_out, (size_t)OH * OW, p.act_func, p.act_slope,
                                                                    p.pre_out);
         B200_LAUNCH_CHECK();
     }
@@ -1643,14 +1645,14 @@ int wgrad_gemm(const b200_conv_geom &g, float *dkernel, int accumulate, const Ac
     const size_t tile_bytes = sizeof(float) * (size_t)taps * c_run * 33;
     if (tile_bytes <= 48 * 1024) {
         const int blocks = ceil_div(K, 32) * ceil_div(C, c_run);
-        wgrad_reduce_tiled_kernel<<<blocks, 256, tile_bytes, s>>>(dkernel, p.partial, p.splits, taps, C, K, c_run, accumulate);
+        Launch(blocks, 256, tile_bytes, s)(wgrad_reduce_tiled_kernel, dkernel, p.partial, p.splits, taps, C, K, c_run, accumulate);
         B200_LAUNCH_CHECK();
         return B200_OK;
     }
     size_t total = (size_t)K * C * taps;
     int grid = (int)((total + 255) / 256);
     if (grid > sm_count() * 16) grid = sm_count() * 16;
-    wgrad_reduce_kernel<<<grid, 256, 0, s>>>(dkernel, p.partial, p.splits, taps, C, K, accumulate);
+    Launch(grid, 256, 0, s)(wgrad_reduce_kernel, dkernel, p.partial, p.splits, taps, C, K, accumulate);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -1659,6 +1661,7 @@ int wgrad_gemm(const b200_conv_geom &g, float *dkernel, int accumulate, const Ac
 // in a shuffle tree (a fixed order: reproducible run to run)
 __global__ void dbias_reduce_kernel(float *__restrict__ dbias, const float *__restrict__ plane_sums, int batch, int K, int accumulate)
 {
+    grid_dependency_wait();
     const int lane = threadIdx.x & 31;
     const int k = (int)((blockIdx.x * blockDim.x + threadIdx.x) >> 5);
     if (k >= K) return;
@@ -1675,7 +1678,7 @@ int dbias_batch(float *dbias, int accumulate, const float *delta, int batch, int
 {
     int r;
     if ((r = b200_summ_xy(db_tmp, batch, delta, batch, K, plane, s))) return r;
-    dbias_reduce_kernel<<<ceil_div(K * 32, 256), 256, 0, s>>>(dbias, db_tmp, batch, K, accumulate);
+    Launch(ceil_div(K * 32, 256), 256, 0, s)(dbias_reduce_kernel, dbias, db_tmp, batch, K, accumulate);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }
@@ -1743,7 +1746,7 @@ int tc_gemm(float *out, const float *a, const float *b, int m, int n, int k, int
         // both operands in one launch: blocks [0, ga) split A, the rest B
         const int ga = (int)((a_elems + 256 * 8 - 1) / (256 * 8)) < sm_count() * 8 ? (int)((a_elems + 256 * 8 - 1) / (256 * 8)) : sm_count() * 8;
         const int gb = (int)((b_elems + 256 * 8 - 1) / (256 * 8)) < sm_count() * 8 ? (int)((b_elems + 256 * 8 - 1) / (256 * 8)) : sm_count() * 8;
-        split_tf32_pair_kernel<<<ga + gb, 256, 0, s>>>(a, a_hi, a_lo, a_elems, b, b_hi, b_lo, b_elems, ga);
+        Launch(ga + gb, 256, 0, s)(split_tf32_pair_kernel, a, a_hi, a_lo, a_elems, b, b_hi, b_lo, b_elems, ga);
         B200_LAUNCH_CHECK();
     }
 
@@ -1787,7 +1790,7 @@ int tc_gemm(float *out, const float *a, const float *b, int m, int n, int k, int
         const size_t total = (size_t)m * n;
         size_t blocks = (total / 4 + 255) / 256;
         if (blocks > (size_t)sm_count() * 16) blocks = (size_t)sm_count() * 16;
-        conv_ksplit_reduce_kernel<<<(unsigned)blocks, 256, 0, s>>>(out, kpartial, ksplit, total, nullptr, 1, total);
+        Launch((unsigned)blocks, 256, 0, s)(conv_ksplit_reduce_kernel, out, kpartial, ksplit, total, nullptr, 1, total, -1, 0.0, nullptr);
         B200_LAUNCH_CHECK();
     }
     return B200_OK;

@@ -715,7 +715,8 @@ def main():
         launches = (lib.b200_launch_count() - n0) // steps
         kms, kn = C.c_double(0), C.c_int(0)
         lib.b200_profile_read(C.byref(kms), C.byref(kn))
-        return ms.item() / steps, clocks, launches, (kms.value / kn.value if kn.value else None)
+        # tensor-core kernel time of one step (sum over its launches) and the launches it took
+        return ms.item() / steps, clocks, launches, ((kms.value / steps, kn.value / steps) if kn.value else None)
 
     if args.vae_only:
         del x, delta, y, dx
@@ -730,15 +731,20 @@ def main():
     for mode_name, mode in (("tf32x3", ops.TF32X3), ("tf32", ops.TF32)):
         ops.set_precision(mode)
         lib.b200_profile_tensor_core(1)
-        ms, clocks, launches, kernel_ms = timed(step, args.steps, args.warmup, sample_clocks=True)
+        ms, clocks, launches, tc_time = timed(step, args.steps, args.warmup, sample_clocks=True)
+        tc_ms_per_step, tc_launches = tc_time if tc_time else (None, None)
+        kernel_ms = tc_ms_per_step / tc_launches if tc_time else None
         lib.b200_profile_tensor_core(0)
         ops.stream_status()
         if rank == 0 and world == 1 and not args.skip_cpu:
             samples["modes"][mode_name] = (y[sample_idx].cpu().numpy(), dx[sample_idx].cpu().numpy())
-        per_launch_flops = step_flops / world / 3.0
+        # flops of an average launch: the three products of a step are equal; large layers run the forward and the
+        # backward-data product as several launches (batch chunks pipelined against the pack), so the step's flops are
+        # divided over the launches it actually took
+        per_launch_flops = step_flops / world / (tc_launches or 3.0)
         # dram__bytes_read+write per tc_kernel launch from the committed ncu capture at batch 128, scaled by the units of a launch
         per_image, traffic_source = profiled_traffic()
-        traffic = per_image * B if per_image else None
+        traffic = per_image * B * 3.0 / (tc_launches or 3.0) if per_image else None
         achieved = per_launch_flops / (kernel_ms * 1e-3) / 1e12 if kernel_ms else None
         # the sustained peak was taken at a lower SM clock than this run holds under the same power cap: the fraction at
         # equal clock says how much of the tensor pipe the kernel uses, the plain fraction how fast it is
@@ -750,8 +756,8 @@ def main():
                           frac=(achieved / tf32_peak) if achieved else None, traffic=traffic if mode == ops.TF32 else None,
                           traffic_source=traffic_source if mode == ops.TF32 else None,
                           frac_of_burst=(achieved / (peaks["bf16_burst"] / 2.0)) if (achieved and peaks.get("bf16_burst")) else None,
-                          kernel="tc_kernel (tcgen05 implicit GEMM), mean of the forward, backward-data and weight-gradient launches",
-                          kernel_ms=kernel_ms, mma_per_product=3 if mode == ops.TF32X3 else 1,
+                          kernel="tc_kernel (tcgen05 implicit GEMM), mean over the forward, backward-data and weight-gradient launches of a step",
+                          kernel_ms=kernel_ms, kernel_launches_per_step=tc_launches, kernel_ms_per_step=tc_ms_per_step, mma_per_product=3 if mode == ops.TF32X3 else 1,
                           peak_sm_mhz=peaks.get("sm_mhz"), frac_at_equal_clock=equal_clock,
                           tensor_pipe_frac=(achieved * (3 if mode == ops.TF32X3 else 1) / tf32_peak) if achieved else None,
                           peak_source=f"{peaks['source']}: bf16_tflops_sustained / 2 (kind::tf32 issues at half the bf16 rate), of measured"))

@@ -77,6 +77,10 @@ int im2col_pack(const b200_conv_geom &g, const ActPack &col, const float *x, int
 int smallc_weights(const b200_conv_geom &g, const float *kernel, float *hi, float *lo, int pitch, bool transposed, cudaStream_t s);
 int col2im_gather(const b200_conv_geom &g, float *dx, const float *t, int batch, cudaStream_t s);
 int smallc_dkernel(const b200_conv_geom &g, float *dkernel, const float *dk, int accumulate, cudaStream_t s);
+// layers with few filters: the same problem read backwards has few channels (g is the layer's own geometry in all three)
+bool mirror_applies(const b200_conv_geom &g);
+b200_conv_geom mirror_geom(const b200_conv_geom &g);
+int mirror_weights(const b200_conv_geom &g, float *dst, const float *src, int back, int accumulate, cudaStream_t s);
 
 // Status word written by device-side waits that gave up (0 = none); clear != 0 resets it.
 unsigned tc_read_status(int clear);

@@ -15,7 +15,7 @@ struct b200_conv_layer {
     int batch;
     int transposed;
     int device;
-    enum { IN_HI, IN_LO, ER_HI, ER_LO, W_HI, W_LO, W2_HI, W2_LO, PARTIAL, DB_TMP, COL_HI, COL_LO, TMP, DK_TMP, KSPLIT, ACT_TMP, NBUF };
+    enum { IN_HI, IN_LO, ER_HI, ER_LO, W_HI, W_LO, W2_HI, W2_LO, PARTIAL, DB_TMP, COL_HI, COL_LO, TMP, DK_TMP, KSPLIT, ACT_TMP, MIRROR_W, MIRROR_DW, NBUF };
     float *buf[NBUF];
     size_t cap[NBUF];            // bytes
     int in_valid;                // the kept input pack matches the last forward call
@@ -34,6 +34,12 @@ struct b200_conv_layer {
     int w_slot;                  // W_HI or W2_HI: the pack the next contraction reads
     int w2_valid, w2_precision;
     const float *w2_kernel;
+    // A convolution layer with few filters (an RGB output layer) computes its input error and its weight gradient on the
+    // mirrored problem, which has few input channels: a second context with the mirrored geometry (NULL for other layers).
+    b200_conv_layer *mirror;
+    // set on a mirror context around its backward call: the packed output error it would make already exists (it is the
+    // owner's packed layer input)
+    const float *lent_er_hi, *lent_er_lo;
 };
 
 namespace b200 {
@@ -232,6 +238,12 @@ int b200_conv_layer_create(b200_conv_layer **layer, const b200_conv_geom *g, int
     l->transposed = transposed != 0;
     l->w_slot = b200_conv_layer::W_HI;
     cudaGetDevice(&l->device);
+    static const bool mirrors = !(getenv("B200CONV_MIRROR") && getenv("B200CONV_MIRROR")[0] == '0');      // debug switch
+    if (mirrors && !l->transposed && mirror_applies(*g)) {
+        const b200_conv_geom q = mirror_geom(*g);
+        const int r = b200_conv_layer_create(&l->mirror, &q, batch, 0);
+        if (r) { delete l; return r; }
+    }
     *layer = l;
     return B200_OK;
 }
@@ -241,6 +253,7 @@ int b200_conv_layer_destroy(b200_conv_layer *l)
     if (!l) return B200_OK;
     for (int i = 0; i < b200_conv_layer::NBUF; i++)
         if (l->buf[i]) cudaFree(l->buf[i]);
+    if (l->mirror) b200_conv_layer_destroy(l->mirror);
     delete l;
     return B200_OK;
 }
@@ -308,6 +321,8 @@ static int layer_forward(b200_conv_layer *l, float *out, const float *input, con
     }
     if (prec != B200_FP32) {
         const bool x3 = prec == B200_TF32X3;
+        // a layer with few filters forms its weight gradient on the mirrored problem, which reads the layer input as a tensor
+        if (l->mirror && in_act && !f->input_act_out && (r = materialise_input())) return r;
         ActPack in = in_shape(l);
         PackFunction pf = {in_act ? f->input_func : -1, in_act ? f->input_slope : 0.0, in_act ? f->input_act_out : nullptr};
         const bool fuse_pack = in_act && !input_materialised;
@@ -368,6 +383,36 @@ int b200_conv_layer_backward(b200_conv_layer *l, float *input_delta, float *dker
     // all-reduce of the gradients while the input error is still being computed) packs the error once.
     const bool reuse_er = l->er_valid && l->er_ptr == output_delta && l->er_precision == prec && !dkernel && input_delta;
     l->er_valid = 0;
+    // Few filters: both products on the mirrored problem (few input channels, taps folded into the channel dimension).  The
+    // layer input must exist as a tensor for the weight gradient (not only as the pack of a fused forward call).
+    if (prec != B200_FP32 && l->mirror && use_smallc(l->mirror) && !(l->fused_input == 1 && dkernel)) {
+        b200_conv_layer *m = l->mirror;
+        const size_t w_count = (size_t)g.kernel_amount * g.in_z * g.kernel_x * g.kernel_y;
+        m->col_valid = 0;                  // whatever the mirror gathered belongs to an earlier output error
+        r = ensure(l, b200_conv_layer::MIRROR_W, sizeof(float) * w_count, s);
+        if (r == B200_OK) r = mirror_weights(g, l->buf[b200_conv_layer::MIRROR_W], kernel, 0, 0, s);
+        // input error = the mirrored layer's forward pass over the output error
+        if (r == B200_OK && input_delta) r = layer_forward(m, input_delta, output_delta, l->buf[b200_conv_layer::MIRROR_W], nullptr, nullptr, stream);
+        if (r == B200_OK && dkernel) {
+            // weight gradient = the mirrored layer's, image and error exchanged, put back into this layer's order
+            if ((r = ensure(l, b200_conv_layer::MIRROR_DW, sizeof(float) * w_count, s)) == B200_OK) {
+                // the mirror's packed output error is this layer's packed input, kept by the forward call
+                if (l->in_valid && l->in_precision == prec) {
+                    m->lent_er_hi = l->buf[b200_conv_layer::IN_HI];
+                    m->lent_er_lo = prec == B200_TF32X3 ? l->buf[b200_conv_layer::IN_LO] : nullptr;
+                }
+                r = b200_conv_layer_backward(m, nullptr, l->buf[b200_conv_layer::MIRROR_DW], nullptr, 0, input, output_delta,
+                                             l->buf[b200_conv_layer::MIRROR_W], stream);
+                m->lent_er_hi = m->lent_er_lo = nullptr;
+            }
+            if (r == B200_OK) r = mirror_weights(g, dkernel, l->buf[b200_conv_layer::MIRROR_DW], 1, accumulate, s);
+            if (r == B200_OK && dbias && (r = ensure(l, b200_conv_layer::DB_TMP, sizeof(float) * (size_t)l->batch * g.kernel_amount, s)) == B200_OK)
+                r = dbias_batch(dbias, accumulate, output_delta, l->batch, g.kernel_amount, (size_t)g.out_y * g.out_x, l->buf[b200_conv_layer::DB_TMP], s);
+        }
+        m->col_valid = 0;
+        if (r == B200_OK) { set_path(B200_PATH_TCGEN05); return r; }
+        return r;
+    }
     if (prec != B200_FP32 && use_smallc(l)) {
         const bool x3 = prec == B200_TF32X3;
         if (!l->transposed) {
@@ -375,7 +420,13 @@ int b200_conv_layer_backward(b200_conv_layer *l, float *input_delta, float *dker
             ActPack er = er_shape(l), col;
             int sum_runs = 0;
             const bool want_sums = dkernel && dbias;
-            r = pack_into(l, b200_conv_layer::ER_HI, er, output_delta, x3, s, want_sums ? &sum_runs : nullptr);
+            if (l->lent_er_hi && !want_sums && (!x3 || l->lent_er_lo)) {
+                er.hi = const_cast<float *>(l->lent_er_hi);
+                er.lo = x3 ? const_cast<float *>(l->lent_er_lo) : nullptr;
+                r = B200_OK;
+            } else {
+                r = pack_into(l, b200_conv_layer::ER_HI, er, output_delta, x3, s, want_sums ? &sum_runs : nullptr);
+            }
             if (r == B200_OK && input_delta) r = smallc_tconv(l, input_delta, er, kernel, x3, s);
             if (r == B200_OK && dkernel) {
                 if (l->col_valid && l->col_precision == prec) {

@@ -114,6 +114,27 @@ __global__ void smallc_dkernel_kernel(float *__restrict__ dkernel, const float *
     }
 }
 
+// Weights of the mirrored problem of a layer with few filters (see mirror_geom): rows and channels change places and the
+// taps run backwards.  dst[c][k*taps + t] = src[k][c*taps + (taps-1-t)]; back = 1 is the inverse for the gradient:
+// dst[k][c*taps + t] (+)= src[c][k*taps + (taps-1-t)].
+__global__ void mirror_weights_kernel(float *__restrict__ dst, const float *__restrict__ src, int K, int C, int taps, int back, int accumulate)
+{
+    grid_dependency_wait();
+    const int total = K * C * taps;
+    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+        if (!back) {
+            const int c = idx / (K * taps), j = idx - c * (K * taps);
+            const int k = j / taps, t = j - k * taps;
+            dst[idx] = src[((size_t)k * C + c) * taps + (taps - 1 - t)];
+        } else {
+            const int k = idx / (C * taps), j = idx - k * (C * taps);
+            const int c = j / taps, t = j - c * taps;
+            const float v = src[((size_t)c * K + k) * taps + (taps - 1 - t)];
+            dst[idx] = accumulate ? dst[idx] + v : v;
+        }
+    }
+}
+
 static inline int grid_for(size_t total)
 {
     size_t blocks = (total + 255) / 256, cap = (size_t)sm_count() * 16;
@@ -169,6 +190,34 @@ int smallc_dkernel(const b200_conv_geom &g, float *dkernel, const float *dk, int
 {
     const int taps = g.kernel_x * g.kernel_y;
     Launch(grid_for((size_t)g.kernel_amount * g.in_z * taps), 256, 0, s)(smallc_dkernel_kernel, dkernel, dk, g.kernel_amount, g.in_z, taps, accumulate);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
+// A stride-1 convolution C -> K channels with padding p is, read backwards, a convolution K -> C with padding k-1-p and the
+// weights of mirror_weights: BackwardConvolution of the one is ForwardConvolution of the other, and the weight gradient of the
+// one is the (re-ordered) weight gradient of the other with image and error exchanged.  For a layer with few FILTERS the
+// mirrored problem has few input CHANNELS, which is what the folded path above serves.
+bool mirror_applies(const b200_conv_geom &g)
+{
+    if (g.stride_x != 1 || g.stride_y != 1 || g.kernel_amount > 8 || g.in_z <= 8) return false;
+    if (g.padding_x > g.kernel_x - 1 || g.padding_y > g.kernel_y - 1) return false;
+    return smallc_applies(mirror_geom(g));
+}
+
+b200_conv_geom mirror_geom(const b200_conv_geom &g)
+{
+    b200_conv_geom q = g;
+    q.in_z = g.kernel_amount; q.in_y = g.out_y; q.in_x = g.out_x;
+    q.kernel_amount = g.in_z; q.out_y = g.in_y; q.out_x = g.in_x;
+    q.padding_x = g.kernel_x - 1 - g.padding_x; q.padding_y = g.kernel_y - 1 - g.padding_y;
+    return q;
+}
+
+int mirror_weights(const b200_conv_geom &g, float *dst, const float *src, int back, int accumulate, cudaStream_t s)
+{
+    const int taps = g.kernel_x * g.kernel_y;
+    Launch(grid_for((size_t)g.kernel_amount * g.in_z * taps), 256, 0, s)(mirror_weights_kernel, dst, src, g.kernel_amount, g.in_z, taps, back, accumulate);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }

@@ -22,8 +22,10 @@ def dev(a):
 
 # the last two: few output pixels and a long contraction (the 8x8 / 4x4 layers of the DCGAN nets), where the library
 # splits the contraction of a tile over several work items and sums the partial outputs in a second kernel
+# the last three: few filters (an RGB output layer), whose input error and weight gradient run on the mirrored problem
 CASES = [(4, 64, 16, 16, 96, 3, 1, 1), (4, 3, 64, 64, 64, 4, 2, 1), (3, 40, 12, 12, 24, 3, 1, 1), (6, 128, 8, 8, 256, 4, 2, 1),
-         (8, 256, 8, 8, 512, 4, 2, 1), (5, 512, 4, 4, 100, 3, 1, 1)]
+         (8, 256, 8, 8, 512, 4, 2, 1), (5, 512, 4, 4, 100, 3, 1, 1),
+         (4, 32, 24, 20, 3, 3, 1, 1), (3, 16, 12, 12, 5, 4, 1, 2), (2, 24, 10, 14, 8, 3, 1, 0)]
 
 
 @pytest.mark.parametrize("case", CASES)
@@ -131,9 +133,37 @@ def test_split_backward_call_reuses_the_packed_error(ops):
     layer.close()
 
 
+def test_few_filter_layer_in_either_call_order(ops, port):
+    """A layer with few filters: the weights-only call followed by the input-only call (the order that lets the gradient
+    exchange start early) gives what the combined call gives, step after step with a changing output error."""
+    B, C, H, W, K, k, s, p = 4, 32, 24, 20, 3, 3, 1, 1
+    ops.set_precision(ops.TF32X3)
+    x, wt, b, d = conv_inputs(77, B, C, H, W, K, k, s, p)
+    X, WT, BI = dev(x), dev(wt), dev(b)
+    layer = ops.ConvLayer(C, H, W, K, k, k, s, s, p, p, B)
+    y = torch.empty(d.shape, device="cuda")
+    for rep in range(3):
+        D = dev(d * (rep + 1) + rep)
+        layer.forward(y, X, WT, BI)
+        dx_a, dk_a, db_a = torch.empty_like(X), torch.empty_like(WT), torch.empty_like(BI)
+        layer.backward(dx_a, dk_a, db_a, D, X, WT, accumulate=False)
+        dx_b, dk_b, db_b = torch.full_like(X, float("nan")), torch.full_like(WT, float("nan")), torch.full_like(BI, float("nan"))
+        layer.backward(None, dk_b, db_b, D, X, WT, accumulate=False)
+        layer.backward(dx_b, None, None, D, X, WT)
+        ops.stream_status()
+        assert ops.last_path() == ops.PATH_TCGEN05
+        assert torch.equal(dx_a, dx_b) and torch.equal(dk_a, dk_b) and torch.equal(db_a, db_b)
+        dn = D.cpu().numpy()
+        zb = np.zeros((1, K), np.float32)
+        assert dot_rel_err(dx_a.cpu().numpy(), port.conv_backward(dn, wt[0], zb, (C, H, W), k, k, s, s, p, p),
+                           port.conv_backward(np.abs(dn), np.abs(wt)[0], zb, (C, H, W), k, k, s, s, p, p)) <= TOL_X3
+    layer.close()
+
+
 FUSED_CASES = [(4, 64, 16, 16, 96, 3, 1, 1, False), (6, 128, 8, 8, 256, 4, 2, 1, False), (5, 512, 4, 4, 100, 3, 1, 1, False),      # plain, strided, split-K
                (4, 3, 64, 64, 64, 4, 2, 1, False), (3, 40, 12, 12, 24, 3, 1, 1, False),                                           # few-channel input, ragged
-               (4, 64, 16, 16, 128, 4, 2, 1, True), (4, 3, 64, 64, 64, 4, 2, 1, True)]                                            # transposed layers
+               (4, 64, 16, 16, 128, 4, 2, 1, True), (4, 3, 64, 64, 64, 4, 2, 1, True),                                            # transposed layers
+               (4, 32, 16, 16, 3, 3, 1, 1, False)]                                                                                # few filters
 
 
 @pytest.mark.parametrize("case", FUSED_CASES)

@@ -14,30 +14,63 @@
 
 namespace b200 {
 
-// col[n][oy][ox][tap*C + c] = x[n][c][oy*sy + ky - py][ox*sx + kx - px] (0 outside), pitch cp floats per position.
-// One block per (n, oy) row of positions; its threads walk (ox, c') with c' fastest, so the writes are contiguous.
-__global__ void im2col_pack_kernel(float *__restrict__ hi, float *__restrict__ lo, const float *__restrict__ x, int N, int C, int H, int W,
-                                   int OH, int OW, int kh, int kw, int sy, int sx, int py, int px, int cp)
+// col[n][oy][ox][tap*C + c] = x[n][c][oy*sy + ky - py][ox*sx + kx - px] (0 outside), pitch cp floats per position (a multiple
+// of 4, at most 256).  One block per (n, oy) row of positions.  The C*kh image rows that the row of positions reads are
+// staged in shared memory with coalesced loads (STAGED; rows too long for shared memory are gathered from global memory
+// instead); a thread then makes four consecutive columns of a position and stores them as one 16-byte vector, the (row, dx)
+// of every column coming from a table in shared memory, so that the inner loop has one division per vector.
+template <bool STAGED>
+__global__ void __launch_bounds__(256) im2col_pack_kernel(float *__restrict__ hi, float *__restrict__ lo, const float *__restrict__ x, int N, int C,
+                                                          int H, int W, int OH, int OW, int kh, int kw, int sy, int sx, int py, int px, int cp)
 {
     grid_dependency_wait();
+    extern __shared__ float staged[];            // STAGED: [C * kh][W]
+    __shared__ int4 column[256];                 // x: row offset (staged) or channel-plane offset, y: dy, z: dx, w: 1 for a real column
     const int cc = C * kh * kw;
-    const int row_elems = OW * cp;
+    for (int j = threadIdx.x; j < cp; j += blockDim.x) {
+        int4 e = make_int4(0, 0, 0, 0);
+        if (j < cc) {
+            const int tap = j / C, c = j - tap * C;
+            const int ky = tap / kw, kx = tap - ky * kw;
+            e = make_int4(STAGED ? (c * kh + ky) * W : c * H * W, ky - py, kx - px, 1);
+        }
+        column[j] = e;
+    }
+    const int qpp = cp / 4;                      // vectors per position
+    const int row_quads = OW * qpp;
     for (int row = blockIdx.x; row < N * OH; row += gridDim.x) {
         const int n = row / OH, oy = row - n * OH;
         const float *xn = x + (size_t)n * C * H * W;
-        const size_t obase = (size_t)row * row_elems;
-        for (int t = threadIdx.x; t < row_elems; t += blockDim.x) {
-            const int ox = t / cp, j = t - ox * cp;
-            float v = 0.f;
-            if (j < cc) {
-                const int tap = j / C, c = j - tap * C;
-                const int ky = tap / kw, kx = tap - ky * kw;
-                const int iy = oy * sy + ky - py, ix = ox * sx + kx - px;
-                if (iy >= 0 && iy < H && ix >= 0 && ix < W) v = xn[((size_t)c * H + iy) * W + ix];
+        __syncthreads();                         // the table is written; the previous row's readers are done with `staged`
+        if (STAGED) {
+            for (int r = threadIdx.x >> 5; r < C * kh; r += blockDim.x >> 5) {        // one warp per image row
+                const int c = r / kh, ky = r - c * kh;
+                const int iy = oy * sy + ky - py;
+                const bool inside = iy >= 0 && iy < H;
+                const float *src = xn + ((size_t)c * H + (inside ? iy : 0)) * W;
+                for (int xx = threadIdx.x & 31; xx < W; xx += 32) staged[r * W + xx] = inside ? src[xx] : 0.f;
             }
-            const float h = ptx::to_tf32(v);
-            hi[obase + t] = h;
-            if (lo) lo[obase + t] = ptx::to_tf32(v - h);
+            __syncthreads();
+        }
+        float4 *hrow = reinterpret_cast<float4 *>(hi + (size_t)row * OW * cp);
+        float4 *lrow = lo ? reinterpret_cast<float4 *>(lo + (size_t)row * OW * cp) : nullptr;
+        for (int q = threadIdx.x; q < row_quads; q += blockDim.x) {
+            const int ox = q / qpp, j0 = (q - ox * qpp) * 4;
+            float v[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int4 e = column[j0 + i];
+                const int ix = ox * sx + e.z;
+                if (STAGED) {
+                    v[i] = (e.w && ix >= 0 && ix < W) ? staged[e.x + ix] : 0.f;
+                } else {
+                    const int iy = oy * sy + e.y;
+                    v[i] = (e.w && iy >= 0 && iy < H && ix >= 0 && ix < W) ? xn[e.x + iy * W + ix] : 0.f;
+                }
+            }
+            const float4 h = make_float4(ptx::to_tf32(v[0]), ptx::to_tf32(v[1]), ptx::to_tf32(v[2]), ptx::to_tf32(v[3]));
+            hrow[q] = h;
+            if (lrow) lrow[q] = make_float4(ptx::to_tf32(v[0] - h.x), ptx::to_tf32(v[1] - h.y), ptx::to_tf32(v[2] - h.z), ptx::to_tf32(v[3] - h.w));
         }
     }
 }
@@ -161,8 +194,14 @@ b200_conv_geom smallc_geom(const b200_conv_geom &g)
 int im2col_pack(const b200_conv_geom &g, const ActPack &col, const float *x, int batch, cudaStream_t s)
 {
     const int rows = batch * g.out_y;
-    Launch(rows < sm_count() * 32 ? rows : sm_count() * 32, 256, 0, s)(im2col_pack_kernel, col.hi, col.lo, x, batch, g.in_z, g.in_y, g.in_x, g.out_y, g.out_x, g.kernel_y,
-                                                      g.kernel_x, g.stride_y, g.stride_x, g.padding_y, g.padding_x, col.cp);
+    const int grid = rows < sm_count() * 32 ? rows : sm_count() * 32;
+    const size_t stage_bytes = sizeof(float) * (size_t)g.in_z * g.kernel_y * g.in_x;
+    if (stage_bytes <= 40 * 1024)
+        Launch(grid, 256, stage_bytes, s)(im2col_pack_kernel<true>, col.hi, col.lo, x, batch, g.in_z, g.in_y, g.in_x, g.out_y, g.out_x, g.kernel_y,
+                                          g.kernel_x, g.stride_y, g.stride_x, g.padding_y, g.padding_x, col.cp);
+    else
+        Launch(grid, 256, 0, s)(im2col_pack_kernel<false>, col.hi, col.lo, x, batch, g.in_z, g.in_y, g.in_x, g.out_y, g.out_x, g.kernel_y,
+                                g.kernel_x, g.stride_y, g.stride_x, g.padding_y, g.padding_x, col.cp);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }

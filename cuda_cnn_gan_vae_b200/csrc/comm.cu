@@ -243,11 +243,11 @@ struct b200_comm {
     bool connected;
 };
 
-static int exchange_grid(size_t n4, int world)
+static int exchange_grid(size_t n4, int world, int threads)
 {
     // the same on every rank: enough CTAs to keep the links busy, no more than the flags of a channel, none idle
     const size_t per = (n4 + world - 1) / world;
-    size_t g = (per + 511) / 512;
+    size_t g = (per + threads - 1) / threads;
     // tuning aid: B200CONV_EXCHANGE_CTAS=<n> caps the grid (read once; must be the same on every rank)
     static const int cap = [] { const char *e = getenv("B200CONV_EXCHANGE_CTAS"); int v = e ? atoi(e) : 0; return (v >= 1 && v <= kCommMaxCtas) ? v : 144; }();
     if (g > (size_t)cap) g = (size_t)cap;
@@ -286,9 +286,16 @@ static int launch_exchange(b200_comm *c, bool adam, int count, const b200_exchan
     p.adam = a; p.corrections = corrections;
     int r = status_word(&p.status);
     if (r) return r;
-    const int grid = exchange_grid(largest, c->world);
-    if (adam) exchange_kernel<true><<<grid, 512, 0, s>>>(p);
-    else exchange_kernel<false><<<grid, 512, 0, s>>>(p);
+    // The fused exchange runs alone at the end of a step: 512-thread CTAs keep the most loads in flight.  The plain sum is
+    // what a caller overlaps with a convolution of another stream: at ~120 registers a 512-thread CTA needs a whole register
+    // file and could not share an SM with a tensor-core CTA (it then waits for the convolution to end, or delays part of its
+    // persistent grid); 256 threads fit beside one.
+    // (tuning aid: B200CONV_EXCHANGE_THREADS=256|512 forces either; read once, must be the same on every rank)
+    static const int forced = [] { const char *e = getenv("B200CONV_EXCHANGE_THREADS"); const int v = e ? atoi(e) : 0; return (v == 256 || v == 512) ? v : 0; }();
+    const int threads = forced ? forced : (adam ? 512 : 256);
+    const int grid = exchange_grid(largest, c->world, threads);
+    if (adam) exchange_kernel<true><<<grid, threads, 0, s>>>(p);
+    else exchange_kernel<false><<<grid, threads, 0, s>>>(p);
     B200_LAUNCH_CHECK();
     return B200_OK;
 }

@@ -25,15 +25,20 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar)
 {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// One poll of the barrier's phase.  The suspend-time hint (nanoseconds) lets the hardware park the thread until the phase
+// completes or the time is up, instead of returning after the short default: the waiting warps of the kernel (producers,
+// issuer) then stop flooding the SM's memory-instruction queue with polls, through which the epilogue's tensor-memory loads
+// also pass (measured: a 16-column tcgen05.ld took ~1000 cycles beside polling warps and ~50 alone).
+constexpr uint32_t kMbarSuspendNs = 1000;
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kMbarSuspendNs)
         : "memory");
     return ok;
 }

@@ -57,6 +57,17 @@ size_t act_pack_rowsum_elems(const ActPack &pk);
 int act_pack_fill_with_sums(const ActPack &pk, const float *src, float *rowsum, int *runs, cudaStream_t s);
 int dbias_from_rowsums(float *dbias, int accumulate, const float *rowsum, int batch, int K, int runs, cudaStream_t s);
 size_t weight_pack_elems(const b200_conv_geom &g, bool backward);
+// The weight packs of several layers in one launch: weight_pack_job fills a job (false: this geometry is packed by the
+// per-layer kernels only), weight_pack_fill_many launches them.
+struct WeightPackJob {
+    const float *src;
+    float *f_hi, *f_lo, *b_hi, *b_lo;      // forward and rotated (backward) pack, high / low plane (low NULL in plain TF32)
+    int K, C, taps, ip_f, ip_b, n_forward, blocks, block_begin;
+};
+constexpr int kMaxPackJobs = 16;
+struct WeightPackJobs { WeightPackJob job[kMaxPackJobs]; int count; };
+bool weight_pack_job(const b200_conv_geom &g, const float *kernel, float *f_hi, float *f_lo, float *b_hi, float *b_lo, WeightPackJob *job);
+int weight_pack_fill_many(WeightPackJobs &jobs, cudaStream_t s);
 int weight_pack_fill(const b200_conv_geom &g, bool backward, const float *kernel, float *hi, float *lo, cudaStream_t s);
 // the forward pack (f_*) and the rotated pack of the backward pass (b_*) in one launch
 int weight_pack_fill_both(const b200_conv_geom &g, const float *kernel, float *f_hi, float *f_lo, float *b_hi, float *b_lo, cudaStream_t s);

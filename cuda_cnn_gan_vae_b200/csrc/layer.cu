@@ -34,6 +34,10 @@ struct b200_conv_layer {
     int w_slot;                  // W_HI or W2_HI: the pack the next contraction reads
     int w2_valid, w2_precision;
     const float *w2_kernel;
+    // b200_conv_layers_prepack packed both orientations for the NEXT forward call (same kernel pointer, same precision mode);
+    // that call consumes the mark, so a forward call without a fresh prepack packs the weights itself.
+    int prepacked, prepacked_precision;
+    const float *prepacked_kernel;
     // A convolution layer with few filters (an RGB output layer) computes its input error and its weight gradient on the
     // mirrored problem, which has few input channels: a second context with the mirrored geometry (NULL for other layers).
     b200_conv_layer *mirror;
@@ -102,6 +106,16 @@ static int pack_weights(b200_conv_layer *l, bool backward, const float *kernel, 
     int r;
     static const bool both = !(getenv("B200CONV_PACK_BOTH") && getenv("B200CONV_PACK_BOTH")[0] == '0');      // debug switch
     const int prec = x3 ? B200_TF32X3 : B200_TF32;
+    if (first_of_step) {
+        const bool ready = l->prepacked && l->prepacked_kernel == kernel && l->prepacked_precision == prec;
+        l->prepacked = 0;
+        if (ready) {
+            // packed by b200_conv_layers_prepack: this pass's orientation lies in W_HI/W_LO, the other one in W2_HI/W2_LO
+            l->w_slot = b200_conv_layer::W_HI;
+            l->w2_valid = 1; l->w2_precision = prec; l->w2_kernel = kernel;
+            return B200_OK;
+        }
+    }
     if (!first_of_step && l->w2_valid && l->w2_kernel == kernel && l->w2_precision == prec) {
         l->w_slot = b200_conv_layer::W2_HI;          // packed by the forward call
         return B200_OK;
@@ -256,6 +270,41 @@ int b200_conv_layer_destroy(b200_conv_layer *l)
     if (l->mirror) b200_conv_layer_destroy(l->mirror);
     delete l;
     return B200_OK;
+}
+
+int b200_conv_layers_prepack(b200_conv_layer *const *layers, const float *const *kernels, int count, void *stream)
+{
+    cudaStream_t s = (cudaStream_t)stream;
+    if (count < 0 || (count && (!layers || !kernels))) return fail(B200_E_ARG, "null argument");
+    const int prec = precision();
+    if (prec == B200_FP32) return B200_OK;                 // the CUDA-core path reads the weights as they are
+    const bool x3 = prec == B200_TF32X3;
+    WeightPackJobs jobs;
+    jobs.count = 0;
+    int r;
+    for (int i = 0; i < count; i++) {
+        b200_conv_layer *l = layers[i];
+        if (!l || !kernels[i]) return fail(B200_E_ARG, "null layer or kernel in the list");
+        l->prepacked = 0;
+        if (use_smallc(l)) continue;                       // few-channel layers fold their weights per call
+        // the forward call of a transposed-convolution layer reads the rotated pack: that one goes to W_HI/W_LO
+        const int f_slot = l->transposed ? b200_conv_layer::W2_HI : b200_conv_layer::W_HI;
+        const int b_slot = l->transposed ? b200_conv_layer::W_HI : b200_conv_layer::W2_HI;
+        const size_t f_bytes = sizeof(float) * weight_pack_elems(l->g, false), b_bytes = sizeof(float) * weight_pack_elems(l->g, true);
+        if ((r = ensure(l, f_slot, f_bytes, s)) || (r = ensure(l, b_slot, b_bytes, s))) return r;
+        if (x3 && ((r = ensure(l, f_slot + 1, f_bytes, s)) || (r = ensure(l, b_slot + 1, b_bytes, s)))) return r;
+        WeightPackJob job;
+        if (!weight_pack_job(l->g, kernels[i], l->buf[f_slot], x3 ? l->buf[f_slot + 1] : nullptr, l->buf[b_slot], x3 ? l->buf[b_slot + 1] : nullptr, &job))
+            continue;
+        jobs.job[jobs.count++] = job;
+        l->prepacked = 1; l->prepacked_precision = prec; l->prepacked_kernel = kernels[i];
+        l->w2_valid = 0;
+        if (jobs.count == kMaxPackJobs) {
+            if ((r = weight_pack_fill_many(jobs, s))) return r;
+            jobs.count = 0;
+        }
+    }
+    return weight_pack_fill_many(jobs, s);
 }
 
 // Forward pass with the optional fusions.  The tensor-core paths apply f->input_func while they pack the layer input and

@@ -1239,6 +1239,43 @@ __global__ void __launch_bounds__(256) pack_weight_both_kernel(const float *__re
     else pack_weight_tile(blockIdx.x - n_forward, src, b_hi, b_lo, K, C, taps, ip_b, 1, tile);
 }
 
+// Both orientations of the weights of up to kMaxPackJobs layers in one launch (the layers of a net packed together at the
+// start of a training step instead of one launch per layer).
+__global__ void __launch_bounds__(256) pack_weight_many_kernel(const __grid_constant__ WeightPackJobs jobs)
+{
+    grid_dependency_wait();
+    __shared__ float tile[32][kMaxTaps + 1];
+    int j = 0;
+    while (j + 1 < jobs.count && (int)blockIdx.x >= jobs.job[j + 1].block_begin) j++;
+    const WeightPackJob &w = jobs.job[j];
+    const int b = (int)blockIdx.x - w.block_begin;
+    if (b < w.n_forward) pack_weight_tile(b, w.src, w.f_hi, w.f_lo, w.K, w.C, w.taps, w.ip_f, 0, tile);
+    else pack_weight_tile(b - w.n_forward, w.src, w.b_hi, w.b_lo, w.K, w.C, w.taps, w.ip_b, 1, tile);
+}
+
+bool weight_pack_job(const b200_conv_geom &g, const float *kernel, float *f_hi, float *f_lo, float *b_hi, float *b_lo, WeightPackJob *job)
+{
+    const int taps = g.kernel_x * g.kernel_y;
+    if (taps < 2 || taps > kMaxTaps) return false;
+    job->src = kernel; job->f_hi = f_hi; job->f_lo = f_lo; job->b_hi = b_hi; job->b_lo = b_lo;
+    job->K = g.kernel_amount; job->C = g.in_z; job->taps = taps;
+    job->ip_f = (int)align_up(g.in_z, 4); job->ip_b = (int)align_up(g.kernel_amount, 4);
+    job->n_forward = g.kernel_amount * ((job->ip_f + 31) / 32);
+    job->blocks = job->n_forward + g.in_z * ((job->ip_b + 31) / 32);
+    job->block_begin = 0;
+    return true;
+}
+
+int weight_pack_fill_many(WeightPackJobs &jobs, cudaStream_t s)
+{
+    int total = 0;
+    for (int i = 0; i < jobs.count; i++) { jobs.job[i].block_begin = total; total += jobs.job[i].blocks; }
+    if (!total) return B200_OK;
+    Launch(total, 256, 0, s)(pack_weight_many_kernel, jobs);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+}
+
 static int pack_weight(const float *src, float *hi, float *lo, int K, int C, int taps, int ip, int rot, cudaStream_t s)
 {
     if (taps > 1 && taps <= kMaxTaps) {

@@ -448,6 +448,14 @@ class Net:
             error = layer.TrainingBackward(error.view((self.batch,) + layer.out_shape), create_delta_weight, need_prev=(i > 0 or need_input_error))
         return error
 
+    @staticmethod
+    def PrepackWeights(nets):
+        """The tensor-core packs of the convolution kernels of all layers of `nets` in one launch (b200_conv_layers_prepack),
+        for the forward passes that follow: call at the start of a training step, after the weights were last changed.  Each
+        layer's next Forward then skips its own weight-pack launch; nothing else changes."""
+        layers = [layer for net in nets for layer in net.layers if isinstance(layer, NetLayerConvolution)]
+        ops.prepack_conv_layers([layer.ctx for layer in layers], [layer.w["kernel"] for layer in layers])
+
     def TrainingUpdateWeightFused(self, speed, iteration, batch_scale=1, beta1=0.9, beta2=0.999, epsilon=1e-8, corrections=None):
         """The data-parallel update in one kernel (b200_allreduce_adam): every rank sums its slice of the gradient arenas of
         all ranks over NVLink, applies Adam to that slice and writes the new weights to all ranks.  Replaces grads.all_reduce()

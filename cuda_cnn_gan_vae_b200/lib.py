@@ -48,6 +48,7 @@ SIGNATURES = {
     "b200_conv_layer_destroy": (_i, [_vp]),
     "b200_conv_layer_forward": (_i, [_vp, _fp, _fp, _fp, _fp, _vp]),
     "b200_conv_layer_forward_fused": (_i, [_vp, _fp, _fp, _fp, _fp, _vp, _vp]),
+    "b200_conv_layers_prepack": (_i, [_vp, _vp, _i, _vp]),
     "b200_conv_layer_backward": (_i, [_vp, _fp, _fp, _fp, _i, _fp, _fp, _fp, _vp]),
     "b200_conv_wgrad_batch_static": (_i, [_G, _fp, _fp, _i, _fp, _fp, _i, _vp]),
     "b200_static_scratch_bytes": (_sz, []),

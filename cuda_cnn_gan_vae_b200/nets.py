@@ -89,6 +89,7 @@ class DCGANStep:
         main = torch.cuda.current_stream()
         self.G.TrainingResetDeltaWeight()
         self.D.TrainingResetDeltaWeight()
+        Net.PrepackWeights([self.G, self.D])        # the weights of both nets change only at the end of the step
         fake = self.G.Forward(self.z)
         out = self.D.Forward(fake)
         ops.CTensorMath.Sub(self.error, out, self.labels)
@@ -205,6 +206,7 @@ class VAEStep:
         self.iteration += 1
         for net in self.nets:
             net.TrainingResetDeltaWeight()
+        Net.PrepackWeights(self.nets)               # all weights change only at the end of the step
         feat = self.encoder.Forward(x)
         mu, logvar = self.mu.Forward(feat), self.logvar.Forward(feat)
         z, self.kl = ops.vae_forward(mu, logvar, eps.view(mu.shape), want_kl=want_kl)

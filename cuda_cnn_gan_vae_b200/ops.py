@@ -430,6 +430,16 @@ def vae_backward(delta, mu, logvar, eps, kl_speed):
     return dmu, dlv
 
 
+def prepack_conv_layers(layers, kernels):
+    """b200_conv_layers_prepack: the tensor-core weight packs of several ConvLayer objects in one launch, each good for the
+    layer's next forward call with that kernel tensor."""
+    if not layers:
+        return
+    handles = (C.c_void_p * len(layers))(*[layer._h for layer in layers])
+    pointers = (C.c_void_p * len(layers))(*[_t(k).data_ptr() for k in kernels])
+    _check(load().b200_conv_layers_prepack(handles, pointers, len(layers), _stream()))
+
+
 class ConvLayer:
     """Forward / TrainingBackward of the reference's convolution layer (netlayer/cnetlayerconvolution.cu.h:310,484)
     or, with transposed=True, of its transposed-convolution layer (netlayer/cnetlayerbackconvolution.cu.h:303,475).

@@ -181,6 +181,13 @@ typedef struct b200_conv_fusion {
 } b200_conv_fusion;
 int b200_conv_layer_forward_fused(b200_conv_layer *layer, float *out, const float *input, const float *kernel, const float *bias,
                                   const b200_conv_fusion *fusion, void *stream);
+/* The weights of several layers re-laid out for the tensor cores in ONE launch, for the next forward call of each (the
+ * reference has no counterpart: its layers read the weights as they are; netlayer/cnetlayerconvolution.cu.h:310).  A training
+ * step that calls this once for all layers of its nets, before their forward passes, saves one launch per layer.  kernels[i]
+ * is the kernel tensor that layer i's next b200_conv_layer_forward(_fused) call will be given.  The mark is good for that one
+ * forward call (and the backward call after it) in the current precision mode; a forward call without it packs the weights
+ * itself, so calling this is never required -- but the weights must not change between this call and the forward call. */
+int b200_conv_layers_prepack(b200_conv_layer *const *layers, const float *const *kernels, int count, void *stream);
 /* input_delta (may be NULL) = error of the layer input; dkernel / dbias (may be NULL) (+)= batch-summed
  * gradients (dbias of a transposed layer is cleared, as the reference does).  `input` must hold what the
  * forward call saw: it is only read when the kept pack cannot be used (no forward call yet, precision

@@ -160,6 +160,47 @@ def test_few_filter_layer_in_either_call_order(ops, port):
     layer.close()
 
 
+@pytest.mark.parametrize("case", [(4, 64, 16, 16, 96, 3, 1, 1, False), (4, 64, 16, 16, 128, 4, 2, 1, True), (4, 3, 64, 64, 64, 4, 2, 1, False),
+                                  (4, 32, 16, 16, 3, 3, 1, 1, False)])
+@pytest.mark.parametrize("mode", ["x3", "tf32", "fp32"])
+def test_prepacked_weights_change_nothing(ops, case, mode):
+    """b200_conv_layers_prepack (the weight packs of several layers in one launch) before a forward call gives bit for bit
+    what the layer's own packing gives, forward and backward; the mark is good for one forward call only, so a forward call
+    after the weights have changed, without a fresh prepack, sees the new weights."""
+    B, C, H, W, K, k, s, p, transposed = case
+    ops.set_precision({"x3": ops.TF32X3, "tf32": ops.TF32, "fp32": ops.FP32}[mode])
+    x, wt, b, d = conv_inputs(sum(case[:8]) + 9, B, C, H, W, K, k, s, p)
+    if transposed:
+        x, d = d, x
+    X, WT, BI, D = dev(x), dev(wt), dev(b), dev(d)
+    bias = None if transposed else BI
+    plain = ops.ConvLayer(C, H, W, K, k, k, s, s, p, p, B, transposed=transposed)
+    packed = ops.ConvLayer(C, H, W, K, k, k, s, s, p, p, B, transposed=transposed)
+    other = ops.ConvLayer(C, H, W, K, k, k, s, s, p, p, B, transposed=transposed)       # a second layer in the same launch
+    WT2 = WT * 0.5
+
+    def run(layer, kernel):
+        y, dx, dk = torch.full_like(D, float("nan")), torch.full_like(X, float("nan")), torch.zeros_like(WT)
+        layer.forward(y, X, kernel, bias)
+        layer.backward(dx, dk, None, D, X, kernel, accumulate=False)
+        return y, dx, dk
+
+    for rep in range(2):
+        want = run(plain, WT)
+        ops.prepack_conv_layers([packed, other], [WT, WT2])
+        got = run(packed, WT)
+        got_other = run(other, WT2)
+        want_other = run(plain, WT2)
+        assert all(torch.equal(a, b) for a, b in zip(got, want))
+        assert all(torch.equal(a, b) for a, b in zip(got_other, want_other))
+        # the weights change in place; no prepack: the layer must pack the new values itself
+        WT.mul_(1.25)
+        assert all(torch.equal(a, b) for a, b in zip(run(packed, WT), run(plain, WT)))
+    ops.stream_status()
+    for layer in (plain, packed, other):
+        layer.close()
+
+
 FUSED_CASES = [(4, 64, 16, 16, 96, 3, 1, 1, False), (6, 128, 8, 8, 256, 4, 2, 1, False), (5, 512, 4, 4, 100, 3, 1, 1, False),      # plain, strided, split-K
                (4, 3, 64, 64, 64, 4, 2, 1, False), (3, 40, 12, 12, 24, 3, 1, 1, False),                                           # few-channel input, ragged
                (4, 64, 16, 16, 128, 4, 2, 1, True), (4, 3, 64, 64, 64, 4, 2, 1, True),                                            # transposed layers

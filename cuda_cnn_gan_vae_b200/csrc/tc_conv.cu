@@ -105,13 +105,20 @@ struct TileCtx {
 // CTA-pair convolution: work item `pair` = two neighbouring M-tiles of one output phase, CTA `rank`
 // takes the rank-th of them.  A phase with an odd tile count ends in a pair whose second tile lies
 // outside the batch: its loads are zero-filled and its stores masked.
+// Division by a small runtime value is some twenty dependent instructions, and the three roles of the kernel run ONE warp
+// each: for layers with a short contraction the decode and the epilogue's index arithmetic per tile weighed as much as the
+// tile's MMAs.  The common divisors (no split-K, one column tile, one tile per row / plane) are therefore branched around.
+__device__ __forceinline__ void div_mod(int v, int d, int &q, int &r)
+{
+    if (d == 1) { q = v; r = 0; } else { q = v / d; r = v - q * d; }
+}
+
 __device__ __forceinline__ TileCtx decode_pair(const TcParams &p, int pair, int rank)
 {
     TileCtx c;
-    c.split = pair % p.ksplit;
-    pair /= p.ksplit;
-    c.nt = pair % p.n_tiles_n;
-    int mp = pair / p.n_tiles_n;
+    div_mod(pair, p.ksplit, pair, c.split);
+    int mp;
+    div_mod(pair, p.n_tiles_n, mp, c.nt);
     int ph = 0;
     while (ph + 1 < p.phases && mp >= p.phase[ph + 1].pair_begin) ph++;
     const PhaseInfo &pi = p.phase[ph];
@@ -119,13 +126,16 @@ __device__ __forceinline__ TileCtx decode_pair(const TcParams &p, int pair, int 
     c.ph = ph;
     {
         const int total = pi.tap_count * p.c_chunks;
-        c.step_begin = total * c.split / p.ksplit;
-        c.nsteps = total * (c.split + 1) / p.ksplit - c.step_begin;
+        if (p.ksplit == 1) { c.step_begin = 0; c.nsteps = total; }
+        else {
+            c.step_begin = total * c.split / p.ksplit;
+            c.nsteps = total * (c.split + 1) / p.ksplit - c.step_begin;
+        }
     }
     if (local < pi.tiles_x * pi.tiles_y * pi.tiles_i) {
-        c.tx = local % pi.tiles_x;
-        c.ty = (local / pi.tiles_x) % pi.tiles_y;
-        c.ig = local / (pi.tiles_x * pi.tiles_y);
+        int rest;
+        div_mod(local, pi.tiles_x, rest, c.tx);
+        div_mod(rest, pi.tiles_y, c.ig, c.ty);
     } else {
         c.tx = 0; c.ty = 0; c.ig = pi.tiles_i;
     }
@@ -137,21 +147,23 @@ __device__ __forceinline__ TileCtx decode_tile(const TcParams &p, int tile, int 
 {
     TileCtx c;
     if (MODE == MODE_CONV) {
-        c.split = tile % p.ksplit;
-        tile /= p.ksplit;
-        c.nt = tile % p.n_tiles_n;
-        int mt = tile / p.n_tiles_n;
+        div_mod(tile, p.ksplit, tile, c.split);
+        int mt;
+        div_mod(tile, p.n_tiles_n, mt, c.nt);
         int ph = 0;
         while (ph + 1 < p.phases && mt >= p.phase[ph + 1].tile_begin) ph++;
         const PhaseInfo &pi = p.phase[ph];
         int local = mt - pi.tile_begin;
         c.ph = ph;
-        c.tx = local % pi.tiles_x;
-        c.ty = (local / pi.tiles_x) % pi.tiles_y;
-        c.ig = local / (pi.tiles_x * pi.tiles_y);
+        int rest;
+        div_mod(local, pi.tiles_x, rest, c.tx);
+        div_mod(rest, pi.tiles_y, c.ig, c.ty);
         const int total = pi.tap_count * p.c_chunks;
-        c.step_begin = total * c.split / p.ksplit;
-        c.nsteps = total * (c.split + 1) / p.ksplit - c.step_begin;
+        if (p.ksplit == 1) { c.step_begin = 0; c.nsteps = total; }
+        else {
+            c.step_begin = total * c.split / p.ksplit;
+            c.nsteps = total * (c.split + 1) / p.ksplit - c.step_begin;
+        }
     } else if (MODE == MODE_WGRAD) {
         // The tap varies fastest: the CTAs that run side by side work on the taps of ONE range of output pixels, so the error
         // chunk they all read and the (shifted) image chunks come from HBM once and from L2 for the other taps.  With the
@@ -440,6 +452,10 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
         // ------------------------------------------------------------------ epilogue (warps 2..5)
         const int q = warp & 3;
         const int row = q * 32 + lane;
+        // CONV: this thread's pixel inside a tile (the same for every tile)
+        const int row_bx = MODE == MODE_CONV ? row % p.BW : 0;
+        const int row_by = MODE == MODE_CONV ? (row / p.BW) % p.BH : 0;
+        const int row_bi = MODE == MODE_CONV ? row / (p.BW * p.BH) : 0;
         int tile_iter = 0;
 #ifdef B200_TC_TIMING
         long long dbg_ew = 0;
@@ -473,8 +489,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
             };
             if (MODE == MODE_CONV) {
                 const PhaseInfo &pi = p.phase[c.ph];
-                const int bx = row % p.BW, by = (row / p.BW) % p.BH, bi = row / (p.BW * p.BH);
-                const int n = c.ig * p.BI + bi, yy = c.ty * p.BH + by, xx = c.tx * p.BW + bx;
+                const int n = c.ig * p.BI + row_bi, yy = c.ty * p.BH + row_by, xx = c.tx * p.BW + row_bx;
                 const bool valid = n < p.n_img && yy < pi.ext_y && xx < pi.ext_x;
                 const size_t plane = (size_t)p.OH * p.OW;
                 float *obase = p.ksplit > 1 ? p.kpartial + (size_t)c.split * (size_t)p.out_elems : p.out;
@@ -485,14 +500,16 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
                 const int func = (!ACT || p.ksplit > 1) ? -1 : p.act_func;
                 for (int c0 = 0; ACT && c0 < p.BN; c0 += 16) {
                     load16(c0);
+                    const int k0 = c.nt * p.BN + c0;
+                    const int live = valid ? p.k_out - k0 : 0;
+                    float *q0 = dst + (size_t)k0 * plane, *q1 = pre ? pre + (size_t)k0 * plane : nullptr;
 #pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        const int k = c.nt * p.BN + c0 + j;
-                        if (valid && k < p.k_out) {
-                            float val = bias ? __fadd_rn(v[j], bias[k]) : v[j];
-                            if (pre) pre[(size_t)k * plane] = val;
+                    for (int j = 0; j < 16; j++, q0 += plane) {
+                        if (j < live) {
+                            float val = bias ? __fadd_rn(v[j], __ldg(bias + k0 + j)) : v[j];
+                            if (q1) q1[(size_t)j * plane] = val;
                             if (func >= 0) val = act_apply(val, func, p.act_slope);      // the function layer fused into the epilogue
-                            dst[(size_t)k * plane] = val;
+                            *q0 = val;
                         }
                     }
                 }
@@ -500,12 +517,24 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
                     // plain epilogue, software-pipelined: the tensor-memory load of the next 16 columns is in flight while
                     // the current 16 are stored (a load-wait-store sequence per 16 columns left the stores idle half the time)
                     uint32_t ra[16], rb[16];
+                    // 16 columns = 16 channel planes of this thread's pixel: the plane pointer is stepped, the number of real
+                    // columns is one subtraction, and the bias values come through the read-only path before the stores
                     auto store16 = [&](const uint32_t *r, int c0) {
+                        const int k0 = c.nt * p.BN + c0;
+                        const int live = valid ? p.k_out - k0 : 0;          // columns j < live are stored
+                        if (live <= 0) return;
+                        float *q0 = dst + (size_t)k0 * plane;
+                        if (bias) {
+                            float bv[16];
 #pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            const int k = c.nt * p.BN + c0 + j;
-                            const float val = __uint_as_float(r[j]);
-                            if (valid && k < p.k_out) dst[(size_t)k * plane] = bias ? __fadd_rn(val, bias[k]) : val;
+                            for (int j = 0; j < 16; j++) bv[j] = j < live ? __ldg(bias + k0 + j) : 0.f;
+#pragma unroll
+                            for (int j = 0; j < 16; j++, q0 += plane)
+                                if (j < live) *q0 = __fadd_rn(__uint_as_float(r[j]), bv[j]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; j++, q0 += plane)
+                                if (j < live) *q0 = __uint_as_float(r[j]);
                         }
                     };
                     ptx::tmem_ld16_issue(taddr, ra);
@@ -543,11 +572,12 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ C
                 float *dst = p.partial + (((size_t)c.split * p.taps_n + tap) * p.c_cols) * p.k_rows + f;
                 for (int c0 = 0; c0 < p.BN; c0 += 16) {
                     load16(c0);
+                    const int ch0 = c.ct * p.BN + c0;
+                    const int live = row_ok ? p.c_cols - ch0 : 0;
+                    float *q0 = dst + (size_t)ch0 * p.k_rows;
 #pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        const int ch = c.ct * p.BN + c0 + j;
-                        if (row_ok && ch < p.c_cols) dst[(size_t)ch * p.k_rows] = v[j];
-                    }
+                    for (int j = 0; j < 16; j++, q0 += p.k_rows)
+                        if (j < live) *q0 = v[j];
                 }
             } else {
                 const int m = c.mt * 128 + row;
